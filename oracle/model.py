@@ -1,0 +1,285 @@
+"""Layer / model composition of the oracle (test infrastructure only).
+
+The reference has no Python forward for a layer or a model: its module classes are
+weight and buffer registries whose forwards raise (tilert/models/base.py:355-371) and the
+real forward lives in the closed native library.  The composition below follows the
+operator registration order of tilert/models/deepseek_v3_2/modules/mla_v2.py:44-63,127-161,
+modules/moe.py:27-46 and modules/mlp.py:24-35, with the residual placement given by the
+``x_in`` arguments of ``unproj_o_allreduce`` (ops/unproj_o_allreduce.py:23-58) and
+``expert_down_allreduce`` (ops/expert_down_allreduce.py:23-63).  The embedding lookup and
+the greedy arg-max are not stated anywhere in the reference; standard forms are used.
+Parity unpinned for the composition itself (each operator inside it is pinned).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, replace
+
+import torch
+
+from . import ops
+from .quant import quantize_weight_block128, weight_dequant
+
+BF16 = torch.bfloat16
+
+
+@dataclass
+class Args:
+    """Same fields and defaults as tilert/models/deepseek_v3_2/model_args.py:51-95."""
+
+    vocab_size: int = 129280
+    dim: int = 7168
+    inter_dim: int = 18432
+    moe_inter_dim: int = 2048
+    n_layers: int = 61
+    n_dense_layers: int = 3
+    n_heads: int = 128
+    n_routed_experts: int = 256
+    n_shared_experts: int = 1
+    n_activated_experts: int = 8
+    n_expert_groups: int = 8
+    n_limited_groups: int = 4
+    route_scale: float = 2.5
+    q_lora_rank: int = 1536
+    kv_lora_rank: int = 512
+    qk_nope_head_dim: int = 128
+    qk_rope_head_dim: int = 64
+    v_head_dim: int = 128
+    original_seq_len: int = 4096
+    rope_theta: float = 10000.0
+    rope_factor: float | None = 40
+    beta_fast: int = 32
+    beta_slow: int = 1
+    index_n_heads: int = 64
+    index_head_dim: int = 128
+    index_topk: int = 2048
+    max_seq_len: int = 160 * 1024
+    eps: float = 1e-6
+
+
+def toy_args() -> Args:
+    """The toy workload: 2 layers (one dense, one MoE), hidden 1024, vocab 4096."""
+    return Args(
+        vocab_size=4096, dim=1024, inter_dim=2048, moe_inter_dim=512, n_layers=2,
+        n_dense_layers=1, n_heads=16, n_routed_experts=32, n_activated_experts=4,
+        n_expert_groups=1, n_limited_groups=1, q_lora_rank=384, index_n_heads=16,
+        index_topk=256, max_seq_len=2048,
+    )
+
+
+def full_layer_args(max_seq_len: int = 160 * 1024) -> Args:
+    """One full-shape DeepSeek-V3.2 MoE layer."""
+    return replace(Args(), n_layers=1, n_dense_layers=0, max_seq_len=max_seq_len)
+
+
+# --------------------------------------------------------------------- weights
+def _fp8_linear(gen, n, k, std, out, key):
+    w = torch.randn(n, k, generator=gen, dtype=torch.float32) * std
+    q, s = quantize_weight_block128(w)
+    out[f"{key}.weight"] = q
+    out[f"{key}.weight_scale_inv"] = s
+
+
+def random_state_dict(args: Args, seed: int = 0, std: float = 0.02,
+                      expert_ids: list[int] | None = None) -> dict[str, torch.Tensor]:
+    """HF-keyed random checkpoint: N(0, std) -> e4m3 + 128x128 f32 scales, norm gains 1,
+    router bias 0.  ``expert_ids`` limits which routed experts are materialised (the full
+    layer has 256 of them; a one-step check touches 8)."""
+    gen = torch.Generator().manual_seed(seed)
+    sd: dict[str, torch.Tensor] = {}
+    a = args
+    sd["model.embed_tokens.weight"] = (torch.randn(a.vocab_size, a.dim, generator=gen, dtype=torch.float32) * std).to(BF16)
+    for li in range(a.n_layers):
+        p = f"model.layers.{li}"
+        sd[f"{p}.input_layernorm.weight"] = torch.ones(a.dim, dtype=torch.float32)
+        sd[f"{p}.post_attention_layernorm.weight"] = torch.ones(a.dim, dtype=torch.float32)
+        at = f"{p}.self_attn"
+        _fp8_linear(gen, a.q_lora_rank, a.dim, std, sd, f"{at}.q_a_proj")
+        sd[f"{at}.q_a_layernorm.weight"] = torch.ones(a.q_lora_rank, dtype=torch.float32)
+        _fp8_linear(gen, a.n_heads * (a.qk_nope_head_dim + a.qk_rope_head_dim), a.q_lora_rank, std, sd,
+                    f"{at}.q_b_proj")
+        _fp8_linear(gen, a.kv_lora_rank + a.qk_rope_head_dim, a.dim, std, sd, f"{at}.kv_a_proj_with_mqa")
+        sd[f"{at}.kv_a_layernorm.weight"] = torch.ones(a.kv_lora_rank, dtype=torch.float32)
+        _fp8_linear(gen, a.n_heads * (a.qk_nope_head_dim + a.v_head_dim), a.kv_lora_rank, std, sd,
+                    f"{at}.kv_b_proj")
+        _fp8_linear(gen, a.dim, a.n_heads * a.v_head_dim, std, sd, f"{at}.o_proj")
+        _fp8_linear(gen, a.index_n_heads * a.index_head_dim, a.q_lora_rank, std, sd, f"{at}.indexer.wq_b")
+        _fp8_linear(gen, a.index_head_dim, a.dim, std, sd, f"{at}.indexer.wk")
+        sd[f"{at}.indexer.k_norm.weight"] = torch.ones(a.index_head_dim, dtype=torch.float32)
+        sd[f"{at}.indexer.k_norm.bias"] = torch.zeros(a.index_head_dim, dtype=torch.float32)
+        sd[f"{at}.indexer.weights_proj.weight"] = (
+            torch.randn(a.index_n_heads, a.dim, generator=gen, dtype=torch.float32) * std).to(BF16)
+        m = f"{p}.mlp"
+        if li < a.n_dense_layers:
+            _fp8_linear(gen, a.inter_dim, a.dim, std, sd, f"{m}.gate_proj")
+            _fp8_linear(gen, a.inter_dim, a.dim, std, sd, f"{m}.up_proj")
+            _fp8_linear(gen, a.dim, a.inter_dim, std, sd, f"{m}.down_proj")
+        else:
+            sd[f"{m}.gate.weight"] = (torch.randn(a.n_routed_experts, a.dim, generator=gen, dtype=torch.float32) * std).to(BF16)
+            sd[f"{m}.gate.e_score_correction_bias"] = torch.zeros(a.n_routed_experts, dtype=torch.float32)
+            names = ["shared_experts"] + [
+                f"experts.{e}" for e in (range(a.n_routed_experts) if expert_ids is None else expert_ids)]
+            for nm in names:
+                _fp8_linear(gen, a.moe_inter_dim, a.dim, std, sd, f"{m}.{nm}.gate_proj")
+                _fp8_linear(gen, a.moe_inter_dim, a.dim, std, sd, f"{m}.{nm}.up_proj")
+                _fp8_linear(gen, a.dim, a.moe_inter_dim, std, sd, f"{m}.{nm}.down_proj")
+    sd["model.norm.weight"] = torch.ones(a.dim, dtype=torch.float32)
+    sd["lm_head.weight"] = (torch.randn(a.vocab_size, a.dim, generator=gen, dtype=torch.float32) * std).to(BF16)
+    return sd
+
+
+class LayerWeights:
+    """bf16-dequantised weights of one layer, held as the reference goldens hold them."""
+
+    def __init__(self, args: Args, sd: dict[str, torch.Tensor], li: int):
+        a = args
+        p = f"model.layers.{li}"
+        at = f"{p}.self_attn"
+
+        def dq(key):
+            return weight_dequant(sd[f"{key}.weight"], sd[f"{key}.weight_scale_inv"])
+
+        self.in_norm = sd[f"{p}.input_layernorm.weight"]
+        self.post_norm = sd[f"{p}.post_attention_layernorm.weight"]
+        self.wq_a = dq(f"{at}.q_a_proj")
+        kv_a = dq(f"{at}.kv_a_proj_with_mqa")
+        self.wkv_a, self.w_pe = kv_a[: a.kv_lora_rank], kv_a[a.kv_lora_rank:]
+        self.q_norm = sd[f"{at}.q_a_layernorm.weight"]
+        self.kv_norm = sd[f"{at}.kv_a_layernorm.weight"]
+        self.wq_b = dq(f"{at}.q_b_proj")
+        wkv_b = dq(f"{at}.kv_b_proj").view(a.n_heads, a.qk_nope_head_dim + a.v_head_dim, a.kv_lora_rank)
+        self.wkv_b_nope = wkv_b[:, : a.qk_nope_head_dim].contiguous()
+        self.wkv_b_v = wkv_b[:, a.qk_nope_head_dim:].contiguous()
+        self.w_o = dq(f"{at}.o_proj")
+        self.wqi = dq(f"{at}.indexer.wq_b")
+        self.wki = dq(f"{at}.indexer.wk")
+        self.k_norm_w = sd[f"{at}.indexer.k_norm.weight"]
+        self.k_norm_b = sd[f"{at}.indexer.k_norm.bias"]
+        self.wis = sd[f"{at}.indexer.weights_proj.weight"]
+        m = f"{p}.mlp"
+        self.dense = li < a.n_dense_layers
+        self._sd, self._m = sd, m
+        self._cache: dict[str, tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
+        if self.dense:
+            self.w_gate, self.w_up, self.w_down = dq(f"{m}.gate_proj"), dq(f"{m}.up_proj"), dq(f"{m}.down_proj")
+        else:
+            self.router = sd[f"{m}.gate.weight"]
+            self.router_bias = sd[f"{m}.gate.e_score_correction_bias"]
+
+    def expert(self, name: str):
+        """(gate, up, down) bf16 of one expert, dequantised on first use."""
+        if name not in self._cache:
+            k = f"{self._m}.{name}"
+            sd = self._sd
+            self._cache[name] = tuple(
+                weight_dequant(sd[f"{k}.{w}.weight"], sd[f"{k}.{w}.weight_scale_inv"])
+                for w in ("gate_proj", "up_proj", "down_proj"))
+        return self._cache[name]
+
+
+class Caches:
+    """Per-layer latent caches [1, T, {512, 64, 128}] bf16 (modules/mla_v2.py:93-113)."""
+
+    def __init__(self, args: Args, t: int):
+        self.kv = torch.zeros(1, t, args.kv_lora_rank, dtype=BF16)
+        self.pe = torch.zeros(1, t, args.qk_rope_head_dim, dtype=BF16)
+        self.ki = torch.zeros(1, t, args.index_head_dim, dtype=BF16)
+
+
+def layer_step(args: Args, w: LayerWeights, c: Caches, x: torch.Tensor, pos: int,
+               freqs_cis: torch.Tensor, trace: dict | None = None,
+               forced_router_scores: torch.Tensor | None = None) -> torch.Tensor:
+    """One decode step of one layer.  ``x`` is [1, S, dim] bf16; the S tokens sit at
+    positions ``pos .. pos+S-1``.  Returns the layer output [1, S, dim] bf16 and updates
+    the caches in place.  ``trace`` (optional) collects every intermediate."""
+    a = args
+    s = x.size(1)
+    fc = freqs_cis[pos: pos + s]
+    tr = trace if trace is not None else {}
+
+    q_a, kv, k_pe = ops.projx_wqkva(x, w.in_norm, w.wq_a, w.wkv_a, w.w_pe, a.eps)
+    _, ki, idx_w = ops.projx_wqakis(x, w.in_norm, w.wq_a, w.wki, w.wis, a.eps)
+    c.kv[:, pos: pos + s] = ops.rmsnorm_kv(kv, w.kv_norm, a.eps)
+    q_nope, q_pe = ops.rmsnorm_projq_wqb(q_a, w.q_norm, w.wq_b, a.n_heads, a.qk_nope_head_dim,
+                                         a.qk_rope_head_dim, a.eps)
+    q_pe, k_rot = ops.qkv_rope(q_pe, k_pe, fc)
+    c.pe[:, pos: pos + s] = k_rot
+    iq = ops.rmsnorm_projq_wqi(q_a, w.q_norm, w.wqi, a.index_head_dim, a.eps)
+    iq = ops.rotate(iq, fc, a.qk_rope_head_dim)
+    c.ki[:, pos: pos + s] = ops.layernorm_rope_rotate(ki, w.k_norm_w, w.k_norm_b, fc, a.qk_rope_head_dim)
+    n_valid = pos + s
+    idx_logits = ops.indexer_logits(iq, c.ki[:, :n_valid], idx_w, n_valid)
+    sel = ops.topk_indices(idx_logits, a.index_topk)
+    q_lat = ops.projq_wqb_absorb(q_nope, w.wkv_b_nope)
+    o_lat = ops.flash_sparse_mla(q_lat, q_pe, c.kv[:, :n_valid], c.pe[:, :n_valid], sel, pos,
+                                 ops.softmax_scale(a))
+    o = ops.projo_wkvb(o_lat, w.wkv_b_v)
+    h = (ops.unproj_o(o, w.w_o).float() + x.float()).to(BF16)
+    tr.update(q_a=q_a, kv=kv, k_pe=k_pe, ki=ki, idx_w=idx_w, q_nope=q_nope, q_pe=q_pe, iq=iq,
+              idx_logits=idx_logits, sel=sel, q_lat=q_lat, o_lat=o_lat, o=o, attn_out=h)
+
+    if w.dense:
+        hid = ops.dense_up_gate_silu(h, w.post_norm, w.w_gate, w.w_up, a.eps)
+        ffn = ops.dense_down(hid, w.w_down, a.inter_dim // a.moe_inter_dim)
+        tr.update(ffn_hidden=hid)
+    else:
+        hn, scores = ops.rmsnorm_expert_proj(h, w.post_norm, w.router, a.eps)
+        scores = scores.view(1, s, -1)
+        if forced_router_scores is not None:
+            scores = forced_router_scores
+        probs, eidx = ops.expert_select_ds(scores, w.router_bias, a.n_expert_groups, a.n_limited_groups,
+                                           a.n_activated_experts, a.route_scale)
+        gl, ul, dl = [], [], []
+        for si in range(s):
+            names = ["shared_experts"] + [f"experts.{int(e)}" for e in eidx[0, si]]
+            trip = [w.expert(nm) for nm in names]
+            gl.append([t[0] for t in trip])
+            ul.append([t[1] for t in trip])
+            dl.append([t[2] for t in trip])
+        hid = ops.expert_up_gate_silu(hn, gl, ul)
+        ffn = ops.expert_down(hid, dl, probs)
+        tr.update(router_scores=scores, probs=probs, eidx=eidx, ffn_hidden=hid, x_mlp_in=hn)
+    out = (ffn.float() + h.float()).to(BF16)
+    tr.update(ffn_out=ffn, out=out)
+    return out
+
+
+class Model:
+    """Whole-model greedy decoder over ``layer_step`` (embedding -> layers -> head)."""
+
+    def __init__(self, args: Args, sd: dict[str, torch.Tensor], cache_len: int | None = None):
+        self.args = args
+        self.embed = sd["model.embed_tokens.weight"]
+        self.layers = [LayerWeights(args, sd, li) for li in range(args.n_layers)]
+        self.final_norm = sd["model.norm.weight"]
+        self.head = sd["lm_head.weight"]
+        self.freqs_cis = ops.precompute_freqs_cis(args)
+        t = cache_len or args.max_seq_len
+        self.caches = [Caches(args, t) for _ in range(args.n_layers)]
+        self.pos = 0
+
+    def step(self, token: int, traces: list | None = None) -> tuple[int, torch.Tensor]:
+        """Feed one token at the current position; returns (arg-max token, f32 logits)."""
+        x = self.embed[token].view(1, 1, -1)
+        for li, (w, c) in enumerate(zip(self.layers, self.caches)):
+            tr = {} if traces is not None else None
+            x = layer_step(self.args, w, c, x, self.pos, self.freqs_cis, tr)
+            if traces is not None:
+                traces.append(tr)
+        logits = ops.rmsnorm_head_proj(x, self.final_norm, self.head, self.args.eps).view(-1)
+        self.pos += 1
+        return int(torch.argmax(logits)), logits
+
+    def generate(self, prompt: list[int], n_new: int) -> tuple[list[int], list[torch.Tensor]]:
+        """Token-by-token prefill (the reference feeds prompts one token at a time,
+        generator.py:220-245) then ``n_new`` greedy steps.  Returns tokens and the logits
+        of every generated position."""
+        nxt = 0
+        for tok in prompt:
+            nxt, lg = self.step(tok)
+        toks, lgs = [nxt], [lg]
+        for _ in range(n_new - 1):
+            nxt, lg = self.step(nxt)
+            toks.append(nxt)
+            lgs.append(lg)
+        return toks, lgs
