@@ -1,0 +1,213 @@
+/*
+ * tilert_b200 -- C ABI of the B200-native batch-1 FP8 decode path.
+ *
+ * The reference library (libtilert_dsv32.so, loaded by tilert/__init__.py:43-77) registers its
+ * kernels as PyTorch operators `torch.ops.tilert.<name>`; the Python wrappers under
+ * tilert/models/deepseek_v3_2/ops/ are the only callers.  Every function below replaces one of
+ * those operators (the wrapper's file:line is cited) with plain pointers and sizes, so it can be
+ * bound from ctypes, a PyTorch extension or any other FFI.
+ *
+ * Conventions
+ *   - every pointer is a CUDA device pointer on the context's device unless marked "host";
+ *   - bf16 tensors are passed as `const void*` / `void*`, e4m3 bytes as `uint8_t*`;
+ *   - outputs are caller-allocated (the reference operators also write into caller tensors);
+ *   - `stream` is a `cudaStream_t`; calls are asynchronous on it;
+ *   - the return value is 0 on success, a negative TB_E* code otherwise; `tilert_b200_last_error`
+ *     gives the message.  A kernel that gives up on a bounded wait records a positive code in the
+ *     context's device status word, read with `tilert_b200_status`;
+ *   - a context owns scratch memory used by the calls made with it: use one context per stream.
+ *
+ * Weight operands named `*_packed` are in the library's block format (128x128 e4m3 tiles in
+ * tensor-core fragment order followed by their scales, see tilert_b200/csrc/formats.h); they are
+ * produced from HF-format tensors (e4m3 weight + f32 `weight_scale_inv` per 128x128 block) by
+ * `tilert_b200.pack`.  Activation operands named `xpack` are in the matching activation block
+ * format, produced by the rmsnorm/pack operators below.
+ */
+#ifndef TILERT_B200_H_
+#define TILERT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TB_OK 0
+#define TB_ECUDA (-1)     /* a CUDA runtime call failed */
+#define TB_EINVAL (-2)    /* bad argument (shape not supported, null pointer, ...) */
+#define TB_ESTATE (-3)    /* library state error (no context, comm not set up) */
+
+typedef struct TbContext TbContext;
+typedef struct TbComm TbComm;
+
+/* ---- runtime -------------------------------------------------------------------------- */
+
+/* tilert_init_op / tilert_force_init_op (tilert/tilert_init.py:11-18): create the per-device
+ * context (scratch for split tiles, status word). */
+int tilert_b200_init(int device, TbContext** ctx_out);
+int tilert_b200_destroy(TbContext* ctx);
+/* Reads and clears the device status word (synchronises the device).  0 = no kernel gave up. */
+int tilert_b200_status(TbContext* ctx, int* status_out);
+const char* tilert_b200_last_error(void);
+int tilert_b200_num_sms(TbContext* ctx);
+/* dsa_temp_vars_size (tilert/models/deepseek_v3_2/temp_var_indices.py:109-118): number of named
+ * scratch tensors the driver shares with Python. */
+int tilert_b200_dsa_temp_vars_size(void);
+/* Bytes of scratch a context allocates (for memory planning). */
+size_t tilert_b200_context_bytes(void);
+/* Number of kernels this library has launched in this process (monotonic; includes launches that
+ * were recorded into a CUDA graph during stream capture). */
+long long tilert_b200_launch_count(void);
+
+/* ---- peer-to-peer plumbing for the fused all-reduce ------------------------------------ */
+/* The reference exchanges raw buffer addresses between its per-GPU threads
+ * (tilert/models/deepseek_v3_2/modules/end2end.py:491-501).  With one process per GPU the same
+ * exchange goes through CUDA IPC handles (64 opaque bytes each, sent over any host channel). */
+size_t tilert_b200_comm_buffer_bytes(int world, int max_rows);
+/* Zero-filled device allocation made directly with cudaMalloc (IPC handles need the base address
+ * of an allocation, which a sub-allocating framework allocator does not give). */
+int tilert_b200_dev_alloc(size_t bytes, void** dev_ptr_out);
+int tilert_b200_dev_free(void* dev_ptr);
+int tilert_b200_ipc_export(void* dev_ptr, uint8_t handle_out[64]);
+int tilert_b200_ipc_import(const uint8_t handle[64], void** dev_ptr_out);
+int tilert_b200_ipc_close(void* dev_ptr);
+/* `buffers[r]` is rank r's communication buffer (own allocation for r == rank, imported mapping
+ * otherwise), each `tilert_b200_comm_buffer_bytes(world, max_rows)` bytes and zero-filled before
+ * any rank's first call. */
+int tilert_b200_comm_create(TbContext* ctx, int world, int rank, void* const* buffers, int max_rows,
+                            TbComm** comm_out);
+int tilert_b200_comm_destroy(TbComm* comm);
+
+/* ---- activation preparation ------------------------------------------------------------ */
+
+/* rmsnorm_quant_op / rmsnorm_op (tilert/models/deepseek_v3_2/ops/rmsnorm_quant.py:19-64).
+ * x [tokens, dim] bf16 -> out bf16 (optional), q_out e4m3 + q_scale_out f32 [tokens, dim/128]
+ * (optional, reference 1x128 quantisation), and xpack (the operand of the FP8 products).
+ * gamma == NULL skips the normalisation (plain packing).  seg_scale (optional, [tokens, n_seg])
+ * multiplies the scales of each run of dim/n_seg activations (routing weights). */
+int tilert_rmsnorm_quant_op(TbContext* ctx, const void* x, const float* gamma, float eps, int tokens, int dim,
+                            void* out, uint8_t* q_out, float* q_scale_out, const float* seg_scale, int n_seg,
+                            uint8_t* xpack, void* stream);
+/* Re-lays reference-format quantised activations (e4m3 [tokens, dim] + f32 [tokens, dim/128]) as
+ * xpack with one column per token (cols_per_token = 1). */
+int tilert_xq_repack_op(TbContext* ctx, const uint8_t* x_q, const float* x_scale, int tokens, int dim,
+                        uint8_t* xpack, void* stream);
+size_t tilert_b200_xpack_bytes(int dim);
+
+/* ---- FP8 weight-streaming products ----------------------------------------------------- */
+
+/* projx_wqkva_op (ops/projx_wqkva.py:22-48) and projx_wqaki_op (ops/projx_wqaki.py:11-44) in one
+ * launch: rows of w_packed are [q_a (q_lora) | kv_a (kv_lora) | k_pe (rope) | indexer wk (ki_dim)];
+ * any of the four parts may have size 0.  k_pe is written to pe_cache[*cur_pos + t]. */
+int tilert_projx_wqkva_op(TbContext* ctx, const uint8_t* xpack, int cols_per_token, const uint8_t* w_packed,
+                          int tokens, int dim, int q_lora, int kv_lora, int rope, int ki_dim, const int* cur_pos,
+                          void* q_out, void* kv_out, void* pe_cache, void* ki_out, void* stream);
+
+/* rmsnorm_proj_qb_op (ops/rmsnorm_projq_wqb.py:21-43) and rmsnorm_proj_qi_op
+ * (ops/rmsnorm_projq_wqi.py:21-40) in one launch: RMSNorm(q) then rows
+ * [q_nope (heads*nope) | q_pe (heads*rope) | iq (iq_heads*iq_dim)]. */
+int tilert_rmsnorm_proj_q_op(TbContext* ctx, const void* q, const float* gamma, float eps, const uint8_t* w_packed,
+                             int tokens, int q_lora, int heads, int nope, int rope, int iq_heads, int iq_dim,
+                             void* q_nope, void* q_pe, void* iq, void* stream);
+
+/* projq_wqb_op (ops/projq_wqb.py:24-54): q_lat[t,h,:] = q_nope[t,h,:] . W_kvb_nope[h]  (per-head). */
+int tilert_projq_wqb_op(TbContext* ctx, const void* q_nope, const uint8_t* w_packed, int tokens, int heads,
+                        int nope, int kv_lora, void* out, void* stream);
+/* projo_wkvb_op (ops/projo_wkvb.py:24-54): o[t,h,:] = o_lat[t,h,:] . W_kvb_v[h]^T  (per-head). */
+int tilert_projo_wkvb_op(TbContext* ctx, const void* o_lat, const uint8_t* w_packed, int tokens, int heads,
+                         int kv_lora, int v_dim, void* out, void* stream);
+
+/* unproj_o_allreduce_op (ops/unproj_o_allreduce.py:23-58): out = all_reduce(W_o_shard . vec) + x_residual.
+ * comm == NULL: single GPU, no reduction.  The reduction runs inside the product kernel. */
+int tilert_unproj_o_allreduce_op(TbContext* ctx, const void* vec, const uint8_t* w_packed, const void* x_residual,
+                                 int tokens, int k, int n, void* out, TbComm* comm, void* stream);
+
+/* expert_select_up_gate_silu_op (ops/expert_sel_up_gate_silu.py:23-48): routing (sigmoid + bias,
+ * group-limited top-k, renormalise, scale) then SiLU(W1 x) * (W3 x) for the shared expert and the
+ * selected routed experts.  w_packed: [n_experts + 1] experts, `expert_stride` bytes apart, the
+ * shared expert last; rows of each expert interleave gate and up in groups of 8.
+ * hidden_out [tokens, top_k + 1, inter] bf16 (slot 0 = shared expert).
+ * slot_ids / slot_w [tokens, top_k + 1]: expert id and weight per slot (inputs of the down op).
+ * Under tensor parallelism every rank holds an `inter`-row slice of every expert. */
+int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const uint8_t* xpack, const float* scores,
+                                         const float* bias, const uint8_t* w_packed, long long expert_stride,
+                                         int tokens, int dim, int inter, int n_experts, int n_groups,
+                                         int n_limited_groups, int top_k, float route_scale, void* hidden_out,
+                                         float* probs_out, int* idx_out, int* slot_ids, float* slot_w,
+                                         void* stream);
+
+/* expert_down_allreduce_op (ops/expert_down_allreduce.py:23-63):
+ * out = all_reduce(sum_slots w_slot * W2[slot_ids] . vec[slot]) + x_residual. */
+int tilert_expert_down_allreduce_op(TbContext* ctx, const void* vec, const uint8_t* w_packed,
+                                    long long expert_stride, const int* slot_ids, const float* slot_w,
+                                    const void* x_residual, int tokens, int inter, int dim, int n_slots, void* out,
+                                    TbComm* comm, void* stream);
+
+/* rmsnorm_up_gate_silu_op (ops/rmsnorm_up_gate_silu.py:26-44): dense FFN first half. */
+int tilert_rmsnorm_up_gate_silu_op(TbContext* ctx, const void* x, const float* gamma, float eps,
+                                   const uint8_t* w_packed, int tokens, int dim, int inter, void* out, void* stream);
+/* down_allreduce_op (ops/down_allreduce.py:24-59): dense FFN second half + all-reduce + residual. */
+int tilert_down_allreduce_op(TbContext* ctx, const void* vec, const uint8_t* w_packed, const void* x_residual,
+                             int tokens, int inter, int dim, void* out, TbComm* comm, void* stream);
+
+/* ---- bf16 products --------------------------------------------------------------------- */
+
+/* proj_w_op (ops/projx_wis.py:21-40): out[t, :] = W[n, k] . x[t, :]   (bf16 in, bf16 out). */
+int tilert_proj_w_op(TbContext* ctx, const void* x, const void* w, int tokens, int n, int k, void* out,
+                     void* stream);
+/* rmsnorm_expert_proj_op (ops/rmsnorm_expert_proj.py:151-169): hidden_out = bf16(RMSNorm(x)),
+ * scores_out[t, :] = W_gate . hidden_out[t, :] in f32.  w_gate is bf16 (gate_is_f32 = 0) or f32.
+ * gamma == NULL: x is already normalised (hidden_out may then be NULL). */
+int tilert_rmsnorm_expert_proj_op(TbContext* ctx, const void* x, const float* gamma, float eps, const void* w_gate,
+                                  int gate_is_f32, int tokens, int dim, int n_experts, float* scores_out,
+                                  void* hidden_out, void* stream);
+/* rmsnorm_head_proj_op (ops/rmsnorm_head_proj.py:19-39): f32 logits of a vocabulary shard. */
+int tilert_rmsnorm_head_proj_op(TbContext* ctx, const void* x, const float* gamma, float eps, const void* w,
+                                int tokens, int dim, int vocab, void* x_norm_out, float* logits_out, void* stream);
+
+/* ---- per-token vector operators -------------------------------------------------------- */
+
+/* rmsnorm_kv_op (ops/rmsnorm_kv.py:20-43): kv_cache[*cur_pos + t] = bf16(RMSNorm(kv[t]) * gamma). */
+int tilert_rmsnorm_kv_op(TbContext* ctx, const void* kv, const float* gamma, float eps, int tokens, int dim,
+                         const int* cur_pos, void* kv_cache, void* stream);
+/* qkv_rope_op (ops/qkv_rope.py:21-50): interleaved RoPE in place on q_pe [tokens, heads, rope] and on
+ * pe_cache[*cur_pos + t].  freqs [tokens, rope/2, 2] f32 = (cos, sin). */
+int tilert_qkv_rope_op(TbContext* ctx, void* q_pe, int heads, int rope, void* pe_cache, const int* cur_pos,
+                       const float* freqs, int tokens, void* stream);
+/* rotate_op (ops/rotate.py:61-105): non-interleaved RoPE on the first `rope` dims + Hadamard-128. */
+int tilert_rotate_op(TbContext* ctx, const void* in, void* out, int heads, int rope, const float* freqs,
+                     int tokens, void* stream);
+/* layernorm_rope_rotate_op (ops/layernorm_rope_rotate.py:23-83): LayerNorm -> RoPE -> Hadamard into
+ * k_cache[*cur_pos + t]. */
+int tilert_layernorm_rope_rotate_op(TbContext* ctx, const void* in, const int* cur_pos, void* k_cache,
+                                    const float* weight, const float* bias, const float* freqs, int rope,
+                                    int tokens, void* stream);
+
+/* ---- DSA indexer and sparse attention ---------------------------------------------------- */
+
+/* sparse_index_op (ops/sparse_index.py:11-69): logits[t, j] = sum_h w[t,h] relu(q[t,h] . k_cache[j])
+ * for j < n_keys, -inf where j > *cur_pos + t.  heads in {16, 32, 64}, head dim 128. */
+int tilert_sparse_index_op(TbContext* ctx, const void* q, const void* k_cache, const void* weights, float* logits,
+                           long long logits_stride, int heads, int tokens, int n_keys, const int* cur_pos,
+                           void* stream);
+/* topk_accurate_op (ops/topk.py:60-109): exact top-k of each of `rows` logit rows (entries >= n or
+ * equal to -inf never selected); indices ascending, unused slots -1. */
+int tilert_topk_accurate_op(TbContext* ctx, const float* logits, long long logits_stride, int rows, int n, int k,
+                            int* indices, void* stream);
+/* sparse_index_topk_dsv32_op (ops/sparse_index.py:72-128): the two above back to back. */
+int tilert_sparse_index_topk_op(TbContext* ctx, const void* q, const void* k_cache, const void* weights,
+                                float* logits, long long logits_stride, int heads, int tokens, int n_keys,
+                                const int* cur_pos, int k, int* indices, void* stream);
+/* flash_sparse_mla_op (ops/flash_sparse_mla.py:18-93): softmax((q.kv + q_pe.pe) * scale) . kv over the
+ * selected rows.  out_acc [tokens, heads, n_splits, 512] f32 and lse_acc [tokens, heads, n_splits] f32
+ * with n_splits = ceil(topk / split_size); split_size a multiple of 64. */
+int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const void* q_pe, const void* kv, const void* k_pe,
+                               const int* indices, int topk, const int* cur_pos, int heads, int tokens, int n_cache,
+                               float softmax_scale, int split_size, void* out, float* out_acc, float* lse,
+                               float* lse_acc, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TILERT_B200_H_ */

@@ -1,0 +1,43 @@
+"""In-tree build of the CUDA library: one nvcc call, sm_100a only.
+
+    python -m tilert_b200.build
+
+writes ``tilert_b200/libtilert_b200.so`` next to the package (the place ``load_backend`` looks).
+"""
+
+from __future__ import annotations
+
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+SRC = PKG / "csrc" / "cabi.cu"
+OUT = PKG / "libtilert_b200.so"
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC",
+]
+
+
+def needs_build() -> bool:
+    if not OUT.exists():
+        return True
+    newest = max(p.stat().st_mtime for p in list((PKG / "csrc").glob("*")) + [PKG.parent / "include" / "tilert_b200.h"])
+    return newest > OUT.stat().st_mtime
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    if not force and not needs_build():
+        return OUT
+    cmd = ["nvcc", *NVCC_FLAGS, *( ["-Xptxas", "-v"] if verbose else []), "-o", str(OUT), str(SRC)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed:\n{res.stdout}\n{res.stderr}")
+    if verbose:
+        print(res.stderr)
+    return OUT
+
+
+if __name__ == "__main__":
+    print(build(force=True, verbose="-v" in sys.argv))

@@ -1,0 +1,769 @@
+// C ABI of the decode path: argument checks, parameter blocks and kernel launches.
+// Declarations and the reference operator each entry point replaces: include/tilert_b200.h.
+#include "../../include/tilert_b200.h"
+
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "actpack.cuh"
+#include "elementwise.cuh"
+#include "gemv_bf16.cuh"
+#include "indexer.cuh"
+#include "sparse_mla.cuh"
+#include "wstream_gemv.cuh"
+
+using namespace tb;
+
+namespace {
+
+thread_local std::string g_last_error;
+long long g_launches = 0;
+
+int fail(int code, const char* fmt, const char* detail = "") {
+  char buf[512];
+  snprintf(buf, sizeof(buf), fmt, detail);
+  g_last_error = buf;
+  return code;
+}
+#define TB_CUDA(expr)                                                        \
+  do {                                                                       \
+    cudaError_t e__ = (expr);                                                \
+    if (e__ != cudaSuccess) return fail(TB_ECUDA, #expr ": %s", cudaGetErrorString(e__)); \
+  } while (0)
+#define TB_REQUIRE(cond) \
+  do {                   \
+    if (!(cond)) return fail(TB_EINVAL, "requirement failed: %s", #cond); \
+  } while (0)
+
+constexpr int kMaxGrid = 256;                       // CTAs a GEMV launch may use (>= SM count)
+constexpr size_t kPartialBytes = 2ull * kMaxGrid * 8 * 32 * 16;
+constexpr int kMaxCounters = 1 << 16;               // row tiles * 8
+constexpr size_t kXpackScratchBytes = 2ull << 20;   // activation blocks of the widest K (2048 blocks)
+constexpr size_t kSmallScratchBytes = 64ull << 10;  // slot ids / weights for routing
+
+}  // namespace
+
+struct TbContext {
+  int device = 0;
+  int num_sms = 0;
+  float* partial = nullptr;
+  int* counters = nullptr;
+  int* status = nullptr;
+  uint8_t* xpack = nullptr;
+  uint8_t* small = nullptr;
+};
+
+struct TbComm {
+  TbContext* ctx = nullptr;
+  int world = 1, rank = 0, max_rows = 0;
+  void* buffers[8] = {};
+};
+
+namespace {
+
+size_t comm_state_offset(int world, int max_rows) {
+  // [2 halves][world][4 tokens][max_rows] f32, then the endpoint state
+  size_t b = 2ull * world * 4 * max_rows * sizeof(float);
+  return (b + 255) / 256 * 256;
+}
+
+int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
+  static bool attr_set[64] = {};
+  if (!attr_set[ctx->device & 63]) {
+    TB_CUDA(cudaFuncSetAttribute(wstream_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBytes));
+    attr_set[ctx->device & 63] = true;
+  }
+  TB_REQUIRE(p.n_tiles > 0 && p.n_kb > 0);
+  TB_REQUIRE(p.n_tiles * 8 <= kMaxCounters);
+  const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
+  int grid = ctx->num_sms < kMaxGrid ? ctx->num_sms : kMaxGrid;
+  if (units < grid) grid = static_cast<int>(units);
+  p.partial = ctx->partial;
+  p.counters = ctx->counters;
+  p.status = ctx->status;
+  wstream_gemv_kernel<<<grid, kGemvThreads, kGemvSmemBytes, st>>>(p);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+void gemv_defaults(GemvParams& p) {
+  memset(&p, 0, sizeof(p));
+  p.only_token = -1;
+  p.cols_per_token = 2;
+  p.epi = EPI_STORE;
+  p.ar.world = 1;
+}
+
+void set_region(GemvParams& p, int row_begin, int rows, void* ptr, long long token_stride, int dtype = 0,
+                const int* pos = nullptr) {
+  if (rows <= 0 || ptr == nullptr) return;
+  OutRegion& r = p.regions[p.n_regions++];
+  r.row_begin = row_begin;
+  r.row_end = row_begin + rows;
+  r.dtype = dtype;
+  r.ptr = ptr;
+  r.token_stride = token_stride;
+  r.pos_ptr = pos;
+}
+
+int set_comm(GemvParams& p, TbComm* comm, int n_rows) {
+  if (comm == nullptr || comm->world <= 1) return TB_OK;
+  TB_REQUIRE(n_rows == comm->max_rows);  // slot stride of the receive buffers
+  p.ar.world = comm->world;
+  p.ar.rank = comm->rank;
+  const size_t off = comm_state_offset(comm->world, comm->max_rows);
+  for (int r = 0; r < comm->world; ++r) {
+    p.ar.recv[r] = reinterpret_cast<float*>(comm->buffers[r]);
+    p.ar.state[r] = reinterpret_cast<AllReduceState*>(reinterpret_cast<uint8_t*>(comm->buffers[r]) + off);
+  }
+  return TB_OK;
+}
+
+int launch_actpack(const ActPackParams& p, cudaStream_t st) {
+  TB_REQUIRE(p.k % TB_KBLOCK == 0 && p.k / TB_KBLOCK <= 32 * kActPackMaxIter);
+  TB_REQUIRE(p.n_tokens >= 1 && p.n_tokens <= 4);
+  actpack_kernel<<<p.n_tokens, kActPackThreads, 0, st>>>(p);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+// Plain (no norm) packing of a flat [tokens, k] bf16 array that may exceed the single-CTA limit of
+// the normalising kernel: split into chunks of at most 32*kActPackMaxIter blocks.
+int pack_flat(const void* x, int tokens, int k, const float* seg_scale, int n_seg, uint8_t* xpack,
+              cudaStream_t st) {
+  const int max_k = 32 * kActPackMaxIter * TB_KBLOCK;
+  TB_REQUIRE(seg_scale == nullptr || k <= max_k);
+  for (int k0 = 0; k0 < k; k0 += max_k) {
+    ActPackParams p{};
+    p.x = reinterpret_cast<const __nv_bfloat16*>(x) + k0;
+    p.x_stride = k;
+    p.k = (k - k0) < max_k ? (k - k0) : max_k;
+    p.n_tokens = tokens;
+    p.seg_scale = seg_scale;
+    p.n_seg = n_seg;
+    p.kb_per_seg = n_seg > 0 ? (k / TB_KBLOCK) / n_seg : 1;
+    p.xpack = xpack + static_cast<size_t>(k0 / TB_KBLOCK) * TB_XBLK_BYTES;
+    int rc = launch_actpack(p, st);
+    if (rc != TB_OK) return rc;
+  }
+  return TB_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------- runtime
+extern "C" const char* tilert_b200_last_error(void) { return g_last_error.c_str(); }
+extern "C" int tilert_b200_dsa_temp_vars_size(void) { return 56; }
+extern "C" size_t tilert_b200_context_bytes(void) {
+  return kPartialBytes + kMaxCounters * sizeof(int) + 256 + kXpackScratchBytes + kSmallScratchBytes;
+}
+extern "C" size_t tilert_b200_xpack_bytes(int dim) { return static_cast<size_t>(dim / TB_KBLOCK) * TB_XBLK_BYTES; }
+
+extern "C" int tilert_b200_init(int device, TbContext** ctx_out) {
+  TB_REQUIRE(ctx_out != nullptr);
+  TB_CUDA(cudaSetDevice(device));
+  TbContext* c = new TbContext();
+  c->device = device;
+  cudaDeviceProp prop;
+  TB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major < 10) {
+    delete c;
+    return fail(TB_ESTATE, "this library is built for sm_100a only; device is %s", prop.name);
+  }
+  c->num_sms = prop.multiProcessorCount;
+  TB_CUDA(cudaMalloc(&c->partial, kPartialBytes));
+  TB_CUDA(cudaMalloc(&c->counters, kMaxCounters * sizeof(int)));
+  TB_CUDA(cudaMalloc(&c->status, 256));
+  TB_CUDA(cudaMalloc(&c->xpack, kXpackScratchBytes));
+  TB_CUDA(cudaMalloc(&c->small, kSmallScratchBytes));
+  TB_CUDA(cudaMemset(c->counters, 0, kMaxCounters * sizeof(int)));
+  TB_CUDA(cudaMemset(c->status, 0, 256));
+  TB_CUDA(cudaMemset(c->xpack, 0, kXpackScratchBytes));
+  TB_CUDA(cudaMemset(c->small, 0, kSmallScratchBytes));
+  TB_CUDA(cudaDeviceSynchronize());
+  *ctx_out = c;
+  return TB_OK;
+}
+
+extern "C" int tilert_b200_destroy(TbContext* ctx) {
+  if (ctx == nullptr) return TB_OK;
+  cudaSetDevice(ctx->device);
+  cudaFree(ctx->partial);
+  cudaFree(ctx->counters);
+  cudaFree(ctx->status);
+  cudaFree(ctx->xpack);
+  cudaFree(ctx->small);
+  delete ctx;
+  return TB_OK;
+}
+
+extern "C" int tilert_b200_status(TbContext* ctx, int* status_out) {
+  TB_REQUIRE(ctx != nullptr && status_out != nullptr);
+  TB_CUDA(cudaSetDevice(ctx->device));
+  TB_CUDA(cudaDeviceSynchronize());
+  TB_CUDA(cudaMemcpy(status_out, ctx->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*status_out != 0) TB_CUDA(cudaMemset(ctx->status, 0, sizeof(int)));
+  return TB_OK;
+}
+
+extern "C" int tilert_b200_num_sms(TbContext* ctx) { return ctx != nullptr ? ctx->num_sms : 0; }
+extern "C" long long tilert_b200_launch_count(void) { return g_launches; }
+extern "C" int tilert_b200_dev_alloc(size_t bytes, void** dev_ptr_out) {
+  TB_REQUIRE(dev_ptr_out != nullptr && bytes > 0);
+  TB_CUDA(cudaMalloc(dev_ptr_out, bytes));
+  TB_CUDA(cudaMemset(*dev_ptr_out, 0, bytes));
+  TB_CUDA(cudaDeviceSynchronize());
+  return TB_OK;
+}
+extern "C" int tilert_b200_dev_free(void* dev_ptr) {
+  TB_CUDA(cudaFree(dev_ptr));
+  return TB_OK;
+}
+
+// ------------------------------------------------------------------------------ p2p plumbing
+extern "C" size_t tilert_b200_comm_buffer_bytes(int world, int max_rows) {
+  return comm_state_offset(world, max_rows) + 256;
+}
+extern "C" int tilert_b200_ipc_export(void* dev_ptr, uint8_t handle_out[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  TB_CUDA(cudaIpcGetMemHandle(&h, dev_ptr));
+  memcpy(handle_out, &h, 64);
+  return TB_OK;
+}
+extern "C" int tilert_b200_ipc_import(const uint8_t handle[64], void** dev_ptr_out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  TB_CUDA(cudaIpcOpenMemHandle(dev_ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+  return TB_OK;
+}
+extern "C" int tilert_b200_ipc_close(void* dev_ptr) {
+  TB_CUDA(cudaIpcCloseMemHandle(dev_ptr));
+  return TB_OK;
+}
+extern "C" int tilert_b200_comm_create(TbContext* ctx, int world, int rank, void* const* buffers, int max_rows,
+                                       TbComm** comm_out) {
+  TB_REQUIRE(ctx != nullptr && comm_out != nullptr && buffers != nullptr);
+  TB_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world && max_rows > 0);
+  TbComm* c = new TbComm();
+  c->ctx = ctx;
+  c->world = world;
+  c->rank = rank;
+  c->max_rows = max_rows;
+  for (int r = 0; r < world; ++r) {
+    if (buffers[r] == nullptr) {
+      delete c;
+      return fail(TB_EINVAL, "comm buffer pointer is null%s");
+    }
+    c->buffers[r] = buffers[r];
+  }
+  *comm_out = c;
+  return TB_OK;
+}
+extern "C" int tilert_b200_comm_destroy(TbComm* comm) {
+  delete comm;
+  return TB_OK;
+}
+
+// --------------------------------------------------------------------- activation preparation
+extern "C" int tilert_rmsnorm_quant_op(TbContext* ctx, const void* x, const float* gamma, float eps, int tokens,
+                                       int dim, void* out, uint8_t* q_out, float* q_scale_out,
+                                       const float* seg_scale, int n_seg, uint8_t* xpack, void* stream) {
+  TB_REQUIRE(ctx != nullptr && x != nullptr);
+  TB_REQUIRE((q_out == nullptr) == (q_scale_out == nullptr));
+  if (xpack == nullptr) xpack = ctx->xpack;  // caller only wants the bf16 / reference-format outputs
+  if (gamma == nullptr && out == nullptr && q_out == nullptr)
+    return pack_flat(x, tokens, dim, seg_scale, n_seg, xpack, static_cast<cudaStream_t>(stream));
+  ActPackParams p{};
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x);
+  p.x_stride = dim;
+  p.k = dim;
+  p.n_tokens = tokens;
+  p.gamma = gamma;
+  p.eps = eps;
+  p.seg_scale = seg_scale;
+  p.n_seg = n_seg;
+  p.kb_per_seg = n_seg > 0 ? (dim / TB_KBLOCK) / n_seg : 1;
+  p.xpack = xpack;
+  p.out_bf16 = reinterpret_cast<__nv_bfloat16*>(out);
+  p.out_stride = dim;
+  p.out_q = q_out;
+  p.out_qscale = q_scale_out;
+  return launch_actpack(p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tilert_xq_repack_op(TbContext* ctx, const uint8_t* x_q, const float* x_scale, int tokens, int dim,
+                                   uint8_t* xpack, void* stream) {
+  TB_REQUIRE(ctx != nullptr && x_q != nullptr && x_scale != nullptr && xpack != nullptr);
+  TB_REQUIRE(dim % TB_KBLOCK == 0 && tokens >= 1 && tokens <= 8);
+  const int n_kb = dim / TB_KBLOCK;
+  xq_repack_kernel<<<(n_kb + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(x_q, x_scale, tokens, dim, xpack);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+// ------------------------------------------------------------------- FP8 streaming products
+extern "C" int tilert_projx_wqkva_op(TbContext* ctx, const uint8_t* xpack, int cols_per_token,
+                                     const uint8_t* w_packed, int tokens, int dim, int q_lora, int kv_lora, int rope,
+                                     int ki_dim, const int* cur_pos, void* q_out, void* kv_out, void* pe_cache,
+                                     void* ki_out, void* stream) {
+  TB_REQUIRE(ctx != nullptr && xpack != nullptr && w_packed != nullptr);
+  TB_REQUIRE(dim % TB_KBLOCK == 0 && (cols_per_token == 1 || cols_per_token == 2));
+  TB_REQUIRE(tokens >= 1 && tokens * cols_per_token <= 8);
+  TB_REQUIRE(rope == 0 || cur_pos != nullptr);
+  const int rows = q_lora + kv_lora + rope + ki_dim;
+  GemvParams p;
+  gemv_defaults(p);
+  p.w = w_packed;
+  p.x = xpack;
+  p.n_tiles = (rows + TB_TILE_ROWS - 1) / TB_TILE_ROWS;
+  p.n_kb = dim / TB_KBLOCK;
+  p.w_kb_per_tile = p.n_kb;
+  p.n_tokens = tokens;
+  p.cols_per_token = cols_per_token;
+  p.n_rows = rows;
+  set_region(p, 0, q_lora, q_out, q_lora);
+  set_region(p, q_lora, kv_lora, kv_out, kv_lora);
+  set_region(p, q_lora + kv_lora, rope, pe_cache, rope, 0, cur_pos);
+  set_region(p, q_lora + kv_lora + rope, ki_dim, ki_out, ki_dim);
+  return launch_gemv(ctx, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tilert_rmsnorm_proj_q_op(TbContext* ctx, const void* q, const float* gamma, float eps,
+                                        const uint8_t* w_packed, int tokens, int q_lora, int heads, int nope,
+                                        int rope, int iq_heads, int iq_dim, void* q_nope, void* q_pe, void* iq,
+                                        void* stream) {
+  TB_REQUIRE(ctx != nullptr && q != nullptr && gamma != nullptr && w_packed != nullptr);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ActPackParams a{};
+  a.x = reinterpret_cast<const __nv_bfloat16*>(q);
+  a.x_stride = q_lora;
+  a.k = q_lora;
+  a.n_tokens = tokens;
+  a.gamma = gamma;
+  a.eps = eps;
+  a.xpack = ctx->xpack;
+  int rc = launch_actpack(a, st);
+  if (rc != TB_OK) return rc;
+  const int r_nope = heads * nope, r_pe = heads * rope, r_iq = iq_heads * iq_dim;
+  GemvParams p;
+  gemv_defaults(p);
+  p.w = w_packed;
+  p.x = ctx->xpack;
+  p.n_rows = r_nope + r_pe + r_iq;
+  p.n_tiles = (p.n_rows + TB_TILE_ROWS - 1) / TB_TILE_ROWS;
+  p.n_kb = q_lora / TB_KBLOCK;
+  p.w_kb_per_tile = p.n_kb;
+  p.n_tokens = tokens;
+  set_region(p, 0, r_nope, q_nope, r_nope);
+  set_region(p, r_nope, r_pe, q_pe, r_pe);
+  set_region(p, r_nope + r_pe, r_iq, iq, r_iq);
+  return launch_gemv(ctx, p, st);
+}
+
+extern "C" int tilert_projq_wqb_op(TbContext* ctx, const void* q_nope, const uint8_t* w_packed, int tokens,
+                                   int heads, int nope, int kv_lora, void* out, void* stream) {
+  TB_REQUIRE(ctx != nullptr && q_nope != nullptr && w_packed != nullptr && out != nullptr);
+  TB_REQUIRE(nope % TB_KBLOCK == 0 && kv_lora % TB_TILE_ROWS == 0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = pack_flat(q_nope, tokens, heads * nope, nullptr, 0, ctx->xpack, st);
+  if (rc != TB_OK) return rc;
+  GemvParams p;
+  gemv_defaults(p);
+  p.w = w_packed;
+  p.x = ctx->xpack;
+  p.n_rows = heads * kv_lora;
+  p.n_tiles = p.n_rows / TB_TILE_ROWS;
+  p.n_kb = nope / TB_KBLOCK;
+  p.w_kb_per_tile = p.n_kb;
+  p.tiles_per_xseg = kv_lora / TB_TILE_ROWS;
+  p.n_tokens = tokens;
+  set_region(p, 0, p.n_rows, out, p.n_rows);
+  return launch_gemv(ctx, p, st);
+}
+
+extern "C" int tilert_projo_wkvb_op(TbContext* ctx, const void* o_lat, const uint8_t* w_packed, int tokens,
+                                    int heads, int kv_lora, int v_dim, void* out, void* stream) {
+  TB_REQUIRE(ctx != nullptr && o_lat != nullptr && w_packed != nullptr && out != nullptr);
+  TB_REQUIRE(kv_lora % TB_KBLOCK == 0 && v_dim % TB_TILE_ROWS == 0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = pack_flat(o_lat, tokens, heads * kv_lora, nullptr, 0, ctx->xpack, st);
+  if (rc != TB_OK) return rc;
+  GemvParams p;
+  gemv_defaults(p);
+  p.w = w_packed;
+  p.x = ctx->xpack;
+  p.n_rows = heads * v_dim;
+  p.n_tiles = p.n_rows / TB_TILE_ROWS;
+  p.n_kb = kv_lora / TB_KBLOCK;
+  p.w_kb_per_tile = p.n_kb;
+  p.tiles_per_xseg = v_dim / TB_TILE_ROWS;
+  p.n_tokens = tokens;
+  set_region(p, 0, p.n_rows, out, p.n_rows);
+  return launch_gemv(ctx, p, st);
+}
+
+extern "C" int tilert_unproj_o_allreduce_op(TbContext* ctx, const void* vec, const uint8_t* w_packed,
+                                            const void* x_residual, int tokens, int k, int n, void* out,
+                                            TbComm* comm, void* stream) {
+  TB_REQUIRE(ctx != nullptr && vec != nullptr && w_packed != nullptr && out != nullptr);
+  TB_REQUIRE(k % TB_KBLOCK == 0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = pack_flat(vec, tokens, k, nullptr, 0, ctx->xpack, st);
+  if (rc != TB_OK) return rc;
+  GemvParams p;
+  gemv_defaults(p);
+  p.w = w_packed;
+  p.x = ctx->xpack;
+  p.n_rows = n;
+  p.n_tiles = (n + TB_TILE_ROWS - 1) / TB_TILE_ROWS;
+  p.n_kb = k / TB_KBLOCK;
+  p.w_kb_per_tile = p.n_kb;
+  p.n_tokens = tokens;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(x_residual);
+  p.residual_stride = n;
+  set_region(p, 0, n, out, n);
+  rc = set_comm(p, comm, n);
+  if (rc != TB_OK) return rc;
+  return launch_gemv(ctx, p, st);
+}
+
+extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const uint8_t* xpack, const float* scores,
+                                                    const float* bias, const uint8_t* w_packed,
+                                                    long long expert_stride, int tokens, int dim, int inter,
+                                                    int n_experts, int n_groups, int n_limited_groups, int top_k,
+                                                    float route_scale, void* hidden_out, float* probs_out,
+                                                    int* idx_out, int* slot_ids, float* slot_w, void* stream) {
+  TB_REQUIRE(ctx != nullptr && xpack != nullptr && scores != nullptr && w_packed != nullptr);
+  TB_REQUIRE(hidden_out != nullptr && probs_out != nullptr && idx_out != nullptr);
+  TB_REQUIRE(n_experts <= 256 && top_k <= 31 && (n_groups == 1 || (32 % n_groups == 0 && n_experts % 32 == 0)));
+  TB_REQUIRE((2 * inter) % TB_TILE_ROWS == 0 && dim % TB_KBLOCK == 0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (slot_ids == nullptr) slot_ids = reinterpret_cast<int*>(ctx->small);
+  if (slot_w == nullptr) slot_w = reinterpret_cast<float*>(ctx->small + 4096);
+  expert_select_kernel<<<(tokens + 3) / 4, 128, 0, st>>>(scores, bias, n_experts, n_groups, n_limited_groups, top_k,
+                                                         route_scale, n_experts, probs_out, idx_out, slot_ids,
+                                                         slot_w, tokens);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  const int n_slots = top_k + 1;
+  for (int t = 0; t < tokens; ++t) {
+    GemvParams p;
+    gemv_defaults(p);
+    p.w = w_packed;
+    p.x = xpack;
+    p.tiles_per_nseg = 2 * inter / TB_TILE_ROWS;
+    p.n_tiles = n_slots * p.tiles_per_nseg;
+    p.n_kb = dim / TB_KBLOCK;
+    p.w_kb_per_tile = p.n_kb;
+    p.nseg_ids = slot_ids + t * n_slots;
+    p.expert_stride = expert_stride;
+    p.n_tokens = tokens;
+    p.only_token = tokens > 1 ? t : -1;
+    p.epi = EPI_SILU_MUL;
+    p.n_rows = n_slots * inter;
+    set_region(p, 0, p.n_rows, hidden_out, p.n_rows);
+    int rc = launch_gemv(ctx, p, st);
+    if (rc != TB_OK) return rc;
+  }
+  return TB_OK;
+}
+
+extern "C" int tilert_expert_down_allreduce_op(TbContext* ctx, const void* vec, const uint8_t* w_packed,
+                                               long long expert_stride, const int* slot_ids, const float* slot_w,
+                                               const void* x_residual, int tokens, int inter, int dim, int n_slots,
+                                               void* out, TbComm* comm, void* stream) {
+  TB_REQUIRE(ctx != nullptr && vec != nullptr && w_packed != nullptr && out != nullptr);
+  TB_REQUIRE(inter % TB_KBLOCK == 0);
+  TB_REQUIRE(comm == nullptr || comm->world == 1 || tokens == 1);  // per-token launches share one reduction slot
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (slot_ids == nullptr) slot_ids = reinterpret_cast<const int*>(ctx->small);
+  if (slot_w == nullptr) slot_w = reinterpret_cast<const float*>(ctx->small + 4096);
+  int rc = pack_flat(vec, tokens, n_slots * inter, slot_w, n_slots, ctx->xpack, st);
+  if (rc != TB_OK) return rc;
+  for (int t = 0; t < tokens; ++t) {
+    GemvParams p;
+    gemv_defaults(p);
+    p.w = w_packed;
+    p.x = ctx->xpack;
+    p.n_rows = dim;
+    p.n_tiles = (dim + TB_TILE_ROWS - 1) / TB_TILE_ROWS;
+    p.kb_per_kseg = inter / TB_KBLOCK;
+    p.n_kb = n_slots * p.kb_per_kseg;
+    p.w_kb_per_tile = p.kb_per_kseg;
+    p.kseg_ids = slot_ids + t * n_slots;
+    p.expert_stride = expert_stride;
+    p.n_tokens = tokens;
+    p.only_token = tokens > 1 ? t : -1;
+    p.residual = reinterpret_cast<const __nv_bfloat16*>(x_residual);
+    p.residual_stride = dim;
+    set_region(p, 0, dim, out, dim);
+    rc = set_comm(p, comm, dim);
+    if (rc != TB_OK) return rc;
+    rc = launch_gemv(ctx, p, st);
+    if (rc != TB_OK) return rc;
+  }
+  return TB_OK;
+}
+
+extern "C" int tilert_rmsnorm_up_gate_silu_op(TbContext* ctx, const void* x, const float* gamma, float eps,
+                                              const uint8_t* w_packed, int tokens, int dim, int inter, void* out,
+                                              void* stream) {
+  TB_REQUIRE(ctx != nullptr && x != nullptr && gamma != nullptr && w_packed != nullptr && out != nullptr);
+  TB_REQUIRE((2 * inter) % TB_TILE_ROWS == 0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ActPackParams a{};
+  a.x = reinterpret_cast<const __nv_bfloat16*>(x);
+  a.x_stride = dim;
+  a.k = dim;
+  a.n_tokens = tokens;
+  a.gamma = gamma;
+  a.eps = eps;
+  a.xpack = ctx->xpack;
+  int rc = launch_actpack(a, st);
+  if (rc != TB_OK) return rc;
+  GemvParams p;
+  gemv_defaults(p);
+  p.w = w_packed;
+  p.x = ctx->xpack;
+  p.n_tiles = 2 * inter / TB_TILE_ROWS;
+  p.n_kb = dim / TB_KBLOCK;
+  p.w_kb_per_tile = p.n_kb;
+  p.n_tokens = tokens;
+  p.epi = EPI_SILU_MUL;
+  p.n_rows = inter;
+  set_region(p, 0, inter, out, inter);
+  return launch_gemv(ctx, p, st);
+}
+
+extern "C" int tilert_down_allreduce_op(TbContext* ctx, const void* vec, const uint8_t* w_packed,
+                                        const void* x_residual, int tokens, int inter, int dim, void* out,
+                                        TbComm* comm, void* stream) {
+  return tilert_unproj_o_allreduce_op(ctx, vec, w_packed, x_residual, tokens, inter, dim, out, comm, stream);
+}
+
+// ------------------------------------------------------------------------------ bf16 products
+namespace {
+int launch_gemv_bf16(TbContext* ctx, GemvBf16Params& p, cudaStream_t st) {
+  TB_REQUIRE(p.n_tokens >= 1 && p.n_tokens <= 4);
+  TB_REQUIRE(p.k % 256 == 0);
+  const int tok_t = p.n_tokens == 1 ? 1 : (p.n_tokens == 2 ? 2 : 4);
+  const size_t smem = static_cast<size_t>(tok_t) * p.k * sizeof(float);
+  const int warps = kGemvBf16Threads / 32;
+  int grid = (p.n + warps - 1) / warps;
+  const int cap = ctx->num_sms * 2;
+  if (grid > cap) grid = cap;
+  static bool attr_set = false;
+  if (!attr_set) {
+    TB_CUDA(cudaFuncSetAttribute(gemv_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    TB_CUDA(cudaFuncSetAttribute(gemv_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    TB_CUDA(cudaFuncSetAttribute(gemv_bf16_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_set = true;
+  }
+  TB_REQUIRE(smem <= 200 * 1024);
+  if (tok_t == 1)
+    gemv_bf16_kernel<1><<<grid, kGemvBf16Threads, smem, st>>>(p);
+  else if (tok_t == 2)
+    gemv_bf16_kernel<2><<<grid, kGemvBf16Threads, smem, st>>>(p);
+  else
+    gemv_bf16_kernel<4><<<grid, kGemvBf16Threads, smem, st>>>(p);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+}  // namespace
+
+extern "C" int tilert_proj_w_op(TbContext* ctx, const void* x, const void* w, int tokens, int n, int k, void* out,
+                                void* stream) {
+  TB_REQUIRE(ctx != nullptr && x != nullptr && w != nullptr && out != nullptr);
+  GemvBf16Params p{};
+  p.w = w;
+  p.n = n;
+  p.k = k;
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x);
+  p.x_stride = k;
+  p.n_tokens = tokens;
+  p.out = out;
+  p.out_bf16 = 1;
+  p.out_stride = n;
+  return launch_gemv_bf16(ctx, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tilert_rmsnorm_expert_proj_op(TbContext* ctx, const void* x, const float* gamma, float eps,
+                                             const void* w_gate, int gate_is_f32, int tokens, int dim,
+                                             int n_experts, float* scores_out, void* hidden_out, void* stream) {
+  TB_REQUIRE(ctx != nullptr && x != nullptr && w_gate != nullptr && scores_out != nullptr);  // gamma == NULL: x is already normalised
+  GemvBf16Params p{};
+  p.w = w_gate;
+  p.w_is_f32 = gate_is_f32;
+  p.n = n_experts;
+  p.k = dim;
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x);
+  p.x_stride = dim;
+  p.n_tokens = tokens;
+  p.gamma = gamma;
+  p.eps = eps;
+  p.round_norm_bf16 = 1;
+  p.xnorm_out = reinterpret_cast<__nv_bfloat16*>(hidden_out);
+  p.xnorm_stride = dim;
+  p.out = scores_out;
+  p.out_stride = n_experts;
+  return launch_gemv_bf16(ctx, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tilert_rmsnorm_head_proj_op(TbContext* ctx, const void* x, const float* gamma, float eps,
+                                           const void* w, int tokens, int dim, int vocab, void* x_norm_out,
+                                           float* logits_out, void* stream) {
+  TB_REQUIRE(ctx != nullptr && x != nullptr && gamma != nullptr && w != nullptr && logits_out != nullptr);
+  GemvBf16Params p{};
+  p.w = w;
+  p.n = vocab;
+  p.k = dim;
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x);
+  p.x_stride = dim;
+  p.n_tokens = tokens;
+  p.gamma = gamma;
+  p.eps = eps;
+  p.round_norm_bf16 = 0;
+  p.xnorm_out = reinterpret_cast<__nv_bfloat16*>(x_norm_out);
+  p.xnorm_stride = dim;
+  p.out = logits_out;
+  p.out_stride = vocab;
+  return launch_gemv_bf16(ctx, p, static_cast<cudaStream_t>(stream));
+}
+
+// -------------------------------------------------------------------- per-token vector operators
+extern "C" int tilert_rmsnorm_kv_op(TbContext* ctx, const void* kv, const float* gamma, float eps, int tokens,
+                                    int dim, const int* cur_pos, void* kv_cache, void* stream) {
+  TB_REQUIRE(ctx != nullptr && kv != nullptr && gamma != nullptr && cur_pos != nullptr && kv_cache != nullptr);
+  rmsnorm_kv_kernel<<<(tokens + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(kv), dim, gamma, eps, dim, cur_pos,
+      reinterpret_cast<__nv_bfloat16*>(kv_cache), tokens);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+extern "C" int tilert_qkv_rope_op(TbContext* ctx, void* q_pe, int heads, int rope, void* pe_cache,
+                                  const int* cur_pos, const float* freqs, int tokens, void* stream) {
+  TB_REQUIRE(ctx != nullptr && q_pe != nullptr && pe_cache != nullptr && cur_pos != nullptr && freqs != nullptr);
+  const int total = tokens * (heads + 1) * (rope / 2);
+  qkv_rope_kernel<<<(total + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(q_pe), heads, rope, reinterpret_cast<__nv_bfloat16*>(pe_cache), cur_pos,
+      freqs, tokens);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+extern "C" int tilert_rotate_op(TbContext* ctx, const void* in, void* out, int heads, int rope, const float* freqs,
+                                int tokens, void* stream) {
+  TB_REQUIRE(ctx != nullptr && in != nullptr && out != nullptr && freqs != nullptr);
+  TB_REQUIRE(rope == 64);
+  const int vecs = tokens * heads;
+  rotate128_kernel<<<(vecs + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), heads, rope, freqs, nullptr,
+      nullptr, nullptr, tokens);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+extern "C" int tilert_layernorm_rope_rotate_op(TbContext* ctx, const void* in, const int* cur_pos, void* k_cache,
+                                               const float* weight, const float* bias, const float* freqs, int rope,
+                                               int tokens, void* stream) {
+  TB_REQUIRE(ctx != nullptr && in != nullptr && cur_pos != nullptr && k_cache != nullptr);
+  TB_REQUIRE(weight != nullptr && bias != nullptr && freqs != nullptr && rope == 64);
+  rotate128_kernel<<<(tokens + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(k_cache), 1, rope, freqs, weight,
+      bias, cur_pos, tokens);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+// ------------------------------------------------------------------ indexer and sparse attention
+extern "C" int tilert_sparse_index_op(TbContext* ctx, const void* q, const void* k_cache, const void* weights,
+                                      float* logits, long long logits_stride, int heads, int tokens, int n_keys,
+                                      const int* cur_pos, void* stream) {
+  TB_REQUIRE(ctx != nullptr && q != nullptr && k_cache != nullptr && weights != nullptr && logits != nullptr);
+  TB_REQUIRE(cur_pos != nullptr && n_keys > 0 && (heads == 16 || heads == 32 || heads == 64));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 grid((n_keys + 63) / 64, tokens);
+  const size_t smem = static_cast<size_t>(heads + 64) * kIdxPitch * 2;
+  const __nv_bfloat16* qq = reinterpret_cast<const __nv_bfloat16*>(q);
+  const __nv_bfloat16* kk = reinterpret_cast<const __nv_bfloat16*>(k_cache);
+  const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(weights);
+  if (heads == 64)
+    indexer_logits_kernel<64><<<grid, kIdxWarps * 32, smem, st>>>(qq, kk, ww, logits, logits_stride, n_keys, cur_pos, 0);
+  else if (heads == 32)
+    indexer_logits_kernel<32><<<grid, kIdxWarps * 32, smem, st>>>(qq, kk, ww, logits, logits_stride, n_keys, cur_pos, 0);
+  else
+    indexer_logits_kernel<16><<<grid, kIdxWarps * 32, smem, st>>>(qq, kk, ww, logits, logits_stride, n_keys, cur_pos, 0);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+extern "C" int tilert_topk_accurate_op(TbContext* ctx, const float* logits, long long logits_stride, int rows, int n,
+                                       int k, int* indices, void* stream) {
+  TB_REQUIRE(ctx != nullptr && logits != nullptr && indices != nullptr && rows >= 1 && n >= 0 && k >= 1);
+  topk_radix_kernel<<<rows, kTopkThreads, 0, static_cast<cudaStream_t>(stream)>>>(logits, logits_stride, n, k,
+                                                                                  indices, k);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+extern "C" int tilert_sparse_index_topk_op(TbContext* ctx, const void* q, const void* k_cache, const void* weights,
+                                           float* logits, long long logits_stride, int heads, int tokens, int n_keys,
+                                           const int* cur_pos, int k, int* indices, void* stream) {
+  int rc = tilert_sparse_index_op(ctx, q, k_cache, weights, logits, logits_stride, heads, tokens, n_keys, cur_pos,
+                                  stream);
+  if (rc != TB_OK) return rc;
+  return tilert_topk_accurate_op(ctx, logits, logits_stride, tokens, n_keys, k, indices, stream);
+}
+
+extern "C" int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const void* q_pe, const void* kv,
+                                          const void* k_pe, const int* indices, int topk, const int* cur_pos,
+                                          int heads, int tokens, int n_cache, float softmax_scale, int split_size,
+                                          void* out, float* out_acc, float* lse, float* lse_acc, void* stream) {
+  TB_REQUIRE(ctx != nullptr && q != nullptr && q_pe != nullptr && kv != nullptr && k_pe != nullptr);
+  TB_REQUIRE(indices != nullptr && cur_pos != nullptr && out != nullptr && out_acc != nullptr && lse_acc != nullptr);
+  TB_REQUIRE(split_size > 0 && split_size % kMlaKeys == 0 && topk > 0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  static bool attr_set = false;
+  if (!attr_set) {
+    TB_CUDA(cudaFuncSetAttribute(sparse_mla_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmemBytes));
+    attr_set = true;
+  }
+  MlaParams p{};
+  p.q_lat = reinterpret_cast<const __nv_bfloat16*>(q);
+  p.q_pe = reinterpret_cast<const __nv_bfloat16*>(q_pe);
+  p.kv = reinterpret_cast<const __nv_bfloat16*>(kv);
+  p.pe = reinterpret_cast<const __nv_bfloat16*>(k_pe);
+  p.idx = indices;
+  p.topk = topk;
+  p.heads = heads;
+  p.n_cache = n_cache;
+  p.pos = cur_pos;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.blocks_per_split = split_size / kMlaKeys;
+  p.n_splits = (topk + split_size - 1) / split_size;
+  p.o_acc = out_acc;
+  p.lse_acc = lse_acc;
+  p.status = ctx->status;
+  const dim3 grid(p.n_splits, (heads + kMlaHeads - 1) / kMlaHeads, tokens);
+  sparse_mla_kernel<<<grid, kMlaThreads, kMlaSmemBytes, st>>>(p);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  sparse_mla_combine_kernel<<<dim3(heads, tokens), 128, 0, st>>>(out_acc, lse_acc, p.n_splits,
+                                                                 reinterpret_cast<__nv_bfloat16*>(out), lse);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}

@@ -1,0 +1,211 @@
+// Small per-token kernels between the projections: latent RMSNorm into the KV cache, rotary
+// embeddings, and the indexer's (LayerNorm ->) RoPE -> Hadamard transform.  A few KB each;
+// launch-latency bound, not bandwidth bound.
+#pragma once
+
+#include "common.cuh"
+
+namespace tb {
+
+// kv [tokens, dim] -> cache[pos + t, dim] = bf16(rmsnorm(kv) * gamma).   One warp per token.
+__global__ void rmsnorm_kv_kernel(const __nv_bfloat16* __restrict__ kv, long long kv_stride,
+                                  const float* __restrict__ gamma, float eps, int dim, const int* __restrict__ pos,
+                                  __nv_bfloat16* __restrict__ cache, int n_tokens) {
+  const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (tok >= n_tokens) return;
+  const __nv_bfloat16* x = kv + tok * kv_stride;
+  float ss = 0.f;
+  for (int i = lane; i < dim; i += 32) {
+    const float v = bf2f(x[i]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float rinv = rsqrtf(ss / static_cast<float>(dim) + eps);
+  __nv_bfloat16* dst = cache + static_cast<long long>(*pos + tok) * dim;
+  for (int i = lane; i < dim; i += 32) dst[i] = f2bf(bf2f(x[i]) * rinv * gamma[i]);
+}
+
+// Interleaved RoPE (pairs (x[2i], x[2i+1])) applied in place to q_pe [tokens, heads, rope] and to the
+// cached key rows pe_cache[pos + t, rope].  freqs: [tokens, rope/2, 2] = (cos, sin).
+__global__ void qkv_rope_kernel(__nv_bfloat16* __restrict__ q_pe, int heads, int rope,
+                                __nv_bfloat16* __restrict__ pe_cache, const int* __restrict__ pos,
+                                const float* __restrict__ freqs, int n_tokens) {
+  const int half = rope / 2;
+  const int per_tok = (heads + 1) * half;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_tokens * per_tok) return;
+  const int tok = idx / per_tok, rem = idx % per_tok;
+  const int h = rem / half, i = rem % half;
+  const float c = freqs[(tok * half + i) * 2], s = freqs[(tok * half + i) * 2 + 1];
+  __nv_bfloat16* v;
+  if (h < heads)
+    v = q_pe + (static_cast<long long>(tok) * heads + h) * rope + 2 * i;
+  else
+    v = pe_cache + static_cast<long long>(*pos + tok) * rope + 2 * i;
+  const float a = bf2f(v[0]), b = bf2f(v[1]);
+  v[0] = f2bf(a * c - b * s);
+  v[1] = f2bf(a * s + b * c);
+}
+
+// 128-point Walsh-Hadamard transform of a warp-distributed vector: lane l holds elements
+// 4l .. 4l+3.  Natural (Sylvester) ordering.
+__device__ __forceinline__ void hadamard128(float (&v)[4]) {
+  // strides 1 and 2 inside the lane
+  float a = v[0] + v[1], b = v[0] - v[1], c = v[2] + v[3], d = v[2] - v[3];
+  v[0] = a + c; v[1] = b + d; v[2] = a - c; v[3] = b - d;
+  // strides 4 .. 64 across lanes
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const bool upper = (threadIdx.x & o) != 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], o);
+      v[j] = upper ? other - v[j] : v[j] + other;
+    }
+  }
+}
+
+// Indexer rotation: optional LayerNorm (weight, bias, eps 1e-6), non-interleaved RoPE on the first
+// `rope` of 128 dims (pairs (x[i], x[i + rope/2])), then Hadamard-128 scaled by 128^-1/2.  Every
+// stage rounds to bf16 as the reference's bf16 tensor pipeline does.  One warp per 128-vector.
+//   in  [tokens, heads, 128];  out: either [tokens, heads, 128] or cache[pos + t, 128] (heads == 1)
+__global__ void rotate128_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int heads,
+                                 int rope, const float* __restrict__ freqs, const float* __restrict__ ln_w,
+                                 const float* __restrict__ ln_b, const int* __restrict__ pos, int n_tokens) {
+  const int vec = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (vec >= n_tokens * heads) return;
+  const int tok = vec / heads;
+  const __nv_bfloat16* x = in + static_cast<long long>(vec) * 128;
+  float v[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = bf2f(x[lane * 4 + j]);
+  if (ln_w != nullptr) {
+    float s = warp_sum(v[0] + v[1] + v[2] + v[3]);
+    const float mean = s * (1.0f / 128.0f);
+    float d2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) d2 += (v[j] - mean) * (v[j] - mean);
+    d2 = warp_sum(d2);
+    const float rstd = rsqrtf(d2 * (1.0f / 128.0f) + 1e-6f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = bf2f(f2bf((v[j] - mean) * rstd * ln_w[lane * 4 + j] + ln_b[lane * 4 + j]));
+  }
+  // non-interleaved RoPE: element i < rope/2 pairs with element i + rope/2.  With rope = 64 the
+  // partner of lane l (< 8) is lane l + 8.
+  const int half = rope / 2;
+  const int lanes_half = half / 4;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float partner = __shfl_xor_sync(0xffffffffu, v[j], lanes_half);
+    const int e = lane * 4 + j;
+    if (e < rope) {
+      const int i = e < half ? e : e - half;
+      const float c = freqs[(tok * half + i) * 2], s = freqs[(tok * half + i) * 2 + 1];
+      const float re = e < half ? v[j] : partner, im = e < half ? partner : v[j];
+      v[j] = bf2f(f2bf(e < half ? re * c - im * s : re * s + im * c));
+    }
+  }
+  hadamard128(v);
+  __nv_bfloat16* dst = out + static_cast<long long>(vec) * 128;
+  if (pos != nullptr) dst = out + static_cast<long long>(*pos + tok) * 128;
+  const float scale = 0.08838834764831845f;  // 128^-1/2 (a Python scalar in the reference: not rounded to bf16)
+#pragma unroll
+  for (int j = 0; j < 4; ++j) dst[lane * 4 + j] = f2bf(bf2f(f2bf(v[j])) * scale);
+}
+
+// MoE routing (sigmoid scores + bias, optional group limiting, top-k, renormalise, scale).
+// One warp per token; n_experts <= 256 (8 per lane).
+//   scores [tokens, n_experts] f32  ->  probs [tokens, top_k] f32, ids [tokens, top_k] i32,
+//   slot_ids [tokens, top_k + 1] i32 = (shared-expert id, ids...), slot_w [tokens, top_k + 1] = (1, probs...)
+__global__ void expert_select_kernel(const float* __restrict__ scores, const float* __restrict__ bias,
+                                     int n_experts, int n_groups, int n_limited, int top_k, float route_scale,
+                                     int shared_id, float* __restrict__ probs, int* __restrict__ ids,
+                                     int* __restrict__ slot_ids, float* __restrict__ slot_w, int n_tokens) {
+  const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (tok >= n_tokens) return;
+  const int per_lane = (n_experts + 31) / 32;  // experts e = lane*per_lane + j  (contiguous per lane)
+  float orig[8], sel[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int e = lane * per_lane + j;
+    if (j < per_lane && e < n_experts) {
+      const float s = 1.0f / (1.0f + expf(-scores[tok * n_experts + e]));
+      orig[j] = s;
+      sel[j] = bias != nullptr ? s + bias[e] : s;
+    } else {
+      orig[j] = 0.f;
+      sel[j] = -INFINITY;
+    }
+  }
+  if (n_groups > 1) {
+    // group score = sum of the two largest biased scores of the group (max if no bias); a group is
+    // lanes_per_group consecutive lanes
+    const int lanes_per_group = 32 / n_groups;
+    float m1 = -INFINITY, m2 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (sel[j] > m1) { m2 = m1; m1 = sel[j]; } else if (sel[j] > m2) { m2 = sel[j]; }
+    }
+    for (int o = 1; o < lanes_per_group; o <<= 1) {
+      const float o1 = __shfl_xor_sync(0xffffffffu, m1, o), o2 = __shfl_xor_sync(0xffffffffu, m2, o);
+      const float n1 = fmaxf(m1, o1);
+      const float n2 = fmaxf(fminf(m1, o1), fmaxf(m2, o2));
+      m1 = n1; m2 = n2;
+    }
+    const float gscore = bias != nullptr ? m1 + m2 : m1;
+    const int my_group = lane / lanes_per_group;
+    // rank of my group: number of groups with a larger score, ties to the lower group index
+    int rank = 0;
+    for (int g = 0; g < n_groups; ++g) {
+      const float gs = __shfl_sync(0xffffffffu, gscore, g * lanes_per_group);
+      if (gs > gscore || (gs == gscore && g < my_group)) ++rank;
+    }
+    if (rank >= n_limited) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sel[j] = -INFINITY;
+    }
+  }
+  float wsum = 0.f;
+  float my_w = 0.f;
+  int my_id = 0;
+  for (int k = 0; k < top_k; ++k) {
+    // arg-max over the warp, ties to the lower expert index
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = lane * per_lane + j;
+      if (j < per_lane && e < n_experts && (sel[j] > best)) { best = sel[j]; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    float w = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (lane * per_lane + j == best_e) { w = orig[j]; sel[j] = -INFINITY; }
+    }
+    w = __shfl_sync(0xffffffffu, w, best_e / per_lane);
+    wsum += w;
+    if (lane == k) { my_w = w; my_id = best_e; }
+  }
+  if (lane < top_k) {
+    const float pr = my_w / wsum * route_scale;
+    probs[tok * top_k + lane] = pr;
+    ids[tok * top_k + lane] = my_id;
+    slot_ids[tok * (top_k + 1) + 1 + lane] = my_id;
+    slot_w[tok * (top_k + 1) + 1 + lane] = pr;
+  }
+  if (lane == 0) {
+    slot_ids[tok * (top_k + 1)] = shared_id;
+    slot_w[tok * (top_k + 1)] = 1.0f;
+  }
+}
+
+}  // namespace tb

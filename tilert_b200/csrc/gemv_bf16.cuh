@@ -1,0 +1,124 @@
+// bf16-weight GEMV with f32 accumulation for the products that are not FP8 in the checkpoint:
+// the MoE router gate, the indexer head-weight projection and the vocabulary head.
+// HBM-bound on the weight stream: each warp owns whole rows and keeps several 16-byte
+// loads per lane in flight; the (optionally RMS-normalised) activations sit in shared memory.
+#pragma once
+
+#include "common.cuh"
+
+namespace tb {
+
+struct GemvBf16Params {
+  const void* w;                 // [n, k] bf16 (w_is_f32 = 0) or f32 (w_is_f32 = 1), row-major
+  int w_is_f32;
+  int n, k;                      // k multiple of 256
+  const __nv_bfloat16* x;        // [tokens, k]
+  long long x_stride;
+  int n_tokens;                  // 1..4
+  const float* gamma;            // optional RMSNorm gain
+  float eps;
+  int round_norm_bf16;           // 1: normalised activations are rounded to bf16 before the product
+  __nv_bfloat16* xnorm_out;      // optional [tokens, k] (written by CTA 0)
+  long long xnorm_stride;
+  void* out;                     // [tokens, n] f32 (out_bf16 = 0) or bf16 (out_bf16 = 1)
+  int out_bf16;
+  long long out_stride;
+};
+
+constexpr int kGemvBf16Threads = 512;
+
+template <int TOK>
+__global__ void __launch_bounds__(kGemvBf16Threads) gemv_bf16_kernel(const GemvBf16Params p) {
+  extern __shared__ __align__(16) float xs[];  // [TOK][k]
+  __shared__ float red[TOK][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwarps = blockDim.x >> 5;
+
+  // stage (and normalise) the activations
+  float ss[TOK];
+#pragma unroll
+  for (int t = 0; t < TOK; ++t) ss[t] = 0.f;
+  for (int i = threadIdx.x; i < p.k; i += blockDim.x) {
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+      const float v = t < p.n_tokens ? bf2f(p.x[t * p.x_stride + i]) : 0.f;
+      xs[t * p.k + i] = v;
+      ss[t] += v * v;
+    }
+  }
+  if (p.gamma != nullptr) {
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+      const float s = warp_sum(ss[t]);
+      if (lane == 0) red[t][warp] = s;
+    }
+    __syncthreads();
+    float rinv[TOK];
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+      float tot = lane < nwarps ? red[t][lane] : 0.f;
+      tot = warp_sum(tot);
+      rinv[t] = rsqrtf(tot / static_cast<float>(p.k) + p.eps);
+    }
+    for (int i = threadIdx.x; i < p.k; i += blockDim.x) {
+      const float g = p.gamma[i];
+#pragma unroll
+      for (int t = 0; t < TOK; ++t) {
+        float v = xs[t * p.k + i] * rinv[t] * g;
+        if (p.round_norm_bf16) v = bf2f(f2bf(v));
+        xs[t * p.k + i] = v;
+        if (p.xnorm_out != nullptr && blockIdx.x == 0 && t < p.n_tokens) p.xnorm_out[t * p.xnorm_stride + i] = f2bf(v);
+      }
+    }
+  }
+  __syncthreads();
+
+  const int gw = blockIdx.x * nwarps + warp, tw = gridDim.x * nwarps;
+  for (int row = gw; row < p.n; row += tw) {
+    float acc[TOK];
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) acc[t] = 0.f;
+    if (p.w_is_f32) {
+      const float* wr = reinterpret_cast<const float*>(p.w) + static_cast<long long>(row) * p.k;
+      for (int k0 = lane * 4; k0 < p.k; k0 += 128) {
+        const float4 wv = __ldg(reinterpret_cast<const float4*>(wr + k0));
+#pragma unroll
+        for (int t = 0; t < TOK; ++t) {
+          const float4 xv = *reinterpret_cast<const float4*>(&xs[t * p.k + k0]);
+          acc[t] += wv.x * xv.x + wv.y * xv.y + wv.z * xv.z + wv.w * xv.w;
+        }
+      }
+    } else {
+      const __nv_bfloat16* wr = reinterpret_cast<const __nv_bfloat16*>(p.w) + static_cast<long long>(row) * p.k;
+#pragma unroll 4
+      for (int k0 = lane * 8; k0 < p.k; k0 += 256) {
+        uint4 wv;
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w)
+                     : "l"(wr + k0));
+        const float w0 = __uint_as_float(wv.x << 16), w1 = __uint_as_float(wv.x & 0xffff0000u);
+        const float w2 = __uint_as_float(wv.y << 16), w3 = __uint_as_float(wv.y & 0xffff0000u);
+        const float w4 = __uint_as_float(wv.z << 16), w5 = __uint_as_float(wv.z & 0xffff0000u);
+        const float w6 = __uint_as_float(wv.w << 16), w7 = __uint_as_float(wv.w & 0xffff0000u);
+#pragma unroll
+        for (int t = 0; t < TOK; ++t) {
+          const float4 xa = *reinterpret_cast<const float4*>(&xs[t * p.k + k0]);
+          const float4 xb = *reinterpret_cast<const float4*>(&xs[t * p.k + k0 + 4]);
+          acc[t] += w0 * xa.x + w1 * xa.y + w2 * xa.z + w3 * xa.w + w4 * xb.x + w5 * xb.y + w6 * xb.z + w7 * xb.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+      const float s = warp_sum(acc[t]);
+      if (lane == 0 && t < p.n_tokens) {
+        if (p.out_bf16)
+          reinterpret_cast<__nv_bfloat16*>(p.out)[t * p.out_stride + row] = f2bf(s);
+        else
+          reinterpret_cast<float*>(p.out)[t * p.out_stride + row] = s;
+      }
+    }
+  }
+}
+
+}  // namespace tb

@@ -1,0 +1,239 @@
+// DSA lightning indexer: scores every cached key for each query token, then selects the top-k
+// key positions with a radix select.
+//
+//   logit[s, t] = sum_h w[s, h] * relu(q[s, h, :] . k[t, :])        t <= position of token s
+//
+// Scoring is HBM-bound on the key scan (256 bytes per key, read once); the dot products run on
+// bf16 tensor-core MMAs (keys are the M dimension, heads the N dimension).  Selection works on
+// the order-preserving unsigned image of the f32 logits, so it is exact: the k largest values,
+// equal values by lower index first.
+#pragma once
+
+#include "common.cuh"
+
+namespace tb {
+
+constexpr int kIdxWarps = 4;
+constexpr int kIdxKeysPerWarp = 16;
+constexpr int kIdxPitch = 136;  // bf16 elements per smem row (128 + 8 pad: conflict-free ldmatrix)
+
+// grid = (ceil(T / 64), tokens); block = 128 threads; dynamic smem = (H + 64) * kIdxPitch * 2 bytes
+template <int H>
+__global__ void __launch_bounds__(kIdxWarps * 32) indexer_logits_kernel(
+    const __nv_bfloat16* __restrict__ q,       // [tokens, H, 128]
+    const __nv_bfloat16* __restrict__ kcache,  // [T, 128]
+    const __nv_bfloat16* __restrict__ w,       // [tokens, H]
+    float* __restrict__ logits,                // [tokens, logits_stride]
+    long long logits_stride, int n_keys,       // keys scored: t in [0, n_keys)
+    const int* __restrict__ pos, int pos_offset  // token s may see keys t <= *pos + pos_offset + s
+) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [H][pitch]
+  __nv_bfloat16* sk = sq + H * kIdxPitch;                          // [64][pitch]
+  __shared__ float sw[H];
+  const int tok = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int key0 = blockIdx.x * (kIdxWarps * kIdxKeysPerWarp);
+
+  // stage q (H x 128) and this CTA's 64 keys with 16-byte loads
+  for (int i = threadIdx.x; i < H * 16; i += blockDim.x) {
+    const int r = i >> 4, c = i & 15;
+    *reinterpret_cast<uint4*>(sq + r * kIdxPitch + c * 8) =
+        *reinterpret_cast<const uint4*>(q + (static_cast<long long>(tok) * H + r) * 128 + c * 8);
+  }
+  for (int i = threadIdx.x; i < 64 * 16; i += blockDim.x) {
+    const int r = i >> 4, c = i & 15;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (key0 + r < n_keys) {
+      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                   : "l"(kcache + static_cast<long long>(key0 + r) * 128 + c * 8));
+    }
+    *reinterpret_cast<uint4*>(sk + r * kIdxPitch + c * 8) = v;
+  }
+  for (int i = threadIdx.x; i < H; i += blockDim.x) sw[i] = bf2f(w[tok * H + i]);
+  __syncthreads();
+
+  float acc[H / 8][4];
+#pragma unroll
+  for (int n = 0; n < H / 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+
+  const __nv_bfloat16* wk = sk + warp * kIdxKeysPerWarp * kIdxPitch;
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    uint32_t a[4];
+    // A (16 keys x 16 dims): matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+    ldmatrix_x4(a, wk + (lane & 15) * kIdxPitch + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+    for (int n2 = 0; n2 < H / 16; ++n2) {
+      uint32_t b[4];
+      // B for two n-tiles: (heads 0-7, k 0-7), (heads 0-7, k 8-15), (heads 8-15, k 0-7), (heads 8-15, k 8-15)
+      ldmatrix_x4(b, sq + (n2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * kIdxPitch + ks * 16 + ((lane >> 3) & 1) * 8);
+      const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+      mma_bf16_16816(acc[2 * n2], a, b0);
+      mma_bf16_16816(acc[2 * n2 + 1], a, b1);
+    }
+  }
+  // relu, weight, sum over heads: thread holds keys (g, g+8) x heads (8n + 2q, 8n + 2q + 1)
+  const int g = lane >> 2, qd = lane & 3;
+  float lo = 0.f, hi = 0.f;
+#pragma unroll
+  for (int n = 0; n < H / 8; ++n) {
+    const float w0 = sw[n * 8 + 2 * qd], w1 = sw[n * 8 + 2 * qd + 1];
+    lo += fmaxf(acc[n][0], 0.f) * w0 + fmaxf(acc[n][1], 0.f) * w1;
+    hi += fmaxf(acc[n][2], 0.f) * w0 + fmaxf(acc[n][3], 0.f) * w1;
+  }
+  lo += __shfl_xor_sync(0xffffffffu, lo, 1);
+  lo += __shfl_xor_sync(0xffffffffu, lo, 2);
+  hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+  hi += __shfl_xor_sync(0xffffffffu, hi, 2);
+  if (qd == 0) {
+    const int last = *pos + pos_offset + tok;
+    const int k_lo = key0 + warp * kIdxKeysPerWarp + g, k_hi = k_lo + 8;
+    if (k_lo < n_keys) logits[tok * logits_stride + k_lo] = k_lo <= last ? lo : -INFINITY;
+    if (k_hi < n_keys) logits[tok * logits_stride + k_hi] = k_hi <= last ? hi : -INFINITY;
+  }
+}
+
+// ------------------------------------------------------------------ radix top-k
+__device__ __forceinline__ uint32_t f32_order_key(float v) {
+  uint32_t u = __float_as_uint(v);
+  if (u == 0x80000000u) u = 0u;  // -0.0 compares equal to +0.0
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+constexpr uint32_t kNegInfKey = 0x007fffffu;  // order key of -inf: never selected
+
+constexpr int kTopkThreads = 1024;
+constexpr int kTopkItems = 8;  // consecutive elements per thread in the ordered compaction
+
+// One CTA per row.  Selects the k largest logits among [0, n) (entries equal to -inf are skipped),
+// ties by lower index, and writes their indices in ascending order; unused slots get -1.
+__global__ void __launch_bounds__(kTopkThreads) topk_radix_kernel(const float* __restrict__ logits,
+                                                                  long long logits_stride, int n, int k,
+                                                                  int* __restrict__ out, long long out_stride) {
+  __shared__ int hist[256];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_remaining;
+  __shared__ int s_warp_gt[32], s_warp_eq[32];
+  __shared__ int s_base_sel, s_base_eq;
+  const float* row = logits + blockIdx.x * logits_stride;
+  int* dst = out + blockIdx.x * out_stride;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // count eligible entries
+  int cnt = 0;
+  for (int i = tid; i < n; i += kTopkThreads) cnt += f32_order_key(row[i]) > kNegInfKey;
+  if (tid < 256) hist[tid] = 0;
+  if (tid == 0) { s_prefix = 0; s_remaining = 0; }
+  __syncthreads();
+  {
+    int wsum = cnt;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+    if (lane == 0) atomicAdd(&s_remaining, wsum);
+  }
+  __syncthreads();
+  const int n_eligible = s_remaining;
+  __syncthreads();
+
+  uint32_t thr = kNegInfKey + 1;  // select everything eligible
+  int need_eq = 0x7fffffff;       // how many entries equal to thr to take
+  bool take_all = n_eligible <= k;
+  if (!take_all) {
+    if (tid == 0) s_remaining = k;
+    __syncthreads();
+    uint32_t prefix = 0, mask = 0;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      if (tid < 256) hist[tid] = 0;
+      __syncthreads();
+      for (int i = tid; i < n; i += kTopkThreads) {
+        const uint32_t key = f32_order_key(row[i]);
+        if (key > kNegInfKey && (key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        int rem = s_remaining;
+        int d = 255;
+        for (; d > 0; --d) {
+          if (hist[d] >= rem) break;
+          rem -= hist[d];
+        }
+        s_remaining = rem;
+        s_prefix = prefix | (static_cast<uint32_t>(d) << shift);
+      }
+      __syncthreads();
+      prefix = s_prefix;
+      mask |= 0xffu << shift;
+      __syncthreads();
+    }
+    thr = prefix;
+    need_eq = s_remaining;
+  }
+
+  // ordered compaction: chunk of kTopkThreads * kTopkItems consecutive elements per pass
+  if (tid == 0) { s_base_sel = 0; s_base_eq = 0; }
+  __syncthreads();
+  for (int base = 0; base < n; base += kTopkThreads * kTopkItems) {
+    const int i0 = base + tid * kTopkItems;
+    uint32_t gt_mask = 0, eq_mask = 0;
+#pragma unroll
+    for (int j = 0; j < kTopkItems; ++j) {
+      const int i = i0 + j;
+      if (i < n) {
+        const uint32_t key = f32_order_key(row[i]);
+        if (key > kNegInfKey) {
+          if (take_all || key > thr) gt_mask |= 1u << j;
+          else if (key == thr) eq_mask |= 1u << j;
+        }
+      }
+    }
+    const int my_gt = __popc(gt_mask), my_eq = __popc(eq_mask);
+    // exclusive scans of (gt, eq) over the CTA in thread order
+    int sc_gt = my_gt, sc_eq = my_eq;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, sc_gt, o), b = __shfl_up_sync(0xffffffffu, sc_eq, o);
+      if (lane >= o) { sc_gt += a; sc_eq += b; }
+    }
+    if (lane == 31) { s_warp_gt[warp] = sc_gt; s_warp_eq[warp] = sc_eq; }
+    __syncthreads();
+    int pre_gt = 0, pre_eq = 0, tot_gt = 0, tot_eq = 0;
+    for (int w2 = 0; w2 < 32; ++w2) {
+      const int a = s_warp_gt[w2], b = s_warp_eq[w2];
+      if (w2 < warp) { pre_gt += a; pre_eq += b; }
+      tot_gt += a; tot_eq += b;
+    }
+    const int base_sel = s_base_sel, base_eq = s_base_eq;
+    // ties consumed before this thread (in index order) and how many of them were taken
+    int eq_before = base_eq + pre_eq + sc_eq - my_eq;
+    int gt_before = pre_gt + sc_gt - my_gt;
+    // selected-so-far = base_sel (all earlier chunks) + gt in this chunk before me + ties taken in this chunk before me
+    const int eq_taken_before_chunk = min(base_eq, need_eq);
+    int eq_taken_before_me = min(eq_before, need_eq) - eq_taken_before_chunk;
+    int w = base_sel + gt_before + eq_taken_before_me;
+#pragma unroll
+    for (int j = 0; j < kTopkItems; ++j) {
+      if (gt_mask & (1u << j)) {
+        if (w < k) dst[w] = i0 + j;
+        ++w;
+      } else if (eq_mask & (1u << j)) {
+        if (eq_before < need_eq) {
+          if (w < k) dst[w] = i0 + j;
+          ++w;
+        }
+        ++eq_before;
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const int eq_taken_chunk = min(base_eq + tot_eq, need_eq) - eq_taken_before_chunk;
+      s_base_sel = base_sel + tot_gt + eq_taken_chunk;
+      s_base_eq = base_eq + tot_eq;
+    }
+    __syncthreads();
+  }
+  const int n_sel = s_base_sel;
+  for (int i = n_sel + tid; i < k; i += kTopkThreads) dst[i] = -1;
+}
+
+}  // namespace tb

@@ -1,0 +1,263 @@
+// Sparse MLA decode attention over the latent KV cache (kv_lora 512 + rope 64).
+//
+// For each query token only the `topk` selected cache rows are touched.  The selected rows
+// are split into chunks (flash-decoding); one CTA handles 16 heads x one chunk: it gathers
+// its 64-row blocks with one bulk async copy (TMA) per row, computes Q.K^T and P.V with bf16
+// tensor-core MMAs in f32, and writes a normalised partial output plus its log-sum-exp.  A
+// second small kernel merges the chunks.  Algorithmic HBM traffic: topk x 1152 bytes per token.
+#pragma once
+
+#include "common.cuh"
+
+namespace tb {
+
+constexpr int kMlaKeys = 64;
+constexpr int kMlaHeads = 16;
+constexpr int kMlaDV = 512;
+constexpr int kMlaDR = 64;
+constexpr int kMlaPitch = 584;   // bf16 elements per smem row: (512 + 64 + 8) -> 1168 bytes
+constexpr int kMlaPPitch = 72;   // bf16 elements per P row
+constexpr int kMlaThreads = 128;
+constexpr int kMlaSmemBytes =
+    (kMlaHeads + kMlaKeys) * kMlaPitch * 2 + kMlaHeads * kMlaPPitch * 2 + 2 * 4 * kMlaHeads * 4 + kMlaKeys * 4 + 16;
+
+struct MlaParams {
+  const __nv_bfloat16* q_lat;   // [tokens, heads, 512]
+  const __nv_bfloat16* q_pe;    // [tokens, heads, 64]
+  const __nv_bfloat16* kv;      // [T, 512]
+  const __nv_bfloat16* pe;      // [T, 64]
+  const int* idx;               // [tokens, topk]
+  int topk;
+  int heads;
+  int n_cache;                  // rows in the cache tensors
+  const int* pos;               // position of token 0
+  float scale_log2;             // softmax scale * log2(e)
+  int blocks_per_split;
+  int n_splits;
+  float* o_acc;                 // [tokens, heads, n_splits, 512]
+  float* lse_acc;               // [tokens, heads, n_splits]
+  int* status;
+};
+
+__global__ void __launch_bounds__(kMlaThreads) sparse_mla_kernel(const MlaParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);
+  __nv_bfloat16* sKV = sQ + kMlaHeads * kMlaPitch;
+  __nv_bfloat16* sP = sKV + kMlaKeys * kMlaPitch;
+  float* sMax = reinterpret_cast<float*>(sP + kMlaHeads * kMlaPPitch);  // [4][16]
+  float* sSum = sMax + 4 * kMlaHeads;                                   // [4][16]
+  int* sValid = reinterpret_cast<int*>(sSum + 4 * kMlaHeads);           // [64]
+  uint64_t* bar = reinterpret_cast<uint64_t*>(sValid + kMlaKeys);
+
+  const int split = blockIdx.x, hg = blockIdx.y, tok = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, qd = lane & 3;
+  const int pos_s = *p.pos + tok;
+
+  if (tid == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+  }
+  // stage the 16 query heads: [512 latent | 64 rope]
+  for (int i = tid; i < kMlaHeads * 72; i += kMlaThreads) {
+    const int r = i / 72, c = i % 72;
+    const int head = hg * kMlaHeads + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (head < p.heads) {
+      const long long th = static_cast<long long>(tok) * p.heads + head;
+      v = c < 64 ? *reinterpret_cast<const uint4*>(p.q_lat + th * kMlaDV + c * 8)
+                 : *reinterpret_cast<const uint4*>(p.q_pe + th * kMlaDR + (c - 64) * 8);
+    }
+    *reinterpret_cast<uint4*>(sQ + r * kMlaPitch + c * 8) = v;
+  }
+  __syncthreads();
+
+  uint32_t phase = 0;  // completed phases of `bar` (a block without valid rows issues no copy)
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  float o[16][4];
+#pragma unroll
+  for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+  for (int blk = 0; blk < p.blocks_per_split; ++blk) {
+    const int key_base = (split * p.blocks_per_split + blk) * kMlaKeys;
+    // ---- gather 64 selected rows ----
+    int my_idx = -1;
+    bool valid = false;
+    if (tid < kMlaKeys) {
+      if (key_base + tid < p.topk) my_idx = p.idx[static_cast<long long>(tok) * p.topk + key_base + tid];
+      valid = my_idx >= 0 && my_idx < p.n_cache && my_idx <= pos_s;
+      sValid[tid] = valid ? 1 : 0;
+    }
+    const int n_valid = __syncthreads_count(valid ? 1 : 0);
+    if (tid == 0 && n_valid > 0) mbar_expect_tx(bar, n_valid * (kMlaDV + kMlaDR) * 2);
+    // the rows were last touched through the generic proxy (ldmatrix reads, zero fills): order
+    // those accesses before the async-proxy writes of the bulk copies issued below
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid < kMlaKeys) {
+      __nv_bfloat16* row = sKV + tid * kMlaPitch;
+      if (valid) {
+        bulk_g2s(row, p.kv + static_cast<long long>(my_idx) * kMlaDV, kMlaDV * 2, bar);
+        bulk_g2s(row + kMlaDV, p.pe + static_cast<long long>(my_idx) * kMlaDR, kMlaDR * 2, bar);
+      } else {
+        for (int c = 0; c < 72; ++c) *reinterpret_cast<uint4*>(row + c * 8) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    if (n_valid > 0) {
+      if (!mbar_wait(bar, phase & 1)) set_status(p.status, ST_WAIT_FULL_TIMEOUT);
+      ++phase;
+    }
+    __syncthreads();
+
+    // ---- S = Q K^T for this warp's 16 keys ----
+    float s[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    const __nv_bfloat16* kbase = sKV + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * kMlaPitch + ((lane >> 3) & 1) * 8;
+    const __nv_bfloat16* qbase = sQ + (lane & 15) * kMlaPitch + (lane >> 4) * 8;
+#pragma unroll 4
+    for (int ks = 0; ks < (kMlaDV + kMlaDR) / 16; ++ks) {
+      uint32_t a[4], b[4];
+      ldmatrix_x4(a, qbase + ks * 16);
+      ldmatrix_x4(b, kbase + ks * 16);
+      const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+      mma_bf16_16816(s[0], a, b0);
+      mma_bf16_16816(s[1], a, b1);
+    }
+    // scale, mask, block max per head row
+    float bmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int key = warp * 16 + n * 8 + 2 * qd + (j & 1);
+        const float v = sValid[key] ? s[n][j] * p.scale_log2 : -INFINITY;
+        s[n][j] = v;
+        bmax[j >> 1] = fmaxf(bmax[j >> 1], v);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      bmax[r] = fmaxf(bmax[r], __shfl_xor_sync(0xffffffffu, bmax[r], 1));
+      bmax[r] = fmaxf(bmax[r], __shfl_xor_sync(0xffffffffu, bmax[r], 2));
+    }
+    if (qd == 0) {
+      sMax[warp * kMlaHeads + g] = bmax[0];
+      sMax[warp * kMlaHeads + g + 8] = bmax[1];
+    }
+    __syncthreads();
+    float alpha[2], m_new[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + 8 * r;
+      float m = m_run[r];
+#pragma unroll
+      for (int w2 = 0; w2 < 4; ++w2) m = fmaxf(m, sMax[w2 * kMlaHeads + row]);
+      m_new[r] = m;
+      alpha[r] = (m == -INFINITY) ? 1.f : exp2f(m_run[r] - m);
+    }
+    float bsum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      float pv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = j >> 1;
+        pv[j] = (m_new[r] == -INFINITY) ? 0.f : exp2f(s[n][j] - m_new[r]);
+        pv[j] = bf2f(f2bf(pv[j]));  // the sum uses the same rounded probabilities as P.V
+        bsum[r] += pv[j];
+      }
+      const int col = warp * 16 + n * 8 + 2 * qd;
+      *reinterpret_cast<uint32_t*>(sP + g * kMlaPPitch + col) = pack_bf16x2(pv[0], pv[1]);
+      *reinterpret_cast<uint32_t*>(sP + (g + 8) * kMlaPPitch + col) = pack_bf16x2(pv[2], pv[3]);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      bsum[r] += __shfl_xor_sync(0xffffffffu, bsum[r], 1);
+      bsum[r] += __shfl_xor_sync(0xffffffffu, bsum[r], 2);
+    }
+    if (qd == 0) {
+      sSum[warp * kMlaHeads + g] = bsum[0];
+      sSum[warp * kMlaHeads + g + 8] = bsum[1];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + 8 * r;
+      float sum = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < 4; ++w2) sum += sSum[w2 * kMlaHeads + row];
+      l_run[r] = l_run[r] * alpha[r] + sum;
+      m_run[r] = m_new[r];
+    }
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+      o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+    }
+    // ---- O += P V for this warp's 128 latent dims ----
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t a[4];
+      ldmatrix_x4(a, sP + (lane & 15) * kMlaPPitch + kk * 16 + (lane >> 4) * 8);
+      const __nv_bfloat16* vbase =
+          sKV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kMlaPitch + warp * 128 + (lane >> 4) * 8;
+#pragma unroll
+      for (int n2 = 0; n2 < 8; ++n2) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vbase + n2 * 16);
+        const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+        mma_bf16_16816(o[2 * n2], a, b0);
+        mma_bf16_16816(o[2 * n2 + 1], a, b1);
+      }
+    }
+    __syncthreads();  // sKV / sP / sMax are rewritten by the next block
+  }
+
+  // ---- normalised partial output and log-sum-exp of this chunk ----
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int head = hg * kMlaHeads + g + 8 * r;
+    if (head >= p.heads) continue;
+    const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+    const long long base = (static_cast<long long>(tok) * p.heads + head) * p.n_splits + split;
+    float* dst = p.o_acc + base * kMlaDV + warp * 128;
+#pragma unroll
+    for (int n = 0; n < 16; ++n)
+      *reinterpret_cast<float2*>(dst + n * 8 + 2 * qd) = make_float2(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
+    if (warp == 0 && qd == 0)
+      p.lse_acc[base] = l_run[r] > 0.f ? m_run[r] * 0.6931471805599453f + logf(l_run[r]) : -INFINITY;
+  }
+}
+
+// Merge the chunks: o = sum_i exp(lse_i - lse) * o_i.   grid = (heads, tokens), block = 128.
+__global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float* __restrict__ o_acc,
+                                                                 const float* __restrict__ lse_acc, int n_splits,
+                                                                 __nv_bfloat16* __restrict__ out,
+                                                                 float* __restrict__ lse_out) {
+  const int head = blockIdx.x, tok = blockIdx.y, heads = gridDim.x;
+  const long long th = static_cast<long long>(tok) * heads + head;
+  const float* lse = lse_acc + th * n_splits;
+  float mx = -INFINITY;
+  for (int i = 0; i < n_splits; ++i) mx = fmaxf(mx, lse[i]);
+  float den = 0.f;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (mx != -INFINITY) {
+    for (int i = 0; i < n_splits; ++i) {
+      const float wgt = expf(lse[i] - mx);
+      if (wgt == 0.f) continue;
+      den += wgt;
+      const float4 v = *reinterpret_cast<const float4*>(o_acc + (th * n_splits + i) * kMlaDV + threadIdx.x * 4);
+      acc[0] += wgt * v.x; acc[1] += wgt * v.y; acc[2] += wgt * v.z; acc[3] += wgt * v.w;
+    }
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  uint2 o2;
+  o2.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
+  o2.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
+  *reinterpret_cast<uint2*>(out + th * kMlaDV + threadIdx.x * 4) = o2;
+  if (threadIdx.x == 0 && lse_out != nullptr) lse_out[th] = mx != -INFINITY ? mx + logf(den) : -INFINITY;
+}
+
+}  // namespace tb

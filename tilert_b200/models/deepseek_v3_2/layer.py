@@ -1,0 +1,232 @@
+"""One decoder layer of the batch-1 decode path: packed weights, scratch tensors, latent caches and
+the operator sequence.
+
+The reference keeps these as registries (tilert/models/deepseek_v3_2/modules/mla_v2.py,
+modules/moe.py, modules/mlp.py, modules/dsa.py:105-229) and runs the sequence inside its native
+library; here the sequence is explicit Python over the operator wrappers, and a whole step can be
+captured in a CUDA graph.  Sharding is symmetric: every rank holds ``n_heads / world`` attention
+heads and a ``1 / world`` slice of every expert's intermediate dimension; the row-parallel
+products (o_proj, down_proj) reduce inside their kernels.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from tilert_b200 import pack
+from . import ops
+from .model_args import ModelArgs
+
+BF16 = torch.bfloat16
+F32 = torch.float32
+I32 = torch.int32
+
+
+def precompute_freqs(args: ModelArgs) -> torch.Tensor:
+    """(cos, sin) table [max_seq_len, rope/2, 2] f32 with the YaRN correction of
+    tilert/models/utils.py:17-118."""
+    dim, base = args.qk_rope_head_dim, args.rope_theta
+    freqs = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+    if args.rope_factor is not None and args.max_seq_len > args.original_seq_len:
+        def corr(n_rot):
+            return dim * math.log(args.original_seq_len / (n_rot * 2 * math.pi)) / (2 * math.log(base))
+        low = float(max(math.floor(corr(args.beta_fast)), 0))
+        high = float(min(math.ceil(corr(args.beta_slow)), dim - 1))
+        if low == high:
+            high += 0.001
+        ramp = torch.clamp((torch.arange(dim // 2, dtype=torch.float32) - low) / (high - low), 0, 1)
+        smooth = 1 - ramp
+        freqs = freqs / args.rope_factor * (1 - smooth) + freqs * smooth
+    ang = torch.outer(torch.arange(args.max_seq_len), freqs)
+    return torch.view_as_real(torch.polar(torch.ones_like(ang), ang)).contiguous()
+
+
+def softmax_scale(args: ModelArgs) -> float:
+    """tilert/models/deepseek_v3_2/ops/flash_sparse_mla.py:125-130."""
+    scale = (args.qk_nope_head_dim + args.qk_rope_head_dim) ** -0.5
+    mscale = 1.0 if args.rope_factor is None else 0.1 * math.log(args.rope_factor) + 1.0
+    return scale * mscale * mscale
+
+
+class LayerWeights:
+    """Packed per-rank weights of one layer, built from an HF-keyed FP8 state dict."""
+
+    def __init__(self, args: ModelArgs, sd: dict[str, torch.Tensor], li: int, device, world: int = 1, rank: int = 0,
+                 expert_ids: list[int] | None = None):
+        a = args
+        dev = torch.device(device)
+        p = f"model.layers.{li}"
+        at = f"{p}.self_attn"
+
+        def g(key):
+            return sd[key].to(dev)
+
+        def f32(key):
+            return sd[key].to(dev, F32).contiguous()
+
+        hl = a.n_heads // world
+        h0 = rank * hl
+        hd = a.qk_nope_head_dim + a.qk_rope_head_dim
+        self.in_norm = f32(f"{p}.input_layernorm.weight")
+        self.post_norm = f32(f"{p}.post_attention_layernorm.weight")
+        self.q_norm = f32(f"{at}.q_a_layernorm.weight")
+        self.kv_norm = f32(f"{at}.kv_a_layernorm.weight")
+        self.k_norm_w = f32(f"{at}.indexer.k_norm.weight")
+        self.k_norm_b = f32(f"{at}.indexer.k_norm.bias")
+        self.wis = g(f"{at}.indexer.weights_proj.weight").to(BF16).contiguous()
+        # q_a | kv_a | k_pe | indexer wk: replicated on every rank
+        self.w_qkva = pack.pack_concat([
+            (g(f"{at}.q_a_proj.weight"), g(f"{at}.q_a_proj.weight_scale_inv")),
+            (g(f"{at}.kv_a_proj_with_mqa.weight"), g(f"{at}.kv_a_proj_with_mqa.weight_scale_inv")),
+            (g(f"{at}.indexer.wk.weight"), g(f"{at}.indexer.wk.weight_scale_inv")),
+        ])
+        # q_b: this rank's heads, plus the (replicated) indexer query projection
+        wq_b, sq_b = g(f"{at}.q_b_proj.weight"), g(f"{at}.q_b_proj.weight_scale_inv")
+        rs_full = pack.row_scales(sq_b, wq_b.shape[0])
+        rows = slice(h0 * hd, (h0 + hl) * hd)
+        self.w_qb = pack.pack_q_b_rows(wq_b.view(torch.uint8)[rows], rs_full[rows], hl, a.qk_nope_head_dim,
+                                       a.qk_rope_head_dim, g(f"{at}.indexer.wq_b.weight"),
+                                       g(f"{at}.indexer.wq_b.weight_scale_inv"))
+        wkv_b, skv_b = g(f"{at}.kv_b_proj.weight"), g(f"{at}.kv_b_proj.weight_scale_inv")
+        per_head = a.qk_nope_head_dim + a.v_head_dim
+        kv_rows = slice(h0 * per_head, (h0 + hl) * per_head)
+        kv_srows = slice(h0 * per_head // 128, (h0 + hl) * per_head // 128)
+        self.w_absorb = pack.pack_kv_b_absorb(wkv_b[kv_rows], skv_b[kv_srows], hl, a.qk_nope_head_dim, a.v_head_dim)
+        self.w_v = pack.pack_kv_b_v(wkv_b[kv_rows], skv_b[kv_srows], hl, a.qk_nope_head_dim, a.v_head_dim)
+        w_o, s_o = g(f"{at}.o_proj.weight"), g(f"{at}.o_proj.weight_scale_inv")
+        oc = slice(h0 * a.v_head_dim, (h0 + hl) * a.v_head_dim)
+        ocs = slice(h0 * a.v_head_dim // 128, (h0 + hl) * a.v_head_dim // 128)
+        self.w_o = pack.pack_matrix(w_o[:, oc].contiguous(), s_o[:, ocs].contiguous())
+
+        m = f"{p}.mlp"
+        self.dense = li < a.n_dense_layers
+        if self.dense:
+            il = a.inter_dim // world
+            r = slice(rank * il, (rank + 1) * il)
+            rs_ = slice(rank * il // 128, (rank + 1) * il // 128)
+            self.w_gu = pack.pack_gate_up(g(f"{m}.gate_proj.weight")[r], g(f"{m}.gate_proj.weight_scale_inv")[rs_],
+                                          g(f"{m}.up_proj.weight")[r], g(f"{m}.up_proj.weight_scale_inv")[rs_])
+            self.w_down = pack.pack_matrix(g(f"{m}.down_proj.weight")[:, r].contiguous(),
+                                           g(f"{m}.down_proj.weight_scale_inv")[:, rs_].contiguous())
+            self.inter_local = il
+        else:
+            il = a.moe_inter_dim // world
+            r = slice(rank * il, (rank + 1) * il)
+            rs_ = slice(rank * il // 128, (rank + 1) * il // 128)
+            self.router = g(f"{m}.gate.weight").contiguous()
+            self.router_bias = f32(f"{m}.gate.e_score_correction_bias")
+            n_e = a.n_routed_experts
+            gu_tiles, n_kb = 2 * il // 128, a.dim // 128
+            # [n_experts + 1] slots, the shared expert last; experts absent from the state dict stay zero
+            self.w_gu = torch.zeros(n_e + 1, gu_tiles, n_kb, pack.WBLK_BYTES, dtype=torch.uint8, device=dev)
+            self.w_down = torch.zeros(n_e + 1, a.dim // 128, il // 128, pack.WBLK_BYTES, dtype=torch.uint8, device=dev)
+            present = range(n_e) if expert_ids is None else expert_ids
+            for slot, name in [(n_e, "shared_experts")] + [(e, f"experts.{e}") for e in present]:
+                k = f"{m}.{name}"
+                self.w_gu[slot] = pack.pack_gate_up(g(f"{k}.gate_proj.weight")[r], g(f"{k}.gate_proj.weight_scale_inv")[rs_],
+                                                    g(f"{k}.up_proj.weight")[r], g(f"{k}.up_proj.weight_scale_inv")[rs_])
+                self.w_down[slot] = pack.pack_matrix(g(f"{k}.down_proj.weight")[:, r].contiguous(),
+                                                     g(f"{k}.down_proj.weight_scale_inv")[:, rs_].contiguous())
+            self.inter_local = il
+
+    def weight_bytes(self, args: ModelArgs) -> int:
+        """Bytes of weights one decode step of this layer streams from HBM on this rank."""
+        n = sum(t.numel() for t in (self.w_qkva, self.w_qb, self.w_absorb, self.w_v, self.w_o))
+        n += self.wis.numel() * 2
+        if self.dense:
+            n += self.w_gu.numel() + self.w_down.numel()
+        else:
+            per = self.w_gu[0].numel() + self.w_down[0].numel()
+            n += per * (args.n_activated_experts + args.n_shared_experts) + self.router.numel() * self.router.element_size()
+        return n
+
+
+class DecoderLayer:
+    """Scratch tensors, caches and the operator sequence of one layer (one rank)."""
+
+    def __init__(self, args: ModelArgs, weights: LayerWeights, device, cache_len: int, max_tokens: int = 1,
+                 world: int = 1, comm: int | None = None):
+        a, dev, s = args, torch.device(device), max_tokens
+        self.args, self.w, self.world, self.comm = a, weights, world, comm
+        self.hl = a.n_heads // world
+        self.cache_len = cache_len
+        z = lambda *shape, dtype=BF16: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
+        self.kv_cache = z(1, cache_len, a.kv_lora_rank)
+        self.pe_cache = z(1, cache_len, a.qk_rope_head_dim)
+        self.ki_cache = z(1, cache_len, a.index_head_dim)
+        self.x_norm = z(1, s, a.dim)
+        self.xp_a = ops.new_xpack(a.dim, dev)
+        self.q_a = z(1, s, a.q_lora_rank)
+        self.kv = z(1, s, a.kv_lora_rank)
+        self.ki = z(1, s, a.index_head_dim)
+        self.idx_w = z(1, s, a.index_n_heads)
+        self.q_nope = z(1, s, self.hl, a.qk_nope_head_dim)
+        self.q_pe = z(1, s, self.hl, a.qk_rope_head_dim)
+        self.iq = z(1, s, a.index_n_heads, a.index_head_dim)
+        self.iq_rt = z(1, s, a.index_n_heads, a.index_head_dim)
+        self.idx_logits = z(1, s, cache_len, dtype=F32)
+        self.sel = torch.full((1, s, a.index_topk), -1, dtype=I32, device=dev)
+        self.q_lat = z(1, s, self.hl, a.kv_lora_rank)
+        self.o_lat = z(1, s, self.hl, a.kv_lora_rank)
+        self.n_splits = (a.index_topk + 63) // 64
+        self.o_acc = z(1, s, self.hl, self.n_splits, a.kv_lora_rank, dtype=F32)
+        self.lse = z(1, s, self.hl, dtype=F32)
+        self.lse_acc = z(1, s, self.hl, self.n_splits, dtype=F32)
+        self.o = z(1, s, self.hl, a.v_head_dim)
+        self.h = z(1, s, a.dim)
+        self.h_norm = z(1, s, a.dim)
+        self.xp_h = ops.new_xpack(a.dim, dev)
+        self.out = z(1, s, a.dim)
+        if weights.dense:
+            self.ffn_hidden = z(1, s, weights.inter_local)
+        else:
+            n_slots = a.n_activated_experts + 1
+            self.scores = z(1, s, a.n_routed_experts, dtype=F32)
+            self.probs = z(1, s, a.n_activated_experts, dtype=F32)
+            self.eidx = z(1, s, a.n_activated_experts, dtype=I32)
+            self.slot_ids = z(s, n_slots, dtype=I32)
+            self.slot_w = z(s, n_slots, dtype=F32)
+            self.ffn_hidden = z(1, s, n_slots, weights.inter_local)
+        self.forced_scores: torch.Tensor | None = None
+        self.scale = softmax_scale(a)
+
+    def forward(self, x: torch.Tensor, cur_pos: torch.Tensor, freqs: torch.Tensor, n_keys: int) -> torch.Tensor:
+        """``x`` [1, S, dim] bf16, ``cur_pos`` int32[1] (position of token 0), ``freqs`` f32 [S, rope/2, 2],
+        ``n_keys`` = number of cache rows the indexer scans (>= cur_pos + S).  Returns [1, S, dim] bf16."""
+        a, w = self.args, self.w
+        s = x.shape[1]
+        v = lambda t: t[:, :s]  # noqa: E731
+        ops.rmsnorm_quant(x, w.in_norm, v(self.x_norm), None, None, eps=a.eps, xpack=self.xp_a)
+        ops.projx_wqkva_packed(self.xp_a, 2, w.w_qkva, s, a.dim, a.q_lora_rank, a.kv_lora_rank, a.qk_rope_head_dim,
+                               a.index_head_dim, cur_pos, v(self.q_a), v(self.kv), self.pe_cache, v(self.ki))
+        ops.projx_wis(v(self.x_norm), w.wis, v(self.idx_w))
+        ops.rmsnorm_kv(v(self.kv), w.kv_norm, cur_pos, self.kv_cache, eps=a.eps)
+        ops.rmsnorm_proj_q(v(self.q_a), w.q_norm, w.w_qb, v(self.q_nope), v(self.q_pe), v(self.iq), eps=a.eps)
+        ops.qkv_rope(v(self.q_pe), self.pe_cache, freqs, cur_pos)
+        ops.rotate(v(self.iq), v(self.iq_rt), freqs, rope=a.qk_rope_head_dim)
+        ops.layernorm_rope_rotate(v(self.ki), cur_pos, self.ki_cache, w.k_norm_w, w.k_norm_b, freqs,
+                                  rope=a.qk_rope_head_dim)
+        ops.sparse_index_topk(v(self.iq_rt), self.ki_cache, v(self.idx_w), self.idx_logits, v(self.sel), cur_pos,
+                              n_keys=n_keys)
+        ops.projq_wqb(v(self.q_nope), w.w_absorb, None, v(self.q_lat))
+        ops.flash_sparse_mla(v(self.q_lat), v(self.q_pe), self.kv_cache, self.pe_cache, v(self.sel), cur_pos,
+                             v(self.o_lat), softmax_scale=self.scale, split_size=64, out_acc=self.o_acc,
+                             lse=self.lse, lse_acc=self.lse_acc)
+        ops.projo_wkvb(v(self.o_lat), w.w_v, None, v(self.o))
+        ops.unproj_o_allreduce(v(self.o), w.w_o, None, x, 0, v(self.h), comm=self.comm)
+        if w.dense:
+            ops.rmsnorm_up_gate_silu(v(self.h), w.post_norm, w.w_gu, v(self.ffn_hidden), eps=a.eps)
+            ops.down_allreduce(v(self.ffn_hidden), w.w_down, None, v(self.h), 0, v(self.out), comm=self.comm)
+        else:
+            ops.rmsnorm_quant(v(self.h), w.post_norm, v(self.h_norm), None, None, eps=a.eps, xpack=self.xp_h)
+            ops.rmsnorm_expert_proj(v(self.h_norm), None, w.router, v(self.scores), None)
+            scores = v(self.scores) if self.forced_scores is None else self.forced_scores
+            ops.expert_select_up_gate_silu(self.xp_h, scores, w.router_bias, w.w_gu, v(self.ffn_hidden), v(self.probs),
+                                           v(self.eidx), dim=a.dim, n_groups=a.n_expert_groups,
+                                           n_limited_groups=a.n_limited_groups, route_scale=a.route_scale,
+                                           slot_ids=self.slot_ids, slot_w=self.slot_w)
+            ops.expert_down_allreduce(v(self.ffn_hidden), w.w_down, None, v(self.eidx), v(self.probs), v(self.h), 0,
+                                      v(self.out), slot_ids=self.slot_ids, slot_w=self.slot_w, comm=self.comm)
+        return v(self.out)

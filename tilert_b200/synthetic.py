@@ -1,0 +1,70 @@
+"""Seeded random-init checkpoints in the HF DeepSeek FP8 format (e4m3 ``weight`` + f32
+``weight_scale_inv`` per 128x128 block), generated on any device.  Used where the reference would
+load real weights (its ``--use-random-weights`` path, tilert/generate.py:106-110, does the same in
+spirit): benchmarks and smoke runs have no checkpoint to read."""
+
+from __future__ import annotations
+
+import torch
+
+from .models.deepseek_v3_2.model_args import ModelArgs
+
+BF16 = torch.bfloat16
+
+
+def quantize_block128(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """f32 [N, K] -> (e4m3 [N, K], f32 scales [ceil(N/128), ceil(K/128)]) with scale = amax / 448."""
+    n, k = w.shape
+    np_, kp = (n + 127) // 128 * 128, (k + 127) // 128 * 128
+    wp = torch.zeros(np_, kp, dtype=torch.float32, device=w.device)
+    wp[:n, :k] = w
+    blk = wp.view(np_ // 128, 128, kp // 128, 128)
+    scale = blk.abs().amax(dim=(1, 3)).clamp_min(1e-12) / 448.0
+    q = (blk / scale[:, None, :, None]).clamp(-448, 448).view(np_, kp)[:n, :k].contiguous()
+    return q.to(torch.float8_e4m3fn), scale.contiguous()
+
+
+def random_layer_state_dict(args: ModelArgs, li: int, device, seed: int = 0, std: float = 0.02,
+                            expert_ids=None) -> dict[str, torch.Tensor]:
+    """One layer's tensors under their HF keys (``model.layers.{li}. ...``)."""
+    a = args
+    gen = torch.Generator(device=device).manual_seed(seed * 1000 + li)
+    sd: dict[str, torch.Tensor] = {}
+
+    def rnd(*shape):
+        return torch.randn(*shape, generator=gen, dtype=torch.float32, device=device) * std
+
+    def fp8(key, n, k):
+        sd[f"{key}.weight"], sd[f"{key}.weight_scale_inv"] = quantize_block128(rnd(n, k))
+
+    p = f"model.layers.{li}"
+    at = f"{p}.self_attn"
+    ones = lambda n: torch.ones(n, dtype=torch.float32, device=device)  # noqa: E731
+    sd[f"{p}.input_layernorm.weight"] = ones(a.dim)
+    sd[f"{p}.post_attention_layernorm.weight"] = ones(a.dim)
+    fp8(f"{at}.q_a_proj", a.q_lora_rank, a.dim)
+    sd[f"{at}.q_a_layernorm.weight"] = ones(a.q_lora_rank)
+    fp8(f"{at}.q_b_proj", a.n_heads * (a.qk_nope_head_dim + a.qk_rope_head_dim), a.q_lora_rank)
+    fp8(f"{at}.kv_a_proj_with_mqa", a.kv_lora_rank + a.qk_rope_head_dim, a.dim)
+    sd[f"{at}.kv_a_layernorm.weight"] = ones(a.kv_lora_rank)
+    fp8(f"{at}.kv_b_proj", a.n_heads * (a.qk_nope_head_dim + a.v_head_dim), a.kv_lora_rank)
+    fp8(f"{at}.o_proj", a.dim, a.n_heads * a.v_head_dim)
+    fp8(f"{at}.indexer.wq_b", a.index_n_heads * a.index_head_dim, a.q_lora_rank)
+    fp8(f"{at}.indexer.wk", a.index_head_dim, a.dim)
+    sd[f"{at}.indexer.k_norm.weight"] = ones(a.index_head_dim)
+    sd[f"{at}.indexer.k_norm.bias"] = torch.zeros(a.index_head_dim, dtype=torch.float32, device=device)
+    sd[f"{at}.indexer.weights_proj.weight"] = rnd(a.index_n_heads, a.dim).to(BF16)
+    m = f"{p}.mlp"
+    if li < a.n_dense_layers:
+        fp8(f"{m}.gate_proj", a.inter_dim, a.dim)
+        fp8(f"{m}.up_proj", a.inter_dim, a.dim)
+        fp8(f"{m}.down_proj", a.dim, a.inter_dim)
+    else:
+        sd[f"{m}.gate.weight"] = rnd(a.n_routed_experts, a.dim).to(BF16)
+        sd[f"{m}.gate.e_score_correction_bias"] = torch.zeros(a.n_routed_experts, dtype=torch.float32, device=device)
+        ids = range(a.n_routed_experts) if expert_ids is None else expert_ids
+        for nm in ["shared_experts"] + [f"experts.{e}" for e in ids]:
+            fp8(f"{m}.{nm}.gate_proj", a.moe_inter_dim, a.dim)
+            fp8(f"{m}.{nm}.up_proj", a.moe_inter_dim, a.dim)
+            fp8(f"{m}.{nm}.down_proj", a.dim, a.moe_inter_dim)
+    return sd
