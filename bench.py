@@ -6,7 +6,7 @@
 Workload: one full-shape DeepSeek-V3.2 MoE decoder layer (hidden 7168, 128 heads, 256 routed
 experts top-8 + 1 shared, indexer 64x128 top-2048), batch 1, one decode step at position 4095 of
 a 4096-row latent cache filled from N(0,1); random-init FP8 weights; router logits forced so the
-eight routed experts are {0, 32, ..., 224}.  A "step" is one pass of the layer over one token.
+eight routed experts are fixed (two in each of four expert groups).  A "step" is one pass of the layer over one token.
 With N > 1 (launched by torch.distributed.run, one rank per GPU) the layer is tensor-parallel
 over N GPUs and the two row-parallel products reduce inside their kernels over peer memory.
 
@@ -40,10 +40,16 @@ WORKLOAD = ("C1: one full-shape DeepSeek-V3.2 MoE decoder layer, batch 1, 1 toke
 
 
 def forced_scores(n_experts: int, top_k: int) -> torch.Tensor:
-    """Router logits that select experts {0, 32, ...} (one per group of n_experts/top_k)."""
+    """Router logits with `top_k` hot experts spread evenly: two in every other group of 32 (the
+    group-limited routing keeps 4 of the 8 groups, so the hot experts must sit in 4 groups)."""
     s = torch.full((1, 1, n_experts), -8.0)
-    s[0, 0, :: n_experts // top_k] = 4.0
+    s[0, 0, hot_experts(n_experts, top_k)] = 4.0
     return s
+
+
+def hot_experts(n_experts: int, top_k: int) -> list[int]:
+    group = n_experts // 8
+    return sorted(g * group + j * (group // 2) for g in range(0, 8, 2) for j in range(top_k // 4))
 
 
 class ClockSampler:
@@ -104,7 +110,7 @@ def cpu_reference_steps(n_steps: int, warmup: int) -> tuple[float, dict]:
 
     torch.manual_seed(0)
     a = om.full_layer_args(max_seq_len=CACHE_LEN)
-    ids = list(range(0, a.n_routed_experts, a.n_routed_experts // a.n_activated_experts))
+    ids = hot_experts(a.n_routed_experts, a.n_activated_experts)
     sd = om.random_state_dict(a, seed=0, expert_ids=ids)
     w = om.LayerWeights(a, sd, 0)
     c = om.Caches(a, CACHE_LEN)
@@ -227,7 +233,7 @@ def run_ours(args) -> None:
     barrier()
     dev_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
     # keep sampling clocks through a longer loaded stretch so the median is meaningful
-    t_end = time.time() + 1.0
+    t_end = time.time() + (0.0 if args.profile else 1.0)
     while time.time() < t_end:
         graph.replay()
     torch.cuda.synchronize()
@@ -246,7 +252,7 @@ def run_ours(args) -> None:
 
     # ---- dominant kernel alone: the routed+shared expert up/gate product (9 experts x 29.4 MB) ----
     n_slots = a.n_activated_experts + 1
-    k_iters = 20
+    k_iters = 2 if args.profile else 20
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     def upgate():
@@ -312,13 +318,47 @@ def run_ours(args) -> None:
             "device_status": int(status),
         }
         if world == 1 and not args.no_cpu_baseline:
-            dt, desc = cpu_reference_steps(2, 1)
-            line["cpu_baseline"] = {"value": 1.0 / dt, "unit": UNIT, **desc}
+            try:
+                dt, desc = cpu_reference_steps(2, 1)
+                line["cpu_baseline"] = {"value": 1.0 / dt, "unit": UNIT, **desc}
+            except Exception as e:  # noqa: BLE001  (report the GPU numbers even if the CPU leg fails)
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "error": f"{type(e).__name__}: {e}"}
         print(json.dumps(line), flush=True)
     if comm is not None:
         comm.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_profile_gemv(args) -> None:
+    """One weight-streaming product alone: N = 7168 rows, K = 32768 (235 MB of FP8 weights, larger
+    than L2), a few launches.  Small device footprint, meant to be captured by a profiler."""
+    import tilert_b200
+    from tilert_b200.models.deepseek_v3_2 import ops
+
+    tilert_b200.load_backend("deepseek_v3_2")
+    tilert_b200.tilert_init(0)
+    dev = torch.device("cuda", 0)
+    n, k = 7168, 32768
+    g = torch.Generator(device=dev).manual_seed(0)
+    w = torch.randint(0, 120, (n // 128, k // 128, 16448), generator=g, dtype=torch.uint8, device=dev)
+    w[:, :, 16384:] = 0
+    w[:, :, 16384:].view(torch.float32).fill_(1e-3)
+    vec = torch.randn(1, 1, k, generator=g, device=dev).to(torch.bfloat16)
+    res = torch.randn(1, 1, n, generator=g, device=dev).to(torch.bfloat16)
+    out = torch.zeros(1, 1, n, dtype=torch.bfloat16, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(max(args.warmup, 1)):
+        ops.unproj_o_allreduce(vec, w, None, res, 0, out)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        ops.unproj_o_allreduce(vec, w, None, res, 0, out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"mode": "profile-gemv", "n": n, "k": k, "weight_bytes": w.numel(), "ms_per_launch_pair": ms,
+                      "gbs_incl_pack_launch": w.numel() / ms / 1e6, "status": tilert_b200.device_status(0)}))
 
 
 def main() -> None:
@@ -328,8 +368,16 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="short run for a profiler: no clock-sampling loop, no CPU baseline")
+    ap.add_argument("--profile-gemv", action="store_true",
+                    help="run only the weight-streaming product on a 235 MB weight (small footprint for ncu)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile:
+        args.no_cpu_baseline = True
+    if args.profile_gemv:
+        run_profile_gemv(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
