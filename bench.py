@@ -256,7 +256,7 @@ def run_ours(args) -> None:
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     def upgate():
-        ops.expert_select_up_gate_silu(layer.xp_h, layer.forced_scores, weights.router_bias, weights.w_gu,
+        ops.expert_select_up_gate_silu(layer.h_norm, layer.forced_scores, weights.router_bias, weights.w_gu,
                                        layer.ffn_hidden, layer.probs, layer.eidx, dim=a.dim,
                                        n_groups=a.n_expert_groups, n_limited_groups=a.n_limited_groups,
                                        route_scale=a.route_scale, slot_ids=layer.slot_ids, slot_w=layer.slot_w)

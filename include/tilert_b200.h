@@ -104,6 +104,13 @@ int tilert_projx_wqkva_op(TbContext* ctx, const uint8_t* xpack, int cols_per_tok
                           int tokens, int dim, int q_lora, int kv_lora, int rope, int ki_dim, const int* cur_pos,
                           void* q_out, void* kv_out, void* pe_cache, void* ki_out, void* stream);
 
+/* RMSNormProjxWqkva.tilert_forward (ops/rmsnorm_projx_wqkva.py:473-509) as ONE launch: the RMSNorm
+ * (rmsnorm_quant_op) runs inside the product kernel, which reads the bf16 hidden state directly. */
+int tilert_rmsnorm_projx_wqkva_op(TbContext* ctx, const void* x, const float* gamma, float eps,
+                                  const uint8_t* w_packed, int tokens, int dim, int q_lora, int kv_lora, int rope,
+                                  int ki_dim, const int* cur_pos, void* q_out, void* kv_out, void* pe_cache,
+                                  void* ki_out, void* stream);
+
 /* rmsnorm_proj_qb_op (ops/rmsnorm_projq_wqb.py:21-43) and rmsnorm_proj_qi_op
  * (ops/rmsnorm_projq_wqi.py:21-40) in one launch: RMSNorm(q) then rows
  * [q_nope (heads*nope) | q_pe (heads*rope) | iq (iq_heads*iq_dim)]. */
@@ -125,12 +132,13 @@ int tilert_unproj_o_allreduce_op(TbContext* ctx, const void* vec, const uint8_t*
 
 /* expert_select_up_gate_silu_op (ops/expert_sel_up_gate_silu.py:23-48): routing (sigmoid + bias,
  * group-limited top-k, renormalise, scale) then SiLU(W1 x) * (W3 x) for the shared expert and the
- * selected routed experts.  w_packed: [n_experts + 1] experts, `expert_stride` bytes apart, the
+ * selected routed experts.  hidden [tokens, dim] bf16 is the normalised post-attention state
+ * (hidden_out of rmsnorm_expert_proj_op).  w_packed: [n_experts + 1] experts, `expert_stride` bytes apart, the
  * shared expert last; rows of each expert interleave gate and up in groups of 8.
  * hidden_out [tokens, top_k + 1, inter] bf16 (slot 0 = shared expert).
  * slot_ids / slot_w [tokens, top_k + 1]: expert id and weight per slot (inputs of the down op).
  * Under tensor parallelism every rank holds an `inter`-row slice of every expert. */
-int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const uint8_t* xpack, const float* scores,
+int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* hidden, const float* scores,
                                          const float* bias, const uint8_t* w_packed, long long expert_stride,
                                          int tokens, int dim, int inter, int n_experts, int n_groups,
                                          int n_limited_groups, int top_k, float route_scale, void* hidden_out,
@@ -153,9 +161,10 @@ int tilert_down_allreduce_op(TbContext* ctx, const void* vec, const uint8_t* w_p
 
 /* ---- bf16 products --------------------------------------------------------------------- */
 
-/* proj_w_op (ops/projx_wis.py:21-40): out[t, :] = W[n, k] . x[t, :]   (bf16 in, bf16 out). */
-int tilert_proj_w_op(TbContext* ctx, const void* x, const void* w, int tokens, int n, int k, void* out,
-                     void* stream);
+/* proj_w_op (ops/projx_wis.py:21-40): out[t, :] = W[n, k] . x[t, :]   (bf16 in, bf16 out).
+ * gamma != NULL: x is the raw hidden state and RMSNorm(x) * gamma (kept in f32) is applied first. */
+int tilert_proj_w_op(TbContext* ctx, const void* x, const float* gamma, float eps, const void* w, int tokens, int n,
+                     int k, void* out, void* stream);
 /* rmsnorm_expert_proj_op (ops/rmsnorm_expert_proj.py:151-169): hidden_out = bf16(RMSNorm(x)),
  * scores_out[t, :] = W_gate . hidden_out[t, :] in f32.  w_gate is bf16 (gate_is_f32 = 0) or f32.
  * gamma == NULL: x is already normalised (hidden_out may then be NULL). */

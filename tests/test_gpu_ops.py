@@ -126,15 +126,11 @@ def test_projx_wqkva_and_indexer_k(env, tokens):
     x = rn(g, 1, tokens, a.dim)
     pos = 37
     cur = torch.tensor([pos], dtype=I32, device="cuda")
-    xn = torch.empty(1, tokens, a.dim, dtype=BF16, device="cuda")
-    xp = ops.new_xpack(a.dim, "cuda")
-    ops.rmsnorm_quant(x.cuda(), gw.in_norm, xn, None, None, eps=a.eps, xpack=xp)
     q = torch.zeros(1, tokens, a.q_lora_rank, dtype=BF16, device="cuda")
     kv = torch.zeros(1, tokens, a.kv_lora_rank, dtype=BF16, device="cuda")
     ki = torch.zeros(1, tokens, a.index_head_dim, dtype=BF16, device="cuda")
     pe = torch.zeros(1, 64, a.qk_rope_head_dim, dtype=BF16, device="cuda")
-    ops.projx_wqkva_packed(xp, 2, gw.w_qkva, tokens, a.dim, a.q_lora_rank, a.kv_lora_rank, a.qk_rope_head_dim,
-                           a.index_head_dim, cur, q, kv, pe, ki)
+    ops.rmsnorm_projx_wqkva(x.cuda(), gw.in_norm, gw.w_qkva, cur, q, kv, pe, ki, eps=a.eps)
     rq, rkv, rpe = oo.projx_wqkva(x, w.in_norm, w.wq_a, w.wkv_a, w.w_pe, a.eps)
     _, rki, rw = oo.projx_wqakis(x, w.in_norm, w.wq_a, w.wki, w.wis, a.eps)
     close("wqkva.q", rq, q)
@@ -143,8 +139,17 @@ def test_projx_wqkva_and_indexer_k(env, tokens):
     close("wqkva.ki", rki, ki)
     assert float(pe[:, :pos].abs().max()) == 0 and float(pe[:, pos + tokens:].abs().max()) == 0
     iw = torch.zeros(1, tokens, a.index_n_heads, dtype=BF16, device="cuda")
-    ops.projx_wis(xn, gw.wis, iw)
+    ops.projx_wis(x.cuda(), gw.wis, iw, gamma=gw.in_norm, eps=a.eps)
     close("wis", rw, iw)
+    # the two-launch form (packed activations prepared by rmsnorm_quant) gives the same result
+    xn = torch.empty(1, tokens, a.dim, dtype=BF16, device="cuda")
+    xp = ops.new_xpack(a.dim, "cuda")
+    ops.rmsnorm_quant(x.cuda(), gw.in_norm, xn, None, None, eps=a.eps, xpack=xp)
+    q2, kv2 = torch.zeros_like(q), torch.zeros_like(kv)
+    ops.projx_wqkva_packed(xp, 2, gw.w_qkva, tokens, a.dim, a.q_lora_rank, a.kv_lora_rank, a.qk_rope_head_dim,
+                           a.index_head_dim, cur, q2, kv2, pe, None)
+    close("wqkva.q.packed", rq, q2)
+    close("wqkva.kv.packed", rkv, kv2)
 
 
 def test_projx_wqkva_reference_format_input(env):
@@ -343,15 +348,13 @@ def test_router_and_expert_path(env):
     close("router.hn", rhn, hn, cos_min=0.99999, l2_max=4e-3)
     close("router.scores", rsc.view(1, tokens, -1), scores, cos_min=0.9999, l2_max=5e-3)
 
-    xp = ops.new_xpack(a.dim, "cuda")
-    ops.act_pack(hn, xp)
     n_slots = a.n_activated_experts + 1
     hid = torch.zeros(1, tokens, n_slots, a.moe_inter_dim, dtype=BF16, device="cuda")
     probs = torch.zeros(1, tokens, a.n_activated_experts, dtype=F32, device="cuda")
     eidx = torch.zeros(1, tokens, a.n_activated_experts, dtype=I32, device="cuda")
     slot_ids = torch.zeros(tokens, n_slots, dtype=I32, device="cuda")
     slot_w = torch.zeros(tokens, n_slots, dtype=F32, device="cuda")
-    ops.expert_select_up_gate_silu(xp, scores, gw.router_bias, gw.w_gu, hid, probs, eidx, dim=a.dim, n_groups=1,
+    ops.expert_select_up_gate_silu(hn, scores, gw.router_bias, gw.w_gu, hid, probs, eidx, dim=a.dim, n_groups=1,
                                    n_limited_groups=1, route_scale=a.route_scale, slot_ids=slot_ids, slot_w=slot_w)
     rp, ri = oo.expert_select_ds(scores.cpu(), w.router_bias, 1, 1, a.n_activated_experts, a.route_scale)
     assert torch.equal(ri.to(I32), eidx.cpu())
@@ -378,7 +381,7 @@ def test_grouped_routing_full_shape(env):
     scores = torch.randn(1, tokens, 256, generator=g)
     bias = torch.randn(256, generator=g) * 0.1
     w = torch.zeros(257, 1, dim // 128, 16448, dtype=torch.uint8, device="cuda")
-    xp = ops.new_xpack(dim, "cuda")
+    xp = torch.zeros(1, tokens, dim, dtype=BF16, device="cuda")
     hid = torch.zeros(1, tokens, 9, inter, dtype=BF16, device="cuda")
     probs = torch.zeros(1, tokens, 8, dtype=F32, device="cuda")
     eidx = torch.zeros(1, tokens, 8, dtype=I32, device="cuda")

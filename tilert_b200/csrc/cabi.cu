@@ -121,6 +121,16 @@ int set_comm(GemvParams& p, TbComm* comm, int n_rows) {
   return TB_OK;
 }
 
+void set_x_bf16(GemvParams& p, const void* x, long long stride, const float* gamma = nullptr, float eps = 0.f,
+                const float* seg_scale = nullptr) {
+  p.x_mode = X_BF16;
+  p.xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  p.xb_stride = stride;
+  p.gamma = gamma;
+  p.eps = eps;
+  p.seg_scale = seg_scale;
+}
+
 int launch_actpack(const ActPackParams& p, cudaStream_t st) {
   TB_REQUIRE(p.k % TB_KBLOCK == 0 && p.k / TB_KBLOCK <= 32 * kActPackMaxIter);
   TB_REQUIRE(p.n_tokens >= 1 && p.n_tokens <= 4);
@@ -333,27 +343,42 @@ extern "C" int tilert_projx_wqkva_op(TbContext* ctx, const uint8_t* xpack, int c
   return launch_gemv(ctx, p, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int tilert_rmsnorm_projx_wqkva_op(TbContext* ctx, const void* x, const float* gamma, float eps,
+                                             const uint8_t* w_packed, int tokens, int dim, int q_lora, int kv_lora,
+                                             int rope, int ki_dim, const int* cur_pos, void* q_out, void* kv_out,
+                                             void* pe_cache, void* ki_out, void* stream) {
+  TB_REQUIRE(ctx != nullptr && x != nullptr && gamma != nullptr && w_packed != nullptr);
+  TB_REQUIRE(dim % TB_KBLOCK == 0 && tokens >= 1 && tokens <= 4);
+  TB_REQUIRE(rope == 0 || cur_pos != nullptr);
+  const int rows = q_lora + kv_lora + rope + ki_dim;
+  GemvParams p;
+  gemv_defaults(p);
+  p.w = w_packed;
+  set_x_bf16(p, x, dim, gamma, eps);
+  p.n_tiles = (rows + TB_TILE_ROWS - 1) / TB_TILE_ROWS;
+  p.n_kb = dim / TB_KBLOCK;
+  p.w_kb_per_tile = p.n_kb;
+  p.n_tokens = tokens;
+  p.n_rows = rows;
+  set_region(p, 0, q_lora, q_out, q_lora);
+  set_region(p, q_lora, kv_lora, kv_out, kv_lora);
+  set_region(p, q_lora + kv_lora, rope, pe_cache, rope, 0, cur_pos);
+  set_region(p, q_lora + kv_lora + rope, ki_dim, ki_out, ki_dim);
+  return launch_gemv(ctx, p, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int tilert_rmsnorm_proj_q_op(TbContext* ctx, const void* q, const float* gamma, float eps,
                                         const uint8_t* w_packed, int tokens, int q_lora, int heads, int nope,
                                         int rope, int iq_heads, int iq_dim, void* q_nope, void* q_pe, void* iq,
                                         void* stream) {
   TB_REQUIRE(ctx != nullptr && q != nullptr && gamma != nullptr && w_packed != nullptr);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  ActPackParams a{};
-  a.x = reinterpret_cast<const __nv_bfloat16*>(q);
-  a.x_stride = q_lora;
-  a.k = q_lora;
-  a.n_tokens = tokens;
-  a.gamma = gamma;
-  a.eps = eps;
-  a.xpack = ctx->xpack;
-  int rc = launch_actpack(a, st);
-  if (rc != TB_OK) return rc;
+  TB_REQUIRE(tokens >= 1 && tokens <= 4 && q_lora % TB_KBLOCK == 0);
   const int r_nope = heads * nope, r_pe = heads * rope, r_iq = iq_heads * iq_dim;
   GemvParams p;
   gemv_defaults(p);
   p.w = w_packed;
-  p.x = ctx->xpack;
+  set_x_bf16(p, q, q_lora, gamma, eps);
   p.n_rows = r_nope + r_pe + r_iq;
   p.n_tiles = (p.n_rows + TB_TILE_ROWS - 1) / TB_TILE_ROWS;
   p.n_kb = q_lora / TB_KBLOCK;
@@ -370,12 +395,11 @@ extern "C" int tilert_projq_wqb_op(TbContext* ctx, const void* q_nope, const uin
   TB_REQUIRE(ctx != nullptr && q_nope != nullptr && w_packed != nullptr && out != nullptr);
   TB_REQUIRE(nope % TB_KBLOCK == 0 && kv_lora % TB_TILE_ROWS == 0);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = pack_flat(q_nope, tokens, heads * nope, nullptr, 0, ctx->xpack, st);
-  if (rc != TB_OK) return rc;
+  TB_REQUIRE(tokens >= 1 && tokens <= 4);
   GemvParams p;
   gemv_defaults(p);
   p.w = w_packed;
-  p.x = ctx->xpack;
+  set_x_bf16(p, q_nope, static_cast<long long>(heads) * nope);
   p.n_rows = heads * kv_lora;
   p.n_tiles = p.n_rows / TB_TILE_ROWS;
   p.n_kb = nope / TB_KBLOCK;
@@ -391,12 +415,11 @@ extern "C" int tilert_projo_wkvb_op(TbContext* ctx, const void* o_lat, const uin
   TB_REQUIRE(ctx != nullptr && o_lat != nullptr && w_packed != nullptr && out != nullptr);
   TB_REQUIRE(kv_lora % TB_KBLOCK == 0 && v_dim % TB_TILE_ROWS == 0);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = pack_flat(o_lat, tokens, heads * kv_lora, nullptr, 0, ctx->xpack, st);
-  if (rc != TB_OK) return rc;
+  TB_REQUIRE(tokens >= 1 && tokens <= 4);
   GemvParams p;
   gemv_defaults(p);
   p.w = w_packed;
-  p.x = ctx->xpack;
+  set_x_bf16(p, o_lat, static_cast<long long>(heads) * kv_lora);
   p.n_rows = heads * v_dim;
   p.n_tiles = p.n_rows / TB_TILE_ROWS;
   p.n_kb = kv_lora / TB_KBLOCK;
@@ -413,12 +436,12 @@ extern "C" int tilert_unproj_o_allreduce_op(TbContext* ctx, const void* vec, con
   TB_REQUIRE(ctx != nullptr && vec != nullptr && w_packed != nullptr && out != nullptr);
   TB_REQUIRE(k % TB_KBLOCK == 0);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = pack_flat(vec, tokens, k, nullptr, 0, ctx->xpack, st);
-  if (rc != TB_OK) return rc;
+  TB_REQUIRE(tokens >= 1 && tokens <= 4);
+  int rc = TB_OK;
   GemvParams p;
   gemv_defaults(p);
   p.w = w_packed;
-  p.x = ctx->xpack;
+  set_x_bf16(p, vec, k);
   p.n_rows = n;
   p.n_tiles = (n + TB_TILE_ROWS - 1) / TB_TILE_ROWS;
   p.n_kb = k / TB_KBLOCK;
@@ -432,14 +455,14 @@ extern "C" int tilert_unproj_o_allreduce_op(TbContext* ctx, const void* vec, con
   return launch_gemv(ctx, p, st);
 }
 
-extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const uint8_t* xpack, const float* scores,
+extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* hidden, const float* scores,
                                                     const float* bias, const uint8_t* w_packed,
                                                     long long expert_stride, int tokens, int dim, int inter,
                                                     int n_experts, int n_groups, int n_limited_groups, int top_k,
                                                     float route_scale, void* hidden_out, float* probs_out,
                                                     int* idx_out, int* slot_ids, float* slot_w, void* stream) {
-  TB_REQUIRE(ctx != nullptr && xpack != nullptr && scores != nullptr && w_packed != nullptr);
-  TB_REQUIRE(hidden_out != nullptr && probs_out != nullptr && idx_out != nullptr);
+  TB_REQUIRE(ctx != nullptr && hidden != nullptr && scores != nullptr && w_packed != nullptr);
+  TB_REQUIRE(hidden_out != nullptr && probs_out != nullptr && idx_out != nullptr && tokens >= 1 && tokens <= 4);
   TB_REQUIRE(n_experts <= 256 && top_k <= 31 && (n_groups == 1 || (32 % n_groups == 0 && n_experts % 32 == 0)));
   TB_REQUIRE((2 * inter) % TB_TILE_ROWS == 0 && dim % TB_KBLOCK == 0);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -455,7 +478,7 @@ extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const uint8_
     GemvParams p;
     gemv_defaults(p);
     p.w = w_packed;
-    p.x = xpack;
+    set_x_bf16(p, hidden, dim);
     p.tiles_per_nseg = 2 * inter / TB_TILE_ROWS;
     p.n_tiles = n_slots * p.tiles_per_nseg;
     p.n_kb = dim / TB_KBLOCK;
@@ -483,13 +506,13 @@ extern "C" int tilert_expert_down_allreduce_op(TbContext* ctx, const void* vec, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (slot_ids == nullptr) slot_ids = reinterpret_cast<const int*>(ctx->small);
   if (slot_w == nullptr) slot_w = reinterpret_cast<const float*>(ctx->small + 4096);
-  int rc = pack_flat(vec, tokens, n_slots * inter, slot_w, n_slots, ctx->xpack, st);
-  if (rc != TB_OK) return rc;
+  TB_REQUIRE(tokens >= 1 && tokens <= 4);
+  int rc = TB_OK;
   for (int t = 0; t < tokens; ++t) {
     GemvParams p;
     gemv_defaults(p);
     p.w = w_packed;
-    p.x = ctx->xpack;
+    set_x_bf16(p, vec, static_cast<long long>(n_slots) * inter, nullptr, 0.f, slot_w);
     p.n_rows = dim;
     p.n_tiles = (dim + TB_TILE_ROWS - 1) / TB_TILE_ROWS;
     p.kb_per_kseg = inter / TB_KBLOCK;
@@ -516,20 +539,11 @@ extern "C" int tilert_rmsnorm_up_gate_silu_op(TbContext* ctx, const void* x, con
   TB_REQUIRE(ctx != nullptr && x != nullptr && gamma != nullptr && w_packed != nullptr && out != nullptr);
   TB_REQUIRE((2 * inter) % TB_TILE_ROWS == 0);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  ActPackParams a{};
-  a.x = reinterpret_cast<const __nv_bfloat16*>(x);
-  a.x_stride = dim;
-  a.k = dim;
-  a.n_tokens = tokens;
-  a.gamma = gamma;
-  a.eps = eps;
-  a.xpack = ctx->xpack;
-  int rc = launch_actpack(a, st);
-  if (rc != TB_OK) return rc;
+  TB_REQUIRE(tokens >= 1 && tokens <= 4 && dim % TB_KBLOCK == 0);
   GemvParams p;
   gemv_defaults(p);
   p.w = w_packed;
-  p.x = ctx->xpack;
+  set_x_bf16(p, x, dim, gamma, eps);
   p.n_tiles = 2 * inter / TB_TILE_ROWS;
   p.n_kb = dim / TB_KBLOCK;
   p.w_kb_per_tile = p.n_kb;
@@ -565,7 +579,22 @@ int launch_gemv_bf16(TbContext* ctx, GemvBf16Params& p, cudaStream_t st) {
     attr_set = true;
   }
   TB_REQUIRE(smem <= 200 * 1024);
-  if (tok_t == 1)
+  if (p.n <= 2048) {
+    static bool attr2_set = false;
+    if (!attr2_set) {
+      TB_CUDA(cudaFuncSetAttribute(gemv_bf16_ksplit_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      TB_CUDA(cudaFuncSetAttribute(gemv_bf16_ksplit_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      TB_CUDA(cudaFuncSetAttribute(gemv_bf16_ksplit_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      attr2_set = true;
+    }
+    const int g2 = (p.n + kGemvBf16SmallRows - 1) / kGemvBf16SmallRows;
+    if (tok_t == 1)
+      gemv_bf16_ksplit_kernel<1><<<g2, kGemvBf16SmallThreads, smem, st>>>(p);
+    else if (tok_t == 2)
+      gemv_bf16_ksplit_kernel<2><<<g2, kGemvBf16SmallThreads, smem, st>>>(p);
+    else
+      gemv_bf16_ksplit_kernel<4><<<g2, kGemvBf16SmallThreads, smem, st>>>(p);
+  } else if (tok_t == 1)
     gemv_bf16_kernel<1><<<grid, kGemvBf16Threads, smem, st>>>(p);
   else if (tok_t == 2)
     gemv_bf16_kernel<2><<<grid, kGemvBf16Threads, smem, st>>>(p);
@@ -577,10 +606,12 @@ int launch_gemv_bf16(TbContext* ctx, GemvBf16Params& p, cudaStream_t st) {
 }
 }  // namespace
 
-extern "C" int tilert_proj_w_op(TbContext* ctx, const void* x, const void* w, int tokens, int n, int k, void* out,
-                                void* stream) {
+extern "C" int tilert_proj_w_op(TbContext* ctx, const void* x, const float* gamma, float eps, const void* w,
+                                int tokens, int n, int k, void* out, void* stream) {
   TB_REQUIRE(ctx != nullptr && x != nullptr && w != nullptr && out != nullptr);
   GemvBf16Params p{};
+  p.gamma = gamma;
+  p.eps = eps;
   p.w = w;
   p.n = n;
   p.k = k;

@@ -121,4 +121,115 @@ __global__ void __launch_bounds__(kGemvBf16Threads) gemv_bf16_kernel(const GemvB
   }
 }
 
+// Variant for few rows (router gate, indexer head weights): one CTA per pair of rows, the warps
+// split K, so the dependent load chain is K / (8 warps * 256) iterations instead of K / 256.
+constexpr int kGemvBf16SmallThreads = 256;
+constexpr int kGemvBf16SmallRows = 2;
+
+template <int TOK>
+__global__ void __launch_bounds__(kGemvBf16SmallThreads) gemv_bf16_ksplit_kernel(const GemvBf16Params p) {
+  extern __shared__ __align__(16) float xs[];  // [TOK][k]
+  __shared__ float red[TOK][8];
+  __shared__ float part[kGemvBf16SmallRows][TOK][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float ss[TOK];
+#pragma unroll
+  for (int t = 0; t < TOK; ++t) ss[t] = 0.f;
+  for (int i = threadIdx.x * 8; i < p.k; i += kGemvBf16SmallThreads * 8) {
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (t < p.n_tokens) raw = *reinterpret_cast<const uint4*>(p.x + t * p.x_stride + i);
+      const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = __uint_as_float(wv[j] << 16), b = __uint_as_float(wv[j] & 0xffff0000u);
+        xs[t * p.k + i + 2 * j] = a;
+        xs[t * p.k + i + 2 * j + 1] = b;
+        ss[t] += a * a + b * b;
+      }
+    }
+  }
+  if (p.gamma != nullptr) {
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+      const float s = warp_sum(ss[t]);
+      if (lane == 0) red[t][warp] = s;
+    }
+    __syncthreads();
+    float rinv[TOK];
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+      float tot = lane < 8 ? red[t][lane] : 0.f;
+      tot = warp_sum(tot);
+      rinv[t] = rsqrtf(tot / static_cast<float>(p.k) + p.eps);
+    }
+    for (int i = threadIdx.x; i < p.k; i += kGemvBf16SmallThreads) {
+      const float g = p.gamma[i];
+#pragma unroll
+      for (int t = 0; t < TOK; ++t) {
+        float v = xs[t * p.k + i] * rinv[t] * g;
+        if (p.round_norm_bf16) v = bf2f(f2bf(v));
+        xs[t * p.k + i] = v;
+        if (p.xnorm_out != nullptr && blockIdx.x == 0 && t < p.n_tokens) p.xnorm_out[t * p.xnorm_stride + i] = f2bf(v);
+      }
+    }
+  }
+  __syncthreads();
+
+  const int kslice = p.k / 8;  // per warp; multiple of 8 elements (k % 256 == 0)
+#pragma unroll
+  for (int r = 0; r < kGemvBf16SmallRows; ++r) {
+    const int row = blockIdx.x * kGemvBf16SmallRows + r;
+    float acc[TOK];
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) acc[t] = 0.f;
+    if (row < p.n) {
+      for (int k0 = warp * kslice + lane * 8; k0 < (warp + 1) * kslice; k0 += 256) {
+        float wf[8];
+        if (p.w_is_f32) {
+          const float* wr = reinterpret_cast<const float*>(p.w) + static_cast<long long>(row) * p.k + k0;
+          const float4 w0 = __ldg(reinterpret_cast<const float4*>(wr)), w1 = __ldg(reinterpret_cast<const float4*>(wr + 4));
+          wf[0] = w0.x; wf[1] = w0.y; wf[2] = w0.z; wf[3] = w0.w; wf[4] = w1.x; wf[5] = w1.y; wf[6] = w1.z; wf[7] = w1.w;
+        } else {
+          const __nv_bfloat16* wr = reinterpret_cast<const __nv_bfloat16*>(p.w) + static_cast<long long>(row) * p.k + k0;
+          const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wr));
+          const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            wf[2 * j] = __uint_as_float(ww[j] << 16);
+            wf[2 * j + 1] = __uint_as_float(ww[j] & 0xffff0000u);
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < TOK; ++t) {
+          const float4 xa = *reinterpret_cast<const float4*>(&xs[t * p.k + k0]);
+          const float4 xb = *reinterpret_cast<const float4*>(&xs[t * p.k + k0 + 4]);
+          acc[t] += wf[0] * xa.x + wf[1] * xa.y + wf[2] * xa.z + wf[3] * xa.w + wf[4] * xb.x + wf[5] * xb.y +
+                    wf[6] * xb.z + wf[7] * xb.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+      const float s = warp_sum(acc[t]);
+      if (lane == 0) part[r][t][warp] = s;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < kGemvBf16SmallRows * TOK) {
+    const int r = threadIdx.x / TOK, t = threadIdx.x % TOK;
+    const int row = blockIdx.x * kGemvBf16SmallRows + r;
+    if (row < p.n && t < p.n_tokens) {
+      float s = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < 8; ++w2) s += part[r][t][w2];
+      if (p.out_bf16)
+        reinterpret_cast<__nv_bfloat16*>(p.out)[t * p.out_stride + row] = f2bf(s);
+      else
+        reinterpret_cast<float*>(p.out)[t * p.out_stride + row] = s;
+    }
+  }
+}
+
 }  // namespace tb

@@ -151,15 +151,41 @@ __global__ void __launch_bounds__(kTopkThreads) topk_radix_kernel(const float* _
         if (key > kNegInfKey && (key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1);
       }
       __syncthreads();
-      if (tid == 0) {
-        int rem = s_remaining;
-        int d = 255;
-        for (; d > 0; --d) {
-          if (hist[d] >= rem) break;
-          rem -= hist[d];
+      if (warp == 0) {
+        // find the digit where the count of larger-or-equal digits reaches the remaining quota:
+        // lane l owns bins 8l .. 8l+7; suffix sums across lanes, then a short scan inside one lane
+        const int rem = s_remaining;
+        int b[8], ssum = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          b[j] = hist[lane * 8 + j];
+          ssum += b[j];
         }
-        s_remaining = rem;
-        s_prefix = prefix | (static_cast<uint32_t>(d) << shift);
+        int suf = ssum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_down_sync(0xffffffffu, suf, o);
+          if (lane + o < 32) suf += v;
+        }
+        int suf_next = __shfl_down_sync(0xffffffffu, suf, 1);
+        if (lane == 31) suf_next = 0;
+        if (suf >= rem && suf_next < rem) {
+          int r = rem - suf_next, d = 0;
+          bool found = false;
+#pragma unroll
+          for (int j = 7; j >= 0; --j) {
+            if (!found) {
+              if (b[j] >= r || j == 0) {
+                d = j;
+                found = true;
+              } else {
+                r -= b[j];
+              }
+            }
+          }
+          s_remaining = r;
+          s_prefix = prefix | (static_cast<uint32_t>(lane * 8 + d) << shift);
+        }
       }
       __syncthreads();
       prefix = s_prefix;

@@ -231,33 +231,46 @@ __global__ void __launch_bounds__(kMlaThreads) sparse_mla_kernel(const MlaParams
   }
 }
 
-// Merge the chunks: o = sum_i exp(lse_i - lse) * o_i.   grid = (heads, tokens), block = 128.
+// Merge the chunks: o = sum_i exp(lse_i - lse) * o_i.   grid = (heads, tokens), block = 128; n_splits <= 64.
 __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float* __restrict__ o_acc,
                                                                  const float* __restrict__ lse_acc, int n_splits,
                                                                  __nv_bfloat16* __restrict__ out,
                                                                  float* __restrict__ lse_out) {
+  __shared__ float s_w[64];
+  __shared__ float s_den, s_mx;
   const int head = blockIdx.x, tok = blockIdx.y, heads = gridDim.x;
   const long long th = static_cast<long long>(tok) * heads + head;
-  const float* lse = lse_acc + th * n_splits;
-  float mx = -INFINITY;
-  for (int i = 0; i < n_splits; ++i) mx = fmaxf(mx, lse[i]);
-  float den = 0.f;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  if (mx != -INFINITY) {
-    for (int i = 0; i < n_splits; ++i) {
-      const float wgt = expf(lse[i] - mx);
-      if (wgt == 0.f) continue;
-      den += wgt;
-      const float4 v = *reinterpret_cast<const float4*>(o_acc + (th * n_splits + i) * kMlaDV + threadIdx.x * 4);
-      acc[0] += wgt * v.x; acc[1] += wgt * v.y; acc[2] += wgt * v.z; acc[3] += wgt * v.w;
+  if (threadIdx.x < 32) {
+    // weights of all chunks, computed once by the first warp
+    const int lane = threadIdx.x;
+    const float l0 = lane < n_splits ? lse_acc[th * n_splits + lane] : -INFINITY;
+    const float l1 = lane + 32 < n_splits ? lse_acc[th * n_splits + lane + 32] : -INFINITY;
+    const float mx = warp_max(fmaxf(l0, l1));
+    const float w0 = mx == -INFINITY ? 0.f : expf(l0 - mx), w1 = mx == -INFINITY ? 0.f : expf(l1 - mx);
+    const float den = warp_sum(w0 + w1);
+    s_w[lane] = w0;
+    s_w[lane + 32] = w1;
+    if (lane == 0) {
+      s_den = den;
+      s_mx = mx;
     }
   }
+  __syncthreads();
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const float* src = o_acc + th * n_splits * kMlaDV + threadIdx.x * 4;
+#pragma unroll 8
+  for (int i = 0; i < n_splits; ++i) {
+    const float4 v = __ldcs(reinterpret_cast<const float4*>(src + static_cast<long long>(i) * kMlaDV));
+    const float wgt = s_w[i];
+    acc[0] += wgt * v.x; acc[1] += wgt * v.y; acc[2] += wgt * v.z; acc[3] += wgt * v.w;
+  }
+  const float den = s_den;
   const float inv = den > 0.f ? 1.f / den : 0.f;
   uint2 o2;
   o2.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
   o2.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
   *reinterpret_cast<uint2*>(out + th * kMlaDV + threadIdx.x * 4) = o2;
-  if (threadIdx.x == 0 && lse_out != nullptr) lse_out[th] = mx != -INFINITY ? mx + logf(den) : -INFINITY;
+  if (threadIdx.x == 0 && lse_out != nullptr) lse_out[th] = den > 0.f ? s_mx + logf(den) : -INFINITY;
 }
 
 }  // namespace tb

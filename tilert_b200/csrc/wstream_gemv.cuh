@@ -49,9 +49,22 @@ struct AllReduce {
   AllReduceState* state[8];   // state[p]: rank p's endpoint state (state[rank] is local memory)
 };
 
+// Where the activations of a launch come from.
+enum XMode : int {
+  X_PACKED = 0,  // X blocks prepared beforehand in global memory (bulk-copied with the weights)
+  X_BF16 = 1,    // bf16 vectors in global memory; a converter warp normalises (optional RMSNorm),
+                 // splits them into two e4m3 terms and writes the X block of each stage itself
+};
+
 struct GemvParams {
   const uint8_t* w;
-  const uint8_t* x;
+  const uint8_t* x;              // X_PACKED: packed blocks
+  int x_mode;
+  const __nv_bfloat16* xb;       // X_BF16: [tokens, n_xsegs * n_kb * 128] bf16
+  long long xb_stride;           // elements between tokens
+  const float* gamma;            // X_BF16: optional RMSNorm gain over the whole vector (n_kb * 128 long)
+  float eps;
+  const float* seg_scale;        // X_BF16: optional [tokens, n_kb / kb_per_kseg] multipliers (routing weights)
   int n_tiles;
   int n_kb;
   const int* nseg_ids;
@@ -78,7 +91,7 @@ struct GemvParams {
 
 constexpr int kGemvStages = 12;
 constexpr int kGemvConsumerWarps = 8;
-constexpr int kGemvThreads = (kGemvConsumerWarps + 1) * 32;
+constexpr int kGemvThreads = (kGemvConsumerWarps + 2) * 32;  // + weight producer warp + activation converter warp
 constexpr int kGemvSmemBytes = kGemvStages * TB_STAGE_BYTES + 2 * kGemvStages * 8 + 64;
 
 __device__ __forceinline__ long long gemv_range_begin(long long units, int grid, int cta) {
@@ -162,7 +175,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kGemvStages; ++s) {
-      mbar_init(&full[s], 1);
+      mbar_init(&full[s], p.x_mode == X_BF16 ? 2 : 1);  // producer (+ converter) arrive once per use
       mbar_init(&empty[s], kGemvConsumerWarps);
     }
     *cta_error = 0;
@@ -202,9 +215,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         const int xseg = p.tiles_per_xseg > 0 ? t / p.tiles_per_xseg : 0;
         const uint8_t* xsrc = p.x + (static_cast<long long>(xseg) * p.n_kb + kb) * TB_XBLK_BYTES;
         uint8_t* dst = smem + s * TB_STAGE_BYTES;
-        mbar_expect_tx(&full[s], TB_STAGE_BYTES);
-        bulk_g2s_stream(dst, wsrc, TB_WBLK_BYTES, &full[s], pol);
-        bulk_g2s(dst + TB_WBLK_BYTES, xsrc, TB_XBLK_BYTES, &full[s]);
+        if (p.x_mode == X_PACKED) {
+          mbar_expect_tx(&full[s], TB_STAGE_BYTES);
+          bulk_g2s_stream(dst, wsrc, TB_WBLK_BYTES, &full[s], pol);
+          bulk_g2s(dst + TB_WBLK_BYTES, xsrc, TB_XBLK_BYTES, &full[s]);
+        } else {
+          mbar_expect_tx(&full[s], TB_WBLK_BYTES);
+          bulk_g2s_stream(dst, wsrc, TB_WBLK_BYTES, &full[s], pol);
+        }
         ++issued;
       }
       // Do not leave the CTA while copies may still be landing in its shared memory: wait
@@ -215,6 +233,111 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           const uint32_t last_use = static_cast<uint32_t>((issued - 1 - s) / kGemvStages);
           mbar_wait(&full[s], last_use & 1);
         }
+      }
+    }
+  } else if (warp == kGemvConsumerWarps + 1) {
+    // ------------------------------------------------- activation converter (X_BF16 only)
+    if (p.x_mode == X_BF16 && u0 < u1) {
+      const int ntok = p.n_tokens;
+      float rinv[4] = {1.f, 1.f, 1.f, 1.f};
+      if (p.gamma != nullptr) {
+        // RMSNorm statistics of the whole vector, once per CTA (overlaps the ring's first fills)
+        float ss[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int kb = 0; kb < p.n_kb; ++kb) {
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            if (t < ntok) {
+              const uint2 raw = *reinterpret_cast<const uint2*>(p.xb + t * p.xb_stride + kb * TB_KBLOCK + lane * 4);
+              const float a0 = __uint_as_float(raw.x << 16), a1 = __uint_as_float(raw.x & 0xffff0000u);
+              const float a2 = __uint_as_float(raw.y << 16), a3 = __uint_as_float(raw.y & 0xffff0000u);
+              ss[t] += a0 * a0 + a1 * a1 + a2 * a2 + a3 * a3;
+            }
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          rinv[t] = rsqrtf(warp_sum(ss[t]) / static_cast<float>(p.n_kb * TB_KBLOCK) + p.eps);
+      }
+      const long long xk = static_cast<long long>(p.n_kb) * TB_KBLOCK;  // activations per x segment
+      // software pipeline: the raw activations of unit u + 2 are requested before unit u is converted
+      // (three statically named register sets, rotated each iteration)
+      struct XRaw {
+        uint2 v[4];
+        float4 g;
+      };
+      auto fetch = [&](long long u) {
+        XRaw o;
+        const int t = static_cast<int>(u / p.n_kb), kb = static_cast<int>(u % p.n_kb);
+        const int xseg = p.tiles_per_xseg > 0 ? t / p.tiles_per_xseg : 0;
+        const long long off = xseg * xk + static_cast<long long>(kb) * TB_KBLOCK + lane * 4;
+#pragma unroll
+        for (int tk = 0; tk < 4; ++tk)
+          o.v[tk] = tk < ntok ? *reinterpret_cast<const uint2*>(p.xb + tk * p.xb_stride + off) : make_uint2(0, 0);
+        o.g = p.gamma != nullptr ? *reinterpret_cast<const float4*>(p.gamma + kb * TB_KBLOCK + lane * 4)
+                                 : make_float4(1.f, 1.f, 1.f, 1.f);
+        return o;
+      };
+      XRaw x0 = fetch(u0), x1 = x0, x2 = x0;
+      if (u0 + 1 < u1) x1 = fetch(u0 + 1);
+      for (long long u = u0; u < u1; ++u) {
+        const long long i = u - u0;
+        const int s = static_cast<int>(i % kGemvStages);
+        const uint32_t use = static_cast<uint32_t>(i / kGemvStages);
+        if (u + 2 < u1) x2 = fetch(u + 2);
+        if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1)) {
+          set_status(p.status, ST_WAIT_EMPTY_TIMEOUT);
+          *cta_error = 1;
+          break;
+        }
+        uint8_t* blk = smem + s * TB_STAGE_BYTES + TB_WBLK_BYTES;
+        const int kb = static_cast<int>(u % p.n_kb);
+        const int c = lane >> 3, r = (lane >> 2) & 1, q4 = lane & 3;
+        const float g4[4] = {x0.g.x, x0.g.y, x0.g.z, x0.g.w};
+#pragma unroll
+        for (int tk = 0; tk < 4; ++tk) {
+          if (tk < ntok) {
+            const uint2 rw = x0.v[tk];
+            float x4[4] = {__uint_as_float(rw.x << 16), __uint_as_float(rw.x & 0xffff0000u),
+                           __uint_as_float(rw.y << 16), __uint_as_float(rw.y & 0xffff0000u)};
+            if (p.gamma != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) x4[j] = bf2f(f2bf(x4[j] * rinv[tk] * g4[j]));
+            }
+            float amax = fmaxf(fmaxf(fabsf(x4[0]), fabsf(x4[1])), fmaxf(fabsf(x4[2]), fabsf(x4[3])));
+            amax = warp_max(amax);
+            // smallest power of two s_hi with amax / s_hi <= 448; 1 for an all-zero block
+            float s_hi = 1.f;
+            if (amax > 0.f) {
+              int e;
+              const float m = frexpf(amax * (1.0f / 448.0f), &e);
+              s_hi = ldexpf(1.f, m == 0.5f ? e - 1 : e);
+            }
+            const float s_lo = s_hi * 0.0625f;
+            uint32_t whi = 0, wlo = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint8_t h = f32_to_e4m3(x4[j] / s_hi);
+              const float rr = x4[j] - e4m3_to_f32(h) * s_hi;
+              const uint8_t l = f32_to_e4m3(rr / s_lo);
+              whi |= static_cast<uint32_t>(h) << (8 * j);
+              wlo |= static_cast<uint32_t>(l) << (8 * j);
+            }
+            *reinterpret_cast<uint32_t*>(blk + (c * 32 + (2 * tk) * 4 + q4) * 8 + 4 * r) = whi;
+            *reinterpret_cast<uint32_t*>(blk + (c * 32 + (2 * tk + 1) * 4 + q4) * 8 + 4 * r) = wlo;
+            if (lane == 0) {
+              float mlt = 1.f;
+              if (p.seg_scale != nullptr) mlt = p.seg_scale[tk * (p.n_kb / p.kb_per_kseg) + kb / p.kb_per_kseg];
+              float* cs = reinterpret_cast<float*>(blk + TB_XBLK_DATA);
+              cs[2 * tk] = s_hi * mlt;
+              cs[2 * tk + 1] = s_lo * mlt;
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[s]);
+        x0 = x1;
+        x1 = x2;
       }
     }
   } else {
@@ -237,15 +360,25 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       }
       const uint8_t* sw = smem + s * TB_STAGE_BYTES;
       const uint8_t* sx = sw + TB_WBLK_BYTES;
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      // four independent MMAs (one per 32-wide k chunk), summed afterwards: no dependent MMA chain
+      float acc4[4][4];
+      uint4 a[4];
+      uint2 b[4];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const uint4 a = *reinterpret_cast<const uint4*>(sw + ((warp * 4 + c) * 32 + lane) * 16);
-        const uint2 b = *reinterpret_cast<const uint2*>(sx + (c * 32 + lane) * 8);
-        mma_e4m3_16832(acc, a, b);
+        a[c] = *reinterpret_cast<const uint4*>(sw + ((warp * 4 + c) * 32 + lane) * 16);
+        b[c] = *reinterpret_cast<const uint2*>(sx + (c * 32 + lane) * 8);
       }
       const float2 ws = *reinterpret_cast<const float2*>(sw + TB_WBLK_DATA + warp * 8);
       const float2 cs = *reinterpret_cast<const float2*>(sx + TB_XBLK_DATA + q * 8);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        acc4[c][0] = acc4[c][1] = acc4[c][2] = acc4[c][3] = 0.f;
+        mma_e4m3_16832(acc4[c], a[c], b[c]);
+      }
+      float acc[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[j] = (acc4[0][j] + acc4[1][j]) + (acc4[2][j] + acc4[3][j]);
       out[0] = fmaf(acc[0], ws.x * cs.x, out[0]);
       out[1] = fmaf(acc[1], ws.x * cs.y, out[1]);
       out[2] = fmaf(acc[2], ws.y * cs.x, out[2]);

@@ -156,8 +156,6 @@ class DecoderLayer:
         self.kv_cache = z(1, cache_len, a.kv_lora_rank)
         self.pe_cache = z(1, cache_len, a.qk_rope_head_dim)
         self.ki_cache = z(1, cache_len, a.index_head_dim)
-        self.x_norm = z(1, s, a.dim)
-        self.xp_a = ops.new_xpack(a.dim, dev)
         self.q_a = z(1, s, a.q_lora_rank)
         self.kv = z(1, s, a.kv_lora_rank)
         self.ki = z(1, s, a.index_head_dim)
@@ -177,7 +175,6 @@ class DecoderLayer:
         self.o = z(1, s, self.hl, a.v_head_dim)
         self.h = z(1, s, a.dim)
         self.h_norm = z(1, s, a.dim)
-        self.xp_h = ops.new_xpack(a.dim, dev)
         self.out = z(1, s, a.dim)
         if weights.dense:
             self.ffn_hidden = z(1, s, weights.inter_local)
@@ -190,6 +187,10 @@ class DecoderLayer:
             self.slot_w = z(s, n_slots, dtype=F32)
             self.ffn_hidden = z(1, s, n_slots, weights.inter_local)
         self.forced_scores: torch.Tensor | None = None
+        # When set ([1, S, topk] int32), replaces the indexer's selection before attention -- the role of
+        # the reference's receive_selected_token_ids (ops/receive_selected_token_ids.py:10-35), used by
+        # parity tests to separate the discrete selection from the floating-point path.
+        self.injected_sel: torch.Tensor | None = None
         self.scale = softmax_scale(a)
 
     def forward(self, x: torch.Tensor, cur_pos: torch.Tensor, freqs: torch.Tensor, n_keys: int) -> torch.Tensor:
@@ -198,10 +199,9 @@ class DecoderLayer:
         a, w = self.args, self.w
         s = x.shape[1]
         v = lambda t: t[:, :s]  # noqa: E731
-        ops.rmsnorm_quant(x, w.in_norm, v(self.x_norm), None, None, eps=a.eps, xpack=self.xp_a)
-        ops.projx_wqkva_packed(self.xp_a, 2, w.w_qkva, s, a.dim, a.q_lora_rank, a.kv_lora_rank, a.qk_rope_head_dim,
-                               a.index_head_dim, cur_pos, v(self.q_a), v(self.kv), self.pe_cache, v(self.ki))
-        ops.projx_wis(v(self.x_norm), w.wis, v(self.idx_w))
+        ops.rmsnorm_projx_wqkva(x, w.in_norm, w.w_qkva, cur_pos, v(self.q_a), v(self.kv), self.pe_cache, v(self.ki),
+                                eps=a.eps)
+        ops.projx_wis(x, w.wis, v(self.idx_w), gamma=w.in_norm, eps=a.eps)
         ops.rmsnorm_kv(v(self.kv), w.kv_norm, cur_pos, self.kv_cache, eps=a.eps)
         ops.rmsnorm_proj_q(v(self.q_a), w.q_norm, w.w_qb, v(self.q_nope), v(self.q_pe), v(self.iq), eps=a.eps)
         ops.qkv_rope(v(self.q_pe), self.pe_cache, freqs, cur_pos)
@@ -210,6 +210,8 @@ class DecoderLayer:
                                   rope=a.qk_rope_head_dim)
         ops.sparse_index_topk(v(self.iq_rt), self.ki_cache, v(self.idx_w), self.idx_logits, v(self.sel), cur_pos,
                               n_keys=n_keys)
+        if self.injected_sel is not None:
+            v(self.sel).copy_(self.injected_sel)
         ops.projq_wqb(v(self.q_nope), w.w_absorb, None, v(self.q_lat))
         ops.flash_sparse_mla(v(self.q_lat), v(self.q_pe), self.kv_cache, self.pe_cache, v(self.sel), cur_pos,
                              v(self.o_lat), softmax_scale=self.scale, split_size=64, out_acc=self.o_acc,
@@ -220,10 +222,9 @@ class DecoderLayer:
             ops.rmsnorm_up_gate_silu(v(self.h), w.post_norm, w.w_gu, v(self.ffn_hidden), eps=a.eps)
             ops.down_allreduce(v(self.ffn_hidden), w.w_down, None, v(self.h), 0, v(self.out), comm=self.comm)
         else:
-            ops.rmsnorm_quant(v(self.h), w.post_norm, v(self.h_norm), None, None, eps=a.eps, xpack=self.xp_h)
-            ops.rmsnorm_expert_proj(v(self.h_norm), None, w.router, v(self.scores), None)
+            ops.rmsnorm_expert_proj(v(self.h), w.post_norm, w.router, v(self.scores), v(self.h_norm), eps=a.eps)
             scores = v(self.scores) if self.forced_scores is None else self.forced_scores
-            ops.expert_select_up_gate_silu(self.xp_h, scores, w.router_bias, w.w_gu, v(self.ffn_hidden), v(self.probs),
+            ops.expert_select_up_gate_silu(v(self.h_norm), scores, w.router_bias, w.w_gu, v(self.ffn_hidden), v(self.probs),
                                            v(self.eidx), dim=a.dim, n_groups=a.n_expert_groups,
                                            n_limited_groups=a.n_limited_groups, route_scale=a.route_scale,
                                            slot_ids=self.slot_ids, slot_w=self.slot_w)

@@ -102,6 +102,25 @@ def projx_wqkva_packed(xpack, cols_per_token, w_packed, tokens, dim, q_lora, kv_
                                               _p(pe_cache), _p(ki_out), _stream()))
 
 
+def rmsnorm_projx_wqkva(x, gamma, w_packed, cur_pos, q_out, kv_out, pe_cache, ki_out=None, *, eps=1e-6):
+    """RMSNormProjxWqkva.tilert_forward (ops/rmsnorm_projx_wqkva.py:473-509) in one launch: RMSNorm,
+    q_a / kv_a / k_pe (into ``pe_cache[cur_pos]``) and, when the packed weight carries them, the indexer
+    key rows."""
+    _need(x, BF16, "x")
+    _need(gamma, F32, "gamma")
+    _need(cur_pos, I32, "cur_pos")
+    _need(q_out, BF16, "q_out")
+    _need(kv_out, BF16, "kv_out")
+    _need(pe_cache, BF16, "pe_cache")
+    _need(ki_out, BF16, "ki_out", optional=True)
+    tokens, dim = x.shape[-2], x.shape[-1]
+    ki_dim = 0 if ki_out is None else ki_out.shape[-1]
+    _tb.check(_tb.lib().tilert_rmsnorm_projx_wqkva_op(_ctx(x), _p(x), _p(gamma), eps, _p(w_packed), tokens, dim,
+                                                      q_out.shape[-1], kv_out.shape[-1], pe_cache.shape[-1], ki_dim,
+                                                      _p(cur_pos), _p(q_out), _p(kv_out), _p(pe_cache), _p(ki_out),
+                                                      _stream()))
+
+
 def projx_wqkva(x_in, x_scale, w_packed, cur_pos, q_out, kv_out, pe_cache, profile_logs=None, *,
                 model_arch="deepseek_v3_2", ki_out=None):
     """ops/projx_wqkva.py:22-48: quantised activations (e4m3 + 1x128 f32 scales) in, q / kv out, k_pe
@@ -187,11 +206,12 @@ def rmsnorm_expert_proj(x, gamma, w_gate, scores_out, hidden_out, profile_logs=N
                                                       _p(scores_out), _p(hidden_out), _stream()))
 
 
-def expert_select_up_gate_silu(hidden_xpack, scores, bias, w_packed, hidden_out, probs_out, idx_out,
+def expert_select_up_gate_silu(hidden_in, scores, bias, w_packed, hidden_out, probs_out, idx_out,
                                profile_logs=None, *, model_arch="deepseek_v3_2", dim, n_groups, n_limited_groups,
                                route_scale, slot_ids=None, slot_w=None):
-    """ops/expert_sel_up_gate_silu.py:23-48.  ``hidden_xpack`` is the packed post-attention norm
-    output; ``w_packed`` is [n_experts + 1, tiles, kblocks, 16448] with the shared expert last."""
+    """ops/expert_sel_up_gate_silu.py:23-48.  ``hidden_in`` is the bf16 post-attention norm output;
+    ``w_packed`` is [n_experts + 1, tiles, kblocks, 16448] with the shared expert last."""
+    _need(hidden_in, BF16, "hidden_in")
     _need(scores, F32, "scores")
     _need(bias, F32, "bias", optional=True)
     _need(hidden_out, BF16, "hidden_out")
@@ -203,7 +223,7 @@ def expert_select_up_gate_silu(hidden_xpack, scores, bias, w_packed, hidden_out,
     inter = hidden_out.shape[-1]
     stride = w_packed.stride(0) * w_packed.element_size()
     _tb.check(_tb.lib().tilert_expert_select_up_gate_silu_op(
-        _ctx(scores), _p(hidden_xpack), _p(scores), _p(bias), _p(w_packed), stride, tokens, dim, inter, n_experts,
+        _ctx(scores), _p(hidden_in), _p(scores), _p(bias), _p(w_packed), stride, tokens, dim, inter, n_experts,
         n_groups, n_limited_groups, top_k, route_scale, _p(hidden_out), _p(probs_out), _p(idx_out), _p(slot_ids),
         _p(slot_w), _stream()))
 
@@ -243,13 +263,15 @@ def down_allreduce(vec_in, w_packed, w_scale, x_in, flag, hidden_out, profile_lo
 
 
 # ------------------------------------------------------------------------ bf16 products
-def projx_wis(x, w, out, profile_logs=None, *, model_arch="deepseek_v3_2"):
-    """ops/projx_wis.py:21-40: indexer head weights, bf16 weight [heads, dim]."""
+def projx_wis(x, w, out, profile_logs=None, *, model_arch="deepseek_v3_2", gamma=None, eps=1e-6):
+    """ops/projx_wis.py:21-40: indexer head weights, bf16 weight [heads, dim].  With ``gamma`` the input
+    is the raw hidden state and the RMSNorm runs inside the kernel."""
     _need(x, BF16, "x")
     _need(w, BF16, "w")
     _need(out, BF16, "out")
-    _tb.check(_tb.lib().tilert_proj_w_op(_ctx(x), _p(x), _p(w), x.shape[-2], w.shape[0], w.shape[1], _p(out),
-                                         _stream()))
+    _need(gamma, F32, "gamma", optional=True)
+    _tb.check(_tb.lib().tilert_proj_w_op(_ctx(x), _p(x), _p(gamma), eps, _p(w), x.shape[-2], w.shape[0], w.shape[1],
+                                         _p(out), _stream()))
 
 
 def rmsnorm_head_proj(x, gamma, w, x_norm_out, logits_out, profile_logs=None, *, model_arch="deepseek_v3_2",
