@@ -122,13 +122,13 @@ def test_toy_model_first_steps(tb, use_graph):
 def test_toy_model_greedy_decode_matches_oracle(tb):
     """The toy workload: 1024 random prompt ids (seed 1), 64 greedy steps.
 
-    Two discrete decisions sit on the path -- the indexer's top-256 key selection and the arg-max over
-    the vocabulary -- and both amplify last-bit differences between two correct bf16 pipelines: with
+    Three discrete decisions sit on the path -- the indexer's top-256 key selection, the router's
+    top-4 expert choice and the arg-max over the vocabulary -- and all amplify last-bit differences between two correct bf16 pipelines: with
     random weights one swapped key at the 256th score changes the attention output by several per
     cent, and the top-2 logit margin is often smaller than the logits' numerical noise.  The check is
     therefore split the way the workload definition splits it:
-      * floating-point path: the device model is fed the oracle's tokens and the oracle's selected key
-        sets; at each of the 64 generated positions its logits must be within rel-L2 2e-2 of the
+      * floating-point path: the device model is fed the oracle's tokens, selected key sets and router
+        scores (the device then routes on identical scores); at each of the 64 generated positions its logits must be within rel-L2 2e-2 of the
         oracle's, every layer output must reach cosine 0.999, and its arg-max must equal the oracle's
         token unless the oracle's top-2 margin is below the measured logit error (a numerical tie);
       * selection: given identical scores the top-k is bit-exact (tests/test_gpu_ops.py); here the
@@ -145,12 +145,13 @@ def test_toy_model_greedy_decode_matches_oracle(tb):
 
     # oracle, free running, keeping each step's selections and layer outputs
     ref = om.Model(a, sd, cache_len=cache_len)
-    fed, sels, outs, rlogits, rtoks = list(prompt), [], [], [], []
+    fed, sels, routes, outs, rlogits, rtoks = list(prompt), [], [], [], [], []
     i = 0
     while i < len(fed):
         traces = []
         nxt, lg = ref.step(fed[i], traces)
         sels.append([t["sel"].clone() for t in traces])
+        routes.append([t.get("router_scores") for t in traces])
         if i >= n_prompt - 1:
             outs.append([t["out"].clone() for t in traces])
             rlogits.append(lg)
@@ -168,6 +169,8 @@ def test_toy_model_greedy_decode_matches_oracle(tb):
     for pos, tok in enumerate(fed):
         for li, layer in enumerate(dev.layers):
             layer.injected_sel = sels[pos][li].cuda()
+            if routes[pos][li] is not None:
+                layer.forced_scores = routes[pos][li].float().cuda()
         dev.forward(tok, pos)
         if pos >= n_prompt - 1:
             torch.cuda.synchronize()

@@ -579,7 +579,7 @@ int launch_gemv_bf16(TbContext* ctx, GemvBf16Params& p, cudaStream_t st) {
     attr_set = true;
   }
   TB_REQUIRE(smem <= 200 * 1024);
-  if (p.n <= 2048) {
+  if (p.n <= 2048 && p.k <= 8192) {
     static bool attr2_set = false;
     if (!attr2_set) {
       TB_CUDA(cudaFuncSetAttribute(gemv_bf16_ksplit_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));

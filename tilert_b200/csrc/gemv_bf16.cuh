@@ -151,6 +151,14 @@ __global__ void __launch_bounds__(kGemvBf16SmallThreads) gemv_bf16_ksplit_kernel
     }
   }
   if (p.gamma != nullptr) {
+    // gains of this thread's elements (k <= 8192: at most 8 groups of 4), requested before the
+    // reduction so their latency hides behind it
+    float4 gm[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int i = (it * kGemvBf16SmallThreads + threadIdx.x) * 4;
+      gm[it] = i < p.k ? __ldg(reinterpret_cast<const float4*>(p.gamma + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 #pragma unroll
     for (int t = 0; t < TOK; ++t) {
       const float s = warp_sum(ss[t]);
@@ -164,14 +172,27 @@ __global__ void __launch_bounds__(kGemvBf16SmallThreads) gemv_bf16_ksplit_kernel
       tot = warp_sum(tot);
       rinv[t] = rsqrtf(tot / static_cast<float>(p.k) + p.eps);
     }
-    for (int i = threadIdx.x; i < p.k; i += kGemvBf16SmallThreads) {
-      const float g = p.gamma[i];
 #pragma unroll
-      for (int t = 0; t < TOK; ++t) {
-        float v = xs[t * p.k + i] * rinv[t] * g;
-        if (p.round_norm_bf16) v = bf2f(f2bf(v));
-        xs[t * p.k + i] = v;
-        if (p.xnorm_out != nullptr && blockIdx.x == 0 && t < p.n_tokens) p.xnorm_out[t * p.xnorm_stride + i] = f2bf(v);
+    for (int it = 0; it < 8; ++it) {
+      const int i = (it * kGemvBf16SmallThreads + threadIdx.x) * 4;
+      if (i < p.k) {
+        const float g4[4] = {gm[it].x, gm[it].y, gm[it].z, gm[it].w};
+#pragma unroll
+        for (int t = 0; t < TOK; ++t) {
+          float4 xv = *reinterpret_cast<float4*>(&xs[t * p.k + i]);
+          float o[4] = {xv.x * rinv[t] * g4[0], xv.y * rinv[t] * g4[1], xv.z * rinv[t] * g4[2], xv.w * rinv[t] * g4[3]};
+          if (p.round_norm_bf16) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o[j] = bf2f(f2bf(o[j]));
+          }
+          *reinterpret_cast<float4*>(&xs[t * p.k + i]) = make_float4(o[0], o[1], o[2], o[3]);
+          if (p.xnorm_out != nullptr && blockIdx.x == 0 && t < p.n_tokens) {
+            uint2 ob;
+            ob.x = pack_bf16x2(o[0], o[1]);
+            ob.y = pack_bf16x2(o[2], o[3]);
+            *reinterpret_cast<uint2*>(p.xnorm_out + t * p.xnorm_stride + i) = ob;
+          }
+        }
       }
     }
   }

@@ -91,7 +91,7 @@ struct GemvParams {
 
 constexpr int kGemvStages = 12;
 constexpr int kGemvConsumerWarps = 8;
-constexpr int kGemvThreads = (kGemvConsumerWarps + 2) * 32;  // + weight producer warp + activation converter warp
+constexpr int kGemvThreads = (kGemvConsumerWarps + 3) * 32;  // + weight producer warp + two activation converter warps
 constexpr int kGemvSmemBytes = kGemvStages * TB_STAGE_BYTES + 2 * kGemvStages * 8 + 64;
 
 __device__ __forceinline__ long long gemv_range_begin(long long units, int grid, int cta) {
@@ -235,13 +235,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         }
       }
     }
-  } else if (warp == kGemvConsumerWarps + 1) {
-    // ------------------------------------------------- activation converter (X_BF16 only)
-    if (p.x_mode == X_BF16 && u0 < u1) {
+  } else if (warp > kGemvConsumerWarps) {
+    // ------------------------------------------------- activation converters (X_BF16 only)
+    // Two warps take alternate units.  Each converts the 128 activations of its unit, for every
+    // token, into the two-term e4m3 X block of the stage: power-of-two scales, so the scaling is a
+    // multiplication and the residual x - hi*s is exact.
+    const int cw = warp - (kGemvConsumerWarps + 1);  // 0 or 1
+    if (p.x_mode == X_BF16 && u0 + cw < u1) {
       const int ntok = p.n_tokens;
       float rinv[4] = {1.f, 1.f, 1.f, 1.f};
       if (p.gamma != nullptr) {
-        // RMSNorm statistics of the whole vector, once per CTA (overlaps the ring's first fills)
+        // RMSNorm statistics of the whole vector, once per warp (overlaps the ring's first fills)
         float ss[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
         for (int kb = 0; kb < p.n_kb; ++kb) {
@@ -260,8 +264,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           rinv[t] = rsqrtf(warp_sum(ss[t]) / static_cast<float>(p.n_kb * TB_KBLOCK) + p.eps);
       }
       const long long xk = static_cast<long long>(p.n_kb) * TB_KBLOCK;  // activations per x segment
-      // software pipeline: the raw activations of unit u + 2 are requested before unit u is converted
-      // (three statically named register sets, rotated each iteration)
       struct XRaw {
         uint2 v[4];
         float4 g;
@@ -278,13 +280,16 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
                                  : make_float4(1.f, 1.f, 1.f, 1.f);
         return o;
       };
-      XRaw x0 = fetch(u0), x1 = x0, x2 = x0;
-      if (u0 + 1 < u1) x1 = fetch(u0 + 1);
-      for (long long u = u0; u < u1; ++u) {
+      // software pipeline over this warp's units (u, u+2, u+4, ...): two requests in flight
+      const long long ub = u0 + cw;
+      XRaw x0 = fetch(ub), x1 = x0, x2 = x0;
+      if (ub + 2 < u1) x1 = fetch(ub + 2);
+      const int c = lane >> 3, r = (lane >> 2) & 1, q4 = lane & 3;
+      for (long long u = ub; u < u1; u += 2) {
         const long long i = u - u0;
         const int s = static_cast<int>(i % kGemvStages);
         const uint32_t use = static_cast<uint32_t>(i / kGemvStages);
-        if (u + 2 < u1) x2 = fetch(u + 2);
+        if (u + 4 < u1) x2 = fetch(u + 4);
         if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1)) {
           set_status(p.status, ST_WAIT_EMPTY_TIMEOUT);
           *cta_error = 1;
@@ -292,7 +297,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         }
         uint8_t* blk = smem + s * TB_STAGE_BYTES + TB_WBLK_BYTES;
         const int kb = static_cast<int>(u % p.n_kb);
-        const int c = lane >> 3, r = (lane >> 2) & 1, q4 = lane & 3;
         const float g4[4] = {x0.g.x, x0.g.y, x0.g.z, x0.g.w};
 #pragma unroll
         for (int tk = 0; tk < 4; ++tk) {
@@ -306,31 +310,36 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
             }
             float amax = fmaxf(fmaxf(fabsf(x4[0]), fabsf(x4[1])), fmaxf(fabsf(x4[2]), fabsf(x4[3])));
             amax = warp_max(amax);
-            // smallest power of two s_hi with amax / s_hi <= 448; 1 for an all-zero block
-            float s_hi = 1.f;
-            if (amax > 0.f) {
-              int e;
-              const float m = frexpf(amax * (1.0f / 448.0f), &e);
-              s_hi = ldexpf(1.f, m == 0.5f ? e - 1 : e);
-            }
-            const float s_lo = s_hi * 0.0625f;
-            uint32_t whi = 0, wlo = 0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint8_t h = f32_to_e4m3(x4[j] / s_hi);
-              const float rr = x4[j] - e4m3_to_f32(h) * s_hi;
-              const uint8_t l = f32_to_e4m3(rr / s_lo);
-              whi |= static_cast<uint32_t>(h) << (8 * j);
-              wlo |= static_cast<uint32_t>(l) << (8 * j);
-            }
+            // s_hi = 2^e: the power of two at or just above amax / 448 (at most one step higher when the
+            // product below rounds up); exponent clamped so that s_hi / 16 and 1 / s_hi stay normal
+            const uint32_t tb = __float_as_uint(amax * (1.0f / 448.0f));
+            int e = static_cast<int>(tb >> 23) + ((tb & 0x7fffffu) != 0u ? 1 : 0);
+            e = amax > 0.f ? min(max(e, 16), 240) : 127;
+            const float s_hi = __uint_as_float(static_cast<uint32_t>(e) << 23);
+            const float inv_hi = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);
+            const float s_lo = s_hi * 0.0625f, inv_lo = inv_hi * 16.f;
+            const __nv_fp8x2_storage_t h01 =
+                __nv_cvt_float2_to_fp8x2(make_float2(x4[0] * inv_hi, x4[1] * inv_hi), __NV_SATFINITE, __NV_E4M3);
+            const __nv_fp8x2_storage_t h23 =
+                __nv_cvt_float2_to_fp8x2(make_float2(x4[2] * inv_hi, x4[3] * inv_hi), __NV_SATFINITE, __NV_E4M3);
+            const __half2_raw hr01 = __nv_cvt_fp8x2_to_halfraw2(h01, __NV_E4M3);
+            const __half2_raw hr23 = __nv_cvt_fp8x2_to_halfraw2(h23, __NV_E4M3);
+            const float2 hf01 = __half22float2(*reinterpret_cast<const __half2*>(&hr01));
+            const float2 hf23 = __half22float2(*reinterpret_cast<const __half2*>(&hr23));
+            const float r0 = fmaf(-hf01.x, s_hi, x4[0]), r1 = fmaf(-hf01.y, s_hi, x4[1]);
+            const float r2 = fmaf(-hf23.x, s_hi, x4[2]), r3 = fmaf(-hf23.y, s_hi, x4[3]);
+            const __nv_fp8x2_storage_t l01 =
+                __nv_cvt_float2_to_fp8x2(make_float2(r0 * inv_lo, r1 * inv_lo), __NV_SATFINITE, __NV_E4M3);
+            const __nv_fp8x2_storage_t l23 =
+                __nv_cvt_float2_to_fp8x2(make_float2(r2 * inv_lo, r3 * inv_lo), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t whi = static_cast<uint32_t>(h01) | (static_cast<uint32_t>(h23) << 16);
+            const uint32_t wlo = static_cast<uint32_t>(l01) | (static_cast<uint32_t>(l23) << 16);
             *reinterpret_cast<uint32_t*>(blk + (c * 32 + (2 * tk) * 4 + q4) * 8 + 4 * r) = whi;
             *reinterpret_cast<uint32_t*>(blk + (c * 32 + (2 * tk + 1) * 4 + q4) * 8 + 4 * r) = wlo;
             if (lane == 0) {
               float mlt = 1.f;
               if (p.seg_scale != nullptr) mlt = p.seg_scale[tk * (p.n_kb / p.kb_per_kseg) + kb / p.kb_per_kseg];
-              float* cs = reinterpret_cast<float*>(blk + TB_XBLK_DATA);
-              cs[2 * tk] = s_hi * mlt;
-              cs[2 * tk + 1] = s_lo * mlt;
+              *reinterpret_cast<float2*>(blk + TB_XBLK_DATA + 8 * tk) = make_float2(s_hi * mlt, s_lo * mlt);
             }
           }
         }
