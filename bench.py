@@ -339,7 +339,7 @@ def run_profile_gemv(args) -> None:
     tilert_b200.load_backend("deepseek_v3_2")
     tilert_b200.tilert_init(0)
     dev = torch.device("cuda", 0)
-    n, k = 7168, 32768
+    n, k = 7168, args.gemv_k
     g = torch.Generator(device=dev).manual_seed(0)
     w = torch.randint(0, 120, (n // 128, k // 128, 16448), generator=g, dtype=torch.uint8, device=dev)
     w[:, :, 16384:] = 0
@@ -351,14 +351,46 @@ def run_profile_gemv(args) -> None:
     for _ in range(max(args.warmup, 1)):
         ops.unproj_o_allreduce(vec, w, None, res, 0, out)
     torch.cuda.synchronize()
+    # back-to-back launches replayed from a CUDA graph: no host launch overhead in the timed region
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(args.steps):
+            ops.unproj_o_allreduce(vec, w, None, res, 0, out)
+    graph.replay()
+    torch.cuda.synchronize()
     e0.record()
-    for _ in range(args.steps):
-        ops.unproj_o_allreduce(vec, w, None, res, 0, out)
+    graph.replay()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
-    print(json.dumps({"mode": "profile-gemv", "n": n, "k": k, "weight_bytes": w.numel(), "ms_per_launch_pair": ms,
-                      "gbs_incl_pack_launch": w.numel() / ms / 1e6, "status": tilert_b200.device_status(0)}))
+    # calibration: a plain read-only pass over 1 GiB with a library reduction
+    big = torch.empty(1 << 28, dtype=torch.int32, device=dev).fill_(1)
+    big.sum()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(5):
+        big.sum()
+    e1.record()
+    torch.cuda.synchronize()
+    read_gbs = 5 * big.numel() * 4 / (e0.elapsed_time(e1) * 1e-3) / 1e9
+    # per-CTA phase stamps of one traced launch
+    import ctypes
+    trace = torch.zeros(256, 8, dtype=torch.int64, device=dev)
+    ctx = ctypes.c_void_p(tilert_b200.tilert_init(0))
+    tilert_b200.check(tilert_b200.lib().tilert_b200_set_profile(ctx, ctypes.c_void_p(trace.data_ptr())))
+    ops.unproj_o_allreduce(vec, w, None, res, 0, out)
+    torch.cuda.synchronize()
+    tilert_b200.check(tilert_b200.lib().tilert_b200_set_profile(ctx, None))
+    tr = trace[:148].cpu().double()
+    t0 = tr[:, 0].min()
+    rel = (tr - t0) / 1e3
+    names = ["entry", "ready", "first_data", "last_unit", "tiles_done", "first_convert", "issued", "exit"]
+    phases = {nm: [round(float(rel[:, i].min()), 2), round(float(rel[:, i].median()), 2), round(float(rel[:, i].max()), 2)]
+              for i, nm in enumerate(names)}
+    print(json.dumps({"trace_us_min_med_max": phases}))
+    print(json.dumps({"mode": "profile-gemv", "n": n, "k": k, "weight_bytes": w.numel(), "ms_per_launch": ms,
+                      "gbs": w.numel() / ms / 1e6, "torch_sum_read_gbs": read_gbs,
+                      "status": tilert_b200.device_status(0)}))
 
 
 def main() -> None:
@@ -370,6 +402,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: no clock-sampling loop, no CPU baseline")
+    ap.add_argument("--gemv-k", type=int, default=32768)
     ap.add_argument("--profile-gemv", action="store_true",
                     help="run only the weight-streaming product on a 235 MB weight (small footprint for ncu)")
     args = ap.parse_args()

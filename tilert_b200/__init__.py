@@ -25,7 +25,11 @@ class TilertError(RuntimeError):
 
 
 def library_path() -> Path:
-    return Path(__file__).resolve().parent / "libtilert_b200.so"
+    """The in-tree library; ``TILERT_B200_LIB`` names another build of the same sources (tuning)."""
+    import os
+
+    override = os.environ.get("TILERT_B200_LIB")
+    return Path(override) if override else Path(__file__).resolve().parent / "libtilert_b200.so"
 
 
 def load_backend(model_type: str = "deepseek_v3_2") -> ctypes.CDLL:

@@ -22,7 +22,7 @@ _SCALARS = {
 
 
 def _ctype(decl: str):
-    decl = decl.replace("const", " ").strip()
+    decl = decl.replace("const", " ").replace("unsigned", " ").strip()
     decl = re.sub(r"\s+", " ", decl)
     if "[" in decl or "*" in decl:
         return ctypes.c_void_p  # every pointer (device or host) travels as an address

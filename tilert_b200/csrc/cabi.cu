@@ -52,6 +52,7 @@ struct TbContext {
   int* status = nullptr;
   uint8_t* xpack = nullptr;
   uint8_t* small = nullptr;
+  unsigned long long* prof = nullptr;  // caller-owned trace buffer, see tilert_b200_set_profile
 };
 
 struct TbComm {
@@ -77,11 +78,13 @@ int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
   TB_REQUIRE(p.n_tiles > 0 && p.n_kb > 0);
   TB_REQUIRE(p.n_tiles * 8 <= kMaxCounters);
   const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
+  TB_REQUIRE(units < (1ll << 30));
   int grid = ctx->num_sms < kMaxGrid ? ctx->num_sms : kMaxGrid;
   if (units < grid) grid = static_cast<int>(units);
   p.partial = ctx->partial;
   p.counters = ctx->counters;
   p.status = ctx->status;
+  p.prof = ctx->prof;
   wstream_gemv_kernel<<<grid, kGemvThreads, kGemvSmemBytes, st>>>(p);
   ++g_launches;
   TB_CUDA(cudaGetLastError());
@@ -221,6 +224,11 @@ extern "C" int tilert_b200_status(TbContext* ctx, int* status_out) {
 
 extern "C" int tilert_b200_num_sms(TbContext* ctx) { return ctx != nullptr ? ctx->num_sms : 0; }
 extern "C" long long tilert_b200_launch_count(void) { return g_launches; }
+extern "C" int tilert_b200_set_profile(TbContext* ctx, unsigned long long* trace) {
+  TB_REQUIRE(ctx != nullptr);
+  ctx->prof = trace;
+  return TB_OK;
+}
 extern "C" int tilert_b200_dev_alloc(size_t bytes, void** dev_ptr_out) {
   TB_REQUIRE(dev_ptr_out != nullptr && bytes > 0);
   TB_CUDA(cudaMalloc(dev_ptr_out, bytes));

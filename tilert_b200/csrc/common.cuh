@@ -61,15 +61,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: returns false (and the caller bails out) when the budget runs out.
+// Bounded wait: returns false (and the caller bails out) when the budget runs out.  The budget is
+// counted on the SM's cycle counter, read only after a batch of failed polls: reading %globaltimer
+// costs about as much as a whole pipeline stage, and a waiting consumer is the normal state of a
+// bandwidth-bound kernel.
+constexpr long long kWaitBudgetCycles = 4000000000ll;  // about two seconds at ~2 GHz
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
+#pragma unroll 1
+  for (int i = 0; i < 32; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
   while (true) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (globaltimer_ns() - t0 > kWaitBudgetNs) return false;
+    if (clock64() - t0 > kWaitBudgetCycles) return false;
   }
 }
 

@@ -6,11 +6,12 @@
 // HBM-bound: every weight byte is read exactly once.  One persistent CTA per SM walks a
 // contiguous range of (row tile, k block) units (stream-K).  A producer thread stages each
 // unit -- one 16448-byte W block and one 1056-byte X block -- into a shared-memory ring with
-// bulk async copies (TMA) that complete on mbarriers; eight consumer warps each own 16 rows of
-// the tile, feed the e4m3 bytes straight into m16n8k32 tensor-core MMAs and apply
-// (weight scale x column scale) in f32 registers once per k block.  Row tiles that straddle
-// two CTAs are finished by the last arriver, which adds the partials in CTA order, so the
-// result does not depend on timing.
+// bulk async copies (TMA) that complete on mbarriers.  Each ring slot is consumed by ONE warp,
+// which feeds the e4m3 bytes of all 128 rows straight into m16n8k32 tensor-core MMAs and applies
+// (weight scale x column scale) in f32 registers once per k block; four consumer warps work on
+// four slots at a time and meet in shared memory when a row tile is complete.  Row tiles that
+// straddle two CTAs are finished by the last arriver, which adds the partials in CTA order, so
+// the result does not depend on timing.
 #pragma once
 
 #include "common.cuh"
@@ -86,13 +87,39 @@ struct GemvParams {
   float* partial;   // scratch: [2 * grid][8 warps][32 lanes] float4
   int* counters;    // scratch: [n_tiles * 8], zero before the first launch, self-resetting
   int* status;
+  unsigned long long* prof;  // optional trace: [grid][8] %globaltimer stamps (see kGemvProf*)
   AllReduce ar;
 };
 
-constexpr int kGemvStages = 12;
-constexpr int kGemvConsumerWarps = 8;
-constexpr int kGemvThreads = (kGemvConsumerWarps + 3) * 32;  // + weight producer warp + two activation converter warps
-constexpr int kGemvSmemBytes = kGemvStages * TB_STAGE_BYTES + 2 * kGemvStages * 8 + 64;
+// Trace slots written per CTA when GemvParams::prof is set (the role of the reference's
+// profile_logs tensors, tilert/utils.py:18-45): nanoseconds of %globaltimer.
+enum GemvProfSlot : int {
+  kGemvProfEntry = 0,         // kernel entry
+  kGemvProfReady = 1,         // barriers initialised
+  kGemvProfFirstData = 2,     // consumer 0: its first unit's data is in shared memory
+  kGemvProfLastUnit = 3,      // consumer 0: its last unit is consumed
+  kGemvProfTilesDone = 4,     // consumer 0: all its tile reductions / epilogues are done
+  kGemvProfFirstConvert = 5,  // converter 0: first X block written
+  kGemvProfIssued = 6,        // producer 0: all its copies issued
+  kGemvProfExit = 7,          // consumer 0: end of kernel (after the all-reduce, if any)
+};
+__device__ __forceinline__ void gemv_stamp(const GemvParams& p, int slot) {
+  if (p.prof != nullptr) p.prof[blockIdx.x * 8 + slot] = globaltimer_ns();
+}
+
+#ifndef TB_GEMV_STAGES
+#define TB_GEMV_STAGES 12
+#endif
+constexpr int kGemvStages = TB_GEMV_STAGES;  // multiple of kGemvProducerWarps
+constexpr int kGemvConsumerWarps = 4;   // unit i of the CTA's range is consumed by warp i % 4
+constexpr int kGemvProducerWarps = 4;   // one issuing thread each; unit i is issued by producer i % 4
+constexpr int kGemvConverterWarps = 2;  // unit i is converted by converter i % 2 (X_BF16 only)
+constexpr int kGemvConsumerThreads = kGemvConsumerWarps * 32;
+constexpr int kGemvHelperWarps = kGemvConsumerWarps + kGemvConverterWarps;  // warps that are not producers
+constexpr int kGemvThreads = (kGemvConsumerWarps + kGemvProducerWarps + kGemvConverterWarps) * 32;
+constexpr int kGemvRedBytes = kGemvConsumerWarps * 8 * 32 * 16;  // per-tile cross-warp reduction buffer
+constexpr int kGemvSmemBytes =
+    kGemvStages * TB_STAGE_BYTES + kGemvRedBytes + 2 * kGemvStages * 8 + 16 + kGemvHelperWarps * 4 * 4 + 32;
 
 __device__ __forceinline__ long long gemv_range_begin(long long units, int grid, int cta) {
   return units * cta / grid;
@@ -163,43 +190,77 @@ __device__ __forceinline__ void gemv_epilogue(const GemvParams& p, int tile, int
 
 __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGemvStages * TB_STAGE_BYTES);
+  float4* red = reinterpret_cast<float4*>(smem + kGemvStages * TB_STAGE_BYTES);  // [warp][n16 tile][lane]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGemvStages * TB_STAGE_BYTES + kGemvRedBytes);
   uint64_t* empty = full + kGemvStages;
   volatile int* cta_error = reinterpret_cast<volatile int*>(empty + kGemvStages);
+  float* norm_part = reinterpret_cast<float*>(const_cast<int*>(cta_error) + 4);  // [helper warps][4 tokens]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grid = gridDim.x, cta = blockIdx.x;
   const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
-  const long long u0 = gemv_range_begin(units, grid, cta);
-  const long long u1 = gemv_range_begin(units, grid, cta + 1);
+  // unit indices fit 32 bits (checked on the host); all per-stage index arithmetic is 32-bit --
+  // 64-bit divisions in these loops cost more than the stage's data movement
+  const int u0 = static_cast<int>(gemv_range_begin(units, grid, cta));
+  const int u1 = static_cast<int>(gemv_range_begin(units, grid, cta + 1));
 
   if (threadIdx.x == 0) {
+    gemv_stamp(p, kGemvProfEntry);
     for (int s = 0; s < kGemvStages; ++s) {
       mbar_init(&full[s], p.x_mode == X_BF16 ? 2 : 1);  // producer (+ converter) arrive once per use
-      mbar_init(&empty[s], kGemvConsumerWarps);
+      mbar_init(&empty[s], 1);                          // the one consumer warp of the slot
     }
     *cta_error = 0;
     mbar_fence_init();
   }
   __syncthreads();
+  if (threadIdx.x == 0) gemv_stamp(p, kGemvProfReady);
 
-  if (warp == kGemvConsumerWarps) {
-    // ------------------------------------------------------------- producer
+  const bool is_consumer = warp < kGemvConsumerWarps;
+  const bool is_producer = !is_consumer && warp < kGemvConsumerWarps + kGemvProducerWarps;
+  if (p.x_mode == X_BF16 && p.gamma != nullptr && !is_producer) {
+    // RMSNorm statistics of the activation vector(s): the non-producer warps split the vector
+    // (the producers are already filling the ring), partial sums meet in shared memory.
+    const int hw = is_consumer ? warp : warp - kGemvProducerWarps;
+    const int n_chunks = p.n_kb * (TB_KBLOCK / 4);  // 8-byte chunks per token
+    float ss[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int ch = hw * 32 + lane; ch < n_chunks; ch += kGemvHelperWarps * 32) {
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        if (t < p.n_tokens) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(p.xb + t * p.xb_stride + ch * 4);
+          const float a0 = __uint_as_float(raw.x << 16), a1 = __uint_as_float(raw.x & 0xffff0000u);
+          const float a2 = __uint_as_float(raw.y << 16), a3 = __uint_as_float(raw.y & 0xffff0000u);
+          ss[t] += a0 * a0 + a1 * a1 + a2 * a2 + a3 * a3;
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float v = warp_sum(ss[t]);
+      if (lane == 0) norm_part[hw * 4 + t] = v;
+    }
+    asm volatile("bar.sync 2, %0;" ::"n"(kGemvHelperWarps * 32) : "memory");
+  }
+
+  if (is_producer) {
+    // ------------------------------------------------------------ producers
+    // Four warps, one issuing thread each; unit i of the CTA's range is issued by producer i % 4
+    // into ring slot i % kGemvStages, so no single thread's instruction latency paces the stream.
     if (lane == 0) {
+      const int pw = warp - kGemvConsumerWarps;
       const uint64_t pol = policy_evict_first();
-      long long issued = 0;
-      bool ok = true;
-      for (long long u = u0; u < u1 && ok; ++u) {
-        const long long i = u - u0;
-        const int s = static_cast<int>(i % kGemvStages);
+      int last_i = -1;
+      int t = (u0 + pw) / p.n_kb, kb = (u0 + pw) % p.n_kb;
+      for (int u = u0 + pw; u < u1; u += kGemvProducerWarps) {
+        const int i = u - u0;
+        const int s = i % kGemvStages;
         const uint32_t use = static_cast<uint32_t>(i / kGemvStages);
         if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1)) {
           set_status(p.status, ST_WAIT_EMPTY_TIMEOUT);
           *cta_error = 1;
-          ok = false;
           break;
         }
-        const int t = static_cast<int>(u / p.n_kb), kb = static_cast<int>(u % p.n_kb);
         long long eid = 0;
         int tl = t, kbl = kb;
         if (p.nseg_ids != nullptr) {
@@ -212,10 +273,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         }
         const uint8_t* wsrc =
             p.w + eid * p.expert_stride + (static_cast<long long>(tl) * p.w_kb_per_tile + kbl) * TB_WBLK_BYTES;
-        const int xseg = p.tiles_per_xseg > 0 ? t / p.tiles_per_xseg : 0;
-        const uint8_t* xsrc = p.x + (static_cast<long long>(xseg) * p.n_kb + kb) * TB_XBLK_BYTES;
         uint8_t* dst = smem + s * TB_STAGE_BYTES;
         if (p.x_mode == X_PACKED) {
+          const int xseg = p.tiles_per_xseg > 0 ? t / p.tiles_per_xseg : 0;
+          const uint8_t* xsrc = p.x + (static_cast<long long>(xseg) * p.n_kb + kb) * TB_XBLK_BYTES;
           mbar_expect_tx(&full[s], TB_STAGE_BYTES);
           bulk_g2s_stream(dst, wsrc, TB_WBLK_BYTES, &full[s], pol);
           bulk_g2s(dst + TB_WBLK_BYTES, xsrc, TB_XBLK_BYTES, &full[s]);
@@ -223,54 +284,48 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           mbar_expect_tx(&full[s], TB_WBLK_BYTES);
           bulk_g2s_stream(dst, wsrc, TB_WBLK_BYTES, &full[s], pol);
         }
-        ++issued;
-      }
-      // Do not leave the CTA while copies may still be landing in its shared memory: wait
-      // (bounded) for the last issued use of every ring slot.  On the normal path these have
-      // all completed already, because the consumers waited on the same phases.
-      for (int s = 0; s < kGemvStages; ++s) {
-        if (issued > s) {
-          const uint32_t last_use = static_cast<uint32_t>((issued - 1 - s) / kGemvStages);
-          mbar_wait(&full[s], last_use & 1);
+        last_i = i;
+        kb += kGemvProducerWarps;
+        while (kb >= p.n_kb) {
+          kb -= p.n_kb;
+          ++t;
         }
       }
+      if (pw == 0) gemv_stamp(p, kGemvProfIssued);
+      // Do not leave the CTA while this thread's copies may still be landing in its shared memory:
+      // wait (bounded) for the last use it issued into each of its ring slots.  On the normal path
+      // these have completed already, because the consumers waited on the same phases.
+      for (int back = 0; back < kGemvStages && last_i - back >= 0; back += kGemvProducerWarps) {
+        const int i = last_i - back;
+        mbar_wait(&full[i % kGemvStages], static_cast<uint32_t>(i / kGemvStages) & 1);
+      }
     }
-  } else if (warp > kGemvConsumerWarps) {
+  } else if (!is_consumer) {
     // ------------------------------------------------- activation converters (X_BF16 only)
     // Two warps take alternate units.  Each converts the 128 activations of its unit, for every
     // token, into the two-term e4m3 X block of the stage: power-of-two scales, so the scaling is a
     // multiplication and the residual x - hi*s is exact.
-    const int cw = warp - (kGemvConsumerWarps + 1);  // 0 or 1
+    const int cw = warp - (kGemvConsumerWarps + kGemvProducerWarps);  // 0 or 1
     if (p.x_mode == X_BF16 && u0 + cw < u1) {
       const int ntok = p.n_tokens;
       float rinv[4] = {1.f, 1.f, 1.f, 1.f};
       if (p.gamma != nullptr) {
-        // RMSNorm statistics of the whole vector, once per warp (overlaps the ring's first fills)
-        float ss[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-        for (int kb = 0; kb < p.n_kb; ++kb) {
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            if (t < ntok) {
-              const uint2 raw = *reinterpret_cast<const uint2*>(p.xb + t * p.xb_stride + kb * TB_KBLOCK + lane * 4);
-              const float a0 = __uint_as_float(raw.x << 16), a1 = __uint_as_float(raw.x & 0xffff0000u);
-              const float a2 = __uint_as_float(raw.y << 16), a3 = __uint_as_float(raw.y & 0xffff0000u);
-              ss[t] += a0 * a0 + a1 * a1 + a2 * a2 + a3 * a3;
-            }
-          }
+        for (int t = 0; t < 4; ++t) {
+          float tot = 0.f;
+#pragma unroll
+          for (int w2 = 0; w2 < kGemvHelperWarps; ++w2) tot += norm_part[w2 * 4 + t];
+          rinv[t] = rsqrtf(tot / static_cast<float>(p.n_kb * TB_KBLOCK) + p.eps);
         }
-#pragma unroll
-        for (int t = 0; t < 4; ++t)
-          rinv[t] = rsqrtf(warp_sum(ss[t]) / static_cast<float>(p.n_kb * TB_KBLOCK) + p.eps);
       }
       const long long xk = static_cast<long long>(p.n_kb) * TB_KBLOCK;  // activations per x segment
       struct XRaw {
         uint2 v[4];
         float4 g;
       };
-      auto fetch = [&](long long u) {
+      auto fetch = [&](int u) {
         XRaw o;
-        const int t = static_cast<int>(u / p.n_kb), kb = static_cast<int>(u % p.n_kb);
+        const int t = u / p.n_kb, kb = u % p.n_kb;
         const int xseg = p.tiles_per_xseg > 0 ? t / p.tiles_per_xseg : 0;
         const long long off = xseg * xk + static_cast<long long>(kb) * TB_KBLOCK + lane * 4;
 #pragma unroll
@@ -281,13 +336,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         return o;
       };
       // software pipeline over this warp's units (u, u+2, u+4, ...): two requests in flight
-      const long long ub = u0 + cw;
+      const int ub = u0 + cw;
       XRaw x0 = fetch(ub), x1 = x0, x2 = x0;
       if (ub + 2 < u1) x1 = fetch(ub + 2);
       const int c = lane >> 3, r = (lane >> 2) & 1, q4 = lane & 3;
-      for (long long u = ub; u < u1; u += 2) {
-        const long long i = u - u0;
-        const int s = static_cast<int>(i % kGemvStages);
+      for (int u = ub; u < u1; u += 2) {
+        const int i = u - u0;
+        const int s = i % kGemvStages;
         const uint32_t use = static_cast<uint32_t>(i / kGemvStages);
         if (u + 4 < u1) x2 = fetch(u + 4);
         if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1)) {
@@ -296,7 +351,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           break;
         }
         uint8_t* blk = smem + s * TB_STAGE_BYTES + TB_WBLK_BYTES;
-        const int kb = static_cast<int>(u % p.n_kb);
+        const int kb = u % p.n_kb;
         const float g4[4] = {x0.g.x, x0.g.y, x0.g.z, x0.g.w};
 #pragma unroll
         for (int tk = 0; tk < 4; ++tk) {
@@ -344,99 +399,144 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&full[s]);
+        if (lane == 0) {
+          mbar_arrive(&full[s]);
+          if (u == u0) gemv_stamp(p, kGemvProfFirstConvert);
+        }
         x0 = x1;
         x1 = x2;
       }
     }
   } else {
     // ------------------------------------------------------------ consumers
+    // Warp w consumes units u0 + w, u0 + w + 4, ...: the whole 128 x 128 block of each (32 MMAs, the
+    // activation fragments shared by the eight 16-row groups).  When a row tile is complete -- or the
+    // CTA's range ends inside it -- the four warps add their accumulators through shared memory and
+    // warp w finishes 16-row groups 2w and 2w + 1.
     const int q = lane & 3;
     unsigned long long ar_epoch = 0;
     if (p.ar.world > 1) ar_epoch = *reinterpret_cast<volatile unsigned long long*>(&p.ar.state[p.ar.rank]->epoch);
     const int ar_half = static_cast<int>(ar_epoch & 1ull);
-    float out[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     bool ok = true;
-    for (long long u = u0; u < u1; ++u) {
-      const long long i = u - u0;
-      const int s = static_cast<int>(i % kGemvStages);
-      const uint32_t use = static_cast<uint32_t>(i / kGemvStages);
-      if (!mbar_wait(&full[s], use & 1)) {
-        set_status(p.status, ST_WAIT_FULL_TIMEOUT);
-        *cta_error = 1;
-        ok = false;
-        break;
-      }
-      const uint8_t* sw = smem + s * TB_STAGE_BYTES;
-      const uint8_t* sx = sw + TB_WBLK_BYTES;
-      // four independent MMAs (one per 32-wide k chunk), summed afterwards: no dependent MMA chain
-      float acc4[4][4];
-      uint4 a[4];
-      uint2 b[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        a[c] = *reinterpret_cast<const uint4*>(sw + ((warp * 4 + c) * 32 + lane) * 16);
-        b[c] = *reinterpret_cast<const uint2*>(sx + (c * 32 + lane) * 8);
-      }
-      const float2 ws = *reinterpret_cast<const float2*>(sw + TB_WBLK_DATA + warp * 8);
-      const float2 cs = *reinterpret_cast<const float2*>(sx + TB_XBLK_DATA + q * 8);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        acc4[c][0] = acc4[c][1] = acc4[c][2] = acc4[c][3] = 0.f;
-        mma_e4m3_16832(acc4[c], a[c], b[c]);
-      }
-      float acc[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[j] = (acc4[0][j] + acc4[1][j]) + (acc4[2][j] + acc4[3][j]);
-      out[0] = fmaf(acc[0], ws.x * cs.x, out[0]);
-      out[1] = fmaf(acc[1], ws.x * cs.y, out[1]);
-      out[2] = fmaf(acc[2], ws.y * cs.x, out[2]);
-      out[3] = fmaf(acc[3], ws.y * cs.y, out[3]);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);
 
-      const int t = static_cast<int>(u / p.n_kb), kb = static_cast<int>(u % p.n_kb);
-      if (kb == p.n_kb - 1 || u == u1 - 1) {
-        // this CTA's share of row tile t is complete
-        const long long tile_u0 = static_cast<long long>(t) * p.n_kb;
-        const long long tile_u1 = tile_u0 + p.n_kb;
-        if (u0 <= tile_u0 && u1 >= tile_u1) {
-          gemv_epilogue(p, t, warp, lane, out, ar_half);
+    // Adds the four warps' accumulators of row tile t and finishes this warp's two 16-row groups.
+    auto finish_tile = [&](int t) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        red[(warp * 8 + j) * 32 + lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerThreads) : "memory");
+      float out2[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        out2[h][0] = out2[h][1] = out2[h][2] = out2[h][3] = 0.f;
+#pragma unroll
+        for (int w2 = 0; w2 < kGemvConsumerWarps; ++w2) {
+          const float4 v = red[(w2 * 8 + 2 * warp + h) * 32 + lane];
+          out2[h][0] += v.x; out2[h][1] += v.y; out2[h][2] += v.z; out2[h][3] += v.w;
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerThreads) : "memory");  // red may be rewritten
+      const int tile_u0 = t * p.n_kb, tile_u1 = tile_u0 + p.n_kb;
+      const bool whole = u0 <= tile_u0 && u1 >= tile_u1;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int n16 = 2 * warp + h;  // 16-row group inside the tile
+        if (whole) {
+          gemv_epilogue(p, t, n16, lane, out2[h], ar_half);
         } else {
           const int c_first = gemv_owner(tile_u0, units, grid);
           const int c_last = gemv_owner(tile_u1 - 1, units, grid);
           const int my_slot = 2 * cta + ((u0 / p.n_kb) == t ? 0 : 1);
           float4* part = reinterpret_cast<float4*>(p.partial);
-          part[(my_slot * 8 + warp) * 32 + lane] = make_float4(out[0], out[1], out[2], out[3]);
+          part[(my_slot * 8 + n16) * 32 + lane] = make_float4(out2[h][0], out2[h][1], out2[h][2], out2[h][3]);
           __threadfence();
           __syncwarp();
           int prev = 0;
-          if (lane == 0) prev = atomicAdd(&p.counters[t * 8 + warp], 1);
+          if (lane == 0) prev = atomicAdd(&p.counters[t * 8 + n16], 1);
           prev = __shfl_sync(0xffffffffu, prev, 0);
           if (prev == c_last - c_first) {
             __threadfence();
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
             for (int cc = c_first; cc <= c_last; ++cc) {
-              const long long cu0 = gemv_range_begin(units, grid, cc);
+              const int cu0 = static_cast<int>(gemv_range_begin(units, grid, cc));
               const int slot = 2 * cc + ((cu0 / p.n_kb) == t ? 0 : 1);
-              const float4 v = __ldcg(&part[(slot * 8 + warp) * 32 + lane]);
+              const float4 v = __ldcg(&part[(slot * 8 + n16) * 32 + lane]);
               sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
             }
-            if (lane == 0) p.counters[t * 8 + warp] = 0;
-            gemv_epilogue(p, t, warp, lane, sum, ar_half);
+            if (lane == 0) p.counters[t * 8 + n16] = 0;
+            gemv_epilogue(p, t, n16, lane, sum, ar_half);
           }
         }
-        out[0] = out[1] = out[2] = out[3] = 0.f;
       }
-    }
+    };
 
+    int cur_t = u0 < u1 ? u0 / p.n_kb : 0;
+    const int last_t = u0 < u1 ? (u1 - 1) / p.n_kb : -1;
+    for (int u = u0 + warp; u < u1; u += kGemvConsumerWarps) {
+      const int t = u / p.n_kb;
+      while (cur_t < t) finish_tile(cur_t++);  // every warp passes through every tile boundary, in order
+      const int i = u - u0;
+      const int s = i % kGemvStages;
+      const uint32_t use = static_cast<uint32_t>(i / kGemvStages);
+      // A warp that gave up on a wait keeps walking its units without touching the ring, so that it
+      // still meets the other warps at every tile boundary (those barriers have no time limit).
+      if (!ok || *cta_error) {
+        ok = false;
+        continue;
+      }
+      if (!mbar_wait(&full[s], use & 1)) {
+        set_status(p.status, ST_WAIT_FULL_TIMEOUT);
+        *cta_error = 1;
+        ok = false;
+        continue;
+      }
+      if (u == u0 && lane == 0) gemv_stamp(p, kGemvProfFirstData);
+      const uint8_t* sw = smem + s * TB_STAGE_BYTES;
+      const uint8_t* sx = sw + TB_WBLK_BYTES;
+      uint2 b[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) b[c] = *reinterpret_cast<const uint2*>(sx + (c * 32 + lane) * 8);
+      const float2 cs = *reinterpret_cast<const float2*>(sx + TB_XBLK_DATA + q * 8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // four independent MMAs (one per 32-wide k chunk), summed afterwards: no dependent MMA chain
+        float a4[4][4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint4 a = *reinterpret_cast<const uint4*>(sw + ((j * 4 + c) * 32 + lane) * 16);
+          a4[c][0] = a4[c][1] = a4[c][2] = a4[c][3] = 0.f;
+#ifndef TB_EXP_SKIP_MMA
+          mma_e4m3_16832(a4[c], a, b[c]);
+#else
+          a4[c][0] = __uint_as_float(a.x ^ b[c].x);
+#endif
+        }
+        const float2 ws = *reinterpret_cast<const float2*>(sw + TB_WBLK_DATA + j * 8);
+        const float s00 = ws.x * cs.x, s01 = ws.x * cs.y, s10 = ws.y * cs.x, s11 = ws.y * cs.y;
+        acc[j][0] = fmaf((a4[0][0] + a4[1][0]) + (a4[2][0] + a4[3][0]), s00, acc[j][0]);
+        acc[j][1] = fmaf((a4[0][1] + a4[1][1]) + (a4[2][1] + a4[3][1]), s01, acc[j][1]);
+        acc[j][2] = fmaf((a4[0][2] + a4[1][2]) + (a4[2][2] + a4[3][2]), s10, acc[j][2]);
+        acc[j][3] = fmaf((a4[0][3] + a4[1][3]) + (a4[2][3] + a4[3][3]), s11, acc[j][3]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    if (warp == 0 && lane == 0) gemv_stamp(p, kGemvProfLastUnit);
+    // tiles this warp has not closed yet (including those in which it had no unit)
+    while (cur_t <= last_t) finish_tile(cur_t++);
+    if (warp == 0 && lane == 0) gemv_stamp(p, kGemvProfTilesDone);
     if (p.ar.world > 1) {
       // ---- one-shot all-reduce over peer memory, fused behind the streaming loop ----
       AllReduceState* self = p.ar.state[p.ar.rank];
       // 1. this CTA's peer stores are done: publish them.  The last CTA of the rank to get here
       //    tells every rank (itself included) that this rank's partial has landed.
       __threadfence_system();
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerThreads) : "memory");
       if (threadIdx.x == 0) {
         const unsigned int prev = atomicAdd(&self->local_arrive, 1u);
         if (prev == static_cast<unsigned int>(grid) - 1u) {
@@ -460,14 +560,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           __nanosleep(32);
         }
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerThreads) : "memory");
       // 3. reduce the world's slots for this CTA's share of rows, add the residual, store.
       if (!*cta_error) {
         const float* mine = p.ar.recv[p.ar.rank];
         const int total = p.n_tokens * p.n_rows;
         const int e0 = static_cast<int>(static_cast<long long>(total) * cta / grid);
         const int e1 = static_cast<int>(static_cast<long long>(total) * (cta + 1) / grid);
-        for (int e = e0 + static_cast<int>(threadIdx.x); e < e1; e += 256) {
+        for (int e = e0 + static_cast<int>(threadIdx.x); e < e1; e += kGemvConsumerThreads) {
           const int tok = e / p.n_rows, row = e % p.n_rows;
           float v = 0.f;
           for (int r = 0; r < p.ar.world; ++r)
@@ -476,7 +576,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         }
       }
       // 4. the last CTA to finish opens the next call (flips the buffer half).
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerThreads) : "memory");
       if (threadIdx.x == 0) {
         const unsigned int prev = atomicAdd(&self->local_done, 1u);
         if (prev == static_cast<unsigned int>(grid) - 1u) {
@@ -486,6 +586,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         }
       }
     }
+    if (warp == 0 && lane == 0) gemv_stamp(p, kGemvProfExit);
   }
 }
 
