@@ -375,7 +375,7 @@ def run_profile_gemv(args) -> None:
     read_gbs = 5 * big.numel() * 4 / (e0.elapsed_time(e1) * 1e-3) / 1e9
     # per-CTA phase stamps of one traced launch
     import ctypes
-    trace = torch.zeros(256, 8, dtype=torch.int64, device=dev)
+    trace = torch.zeros(256, 16, dtype=torch.int64, device=dev)
     ctx = ctypes.c_void_p(tilert_b200.tilert_init(0))
     tilert_b200.check(tilert_b200.lib().tilert_b200_set_profile(ctx, ctypes.c_void_p(trace.data_ptr())))
     ops.unproj_o_allreduce(vec, w, None, res, 0, out)
@@ -383,10 +383,13 @@ def run_profile_gemv(args) -> None:
     tilert_b200.check(tilert_b200.lib().tilert_b200_set_profile(ctx, None))
     tr = trace[:148].cpu().double()
     t0 = tr[:, 0].min()
-    rel = (tr - t0) / 1e3
+    rel = (tr[:, :8] - t0) / 1e3
     names = ["entry", "ready", "first_data", "last_unit", "tiles_done", "first_convert", "issued", "exit"]
     phases = {nm: [round(float(rel[:, i].min()), 2), round(float(rel[:, i].median()), 2), round(float(rel[:, i].max()), 2)]
               for i, nm in enumerate(names)}
+    units = tr[:, 10].clamp_min(1)
+    phases["wait_cycles_per_unit"] = round(float((tr[:, 8] / units).median()), 1)
+    phases["math_cycles_per_unit"] = round(float((tr[:, 9] / units).median()), 1)
     print(json.dumps({"trace_us_min_med_max": phases}))
     print(json.dumps({"mode": "profile-gemv", "n": n, "k": k, "weight_bytes": w.numel(), "ms_per_launch": ms,
                       "gbs": w.numel() / ms / 1e6, "torch_sum_read_gbs": read_gbs,

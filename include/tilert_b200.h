@@ -60,9 +60,9 @@ size_t tilert_b200_context_bytes(void);
  * were recorded into a CUDA graph during stream capture). */
 long long tilert_b200_launch_count(void);
 /* Tracing, the role of the reference's `profile_logs` argument (tilert/utils.py:18-45): while
- * `trace` (device memory, u64 [256][8]) is set, every weight-streaming launch records eight
- * %globaltimer stamps per CTA (entry, ready, first data, last unit, tiles done, first conversion,
- * copies issued, exit).  NULL switches tracing off. */
+ * `trace` (device memory, u64 [256][16]) is set, every weight-streaming launch records per CTA eight
+ * %globaltimer stamps (entry, ready, first data, last unit, tiles done, first conversion, copies
+ * issued, exit) and three counters of its first consumer warp (cycles waiting, cycles consuming, units).  NULL switches tracing off. */
 int tilert_b200_set_profile(TbContext* ctx, unsigned long long* trace);
 
 /* ---- peer-to-peer plumbing for the fused all-reduce ------------------------------------ */

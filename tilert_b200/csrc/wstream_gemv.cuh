@@ -6,9 +6,9 @@
 // HBM-bound: every weight byte is read exactly once.  One persistent CTA per SM walks a
 // contiguous range of (row tile, k block) units (stream-K).  A producer thread stages each
 // unit -- one 16448-byte W block and one 1056-byte X block -- into a shared-memory ring with
-// bulk async copies (TMA) that complete on mbarriers.  Each ring slot is consumed by ONE warp,
-// which feeds the e4m3 bytes of all 128 rows straight into m16n8k32 tensor-core MMAs and applies
-// (weight scale x column scale) in f32 registers once per k block; four consumer warps work on
+// bulk async copies (TMA) that complete on mbarriers.  Each ring slot is consumed by TWO warps
+// (64 rows each), which feed the e4m3 bytes straight into m16n8k32 tensor-core MMAs and apply
+// (weight scale x column scale) in f32 registers once per k block; eight consumer warps work on
 // four slots at a time and meet in shared memory when a row tile is complete.  Row tiles that
 // straddle two CTAs are finished by the last arriver, which adds the partials in CTA order, so
 // the result does not depend on timing.
@@ -87,7 +87,7 @@ struct GemvParams {
   float* partial;   // scratch: [2 * grid][8 warps][32 lanes] float4
   int* counters;    // scratch: [n_tiles * 8], zero before the first launch, self-resetting
   int* status;
-  unsigned long long* prof;  // optional trace: [grid][8] %globaltimer stamps (see kGemvProf*)
+  unsigned long long* prof;  // optional trace: [grid][16] (see GemvProfSlot)
   AllReduce ar;
 };
 
@@ -102,22 +102,25 @@ enum GemvProfSlot : int {
   kGemvProfFirstConvert = 5,  // converter 0: first X block written
   kGemvProfIssued = 6,        // producer 0: all its copies issued
   kGemvProfExit = 7,          // consumer 0: end of kernel (after the all-reduce, if any)
+  kGemvProfWaitCycles = 8,    // consumer 0: SM cycles spent waiting for data, summed over its units
+  kGemvProfMathCycles = 9,    // consumer 0: SM cycles spent consuming, summed over its units
+  kGemvProfUnits = 10,        // consumer 0: number of units it consumed
 };
 __device__ __forceinline__ void gemv_stamp(const GemvParams& p, int slot) {
-  if (p.prof != nullptr) p.prof[blockIdx.x * 8 + slot] = globaltimer_ns();
+  if (p.prof != nullptr) p.prof[blockIdx.x * 16 + slot] = globaltimer_ns();
 }
 
 #ifndef TB_GEMV_STAGES
 #define TB_GEMV_STAGES 12
 #endif
 constexpr int kGemvStages = TB_GEMV_STAGES;  // multiple of kGemvProducerWarps
-constexpr int kGemvConsumerWarps = 4;   // unit i of the CTA's range is consumed by warp i % 4
+constexpr int kGemvConsumerWarps = 8;   // unit i is consumed by warps i % 4 (rows 0-63) and 4 + i % 4 (rows 64-127)
 constexpr int kGemvProducerWarps = 4;   // one issuing thread each; unit i is issued by producer i % 4
 constexpr int kGemvConverterWarps = 2;  // unit i is converted by converter i % 2 (X_BF16 only)
 constexpr int kGemvConsumerThreads = kGemvConsumerWarps * 32;
 constexpr int kGemvHelperWarps = kGemvConsumerWarps + kGemvConverterWarps;  // warps that are not producers
 constexpr int kGemvThreads = (kGemvConsumerWarps + kGemvProducerWarps + kGemvConverterWarps) * 32;
-constexpr int kGemvRedBytes = kGemvConsumerWarps * 8 * 32 * 16;  // per-tile cross-warp reduction buffer
+constexpr int kGemvRedBytes = kGemvConsumerWarps * 4 * 32 * 16;  // per-tile cross-warp reduction buffer
 constexpr int kGemvSmemBytes =
     kGemvStages * TB_STAGE_BYTES + kGemvRedBytes + 2 * kGemvStages * 8 + 16 + kGemvHelperWarps * 4 * 4 + 32;
 
@@ -208,7 +211,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     gemv_stamp(p, kGemvProfEntry);
     for (int s = 0; s < kGemvStages; ++s) {
       mbar_init(&full[s], p.x_mode == X_BF16 ? 2 : 1);  // producer (+ converter) arrive once per use
-      mbar_init(&empty[s], 1);                          // the one consumer warp of the slot
+      mbar_init(&empty[s], 2);                          // the two consumer warps of the slot
     }
     *cta_error = 0;
     mbar_fence_init();
@@ -409,75 +412,70 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     }
   } else {
     // ------------------------------------------------------------ consumers
-    // Warp w consumes units u0 + w, u0 + w + 4, ...: the whole 128 x 128 block of each (32 MMAs, the
-    // activation fragments shared by the eight 16-row groups).  When a row tile is complete -- or the
-    // CTA's range ends inside it -- the four warps add their accumulators through shared memory and
-    // warp w finishes 16-row groups 2w and 2w + 1.
+    // Warps w and w + 4 consume units u0 + w, u0 + w + 4, ... (w < 4): rows 0-63 and 64-127 of each
+    // 128 x 128 block, four 16-row groups per warp sharing the activation fragments.  When a row tile
+    // is complete -- or the CTA's range ends inside it -- the warps add their accumulators through
+    // shared memory and warp w finishes 16-row group w.
     const int q = lane & 3;
+    const int wq = warp & 3, half = warp >> 2;
     unsigned long long ar_epoch = 0;
     if (p.ar.world > 1) ar_epoch = *reinterpret_cast<volatile unsigned long long*>(&p.ar.state[p.ar.rank]->epoch);
     const int ar_half = static_cast<int>(ar_epoch & 1ull);
-    float acc[8][4];
+    float acc[4][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int j = 0; j < 4; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     bool ok = true;
+    long long prof_wait = 0, prof_math = 0, prof_units = 0;
 
-    // Adds the four warps' accumulators of row tile t and finishes this warp's two 16-row groups.
+    // Adds the warps' accumulators of row tile t and finishes this warp's 16-row group.
     auto finish_tile = [&](int t) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        red[(warp * 8 + j) * 32 + lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+      for (int j = 0; j < 4; ++j) {
+        red[(warp * 4 + j) * 32 + lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
         acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerThreads) : "memory");
-      float out2[2][4];
+      // 16-row group `warp` = local group wq of half `half`: partial sums sit with the four warps of that half
+      float out[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        out2[h][0] = out2[h][1] = out2[h][2] = out2[h][3] = 0.f;
-#pragma unroll
-        for (int w2 = 0; w2 < kGemvConsumerWarps; ++w2) {
-          const float4 v = red[(w2 * 8 + 2 * warp + h) * 32 + lane];
-          out2[h][0] += v.x; out2[h][1] += v.y; out2[h][2] += v.z; out2[h][3] += v.w;
-        }
+      for (int w2 = 0; w2 < 4; ++w2) {
+        const float4 v = red[((half * 4 + w2) * 4 + wq) * 32 + lane];
+        out[0] += v.x; out[1] += v.y; out[2] += v.z; out[3] += v.w;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerThreads) : "memory");  // red may be rewritten
       const int tile_u0 = t * p.n_kb, tile_u1 = tile_u0 + p.n_kb;
-      const bool whole = u0 <= tile_u0 && u1 >= tile_u1;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int n16 = 2 * warp + h;  // 16-row group inside the tile
-        if (whole) {
-          gemv_epilogue(p, t, n16, lane, out2[h], ar_half);
-        } else {
-          const int c_first = gemv_owner(tile_u0, units, grid);
-          const int c_last = gemv_owner(tile_u1 - 1, units, grid);
-          const int my_slot = 2 * cta + ((u0 / p.n_kb) == t ? 0 : 1);
-          float4* part = reinterpret_cast<float4*>(p.partial);
-          part[(my_slot * 8 + n16) * 32 + lane] = make_float4(out2[h][0], out2[h][1], out2[h][2], out2[h][3]);
+      const int n16 = warp;  // 16-row group inside the tile
+      if (u0 <= tile_u0 && u1 >= tile_u1) {
+        gemv_epilogue(p, t, n16, lane, out, ar_half);
+      } else {
+        const int c_first = gemv_owner(tile_u0, units, grid);
+        const int c_last = gemv_owner(tile_u1 - 1, units, grid);
+        const int my_slot = 2 * cta + ((u0 / p.n_kb) == t ? 0 : 1);
+        float4* part = reinterpret_cast<float4*>(p.partial);
+        part[(my_slot * 8 + n16) * 32 + lane] = make_float4(out[0], out[1], out[2], out[3]);
+        __threadfence();
+        __syncwarp();
+        int prev = 0;
+        if (lane == 0) prev = atomicAdd(&p.counters[t * 8 + n16], 1);
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev == c_last - c_first) {
           __threadfence();
-          __syncwarp();
-          int prev = 0;
-          if (lane == 0) prev = atomicAdd(&p.counters[t * 8 + n16], 1);
-          prev = __shfl_sync(0xffffffffu, prev, 0);
-          if (prev == c_last - c_first) {
-            __threadfence();
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int cc = c_first; cc <= c_last; ++cc) {
-              const int cu0 = static_cast<int>(gemv_range_begin(units, grid, cc));
-              const int slot = 2 * cc + ((cu0 / p.n_kb) == t ? 0 : 1);
-              const float4 v = __ldcg(&part[(slot * 8 + n16) * 32 + lane]);
-              sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
-            }
-            if (lane == 0) p.counters[t * 8 + n16] = 0;
-            gemv_epilogue(p, t, n16, lane, sum, ar_half);
+          float sum[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int cc = c_first; cc <= c_last; ++cc) {
+            const int cu0 = static_cast<int>(gemv_range_begin(units, grid, cc));
+            const int slot = 2 * cc + ((cu0 / p.n_kb) == t ? 0 : 1);
+            const float4 v = __ldcg(&part[(slot * 8 + n16) * 32 + lane]);
+            sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
           }
+          if (lane == 0) p.counters[t * 8 + n16] = 0;
+          gemv_epilogue(p, t, n16, lane, sum, ar_half);
         }
       }
     };
 
     int cur_t = u0 < u1 ? u0 / p.n_kb : 0;
     const int last_t = u0 < u1 ? (u1 - 1) / p.n_kb : -1;
-    for (int u = u0 + warp; u < u1; u += kGemvConsumerWarps) {
+    for (int u = u0 + wq; u < u1; u += 4) {
       const int t = u / p.n_kb;
       while (cur_t < t) finish_tile(cur_t++);  // every warp passes through every tile boundary, in order
       const int i = u - u0;
@@ -489,12 +487,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         ok = false;
         continue;
       }
+      const long long c0 = p.prof != nullptr ? clock64() : 0;
       if (!mbar_wait(&full[s], use & 1)) {
         set_status(p.status, ST_WAIT_FULL_TIMEOUT);
         *cta_error = 1;
         ok = false;
         continue;
       }
+      const long long c1 = p.prof != nullptr ? clock64() : 0;
       if (u == u0 && lane == 0) gemv_stamp(p, kGemvProfFirstData);
       const uint8_t* sw = smem + s * TB_STAGE_BYTES;
       const uint8_t* sx = sw + TB_WBLK_BYTES;
@@ -502,31 +502,44 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
 #pragma unroll
       for (int c = 0; c < 4; ++c) b[c] = *reinterpret_cast<const uint2*>(sx + (c * 32 + lane) * 8);
       const float2 cs = *reinterpret_cast<const float2*>(sx + TB_XBLK_DATA + q * 8);
+      // four independent accumulation chains (one per 16-row group), each over the four k chunks
+      float d[4][4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        // four independent MMAs (one per 32-wide k chunk), summed afterwards: no dependent MMA chain
-        float a4[4][4];
+      for (int j = 0; j < 4; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.f;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint4 a = *reinterpret_cast<const uint4*>(sw + ((j * 4 + c) * 32 + lane) * 16);
-          a4[c][0] = a4[c][1] = a4[c][2] = a4[c][3] = 0.f;
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 a = *reinterpret_cast<const uint4*>(sw + (((half * 4 + j) * 4 + c) * 32 + lane) * 16);
 #ifndef TB_EXP_SKIP_MMA
-          mma_e4m3_16832(a4[c], a, b[c]);
+          mma_e4m3_16832(d[j], a, b[c]);
 #else
-          a4[c][0] = __uint_as_float(a.x ^ b[c].x);
+          d[j][0] += __uint_as_float(a.x ^ b[c].x);
 #endif
         }
-        const float2 ws = *reinterpret_cast<const float2*>(sw + TB_WBLK_DATA + j * 8);
-        const float s00 = ws.x * cs.x, s01 = ws.x * cs.y, s10 = ws.y * cs.x, s11 = ws.y * cs.y;
-        acc[j][0] = fmaf((a4[0][0] + a4[1][0]) + (a4[2][0] + a4[3][0]), s00, acc[j][0]);
-        acc[j][1] = fmaf((a4[0][1] + a4[1][1]) + (a4[2][1] + a4[3][1]), s01, acc[j][1]);
-        acc[j][2] = fmaf((a4[0][2] + a4[1][2]) + (a4[2][2] + a4[3][2]), s10, acc[j][2]);
-        acc[j][3] = fmaf((a4[0][3] + a4[1][3]) + (a4[2][3] + a4[3][3]), s11, acc[j][3]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 ws = *reinterpret_cast<const float2*>(sw + TB_WBLK_DATA + (half * 4 + j) * 8);
+        acc[j][0] = fmaf(d[j][0], ws.x * cs.x, acc[j][0]);
+        acc[j][1] = fmaf(d[j][1], ws.x * cs.y, acc[j][1]);
+        acc[j][2] = fmaf(d[j][2], ws.y * cs.x, acc[j][2]);
+        acc[j][3] = fmaf(d[j][3], ws.y * cs.y, acc[j][3]);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
+      if (p.prof != nullptr) {
+        prof_wait += c1 - c0;
+        prof_math += clock64() - c1;
+        ++prof_units;
+      }
     }
     if (warp == 0 && lane == 0) gemv_stamp(p, kGemvProfLastUnit);
+    if (warp == 0 && lane == 0 && p.prof != nullptr) {
+      p.prof[blockIdx.x * 16 + kGemvProfWaitCycles] = prof_wait;
+      p.prof[blockIdx.x * 16 + kGemvProfMathCycles] = prof_math;
+      p.prof[blockIdx.x * 16 + kGemvProfUnits] = prof_units;
+    }
     // tiles this warp has not closed yet (including those in which it had no unit)
     while (cur_t <= last_t) finish_tile(cur_t++);
     if (warp == 0 && lane == 0) gemv_stamp(p, kGemvProfTilesDone);
