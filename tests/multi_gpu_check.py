@@ -1,0 +1,88 @@
+"""Tensor-parallel parity check, run as one process per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 tests/multi_gpu_check.py
+
+Every rank runs its shard of both toy layers (heads / N, expert intermediate / N) with the fused
+peer-memory all-reduce; every rank's output must match the CPU oracle's unsharded layer (cosine
+>= 0.999, rel-L2 <= 2e-2) and all ranks must hold bit-identical results.  Several steps are run
+back to back so that both halves of the receive buffers and the epoch bookkeeping are exercised.
+"""
+
+import os
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+import torch
+import torch.distributed as dist
+
+from oracle import model as om
+from oracle import ops as oo
+
+
+def main() -> int:
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    import tilert_b200
+    from tilert_b200.comm import Comm
+    from tilert_b200.models.deepseek_v3_2 import layer as L
+    from tilert_b200.models.deepseek_v3_2.model_args import toy_model_args
+
+    tilert_b200.load_backend("deepseek_v3_2")
+    tilert_b200.tilert_init(local)
+    a, margs = om.toy_args(), toy_model_args()
+    sd = om.random_state_dict(a, seed=0)
+    comm = Comm(a.dim, local)
+    fc = oo.precompute_freqs_cis(a)
+    failures = []
+    for li in (0, 1):
+        for tokens in (1, 2) if li == 0 else (1,):
+            g = torch.Generator().manual_seed(300 + li + tokens)
+            t_ctx, cache_len, n_steps = 400, 512, 3
+            ow, oc = om.LayerWeights(a, sd, li), om.Caches(a, cache_len)
+            for c in (oc.kv, oc.pe, oc.ki):
+                c[:, :t_ctx] = torch.randn(1, t_ctx, c.size(-1), generator=g, dtype=torch.float32).to(torch.bfloat16)
+            gl = L.DecoderLayer(margs, L.LayerWeights(margs, sd, li, dev, world, rank), dev, cache_len, tokens, world,
+                                comm.handle)
+            gl.kv_cache.copy_(oc.kv); gl.pe_cache.copy_(oc.pe); gl.ki_cache.copy_(oc.ki)
+            for step in range(n_steps):
+                pos = t_ctx + step * tokens
+                x = torch.randn(1, tokens, a.dim, generator=g, dtype=torch.float32).to(torch.bfloat16)
+                cur = torch.tensor([pos], dtype=torch.int32, device=dev)
+                fr = torch.view_as_real(fc[pos: pos + tokens]).contiguous().to(dev)
+                trace = {}
+                ref = om.layer_step(a, ow, oc, x, pos, fc, trace)
+                gl.injected_sel = trace["sel"].to(dev)      # identical selections on every rank and in the oracle
+                if "router_scores" in trace:
+                    gl.forced_scores = trace["router_scores"].float().to(dev)
+                out = gl.forward(x.to(dev), cur, fr, n_keys=pos + tokens).clone()
+                torch.cuda.synchronize()
+                o = out.float().cpu()
+                cos = torch.nn.functional.cosine_similarity(ref.float().flatten(), o.flatten(), dim=0).item()
+                l2 = (torch.norm(ref.float() - o) / torch.norm(ref.float())).item()
+                gathered = [torch.empty_like(out) for _ in range(world)]
+                dist.all_gather(gathered, out)
+                same = all(torch.equal(gathered[0], t) for t in gathered)
+                if rank == 0:
+                    print(f"layer {li} tokens {tokens} step {step}: cos {cos:.6f} rel_l2 {l2:.3e} ranks_identical {same}",
+                          flush=True)
+                if not (cos >= 0.999 and l2 <= 2e-2 and same):
+                    failures.append((li, tokens, step, cos, l2, same))
+    status = tilert_b200.device_status(local)
+    if status != 0:
+        failures.append(("device_status", status))
+    comm.close()
+    dist.destroy_process_group()
+    if failures:
+        print(f"rank {rank} FAILURES: {failures}", flush=True)
+        return 1
+    if rank == 0:
+        print("multi_gpu_check: OK", flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
