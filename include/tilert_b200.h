@@ -221,6 +221,28 @@ int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const void* q_pe, 
                                float softmax_scale, int split_size, void* out, float* out_acc, float* lse,
                                float* lse_acc, void* stream);
 
+/* ---- allocation-free product ------------------------------------------------------------ */
+
+/* No counterpart in the reference.  out[t, :] = W . x[t, :] (+ residual[t, :]) with the same FP8
+ * weight-streaming kernel as unproj_o_allreduce_op on one GPU, for callers that must not allocate
+ * device memory: code running under a host runtime that owns the whole memory pool and forbids
+ * cudaMalloc from plug-ins, or a serving loop with a frozen memory budget in which an allocation
+ * would synchronise the device.  It takes no TbContext (creating one allocates) and calls no
+ * cudaMalloc, cudaFree or allocating library routine.  Its scratch -- partial sums of row tiles
+ * shared by two thread blocks, and their arrival counters -- is a fixed ~2.1 MB array inside the
+ * library image, held by every GPU that loads the library until the process exits.
+ *
+ *   x [tokens, k] bf16, w_packed for [n, k], residual [tokens, n] bf16 or NULL, out [tokens, n] bf16;
+ *   tokens 1..4, k a multiple of 128, n at most 131072 rows (a larger n returns TB_EINVAL);
+ *   status_out_dev: optional device int that receives the kernel's status word (0 = completed).
+ *
+ * The first call on each device looks up the array's device address and sets a function
+ * attribute; make that call outside any stream capture.  All calls on a device share the one
+ * array: the counters are cleared at the start of every call, and two calls whose kernels overlap
+ * on the GPU (different streams) race on it -- serialise them. */
+int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_packed, const void* residual, int tokens, int k,
+                                  int n, void* out, int* status_out_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -806,3 +806,79 @@ extern "C" int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const v
   TB_CUDA(cudaGetLastError());
   return TB_OK;
 }
+
+// ------------------------------------------------------------ allocation-free entry point
+// Scratch for tilert_b200_matvec_fp8_static: partial sums of row tiles that straddle two CTAs
+// (2 * kMaxGrid slots of 4 KB), one arrival counter per 16-row group, and a status word.  It lives
+// in the library image, so every GPU that loads the library holds these ~2.1 MB until exit.
+namespace {
+constexpr int kStaticMaxTiles = 1024;                                   // rows <= 131072
+constexpr size_t kStaticCounterBytes = kStaticMaxTiles * 8 * sizeof(int);
+constexpr size_t kStaticScratchBytes = kPartialBytes + kStaticCounterBytes + 256;
+}  // namespace
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+struct StaticScratchView {
+  unsigned char* base = nullptr;  // DEVICE address of g_static_scratch on this device
+  int num_sms = 0;
+};
+StaticScratchView g_static_view[64];
+}  // namespace
+
+extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_packed, const void* residual,
+                                             int tokens, int k, int n, void* out, int* status_out_dev,
+                                             void* stream) {
+  TB_REQUIRE(x != nullptr && w_packed != nullptr && out != nullptr);
+  TB_REQUIRE(tokens >= 1 && tokens <= 4 && k > 0 && k % TB_KBLOCK == 0 && n > 0);
+  const int n_tiles = (n + TB_TILE_ROWS - 1) / TB_TILE_ROWS;
+  if (n_tiles > kStaticMaxTiles)
+    return fail(TB_EINVAL, "tilert_b200_matvec_fp8_static: n exceeds the static scratch (at most 131072 rows)%s");
+  TB_REQUIRE(static_cast<long long>(n_tiles) * (k / TB_KBLOCK) < (1ll << 30));
+  int device = 0;
+  TB_CUDA(cudaGetDevice(&device));
+  TB_REQUIRE(device >= 0 && device < 64);
+  StaticScratchView& view = g_static_view[device];
+  if (view.base == nullptr) {
+    // One-time set-up for this device (it must be the current device, which it is).  In host code
+    // the array's name is only a handle: the address a kernel can use comes from the runtime.
+    void* dev_addr = nullptr;
+    TB_CUDA(cudaGetSymbolAddress(&dev_addr, g_static_scratch));
+    int sms = 0;
+    TB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    TB_CUDA(cudaFuncSetAttribute(wstream_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBytes));
+    view.num_sms = sms;
+    view.base = static_cast<unsigned char*>(dev_addr);
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* partial = reinterpret_cast<float*>(view.base);
+  int* counters = reinterpret_cast<int*>(view.base + kPartialBytes);
+  int* status = reinterpret_cast<int*>(view.base + kPartialBytes + kStaticCounterBytes);
+  // The array keeps whatever the previous call left: the arrival counters and the status word must
+  // start at zero (a call that was cut short would otherwise leave them counting).
+  TB_CUDA(cudaMemsetAsync(counters, 0, kStaticCounterBytes + 256, st));
+  GemvParams p;
+  gemv_defaults(p);
+  p.w = w_packed;
+  set_x_bf16(p, x, k);
+  p.n_rows = n;
+  p.n_tiles = n_tiles;
+  p.n_kb = k / TB_KBLOCK;
+  p.w_kb_per_tile = p.n_kb;
+  p.n_tokens = tokens;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.residual_stride = n;
+  set_region(p, 0, n, out, n);
+  p.partial = partial;
+  p.counters = counters;
+  p.status = status;
+  const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
+  int grid = view.num_sms < kMaxGrid ? view.num_sms : kMaxGrid;
+  if (units < grid) grid = static_cast<int>(units);
+  wstream_gemv_kernel<<<grid, kGemvThreads, kGemvSmemBytes, st>>>(p);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  if (status_out_dev != nullptr)
+    TB_CUDA(cudaMemcpyAsync(status_out_dev, status, sizeof(int), cudaMemcpyDeviceToDevice, st));
+  return TB_OK;
+}
