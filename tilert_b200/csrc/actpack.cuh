@@ -43,6 +43,8 @@ __device__ __forceinline__ float pow2_ceil_scale(float amax) {
 
 // One CTA per token.
 __global__ void __launch_bounds__(kActPackThreads) actpack_kernel(const ActPackParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[32];
   const int tok = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -137,6 +139,8 @@ __global__ void __launch_bounds__(kActPackThreads) actpack_kernel(const ActPackP
 // -> X blocks in direct mode (one column per token).  One warp per k block.
 __global__ void xq_repack_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs, int n_tokens, int k,
                                  uint8_t* __restrict__ xpack) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int n_kb = k / TB_KBLOCK;
   const int kb = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;

@@ -3,8 +3,10 @@
 #include "../../include/tilert_b200.h"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
+#include <utility>
 
 #include "actpack.cuh"
 #include "elementwise.cuh"
@@ -35,6 +37,30 @@ int fail(int code, const char* fmt, const char* detail = "") {
   do {                   \
     if (!(cond)) return fail(TB_EINVAL, "requirement failed: %s", #cond); \
   } while (0)
+
+// Every kernel is launched with programmatic stream serialisation (see pdl_wait in common.cuh);
+// TILERT_B200_PDL=0 in the environment switches it off.
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("TILERT_B200_PDL");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 constexpr int kMaxGrid = 256;                       // CTAs a GEMV launch may use (>= SM count)
 constexpr size_t kPartialBytes = 2ull * kMaxGrid * 8 * 32 * 16;
@@ -85,7 +111,7 @@ int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
   p.counters = ctx->counters;
   p.status = ctx->status;
   p.prof = ctx->prof;
-  wstream_gemv_kernel<<<grid, kGemvThreads, kGemvSmemBytes, st>>>(p);
+  TB_CUDA(launch(wstream_gemv_kernel, dim3(grid), dim3(kGemvThreads), kGemvSmemBytes, st, p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;
@@ -137,7 +163,7 @@ void set_x_bf16(GemvParams& p, const void* x, long long stride, const float* gam
 int launch_actpack(const ActPackParams& p, cudaStream_t st) {
   TB_REQUIRE(p.k % TB_KBLOCK == 0 && p.k / TB_KBLOCK <= 32 * kActPackMaxIter);
   TB_REQUIRE(p.n_tokens >= 1 && p.n_tokens <= 4);
-  actpack_kernel<<<p.n_tokens, kActPackThreads, 0, st>>>(p);
+  TB_CUDA(launch(actpack_kernel, dim3(p.n_tokens), dim3(kActPackThreads), 0, st, p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;
@@ -476,9 +502,9 @@ extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (slot_ids == nullptr) slot_ids = reinterpret_cast<int*>(ctx->small);
   if (slot_w == nullptr) slot_w = reinterpret_cast<float*>(ctx->small + 4096);
-  expert_select_kernel<<<(tokens + 3) / 4, 128, 0, st>>>(scores, bias, n_experts, n_groups, n_limited_groups, top_k,
+  TB_CUDA(launch(expert_select_kernel, dim3((tokens + 3) / 4), dim3(128), 0, st, scores, bias, n_experts, n_groups, n_limited_groups, top_k,
                                                          route_scale, n_experts, probs_out, idx_out, slot_ids,
-                                                         slot_w, tokens);
+                                                         slot_w, tokens));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   const int n_slots = top_k + 1;
@@ -597,17 +623,17 @@ int launch_gemv_bf16(TbContext* ctx, GemvBf16Params& p, cudaStream_t st) {
     }
     const int g2 = (p.n + kGemvBf16SmallRows - 1) / kGemvBf16SmallRows;
     if (tok_t == 1)
-      gemv_bf16_ksplit_kernel<1><<<g2, kGemvBf16SmallThreads, smem, st>>>(p);
+      TB_CUDA(launch(gemv_bf16_ksplit_kernel<1>, dim3(g2), dim3(kGemvBf16SmallThreads), smem, st, p));
     else if (tok_t == 2)
-      gemv_bf16_ksplit_kernel<2><<<g2, kGemvBf16SmallThreads, smem, st>>>(p);
+      TB_CUDA(launch(gemv_bf16_ksplit_kernel<2>, dim3(g2), dim3(kGemvBf16SmallThreads), smem, st, p));
     else
-      gemv_bf16_ksplit_kernel<4><<<g2, kGemvBf16SmallThreads, smem, st>>>(p);
+      TB_CUDA(launch(gemv_bf16_ksplit_kernel<4>, dim3(g2), dim3(kGemvBf16SmallThreads), smem, st, p));
   } else if (tok_t == 1)
-    gemv_bf16_kernel<1><<<grid, kGemvBf16Threads, smem, st>>>(p);
+    TB_CUDA(launch(gemv_bf16_kernel<1>, dim3(grid), dim3(kGemvBf16Threads), smem, st, p));
   else if (tok_t == 2)
-    gemv_bf16_kernel<2><<<grid, kGemvBf16Threads, smem, st>>>(p);
+    TB_CUDA(launch(gemv_bf16_kernel<2>, dim3(grid), dim3(kGemvBf16Threads), smem, st, p));
   else
-    gemv_bf16_kernel<4><<<grid, kGemvBf16Threads, smem, st>>>(p);
+    TB_CUDA(launch(gemv_bf16_kernel<4>, dim3(grid), dim3(kGemvBf16Threads), smem, st, p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;
@@ -738,11 +764,11 @@ extern "C" int tilert_sparse_index_op(TbContext* ctx, const void* q, const void*
   const __nv_bfloat16* kk = reinterpret_cast<const __nv_bfloat16*>(k_cache);
   const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(weights);
   if (heads == 64)
-    indexer_logits_kernel<64><<<grid, kIdxWarps * 32, smem, st>>>(qq, kk, ww, logits, logits_stride, n_keys, cur_pos, 0);
+    TB_CUDA(launch(indexer_logits_kernel<64>, dim3(grid), dim3(kIdxWarps * 32), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, 0));
   else if (heads == 32)
-    indexer_logits_kernel<32><<<grid, kIdxWarps * 32, smem, st>>>(qq, kk, ww, logits, logits_stride, n_keys, cur_pos, 0);
+    TB_CUDA(launch(indexer_logits_kernel<32>, dim3(grid), dim3(kIdxWarps * 32), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, 0));
   else
-    indexer_logits_kernel<16><<<grid, kIdxWarps * 32, smem, st>>>(qq, kk, ww, logits, logits_stride, n_keys, cur_pos, 0);
+    TB_CUDA(launch(indexer_logits_kernel<16>, dim3(grid), dim3(kIdxWarps * 32), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, 0));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;
@@ -797,11 +823,11 @@ extern "C" int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const v
   p.lse_acc = lse_acc;
   p.status = ctx->status;
   const dim3 grid(p.n_splits, (heads + kMlaHeads - 1) / kMlaHeads, tokens);
-  sparse_mla_kernel<<<grid, kMlaThreads, kMlaSmemBytes, st>>>(p);
+  TB_CUDA(launch(sparse_mla_kernel, dim3(grid), dim3(kMlaThreads), kMlaSmemBytes, st, p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
-  sparse_mla_combine_kernel<<<dim3(heads, tokens), 128, 0, st>>>(out_acc, lse_acc, p.n_splits,
-                                                                 reinterpret_cast<__nv_bfloat16*>(out), lse);
+  TB_CUDA(launch(sparse_mla_combine_kernel, dim3(dim3(heads, tokens)), dim3(128), 0, st, out_acc, lse_acc, p.n_splits,
+                                                                 reinterpret_cast<__nv_bfloat16*>(out), lse));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;
@@ -875,7 +901,7 @@ extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_pac
   const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
   int grid = view.num_sms < kMaxGrid ? view.num_sms : kMaxGrid;
   if (units < grid) grid = static_cast<int>(units);
-  wstream_gemv_kernel<<<grid, kGemvThreads, kGemvSmemBytes, st>>>(p);
+  TB_CUDA(launch(wstream_gemv_kernel, dim3(grid), dim3(kGemvThreads), kGemvSmemBytes, st, p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   if (status_out_dev != nullptr)

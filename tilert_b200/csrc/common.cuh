@@ -36,6 +36,15 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// ---- programmatic dependent launch ----
+// Kernels are launched with programmatic stream serialisation: a kernel may start while its
+// predecessor in the stream is still running.  `pdl_wait` blocks until the predecessor has completed
+// and its memory is visible (nothing produced by earlier kernels may be read, and nothing they might
+// still read or write may be written, before it); `pdl_launch_dependents` lets the successor start.
+// Both are no-ops in a launch without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier ----
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));

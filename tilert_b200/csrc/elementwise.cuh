@@ -11,6 +11,8 @@ namespace tb {
 __global__ void rmsnorm_kv_kernel(const __nv_bfloat16* __restrict__ kv, long long kv_stride,
                                   const float* __restrict__ gamma, float eps, int dim, const int* __restrict__ pos,
                                   __nv_bfloat16* __restrict__ cache, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (tok >= n_tokens) return;
@@ -31,6 +33,8 @@ __global__ void rmsnorm_kv_kernel(const __nv_bfloat16* __restrict__ kv, long lon
 __global__ void qkv_rope_kernel(__nv_bfloat16* __restrict__ q_pe, int heads, int rope,
                                 __nv_bfloat16* __restrict__ pe_cache, const int* __restrict__ pos,
                                 const float* __restrict__ freqs, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int half = rope / 2;
   const int per_tok = (heads + 1) * half;
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -73,6 +77,8 @@ __device__ __forceinline__ void hadamard128(float (&v)[4]) {
 __global__ void rotate128_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int heads,
                                  int rope, const float* __restrict__ freqs, const float* __restrict__ ln_w,
                                  const float* __restrict__ ln_b, const int* __restrict__ pos, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int vec = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (vec >= n_tokens * heads) return;
@@ -123,6 +129,8 @@ __global__ void expert_select_kernel(const float* __restrict__ scores, const flo
                                      int n_experts, int n_groups, int n_limited, int top_k, float route_scale,
                                      int shared_id, float* __restrict__ probs, int* __restrict__ ids,
                                      int* __restrict__ slot_ids, float* __restrict__ slot_w, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (tok >= n_tokens) return;

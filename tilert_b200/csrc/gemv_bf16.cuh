@@ -29,6 +29,8 @@ constexpr int kGemvBf16Threads = 512;
 
 template <int TOK>
 __global__ void __launch_bounds__(kGemvBf16Threads) gemv_bf16_kernel(const GemvBf16Params p) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) float xs[];  // [TOK][k]
   __shared__ float red[TOK][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -128,6 +130,8 @@ constexpr int kGemvBf16SmallRows = 2;
 
 template <int TOK>
 __global__ void __launch_bounds__(kGemvBf16SmallThreads) gemv_bf16_ksplit_kernel(const GemvBf16Params p) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) float xs[];  // [TOK][k]
   __shared__ float red[TOK][8];
   __shared__ float part[kGemvBf16SmallRows][TOK][8];

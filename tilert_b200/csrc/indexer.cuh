@@ -27,6 +27,8 @@ __global__ void __launch_bounds__(kIdxWarps * 32) indexer_logits_kernel(
     long long logits_stride, int n_keys,       // keys scored: t in [0, n_keys)
     const int* __restrict__ pos, int pos_offset  // token s may see keys t <= *pos + pos_offset + s
 ) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [H][pitch]
   __nv_bfloat16* sk = sq + H * kIdxPitch;                          // [64][pitch]
@@ -111,6 +113,8 @@ constexpr int kTopkItems = 8;  // consecutive elements per thread in the ordered
 __global__ void __launch_bounds__(kTopkThreads) topk_radix_kernel(const float* __restrict__ logits,
                                                                   long long logits_stride, int n, int k,
                                                                   int* __restrict__ out, long long out_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ int hist[256];
   __shared__ uint32_t s_prefix;
   __shared__ int s_remaining;

@@ -40,6 +40,8 @@ struct MlaParams {
 };
 
 __global__ void __launch_bounds__(kMlaThreads) sparse_mla_kernel(const MlaParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(128) uint8_t smem[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);
   __nv_bfloat16* sKV = sQ + kMlaHeads * kMlaPitch;
@@ -236,6 +238,8 @@ __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float* __
                                                                  const float* __restrict__ lse_acc, int n_splits,
                                                                  __nv_bfloat16* __restrict__ out,
                                                                  float* __restrict__ lse_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float s_w[64];
   __shared__ float s_den, s_mx;
   const int head = blockIdx.x, tok = blockIdx.y, heads = gridDim.x;

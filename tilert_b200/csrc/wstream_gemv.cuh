@@ -207,6 +207,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
   const int u0 = static_cast<int>(gemv_range_begin(units, grid, cta));
   const int u1 = static_cast<int>(gemv_range_begin(units, grid, cta + 1));
 
+  // The successor may start right away.  Weight prefetch does not depend on the predecessor, so only
+  // threads that read activations / routing ids / residuals or write results wait for it (below).
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     gemv_stamp(p, kGemvProfEntry);
     for (int s = 0; s < kGemvStages; ++s) {
@@ -221,6 +224,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
 
   const bool is_consumer = warp < kGemvConsumerWarps;
   const bool is_producer = !is_consumer && warp < kGemvConsumerWarps + kGemvProducerWarps;
+  // Producers stream weights, which no kernel of the step writes; they wait for the predecessor only
+  // when their addresses depend on it (routing ids) or when they also copy packed activations.
+  if (!is_producer || p.x_mode == X_PACKED || p.nseg_ids != nullptr || p.kseg_ids != nullptr) pdl_wait();
   if (p.x_mode == X_BF16 && p.gamma != nullptr && !is_producer) {
     // RMSNorm statistics of the activation vector(s): the non-producer warps split the vector
     // (the producers are already filling the ring), partial sums meet in shared memory.
