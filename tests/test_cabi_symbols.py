@@ -52,11 +52,11 @@ def test_weight_pack_round_trip_and_fragment_map():
     w2, rs = pack.unpack_rows(p, 576)
     assert torch.equal(w2, w) and torch.equal(rs, pack.row_scales(s, 576))
     # the documented byte map of a W block (tilert_b200/csrc/formats.h)
-    for t, kb, wv, c, lane, r, b in [(0, 0, 0, 0, 0, 0, 0), (4, 7, 3, 2, 17, 3, 1), (2, 5, 7, 3, 31, 2, 3)]:
-        row = t * 128 + 16 * wv + lane // 4 + 8 * (r & 1)
-        col = kb * 128 + 32 * c + 16 * (r >> 1) + 4 * (lane % 4) + b
+    for t, kb, c, rg, kc, r, b in [(0, 0, 0, 0, 0, 0, 0), (4, 7, 3, 9, 1, 5, 13), (2, 5, 2, 15, 0, 7, 3)]:
+        row = t * 128 + rg * 8 + r
+        col = kb * 128 + 32 * c + 16 * kc + b
         exp = int(w[row, col]) if row < 576 else 0
-        assert int(p[t, kb, ((wv * 4 + c) * 32 + lane) * 16 + 4 * r + b]) == exp
+        assert int(p[t, kb, c * 4096 + rg * 256 + kc * 128 + r * 16 + b]) == exp
 
 
 def test_gate_up_interleave_and_absorb_transpose():

@@ -68,8 +68,8 @@ def rn(gen, *shape, scale=1.0):
 def decode_xpack(xp: torch.Tensor, n_kb: int, cols: int) -> torch.Tensor:
     """Host model of the X-block format: returns f32 [cols, n_kb*128] = e4m3 value * column scale."""
     blk = xp.cpu().view(n_kb, 1056)
-    data = blk[:, :1024].reshape(n_kb, 4, 8, 4, 2, 4)          # kb, c, col, q, r, b
-    vals = data.permute(2, 0, 1, 4, 3, 5).reshape(8, n_kb, 128)  # col, kb, (c, r, q, b)
+    data = blk[:, :1024].reshape(n_kb, 4, 2, 8, 16)            # kb, c, kc, col, b
+    vals = data.permute(3, 0, 1, 2, 4).reshape(8, n_kb, 128)     # col, kb, (c, kc, b)
     scales = blk[:, 1024:].contiguous().view(torch.float32).view(n_kb, 8).t()  # col, kb
     f = vals.contiguous().view(torch.float8_e4m3fn).float() * scales[:, :, None]
     return f.reshape(8, n_kb * 128)[:cols]

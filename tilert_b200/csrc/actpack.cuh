@@ -123,8 +123,8 @@ __global__ void __launch_bounds__(kActPackThreads) actpack_kernel(const ActPackP
     uint8_t* blk = p.xpack + static_cast<long long>(kb) * TB_XBLK_BYTES;
     const int c = lane >> 3, r = (lane >> 2) & 1, q = lane & 3;
     const int col_hi = 2 * tok, col_lo = 2 * tok + 1;
-    *reinterpret_cast<uint32_t*>(blk + (c * 32 + col_hi * 4 + q) * 8 + 4 * r) = whi;
-    *reinterpret_cast<uint32_t*>(blk + (c * 32 + col_lo * 4 + q) * 8 + 4 * r) = wlo;
+    *reinterpret_cast<uint32_t*>(blk + c * 256 + r * 128 + col_hi * 16 + q * 4) = whi;
+    *reinterpret_cast<uint32_t*>(blk + c * 256 + r * 128 + col_lo * 16 + q * 4) = wlo;
     if (lane == 0) {
       float m = 1.f;
       if (p.seg_scale != nullptr) m = p.seg_scale[tok * p.n_seg + kb / p.kb_per_seg];
@@ -151,7 +151,7 @@ __global__ void xq_repack_kernel(const uint8_t* __restrict__ xq, const float* __
     uint32_t w = 0;
     if (tok < n_tokens)
       w = *reinterpret_cast<const uint32_t*>(xq + static_cast<long long>(tok) * k + kb * TB_KBLOCK + lane * 4);
-    *reinterpret_cast<uint32_t*>(blk + (c * 32 + tok * 4 + q) * 8 + 4 * r) = w;
+    *reinterpret_cast<uint32_t*>(blk + c * 256 + r * 128 + tok * 16 + q * 4) = w;
     if (lane == 0) reinterpret_cast<float*>(blk + TB_XBLK_DATA)[tok] = tok < n_tokens ? xs[tok * n_kb + kb] : 0.f;
   }
 }

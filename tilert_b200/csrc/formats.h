@@ -2,12 +2,11 @@
 //
 // Weight block ("W block"): one 128-row x 128-column e4m3 tile of a weight matrix plus its
 // dequantisation scales, laid out so that one bulk copy brings a whole pipeline stage into
-// shared memory and every warp reads its m16n8k32 A fragments with one conflict-free 16-byte
-// load per lane:
+// shared memory in the form the tensor core reads through a shared-memory descriptor (K-major,
+// no swizzle: 8-row x 16-byte "core matrices" of 128 contiguous bytes):
 //
-//   byte ((w*4 + c)*32 + lane)*16 + 4*r + b   holds   W[row, col]   with
-//       row = 16*w + (lane/4) + 8*(r&1),   col = 32*c + 16*(r>>1) + 4*(lane%4) + b
-//   for warp w in 0..7 (16 rows each), k-chunk c in 0..3, register r in 0..3, byte b in 0..3;
+//   byte c*4096 + (row/8)*256 + kc*128 + (row%8)*16 + b   holds   W[row, 32*c + 16*kc + b]
+//   for k chunk c in 0..3 (one MMA each), core column kc in 0..1, b in 0..15;
 //   bytes 16384 .. 16447: 16 f32 scales, one per group of 8 consecutive packed rows.
 //
 // A matrix [N, K] is stored as blocks in (row tile, k block) order, the k blocks of one
@@ -15,10 +14,9 @@
 // as each aligned group of 8 packed rows shares one source scale.
 //
 // Activation block ("X block"): the 128 activations of one k block for up to 8 columns
-// (tokens, or hi/lo halves of tokens), in m16n8k32 B-fragment order, plus one f32 scale per
-// column:
+// (tokens, or hi/lo halves of tokens) in the same core-matrix form, plus one f32 scale per column:
 //
-//   byte (c*32 + lane)*8 + 4*r + b   holds   X[col = lane/4, k = 32*c + 16*r + 4*(lane%4) + b]
+//   byte c*256 + kc*128 + col*16 + b   holds   X[col, k = 32*c + 16*kc + b]
 //   bytes 1024 .. 1055: 8 f32 column scales.
 //
 // In "split" mode column 2t holds the leading e4m3 term of token t and column 2t+1 the e4m3

@@ -6,10 +6,11 @@
 // HBM-bound: every weight byte is read exactly once.  One persistent CTA per SM walks a
 // contiguous range of (row tile, k block) units (stream-K).  A producer thread stages each
 // unit -- one 16448-byte W block and one 1056-byte X block -- into a shared-memory ring with
-// bulk async copies (TMA) that complete on mbarriers.  Each ring slot is consumed by TWO warps
-// (64 rows each), which feed the e4m3 bytes straight into m16n8k32 tensor-core MMAs and apply
-// (weight scale x column scale) in f32 registers once per k block; eight consumer warps work on
-// four slots at a time and meet in shared memory when a row tile is complete.  Row tiles that
+// bulk async copies (TMA) that complete on mbarriers.  One thread issues the tensor-core work: per
+// unit four tcgen05.mma (M = 128 weight rows x N = 16 x K = 32, e4m3 operands read straight from
+// the slot through shared-memory descriptors; 8 real activation columns) into one of four TMEM
+// accumulators.  Four epilogue warps (one thread per weight row) read each accumulator back with
+// tcgen05.ld and apply (weight scale x column scale) in f32 registers once per k block.  Row tiles that
 // straddle two CTAs are finished by the last arriver, which adds the partials in CTA order, so
 // the result does not depend on timing.
 #pragma once
@@ -114,15 +115,53 @@ __device__ __forceinline__ void gemv_stamp(const GemvParams& p, int slot) {
 #define TB_GEMV_STAGES 12
 #endif
 constexpr int kGemvStages = TB_GEMV_STAGES;  // multiple of kGemvProducerWarps
-constexpr int kGemvConsumerWarps = 8;   // unit i is consumed by warps i % 4 (rows 0-63) and 4 + i % 4 (rows 64-127)
-constexpr int kGemvProducerWarps = 4;   // one issuing thread each; unit i is issued by producer i % 4
-constexpr int kGemvConverterWarps = 2;  // unit i is converted by converter i % 2 (X_BF16 only)
-constexpr int kGemvConsumerThreads = kGemvConsumerWarps * 32;
-constexpr int kGemvHelperWarps = kGemvConsumerWarps + kGemvConverterWarps;  // warps that are not producers
-constexpr int kGemvThreads = (kGemvConsumerWarps + kGemvProducerWarps + kGemvConverterWarps) * 32;
-constexpr int kGemvRedBytes = kGemvConsumerWarps * 4 * 32 * 16;  // per-tile cross-warp reduction buffer
-constexpr int kGemvSmemBytes =
-    kGemvStages * TB_STAGE_BYTES + kGemvRedBytes + 2 * kGemvStages * 8 + 16 + kGemvHelperWarps * 4 * 4 + 32;
+constexpr int kGemvAccs = 4;            // TMEM accumulators in flight
+constexpr int kGemvAccCols = 16;        // columns per accumulator: N = 16 is the smallest N at M = 128
+constexpr int kGemvTmemCols = 64;       // kGemvAccs * kGemvAccCols, a power of two >= 32
+constexpr int kGemvEpilogueWarps = 4;   // warps 0-3: TMEM lanes 32w .. 32w+31 = weight rows of the tile
+constexpr int kGemvProducerWarps = 4;   // warps 5-8: one issuing thread each; unit i is issued by producer i % 4
+constexpr int kGemvConverterWarps = 2;  // warps 9-10: unit i is converted by converter i % 2 (X_BF16 only)
+constexpr int kGemvEpilogueThreads = kGemvEpilogueWarps * 32;
+constexpr int kGemvMmaWarp = kGemvEpilogueWarps;  // warp 4: TMEM owner, one lane issues the MMAs
+constexpr int kGemvHelperWarps = kGemvEpilogueWarps + kGemvConverterWarps;  // warps that share the norm prologue
+constexpr int kGemvThreads = (kGemvEpilogueWarps + 1 + kGemvProducerWarps + kGemvConverterWarps) * 32;
+constexpr int kGemvBarBytes = (2 * kGemvStages + 2 * kGemvAccs) * 8;
+constexpr int kGemvSmemBytes = kGemvStages * TB_STAGE_BYTES + kGemvBarBytes + 16 + kGemvHelperWarps * 4 * 4 + 32;
+
+// ---- tcgen05 helpers ----
+// Shared-memory operand descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; `lbo` =
+// bytes between the two core matrices along K, `sbo` = bytes between 8-row groups.
+__device__ __forceinline__ uint64_t umma_desc(const void* smem_ptr, uint32_t lbo, uint32_t sbo) {
+  return static_cast<uint64_t>((smem_u32(smem_ptr) >> 4) & 0x3fffu) | (static_cast<uint64_t>(lbo >> 4) << 16) |
+         (static_cast<uint64_t>(sbo >> 4) << 32) | (1ull << 46);
+}
+// Instruction descriptor: D = f32, A = B = e4m3, both K-major, N = 16, M = 128.  Only 8 activation
+// columns exist: the B descriptor's 8-column group stride is 0, so columns 8-15 repeat columns 0-7
+// and are never read back.
+constexpr uint32_t kUmmaIdesc = (1u << 4) | (2u << 17) | (8u << 24);
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kUmmaIdesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&d)[8]) {
+  uint32_t r[8];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) d[i] = __uint_as_float(r[i]);
+}
 
 __device__ __forceinline__ long long gemv_range_begin(long long units, int grid, int cta) {
   return units * cta / grid;
@@ -150,53 +189,64 @@ __device__ __forceinline__ void gemv_store(const GemvParams& p, int row, int tok
   }
 }
 
-// Final values of one warp's 16 rows x 8 columns (m16n8 accumulator layout).
-__device__ __forceinline__ void gemv_epilogue(const GemvParams& p, int tile, int warp, int lane,
-                                              const float (&v)[4], int ar_half) {
-  const int g = lane >> 2, q = lane & 3;
-  const int n16 = tile * 8 + warp;
-  float lo[2], hi[2];
-  int tok[2], ntok;
+// Final values of one weight row (8 accumulator columns) of row tile `tile`; the calling warp holds
+// rows 32*warp .. 32*warp+31 of the tile, one per lane.
+__device__ __forceinline__ void gemv_epilogue_row(const GemvParams& p, int tile, int warp, int lane,
+                                                  const float (&v)[8], int ar_half) {
+  const int row_in_tile = warp * 32 + lane;
+  float val[8];
+  int ntok;
   if (p.cols_per_token == 2) {
-    lo[0] = v[0] + v[1];
-    hi[0] = v[2] + v[3];
-    tok[0] = q;
-    ntok = 1;
+    ntok = 4;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) val[t] = v[2 * t] + v[2 * t + 1];
   } else {
-    lo[0] = v[0]; lo[1] = v[1];
-    hi[0] = v[2]; hi[1] = v[3];
-    tok[0] = 2 * q; tok[1] = 2 * q + 1;
-    ntok = 2;
+    ntok = 8;
+#pragma unroll
+    for (int t = 0; t < 8; ++t) val[t] = v[t];
   }
-  for (int i = 0; i < ntok; ++i) {
-    if (p.epi == EPI_SILU_MUL) {
-      const float gate = lo[i], up = hi[i];
-      const float h = gate / (1.0f + __expf(-gate)) * up;
-      gemv_store(p, n16 * 8 + g, tok[i], h);
-    } else if (p.ar.world > 1) {
-      // push this rank's partial into every rank's receive slot (plain peer stores)
-      const int par = ar_half;
-      if (tok[i] < p.n_tokens) {
-        const long long base = ((static_cast<long long>(par) * p.ar.world + p.ar.rank) * 4 + tok[i]) * p.n_rows;
-        const int r0 = n16 * 16 + g, r1 = r0 + 8;
-        for (int pr = 0; pr < p.ar.world; ++pr) {
-          if (r0 < p.n_rows) p.ar.recv[pr][base + r0] = lo[i];
-          if (r1 < p.n_rows) p.ar.recv[pr][base + r1] = hi[i];
+  if (p.epi == EPI_SILU_MUL) {
+    // every 16 packed rows are 8 gate rows followed by their 8 up rows: lane l (bit 3 clear) pairs with l + 8
+    const int n16 = (tile * TB_TILE_ROWS + row_in_tile) >> 4;
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      if (t < ntok) {
+        const float up = __shfl_xor_sync(0xffffffffu, val[t], 8);
+        if ((lane & 8) == 0) {
+          const float gate = val[t];
+          gemv_store(p, n16 * 8 + (lane & 7), t, gate / (1.0f + __expf(-gate)) * up);
         }
       }
-    } else {
-      gemv_store(p, n16 * 16 + g, tok[i], lo[i]);
-      gemv_store(p, n16 * 16 + g + 8, tok[i], hi[i]);
     }
+    return;
   }
+  const int row = tile * TB_TILE_ROWS + row_in_tile;
+  if (p.ar.world > 1) {
+    // push this rank's partial into every rank's receive slot (plain peer stores)
+    if (row < p.n_rows) {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        if (t < ntok && t < p.n_tokens) {
+          const long long idx = ((static_cast<long long>(ar_half) * p.ar.world + p.ar.rank) * 4 + t) * p.n_rows + row;
+          for (int pr = 0; pr < p.ar.world; ++pr) p.ar.recv[pr][idx] = val[t];
+        }
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int t = 0; t < 8; ++t)
+    if (t < ntok) gemv_store(p, row, t, val[t]);
 }
 
 __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  float4* red = reinterpret_cast<float4*>(smem + kGemvStages * TB_STAGE_BYTES);  // [warp][n16 tile][lane]
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGemvStages * TB_STAGE_BYTES + kGemvRedBytes);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGemvStages * TB_STAGE_BYTES);
   uint64_t* empty = full + kGemvStages;
-  volatile int* cta_error = reinterpret_cast<volatile int*>(empty + kGemvStages);
+  uint64_t* acc_full = empty + kGemvStages;
+  uint64_t* acc_empty = acc_full + kGemvAccs;
+  volatile int* cta_error = reinterpret_cast<volatile int*>(acc_empty + kGemvAccs);
+  volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(const_cast<int*>(cta_error) + 1);
   float* norm_part = reinterpret_cast<float*>(const_cast<int*>(cta_error) + 4);  // [helper warps][4 tokens]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -214,23 +264,41 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     gemv_stamp(p, kGemvProfEntry);
     for (int s = 0; s < kGemvStages; ++s) {
       mbar_init(&full[s], p.x_mode == X_BF16 ? 2 : 1);  // producer (+ converter) arrive once per use
-      mbar_init(&empty[s], 2);                          // the two consumer warps of the slot
+      mbar_init(&empty[s], 1 + kGemvEpilogueWarps);     // MMA completion + the epilogue warps' scale reads
+    }
+    for (int a = 0; a < kGemvAccs; ++a) {
+      mbar_init(&acc_full[a], 1);                       // MMA completion
+      mbar_init(&acc_empty[a], kGemvEpilogueWarps);     // accumulator read back by the four warps
     }
     *cta_error = 0;
     mbar_fence_init();
   }
+  if (warp == kGemvMmaWarp) {
+    // tensor memory: kGemvTmemCols columns for this CTA (the whole warp executes the allocation)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(const_cast<uint32_t*>(tmem_base_slot))),
+                 "r"(kGemvTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
   if (threadIdx.x == 0) gemv_stamp(p, kGemvProfReady);
 
-  const bool is_consumer = warp < kGemvConsumerWarps;
-  const bool is_producer = !is_consumer && warp < kGemvConsumerWarps + kGemvProducerWarps;
+  const bool is_epilogue = warp < kGemvEpilogueWarps;
+  const bool is_mma = warp == kGemvMmaWarp;
+  const bool is_producer = warp > kGemvMmaWarp && warp <= kGemvMmaWarp + kGemvProducerWarps;
+  const bool is_converter = warp > kGemvMmaWarp + kGemvProducerWarps;
   // Producers stream weights, which no kernel of the step writes; they wait for the predecessor only
   // when their addresses depend on it (routing ids) or when they also copy packed activations.
   if (!is_producer || p.x_mode == X_PACKED || p.nseg_ids != nullptr || p.kseg_ids != nullptr) pdl_wait();
-  if (p.x_mode == X_BF16 && p.gamma != nullptr && !is_producer) {
-    // RMSNorm statistics of the activation vector(s): the non-producer warps split the vector
-    // (the producers are already filling the ring), partial sums meet in shared memory.
-    const int hw = is_consumer ? warp : warp - kGemvProducerWarps;
+
+  if (p.x_mode == X_BF16 && p.gamma != nullptr && (is_epilogue || is_converter)) {
+    // RMSNorm statistics of the activation vector(s): the epilogue and converter warps split the
+    // vector (the producers are already filling the ring), partial sums meet in shared memory.
+    const int hw = is_epilogue ? warp : warp - 1 - kGemvProducerWarps;
     const int n_chunks = p.n_kb * (TB_KBLOCK / 4);  // 8-byte chunks per token
     float ss[4] = {0.f, 0.f, 0.f, 0.f};
     for (int ch = hw * 32 + lane; ch < n_chunks; ch += kGemvHelperWarps * 32) {
@@ -257,7 +325,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     // Four warps, one issuing thread each; unit i of the CTA's range is issued by producer i % 4
     // into ring slot i % kGemvStages, so no single thread's instruction latency paces the stream.
     if (lane == 0) {
-      const int pw = warp - kGemvConsumerWarps;
+      const int pw = warp - kGemvMmaWarp - 1;
       const uint64_t pol = policy_evict_first();
       int last_i = -1;
       int t = (u0 + pw) / p.n_kb, kb = (u0 + pw) % p.n_kb;
@@ -309,12 +377,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         mbar_wait(&full[i % kGemvStages], static_cast<uint32_t>(i / kGemvStages) & 1);
       }
     }
-  } else if (!is_consumer) {
+  } else if (is_converter) {
     // ------------------------------------------------- activation converters (X_BF16 only)
     // Two warps take alternate units.  Each converts the 128 activations of its unit, for every
     // token, into the two-term e4m3 X block of the stage: power-of-two scales, so the scaling is a
     // multiplication and the residual x - hi*s is exact.
-    const int cw = warp - (kGemvConsumerWarps + kGemvProducerWarps);  // 0 or 1
+    const int cw = warp - (kGemvEpilogueWarps + 1 + kGemvProducerWarps);  // 0 or 1
     if (p.x_mode == X_BF16 && u0 + cw < u1) {
       const int ntok = p.n_tokens;
       float rinv[4] = {1.f, 1.f, 1.f, 1.f};
@@ -398,8 +466,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
                 __nv_cvt_float2_to_fp8x2(make_float2(r2 * inv_lo, r3 * inv_lo), __NV_SATFINITE, __NV_E4M3);
             const uint32_t whi = static_cast<uint32_t>(h01) | (static_cast<uint32_t>(h23) << 16);
             const uint32_t wlo = static_cast<uint32_t>(l01) | (static_cast<uint32_t>(l23) << 16);
-            *reinterpret_cast<uint32_t*>(blk + (c * 32 + (2 * tk) * 4 + q4) * 8 + 4 * r) = whi;
-            *reinterpret_cast<uint32_t*>(blk + (c * 32 + (2 * tk + 1) * 4 + q4) * 8 + 4 * r) = wlo;
+            *reinterpret_cast<uint32_t*>(blk + c * 256 + r * 128 + (2 * tk) * 16 + q4 * 4) = whi;
+            *reinterpret_cast<uint32_t*>(blk + c * 256 + r * 128 + (2 * tk + 1) * 16 + q4 * 4) = wlo;
             if (lane == 0) {
               float mlt = 1.f;
               if (p.seg_scale != nullptr) mlt = p.seg_scale[tk * (p.n_kb / p.kb_per_kseg) + kb / p.kb_per_kseg];
@@ -407,6 +475,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
             }
           }
         }
+        // the X block was written through the generic proxy and is read by the tensor core (async proxy)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(&full[s]);
@@ -416,146 +486,157 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         x1 = x2;
       }
     }
+  } else if (is_mma) {
+    // ------------------------------------------------------------ tensor-core issue
+    // One thread.  Per unit: wait for the slot (weights landed, X block written) and for a free
+    // accumulator, issue four K = 32 MMAs into it, then let the hardware signal both "slot no longer
+    // read" and "accumulator complete" when they have finished.
+    if (lane == 0) {
+      for (int u = u0; u < u1; ++u) {
+        const int i = u - u0;
+        const int s = i % kGemvStages, a = i % kGemvAccs;
+        if (!mbar_wait(&full[s], static_cast<uint32_t>(i / kGemvStages) & 1) ||
+            (i >= kGemvAccs && !mbar_wait(&acc_empty[a], static_cast<uint32_t>(i / kGemvAccs - 1) & 1))) {
+          set_status(p.status, ST_WAIT_FULL_TIMEOUT);
+          *cta_error = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint8_t* sw = smem + s * TB_STAGE_BYTES;
+        const uint8_t* sx = sw + TB_WBLK_BYTES;
+        const uint32_t d = tmem_base + static_cast<uint32_t>(a * kGemvAccCols);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          umma_f8(d, umma_desc(sw + c * 4096, 128, 256), umma_desc(sx + c * 256, 128, 0), c > 0 ? 1u : 0u);
+        umma_commit(&empty[s]);
+        umma_commit(&acc_full[a]);
+      }
+    }
   } else {
-    // ------------------------------------------------------------ consumers
-    // Warps w and w + 4 consume units u0 + w, u0 + w + 4, ... (w < 4): rows 0-63 and 64-127 of each
-    // 128 x 128 block, four 16-row groups per warp sharing the activation fragments.  When a row tile
-    // is complete -- or the CTA's range ends inside it -- the warps add their accumulators through
-    // shared memory and warp w finishes 16-row group w.
-    const int q = lane & 3;
-    const int wq = warp & 3, half = warp >> 2;
+    // ------------------------------------------------------------ epilogue warps
+    // Thread (warp w, lane l) owns weight row 32w + l of the current row tile: eight f32 sums, one
+    // per activation column.  Per unit it reads its row's scale and the column scales from the slot,
+    // then the unit's accumulator from TMEM, and adds scale * accumulator.
     unsigned long long ar_epoch = 0;
     if (p.ar.world > 1) ar_epoch = *reinterpret_cast<volatile unsigned long long*>(&p.ar.state[p.ar.rank]->epoch);
     const int ar_half = static_cast<int>(ar_epoch & 1ull);
-    float acc[4][4];
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    float out[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int c = 0; c < 8; ++c) out[c] = 0.f;
     bool ok = true;
     long long prof_wait = 0, prof_math = 0, prof_units = 0;
 
-    // Adds the warps' accumulators of row tile t and finishes this warp's 16-row group.
     auto finish_tile = [&](int t) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        red[(warp * 4 + j) * 32 + lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
-        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerThreads) : "memory");
-      // 16-row group `warp` = local group wq of half `half`: partial sums sit with the four warps of that half
-      float out[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int w2 = 0; w2 < 4; ++w2) {
-        const float4 v = red[((half * 4 + w2) * 4 + wq) * 32 + lane];
-        out[0] += v.x; out[1] += v.y; out[2] += v.z; out[3] += v.w;
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerThreads) : "memory");  // red may be rewritten
       const int tile_u0 = t * p.n_kb, tile_u1 = tile_u0 + p.n_kb;
-      const int n16 = warp;  // 16-row group inside the tile
       if (u0 <= tile_u0 && u1 >= tile_u1) {
-        gemv_epilogue(p, t, n16, lane, out, ar_half);
+        gemv_epilogue_row(p, t, warp, lane, out, ar_half);
       } else {
         const int c_first = gemv_owner(tile_u0, units, grid);
         const int c_last = gemv_owner(tile_u1 - 1, units, grid);
         const int my_slot = 2 * cta + ((u0 / p.n_kb) == t ? 0 : 1);
         float4* part = reinterpret_cast<float4*>(p.partial);
-        part[(my_slot * 8 + n16) * 32 + lane] = make_float4(out[0], out[1], out[2], out[3]);
+        part[((my_slot * 4 + warp) * 32 + lane) * 2] = make_float4(out[0], out[1], out[2], out[3]);
+        part[((my_slot * 4 + warp) * 32 + lane) * 2 + 1] = make_float4(out[4], out[5], out[6], out[7]);
         __threadfence();
         __syncwarp();
         int prev = 0;
-        if (lane == 0) prev = atomicAdd(&p.counters[t * 8 + n16], 1);
+        if (lane == 0) prev = atomicAdd(&p.counters[t * 8 + warp], 1);
         prev = __shfl_sync(0xffffffffu, prev, 0);
         if (prev == c_last - c_first) {
           __threadfence();
-          float sum[4] = {0.f, 0.f, 0.f, 0.f};
+          float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
           for (int cc = c_first; cc <= c_last; ++cc) {
             const int cu0 = static_cast<int>(gemv_range_begin(units, grid, cc));
             const int slot = 2 * cc + ((cu0 / p.n_kb) == t ? 0 : 1);
-            const float4 v = __ldcg(&part[(slot * 8 + n16) * 32 + lane]);
-            sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
+            const float4 v0 = __ldcg(&part[((slot * 4 + warp) * 32 + lane) * 2]);
+            const float4 v1 = __ldcg(&part[((slot * 4 + warp) * 32 + lane) * 2 + 1]);
+            sum[0] += v0.x; sum[1] += v0.y; sum[2] += v0.z; sum[3] += v0.w;
+            sum[4] += v1.x; sum[5] += v1.y; sum[6] += v1.z; sum[7] += v1.w;
           }
-          if (lane == 0) p.counters[t * 8 + n16] = 0;
-          gemv_epilogue(p, t, n16, lane, sum, ar_half);
+          if (lane == 0) p.counters[t * 8 + warp] = 0;
+          gemv_epilogue_row(p, t, warp, lane, sum, ar_half);
         }
       }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) out[c] = 0.f;
     };
 
-    int cur_t = u0 < u1 ? u0 / p.n_kb : 0;
-    const int last_t = u0 < u1 ? (u1 - 1) / p.n_kb : -1;
-    for (int u = u0 + wq; u < u1; u += 4) {
-      const int t = u / p.n_kb;
-      while (cur_t < t) finish_tile(cur_t++);  // every warp passes through every tile boundary, in order
+    int kb = u0 < u1 ? u0 % p.n_kb : 0, t = u0 < u1 ? u0 / p.n_kb : 0;
+    for (int u = u0; u < u1; ++u, ++kb) {
+      if (kb == p.n_kb) {
+        kb = 0;
+        ++t;
+      }
       const int i = u - u0;
-      const int s = i % kGemvStages;
-      const uint32_t use = static_cast<uint32_t>(i / kGemvStages);
-      // A warp that gave up on a wait keeps walking its units without touching the ring, so that it
-      // still meets the other warps at every tile boundary (those barriers have no time limit).
-      if (!ok || *cta_error) {
-        ok = false;
-        continue;
-      }
-      const long long c0 = p.prof != nullptr ? clock64() : 0;
-      if (!mbar_wait(&full[s], use & 1)) {
-        set_status(p.status, ST_WAIT_FULL_TIMEOUT);
-        *cta_error = 1;
-        ok = false;
-        continue;
-      }
-      const long long c1 = p.prof != nullptr ? clock64() : 0;
-      if (u == u0 && lane == 0) gemv_stamp(p, kGemvProfFirstData);
-      const uint8_t* sw = smem + s * TB_STAGE_BYTES;
-      const uint8_t* sx = sw + TB_WBLK_BYTES;
-      uint2 b[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) b[c] = *reinterpret_cast<const uint2*>(sx + (c * 32 + lane) * 8);
-      const float2 cs = *reinterpret_cast<const float2*>(sx + TB_XBLK_DATA + q * 8);
-      // four independent accumulation chains (one per 16-row group), each over the four k chunks
-      float d[4][4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint4 a = *reinterpret_cast<const uint4*>(sw + (((half * 4 + j) * 4 + c) * 32 + lane) * 16);
-#ifndef TB_EXP_SKIP_MMA
-          mma_e4m3_16832(d[j], a, b[c]);
-#else
-          d[j][0] += __uint_as_float(a.x ^ b[c].x);
-#endif
+      const int s = i % kGemvStages, a = i % kGemvAccs;
+      // every decision below is made warp-uniform: tcgen05.ld needs the whole warp
+      if (__all_sync(0xffffffffu, ok && !*cta_error)) {
+        const long long c0 = p.prof != nullptr ? clock64() : 0;
+        if (!__all_sync(0xffffffffu, mbar_wait(&full[s], static_cast<uint32_t>(i / kGemvStages) & 1))) {
+          set_status(p.status, ST_WAIT_FULL_TIMEOUT);
+          *cta_error = 1;
+          ok = false;
+        } else {
+          if (u == u0 && warp == 0 && lane == 0) gemv_stamp(p, kGemvProfFirstData);
+          const uint8_t* sw = smem + s * TB_STAGE_BYTES;
+          const float ws = *reinterpret_cast<const float*>(sw + TB_WBLK_DATA + ((warp * 32 + lane) >> 3) * 4);
+          const float4 cs0 = *reinterpret_cast<const float4*>(sw + TB_WBLK_BYTES + TB_XBLK_DATA);
+          const float4 cs1 = *reinterpret_cast<const float4*>(sw + TB_WBLK_BYTES + TB_XBLK_DATA + 16);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty[s]);
+          if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[a], static_cast<uint32_t>(i / kGemvAccs) & 1))) {
+            set_status(p.status, ST_WAIT_FULL_TIMEOUT);
+            *cta_error = 1;
+            ok = false;
+          } else {
+            const long long c1 = p.prof != nullptr ? clock64() : 0;
+            tc_fence_after();
+            float d[8];
+            tmem_ld8(tmem_base + lane_base + static_cast<uint32_t>(a * kGemvAccCols), d);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[a]);
+            out[0] = fmaf(d[0], ws * cs0.x, out[0]);
+            out[1] = fmaf(d[1], ws * cs0.y, out[1]);
+            out[2] = fmaf(d[2], ws * cs0.z, out[2]);
+            out[3] = fmaf(d[3], ws * cs0.w, out[3]);
+            out[4] = fmaf(d[4], ws * cs1.x, out[4]);
+            out[5] = fmaf(d[5], ws * cs1.y, out[5]);
+            out[6] = fmaf(d[6], ws * cs1.z, out[6]);
+            out[7] = fmaf(d[7], ws * cs1.w, out[7]);
+            if (p.prof != nullptr) {
+              prof_wait += c1 - c0;
+              prof_math += clock64() - c1;
+              ++prof_units;
+            }
+          }
         }
       }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 ws = *reinterpret_cast<const float2*>(sw + TB_WBLK_DATA + (half * 4 + j) * 8);
-        acc[j][0] = fmaf(d[j][0], ws.x * cs.x, acc[j][0]);
-        acc[j][1] = fmaf(d[j][1], ws.x * cs.y, acc[j][1]);
-        acc[j][2] = fmaf(d[j][2], ws.y * cs.x, acc[j][2]);
-        acc[j][3] = fmaf(d[j][3], ws.y * cs.y, acc[j][3]);
+      else {
+        ok = false;
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);
+      if (kb == p.n_kb - 1 || u == u1 - 1) {
+        if (u == u1 - 1 && warp == 0 && lane == 0) gemv_stamp(p, kGemvProfLastUnit);
+        finish_tile(t);
+      }
+    }
+    if (warp == 0 && lane == 0) {
+      gemv_stamp(p, kGemvProfTilesDone);
       if (p.prof != nullptr) {
-        prof_wait += c1 - c0;
-        prof_math += clock64() - c1;
-        ++prof_units;
+        p.prof[blockIdx.x * 16 + kGemvProfWaitCycles] = prof_wait;
+        p.prof[blockIdx.x * 16 + kGemvProfMathCycles] = prof_math;
+        p.prof[blockIdx.x * 16 + kGemvProfUnits] = prof_units;
       }
     }
-    if (warp == 0 && lane == 0) gemv_stamp(p, kGemvProfLastUnit);
-    if (warp == 0 && lane == 0 && p.prof != nullptr) {
-      p.prof[blockIdx.x * 16 + kGemvProfWaitCycles] = prof_wait;
-      p.prof[blockIdx.x * 16 + kGemvProfMathCycles] = prof_math;
-      p.prof[blockIdx.x * 16 + kGemvProfUnits] = prof_units;
-    }
-    // tiles this warp has not closed yet (including those in which it had no unit)
-    while (cur_t <= last_t) finish_tile(cur_t++);
-    if (warp == 0 && lane == 0) gemv_stamp(p, kGemvProfTilesDone);
+
     if (p.ar.world > 1) {
       // ---- one-shot all-reduce over peer memory, fused behind the streaming loop ----
       AllReduceState* self = p.ar.state[p.ar.rank];
       // 1. this CTA's peer stores are done: publish them.  The last CTA of the rank to get here
       //    tells every rank (itself included) that this rank's partial has landed.
       __threadfence_system();
-      asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerThreads) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemvEpilogueThreads) : "memory");
       if (threadIdx.x == 0) {
         const unsigned int prev = atomicAdd(&self->local_arrive, 1u);
         if (prev == static_cast<unsigned int>(grid) - 1u) {
@@ -579,14 +660,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           __nanosleep(32);
         }
       }
-      asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerThreads) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemvEpilogueThreads) : "memory");
       // 3. reduce the world's slots for this CTA's share of rows, add the residual, store.
       if (!*cta_error) {
         const float* mine = p.ar.recv[p.ar.rank];
         const int total = p.n_tokens * p.n_rows;
         const int e0 = static_cast<int>(static_cast<long long>(total) * cta / grid);
         const int e1 = static_cast<int>(static_cast<long long>(total) * (cta + 1) / grid);
-        for (int e = e0 + static_cast<int>(threadIdx.x); e < e1; e += kGemvConsumerThreads) {
+        for (int e = e0 + static_cast<int>(threadIdx.x); e < e1; e += kGemvEpilogueThreads) {
           const int tok = e / p.n_rows, row = e % p.n_rows;
           float v = 0.f;
           for (int r = 0; r < p.ar.world; ++r)
@@ -595,7 +676,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         }
       }
       // 4. the last CTA to finish opens the next call (flips the buffer half).
-      asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerThreads) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemvEpilogueThreads) : "memory");
       if (threadIdx.x == 0) {
         const unsigned int prev = atomicAdd(&self->local_done, 1u);
         if (prev == static_cast<unsigned int>(grid) - 1u) {
@@ -606,6 +687,15 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       }
     }
     if (warp == 0 && lane == 0) gemv_stamp(p, kGemvProfExit);
+  }
+
+  // ---- common tail: every warp arrives here on every path; then the tensor memory is returned ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kGemvMmaWarp) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kGemvTmemCols)
+                 : "memory");
   }
 }
 

@@ -41,9 +41,9 @@ def pack_rows(w: torch.Tensor, rscale: torch.Tensor) -> torch.Tensor:
     g8 = rscale.view(npad // 8, 8, n_kb)
     if not bool((g8 == g8[:, :1]).all()):
         raise ValueError("each aligned group of 8 packed rows must share one scale per k block")
-    # rows: t, warp(8), rlo(2), g(8)      cols: kb, c(4), rhi(2), q(4), b(4)
-    v = w.view(n_t, 8, 2, 8, n_kb, 4, 2, 4, 4)
-    data = v.permute(0, 4, 1, 5, 3, 7, 6, 2, 8).reshape(n_t, n_kb, 16384)
+    # rows: t, row group(16), r(8)      cols: kb, c(4), kc(2), b(16)   ->   t, kb, c, row group, kc, r, b
+    v = w.view(n_t, 16, 8, n_kb, 4, 2, 16)
+    data = v.permute(0, 3, 4, 1, 5, 2, 6).reshape(n_t, n_kb, 16384)
     sc = g8[:, 0].view(n_t, 16, n_kb).permute(0, 2, 1).contiguous().float()
     sc_bytes = sc.view(torch.uint8).view(n_t, n_kb, 64)
     return torch.cat([data, sc_bytes], dim=2).contiguous()
@@ -122,8 +122,8 @@ def pack_gate_up(w_gate, s_gate, w_up, s_up) -> torch.Tensor:
 def unpack_rows(packed: torch.Tensor, n: int) -> tuple[torch.Tensor, torch.Tensor]:
     """Inverse of ``pack_rows`` (for round-trip tests): returns (uint8 [n, K], row scales [n/8.., ...])."""
     n_t, n_kb, _ = packed.shape
-    data = packed[:, :, :16384].reshape(n_t, n_kb, 8, 4, 8, 4, 2, 2, 4)  # t kb w c g q rhi rlo b
-    w = data.permute(0, 2, 7, 4, 1, 3, 6, 5, 8).reshape(n_t * TILE, n_kb * KB)
+    data = packed[:, :, :16384].reshape(n_t, n_kb, 4, 16, 2, 8, 16)  # t kb c rg kc r b
+    w = data.permute(0, 3, 5, 1, 2, 4, 6).reshape(n_t * TILE, n_kb * KB)
     sc = packed[:, :, 16384:].contiguous().view(torch.float32).view(n_t, n_kb, 16).permute(0, 2, 1)
     rs = sc.reshape(n_t * 16, n_kb).repeat_interleave(8, dim=0)
     return w[:n].contiguous(), rs[:n].contiguous()
