@@ -348,14 +348,23 @@ def run_profile_gemv(args) -> None:
     res = torch.randn(1, 1, n, generator=g, device=dev).to(torch.bfloat16)
     out = torch.zeros(1, 1, n, dtype=torch.bfloat16, device=dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.gemv_packed:
+        xp = ops.new_xpack(k, dev)
+        ops.act_pack(vec, xp)
+
+        def launch():
+            ops.projx_wqkva_packed(xp, 2, w, 1, k, n, 0, 0, 0, None, out, None, None, None)
+    else:
+        def launch():
+            ops.unproj_o_allreduce(vec, w, None, res, 0, out)
     for _ in range(max(args.warmup, 1)):
-        ops.unproj_o_allreduce(vec, w, None, res, 0, out)
+        launch()
     torch.cuda.synchronize()
     # back-to-back launches replayed from a CUDA graph: no host launch overhead in the timed region
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         for _ in range(args.steps):
-            ops.unproj_o_allreduce(vec, w, None, res, 0, out)
+            launch()
     graph.replay()
     torch.cuda.synchronize()
     e0.record()
@@ -378,7 +387,7 @@ def run_profile_gemv(args) -> None:
     trace = torch.zeros(256, 16, dtype=torch.int64, device=dev)
     ctx = ctypes.c_void_p(tilert_b200.tilert_init(0))
     tilert_b200.check(tilert_b200.lib().tilert_b200_set_profile(ctx, ctypes.c_void_p(trace.data_ptr())))
-    ops.unproj_o_allreduce(vec, w, None, res, 0, out)
+    launch()
     torch.cuda.synchronize()
     tilert_b200.check(tilert_b200.lib().tilert_b200_set_profile(ctx, None))
     tr = trace[:148].cpu().double()
@@ -390,6 +399,11 @@ def run_profile_gemv(args) -> None:
     units = tr[:, 10].clamp_min(1)
     phases["wait_cycles_per_unit"] = round(float((tr[:, 8] / units).median()), 1)
     phases["math_cycles_per_unit"] = round(float((tr[:, 9] / units).median()), 1)
+    for idx, nm in ((11, "mma0_wait_full_x2"), (12, "mma0_issue_x2"), (14, "prod0_wait_empty_x4"),
+                    (15, "conv0_cycles_x2")):
+        phases[nm + "_per_unit"] = round(float((tr[:, idx] / units).median()), 1)
+    if os.environ.get("TB_TRACE_DUMP"):
+        torch.save(tr, os.environ["TB_TRACE_DUMP"])
     print(json.dumps({"trace_us_min_med_max": phases}))
     print(json.dumps({"mode": "profile-gemv", "n": n, "k": k, "weight_bytes": w.numel(), "ms_per_launch": ms,
                       "gbs": w.numel() / ms / 1e6, "torch_sum_read_gbs": read_gbs,
@@ -406,6 +420,7 @@ def main() -> None:
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: no clock-sampling loop, no CPU baseline")
     ap.add_argument("--gemv-k", type=int, default=32768)
+    ap.add_argument("--gemv-packed", action="store_true", help="profile-gemv: activations packed beforehand")
     ap.add_argument("--profile-gemv", action="store_true",
                     help="run only the weight-streaming product on a 235 MB weight (small footprint for ncu)")
     args = ap.parse_args()

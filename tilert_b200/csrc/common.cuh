@@ -88,6 +88,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
 }
 
+// Same, but also gives up (returns false) soon after another warp of the CTA has raised `abort`, so
+// that one role's failure does not make every other role sit out its own full budget.  The flag is
+// read only on the slow path.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort) {
+#pragma unroll 1
+  for (int i = 0; i < 32; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort != 0 || clock64() - t0 > kWaitBudgetCycles) return false;
+  }
+}
+
 // ---- bulk async copy (TMA, untiled): global -> this CTA's shared memory ----
 // Both addresses 16-byte aligned, size a multiple of 16 bytes.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {

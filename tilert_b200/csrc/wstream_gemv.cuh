@@ -6,13 +6,18 @@
 // HBM-bound: every weight byte is read exactly once.  One persistent CTA per SM walks a
 // contiguous range of (row tile, k block) units (stream-K).  A producer thread stages each
 // unit -- one 16448-byte W block and one 1056-byte X block -- into a shared-memory ring with
-// bulk async copies (TMA) that complete on mbarriers.  One thread issues the tensor-core work: per
-// unit four tcgen05.mma (M = 128 weight rows x N = 16 x K = 32, e4m3 operands read straight from
-// the slot through shared-memory descriptors; 8 real activation columns) into one of four TMEM
-// accumulators.  Four epilogue warps (one thread per weight row) read each accumulator back with
-// tcgen05.ld and apply (weight scale x column scale) in f32 registers once per k block.  Row tiles that
-// straddle two CTAs are finished by the last arriver, which adds the partials in CTA order, so
-// the result does not depend on timing.
+// bulk async copies (TMA) that complete on mbarriers.  The tensor-core work of a unit is four
+// tcgen05.mma (M = 128 weight rows x N = 16 x K = 32, e4m3 operands read straight from the slot
+// through shared-memory descriptors; 8 real activation columns) into the TMEM accumulator that
+// belongs to the slot.  Epilogue warps (one thread per weight row) read each accumulator back with
+// tcgen05.ld and apply (weight scale x column scale) in f32 registers once per k block.
+//
+// Every role is a serial loop whose per-unit latency (a barrier wait alone is ~100 cycles) would
+// otherwise pace the stream at well under the memory rate, so every role is spread over several
+// warps that take units round-robin: 4 producer threads, 2 MMA-issuing threads, 2 groups of 4
+// epilogue warps, 2 converter warps.  The two epilogue groups merge their sums through shared
+// memory at the end of a row tile.  Row tiles that straddle two CTAs are finished by the last
+// arriver, which adds the partials in CTA order, so the result does not depend on timing.
 #pragma once
 
 #include "common.cuh"
@@ -106,6 +111,11 @@ enum GemvProfSlot : int {
   kGemvProfWaitCycles = 8,    // consumer 0: SM cycles spent waiting for data, summed over its units
   kGemvProfMathCycles = 9,    // consumer 0: SM cycles spent consuming, summed over its units
   kGemvProfUnits = 10,        // consumer 0: number of units it consumed
+  kGemvProfMmaWaitFull = 11,  // MMA warp 0: cycles waiting for its slots to fill
+  kGemvProfMmaIssue = 12,     // MMA warp 0: cycles issuing MMAs and their commit
+  kGemvProfUnused13 = 13,
+  kGemvProfProdWait = 14,     // producer 0: cycles waiting for free slots
+  kGemvProfConvCycles = 15,   // converter 0: cycles converting (excluding waits)
 };
 __device__ __forceinline__ void gemv_stamp(const GemvParams& p, int slot) {
   if (p.prof != nullptr) p.prof[blockIdx.x * 16 + slot] = globaltimer_ns();
@@ -114,19 +124,33 @@ __device__ __forceinline__ void gemv_stamp(const GemvParams& p, int slot) {
 #ifndef TB_GEMV_STAGES
 #define TB_GEMV_STAGES 12
 #endif
-constexpr int kGemvStages = TB_GEMV_STAGES;  // multiple of kGemvProducerWarps
-constexpr int kGemvAccs = 4;            // TMEM accumulators in flight
-constexpr int kGemvAccCols = 16;        // columns per accumulator: N = 16 is the smallest N at M = 128
-constexpr int kGemvTmemCols = 64;       // kGemvAccs * kGemvAccCols, a power of two >= 32
-constexpr int kGemvEpilogueWarps = 4;   // warps 0-3: TMEM lanes 32w .. 32w+31 = weight rows of the tile
-constexpr int kGemvProducerWarps = 4;   // warps 5-8: one issuing thread each; unit i is issued by producer i % 4
-constexpr int kGemvConverterWarps = 2;  // warps 9-10: unit i is converted by converter i % 2 (X_BF16 only)
+constexpr int kGemvStages = TB_GEMV_STAGES;  // ring slots; a multiple of every role's warp count
+constexpr int kGemvAccCols = 16;        // TMEM columns per accumulator: N = 16 is the smallest N at M = 128
+constexpr int kGemvTmemCols = 256;      // one accumulator per slot; a power of two >= kGemvStages * kGemvAccCols
+constexpr int kGemvEpilogueGroups = 2;  // unit i is read back by group i % 2
+constexpr int kGemvGroupWarps = 4;      // warps 4g .. 4g+3: TMEM lanes 32(w%4) .. +31 = weight rows of the tile
+constexpr int kGemvEpilogueWarps = kGemvEpilogueGroups * kGemvGroupWarps;  // warps 0-7
+constexpr int kGemvMmaWarps = 2;        // warps 8-9: one issuing thread each; unit i is issued by MMA warp i % 2
+constexpr int kGemvProducerWarps = 4;   // warps 10-13: one issuing thread each; unit i is copied by producer i % 4
+constexpr int kGemvConverterWarps = 2;  // warps 14-15: unit i is converted by converter i % 2 (X_BF16 only)
+constexpr int kGemvGroupThreads = kGemvGroupWarps * 32;
 constexpr int kGemvEpilogueThreads = kGemvEpilogueWarps * 32;
-constexpr int kGemvMmaWarp = kGemvEpilogueWarps;  // warp 4: TMEM owner, one lane issues the MMAs
+constexpr int kGemvFirstMmaWarp = kGemvEpilogueWarps;
+constexpr int kGemvFirstProducerWarp = kGemvFirstMmaWarp + kGemvMmaWarps;
+constexpr int kGemvFirstConverterWarp = kGemvFirstProducerWarp + kGemvProducerWarps;
 constexpr int kGemvHelperWarps = kGemvEpilogueWarps + kGemvConverterWarps;  // warps that share the norm prologue
-constexpr int kGemvThreads = (kGemvEpilogueWarps + 1 + kGemvProducerWarps + kGemvConverterWarps) * 32;
-constexpr int kGemvBarBytes = (2 * kGemvStages + 2 * kGemvAccs) * 8;
-constexpr int kGemvSmemBytes = kGemvStages * TB_STAGE_BYTES + kGemvBarBytes + 16 + kGemvHelperWarps * 4 * 4 + 32;
+constexpr int kGemvThreads = (kGemvFirstConverterWarp + kGemvConverterWarps) * 32;
+static_assert(kGemvStages % kGemvProducerWarps == 0 && kGemvStages % kGemvMmaWarps == 0 &&
+                  kGemvStages % kGemvEpilogueGroups == 0 && kGemvStages % kGemvConverterWarps == 0,
+              "a slot must always be served by the same warp of each role");
+static_assert(kGemvStages * kGemvAccCols <= kGemvTmemCols, "one accumulator per slot");
+// Ring slot: W block at offset 0, X block at kGemvSlotXOff; both start on a 128-byte line of shared memory
+constexpr int kGemvSlotXOff = 16512;
+constexpr int kGemvSlotStride = 17664;
+constexpr int kGemvBarBytes = 3 * kGemvStages * 8;
+constexpr int kGemvMergeBytes = 2 * kGemvGroupThreads * 8 * 4;  // double-buffered sums of epilogue group 1
+constexpr int kGemvSmemBytes =
+    kGemvStages * kGemvSlotStride + kGemvMergeBytes + kGemvBarBytes + 16 + kGemvHelperWarps * 4 * 4 + 32;
 
 // ---- tcgen05 helpers ----
 // Shared-memory operand descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; `lbo` =
@@ -153,6 +177,19 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Issue / completion halves of the same load, so that other work can overlap its latency.  The
+// registers must not be read before tmem_ld_wait.
+__device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[8]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
+               :
+               : "memory");
+}
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&d)[8]) {
   uint32_t r[8];
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -241,11 +278,11 @@ __device__ __forceinline__ void gemv_epilogue_row(const GemvParams& p, int tile,
 
 __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGemvStages * TB_STAGE_BYTES);
+  float* merge = reinterpret_cast<float*>(smem + kGemvStages * kGemvSlotStride);  // [2][group threads][8]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGemvStages * kGemvSlotStride + kGemvMergeBytes);
   uint64_t* empty = full + kGemvStages;
   uint64_t* acc_full = empty + kGemvStages;
-  uint64_t* acc_empty = acc_full + kGemvAccs;
-  volatile int* cta_error = reinterpret_cast<volatile int*>(acc_empty + kGemvAccs);
+  volatile int* cta_error = reinterpret_cast<volatile int*>(acc_full + kGemvStages);
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(const_cast<int*>(cta_error) + 1);
   float* norm_part = reinterpret_cast<float*>(const_cast<int*>(cta_error) + 4);  // [helper warps][4 tokens]
 
@@ -264,17 +301,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     gemv_stamp(p, kGemvProfEntry);
     for (int s = 0; s < kGemvStages; ++s) {
       mbar_init(&full[s], p.x_mode == X_BF16 ? 2 : 1);  // producer (+ converter) arrive once per use
-      mbar_init(&empty[s], 1 + kGemvEpilogueWarps);     // MMA completion + the epilogue warps' scale reads
-    }
-    for (int a = 0; a < kGemvAccs; ++a) {
-      mbar_init(&acc_full[a], 1);                       // MMA completion
-      mbar_init(&acc_empty[a], kGemvEpilogueWarps);     // accumulator read back by the four warps
+      mbar_init(&empty[s], kGemvGroupWarps);            // the warps of the epilogue group that read the unit back
+      mbar_init(&acc_full[s], 1);                       // completion of the unit's MMAs
     }
     *cta_error = 0;
     mbar_fence_init();
   }
-  if (warp == kGemvMmaWarp) {
-    // tensor memory: kGemvTmemCols columns for this CTA (the whole warp executes the allocation)
+  if (warp == kGemvFirstMmaWarp) {
+    // tensor memory: one accumulator per ring slot (the whole warp executes the allocation)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(const_cast<uint32_t*>(tmem_base_slot))),
                  "r"(kGemvTmemCols)
@@ -288,9 +322,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
   if (threadIdx.x == 0) gemv_stamp(p, kGemvProfReady);
 
   const bool is_epilogue = warp < kGemvEpilogueWarps;
-  const bool is_mma = warp == kGemvMmaWarp;
-  const bool is_producer = warp > kGemvMmaWarp && warp <= kGemvMmaWarp + kGemvProducerWarps;
-  const bool is_converter = warp > kGemvMmaWarp + kGemvProducerWarps;
+  const bool is_mma = warp >= kGemvFirstMmaWarp && warp < kGemvFirstProducerWarp;
+  const bool is_producer = warp >= kGemvFirstProducerWarp && warp < kGemvFirstConverterWarp;
+  const bool is_converter = warp >= kGemvFirstConverterWarp;
   // Producers stream weights, which no kernel of the step writes; they wait for the predecessor only
   // when their addresses depend on it (routing ids) or when they also copy packed activations.
   if (!is_producer || p.x_mode == X_PACKED || p.nseg_ids != nullptr || p.kseg_ids != nullptr) pdl_wait();
@@ -298,7 +332,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
   if (p.x_mode == X_BF16 && p.gamma != nullptr && (is_epilogue || is_converter)) {
     // RMSNorm statistics of the activation vector(s): the epilogue and converter warps split the
     // vector (the producers are already filling the ring), partial sums meet in shared memory.
-    const int hw = is_epilogue ? warp : warp - 1 - kGemvProducerWarps;
+    const int hw = is_epilogue ? warp : warp - kGemvFirstConverterWarp + kGemvEpilogueWarps;
     const int n_chunks = p.n_kb * (TB_KBLOCK / 4);  // 8-byte chunks per token
     float ss[4] = {0.f, 0.f, 0.f, 0.f};
     for (int ch = hw * 32 + lane; ch < n_chunks; ch += kGemvHelperWarps * 32) {
@@ -322,22 +356,25 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
 
   if (is_producer) {
     // ------------------------------------------------------------ producers
-    // Four warps, one issuing thread each; unit i of the CTA's range is issued by producer i % 4
-    // into ring slot i % kGemvStages, so no single thread's instruction latency paces the stream.
+    // One issuing thread per warp; unit i of the CTA's range is copied by producer i % 4 into ring
+    // slot i % kGemvStages.
     if (lane == 0) {
-      const int pw = warp - kGemvMmaWarp - 1;
+      const int pw = warp - kGemvFirstProducerWarp;
       const uint64_t pol = policy_evict_first();
       int last_i = -1;
+      long long pw_wait = 0;
       int t = (u0 + pw) / p.n_kb, kb = (u0 + pw) % p.n_kb;
+      int s = pw;
+      uint32_t ph_empty = 1;  // parity of the previous use's release
       for (int u = u0 + pw; u < u1; u += kGemvProducerWarps) {
         const int i = u - u0;
-        const int s = i % kGemvStages;
-        const uint32_t use = static_cast<uint32_t>(i / kGemvStages);
-        if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1)) {
+        const long long w0 = p.prof != nullptr ? clock64() : 0;
+        if (i >= kGemvStages && !mbar_wait(&empty[s], ph_empty, cta_error)) {
           set_status(p.status, ST_WAIT_EMPTY_TIMEOUT);
           *cta_error = 1;
           break;
         }
+        if (p.prof != nullptr) pw_wait += clock64() - w0;
         long long eid = 0;
         int tl = t, kbl = kb;
         if (p.nseg_ids != nullptr) {
@@ -350,13 +387,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         }
         const uint8_t* wsrc =
             p.w + eid * p.expert_stride + (static_cast<long long>(tl) * p.w_kb_per_tile + kbl) * TB_WBLK_BYTES;
-        uint8_t* dst = smem + s * TB_STAGE_BYTES;
+        uint8_t* dst = smem + s * kGemvSlotStride;
         if (p.x_mode == X_PACKED) {
           const int xseg = p.tiles_per_xseg > 0 ? t / p.tiles_per_xseg : 0;
           const uint8_t* xsrc = p.x + (static_cast<long long>(xseg) * p.n_kb + kb) * TB_XBLK_BYTES;
-          mbar_expect_tx(&full[s], TB_STAGE_BYTES);
+          mbar_expect_tx(&full[s], TB_WBLK_BYTES + TB_XBLK_BYTES);
           bulk_g2s_stream(dst, wsrc, TB_WBLK_BYTES, &full[s], pol);
-          bulk_g2s(dst + TB_WBLK_BYTES, xsrc, TB_XBLK_BYTES, &full[s]);
+          bulk_g2s(dst + kGemvSlotXOff, xsrc, TB_XBLK_BYTES, &full[s]);
         } else {
           mbar_expect_tx(&full[s], TB_WBLK_BYTES);
           bulk_g2s_stream(dst, wsrc, TB_WBLK_BYTES, &full[s], pol);
@@ -367,8 +404,16 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           kb -= p.n_kb;
           ++t;
         }
+        s += kGemvProducerWarps;
+        if (s >= kGemvStages) {
+          s -= kGemvStages;
+          ph_empty ^= 1u;
+        }
       }
-      if (pw == 0) gemv_stamp(p, kGemvProfIssued);
+      if (pw == 0) {
+        gemv_stamp(p, kGemvProfIssued);
+        if (p.prof != nullptr) p.prof[blockIdx.x * 16 + kGemvProfProdWait] = pw_wait;
+      }
       // Do not leave the CTA while this thread's copies may still be landing in its shared memory:
       // wait (bounded) for the last use it issued into each of its ring slots.  On the normal path
       // these have completed already, because the consumers waited on the same phases.
@@ -382,7 +427,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     // Two warps take alternate units.  Each converts the 128 activations of its unit, for every
     // token, into the two-term e4m3 X block of the stage: power-of-two scales, so the scaling is a
     // multiplication and the residual x - hi*s is exact.
-    const int cw = warp - (kGemvEpilogueWarps + 1 + kGemvProducerWarps);  // 0 or 1
+    const int cw = warp - kGemvFirstConverterWarp;  // 0 or 1
     if (p.x_mode == X_BF16 && u0 + cw < u1) {
       const int ntok = p.n_tokens;
       float rinv[4] = {1.f, 1.f, 1.f, 1.f};
@@ -414,20 +459,22 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       };
       // software pipeline over this warp's units (u, u+2, u+4, ...): two requests in flight
       const int ub = u0 + cw;
+      long long conv_cycles = 0;
       XRaw x0 = fetch(ub), x1 = x0, x2 = x0;
       if (ub + 2 < u1) x1 = fetch(ub + 2);
       const int c = lane >> 3, r = (lane >> 2) & 1, q4 = lane & 3;
-      for (int u = ub; u < u1; u += 2) {
+      for (int u = ub; u < u1; u += kGemvConverterWarps) {
         const int i = u - u0;
         const int s = i % kGemvStages;
         const uint32_t use = static_cast<uint32_t>(i / kGemvStages);
         if (u + 4 < u1) x2 = fetch(u + 4);
-        if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1)) {
+        if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1, cta_error)) {
           set_status(p.status, ST_WAIT_EMPTY_TIMEOUT);
           *cta_error = 1;
           break;
         }
-        uint8_t* blk = smem + s * TB_STAGE_BYTES + TB_WBLK_BYTES;
+        const long long v0 = p.prof != nullptr ? clock64() : 0;
+        uint8_t* blk = smem + s * kGemvSlotStride + kGemvSlotXOff;
         const int kb = u % p.n_kb;
         const float g4[4] = {x0.g.x, x0.g.y, x0.g.z, x0.g.w};
 #pragma unroll
@@ -484,78 +531,120 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         }
         x0 = x1;
         x1 = x2;
+        if (p.prof != nullptr) conv_cycles += clock64() - v0;
       }
+      if (cw == 0 && lane == 0 && p.prof != nullptr) p.prof[blockIdx.x * 16 + kGemvProfConvCycles] = conv_cycles;
     }
   } else if (is_mma) {
     // ------------------------------------------------------------ tensor-core issue
-    // One thread.  Per unit: wait for the slot (weights landed, X block written) and for a free
-    // accumulator, issue four K = 32 MMAs into it, then let the hardware signal both "slot no longer
-    // read" and "accumulator complete" when they have finished.
+    // One thread per warp; unit i is issued by MMA warp i % 2.  Per unit: wait for the slot (weights
+    // landed, X block written), issue four K = 32 MMAs into the slot's accumulator, and let the
+    // hardware signal their completion.  The accumulator is free whenever the slot is full: the
+    // epilogue released the slot only after reading the accumulator of the slot's previous unit.
     if (lane == 0) {
-      for (int u = u0; u < u1; ++u) {
-        const int i = u - u0;
-        const int s = i % kGemvStages, a = i % kGemvAccs;
-        if (!mbar_wait(&full[s], static_cast<uint32_t>(i / kGemvStages) & 1) ||
-            (i >= kGemvAccs && !mbar_wait(&acc_empty[a], static_cast<uint32_t>(i / kGemvAccs - 1) & 1))) {
+      const int mw = warp - kGemvFirstMmaWarp;
+      // descriptors differ only in their 14-bit start-address field (16-byte units): one add per operand
+      const uint32_t smem16 = smem_u32(smem) >> 4;
+      const uint64_t desc_a_hi =
+          (static_cast<uint64_t>(128 >> 4) << 16) | (static_cast<uint64_t>(256 >> 4) << 32) | (1ull << 46);
+      const uint64_t desc_b_hi = (static_cast<uint64_t>(128 >> 4) << 16) | (1ull << 46);
+      int s = mw;
+      uint32_t ph_full = 0;
+      long long pf_full = 0, pf_issue = 0;
+      for (int u = u0 + mw; u < u1; u += kGemvMmaWarps) {
+        const long long m0 = p.prof != nullptr ? clock64() : 0;
+        if (!mbar_wait(&full[s], ph_full, cta_error)) {
           set_status(p.status, ST_WAIT_FULL_TIMEOUT);
           *cta_error = 1;
           break;
         }
+        const long long m1 = p.prof != nullptr ? clock64() : 0;
         tc_fence_after();
-        const uint8_t* sw = smem + s * TB_STAGE_BYTES;
-        const uint8_t* sx = sw + TB_WBLK_BYTES;
-        const uint32_t d = tmem_base + static_cast<uint32_t>(a * kGemvAccCols);
+        const uint32_t wa = smem16 + static_cast<uint32_t>(s) * (kGemvSlotStride >> 4);
+        const uint32_t xa = wa + (kGemvSlotXOff >> 4);
+        const uint32_t d = tmem_base + static_cast<uint32_t>(s * kGemvAccCols);
 #pragma unroll
         for (int c = 0; c < 4; ++c)
-          umma_f8(d, umma_desc(sw + c * 4096, 128, 256), umma_desc(sx + c * 256, 128, 0), c > 0 ? 1u : 0u);
-        umma_commit(&empty[s]);
-        umma_commit(&acc_full[a]);
+          umma_f8(d, desc_a_hi | (wa + c * (4096 >> 4)), desc_b_hi | (xa + c * (256 >> 4)), c > 0 ? 1u : 0u);
+        umma_commit(&acc_full[s]);
+        if (p.prof != nullptr) {
+          pf_full += m1 - m0;
+          pf_issue += clock64() - m1;
+        }
+        s += kGemvMmaWarps;
+        if (s >= kGemvStages) {
+          s -= kGemvStages;
+          ph_full ^= 1u;
+        }
+      }
+      if (mw == 0 && p.prof != nullptr) {
+        p.prof[blockIdx.x * 16 + kGemvProfMmaWaitFull] = pf_full;
+        p.prof[blockIdx.x * 16 + kGemvProfMmaIssue] = pf_issue;
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
-    // Thread (warp w, lane l) owns weight row 32w + l of the current row tile: eight f32 sums, one
-    // per activation column.  Per unit it reads its row's scale and the column scales from the slot,
-    // then the unit's accumulator from TMEM, and adds scale * accumulator.
+    // Two groups of four warps; unit i is read back by group i % 2.  Thread (warp w, lane l) owns
+    // weight row 32(w%4) + l of the current row tile: eight f32 sums, one per activation column,
+    // over its group's units.  Per unit it waits for the MMAs, reads the accumulator from TMEM and
+    // its row's scale and the column scales from the slot, releases the slot, and adds
+    // scale * accumulator.  At the end of a row tile group 1 hands its sums to group 0 through
+    // shared memory; group 0 finishes the tile.
+    const int eg = warp / kGemvGroupWarps, gw = warp % kGemvGroupWarps;
     unsigned long long ar_epoch = 0;
     if (p.ar.world > 1) ar_epoch = *reinterpret_cast<volatile unsigned long long*>(&p.ar.state[p.ar.rank]->epoch);
     const int ar_half = static_cast<int>(ar_epoch & 1ull);
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_base = static_cast<uint32_t>(gw * 32) << 16;
     float out[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) out[c] = 0.f;
     bool ok = true;
     long long prof_wait = 0, prof_math = 0, prof_units = 0;
+    int merge_buf = 0;
 
     auto finish_tile = [&](int t) {
-      const int tile_u0 = t * p.n_kb, tile_u1 = tile_u0 + p.n_kb;
-      if (u0 <= tile_u0 && u1 >= tile_u1) {
-        gemv_epilogue_row(p, t, warp, lane, out, ar_half);
-      } else {
-        const int c_first = gemv_owner(tile_u0, units, grid);
-        const int c_last = gemv_owner(tile_u1 - 1, units, grid);
-        const int my_slot = 2 * cta + ((u0 / p.n_kb) == t ? 0 : 1);
-        float4* part = reinterpret_cast<float4*>(p.partial);
-        part[((my_slot * 4 + warp) * 32 + lane) * 2] = make_float4(out[0], out[1], out[2], out[3]);
-        part[((my_slot * 4 + warp) * 32 + lane) * 2 + 1] = make_float4(out[4], out[5], out[6], out[7]);
-        __threadfence();
-        __syncwarp();
-        int prev = 0;
-        if (lane == 0) prev = atomicAdd(&p.counters[t * 8 + warp], 1);
-        prev = __shfl_sync(0xffffffffu, prev, 0);
-        if (prev == c_last - c_first) {
+      // ---- merge the two groups' sums (every epilogue warp gets here for every tile, on every path) ----
+      float* mb = merge + (merge_buf * kGemvGroupThreads + gw * 32 + lane) * 8;
+      if (eg == 1) {
+        *reinterpret_cast<float4*>(mb) = make_float4(out[0], out[1], out[2], out[3]);
+        *reinterpret_cast<float4*>(mb + 4) = make_float4(out[4], out[5], out[6], out[7]);
+      }
+      asm volatile("bar.sync 3, %0;" ::"n"(kGemvEpilogueThreads) : "memory");
+      merge_buf ^= 1;
+      if (eg == 0) {
+        const float4 m0 = *reinterpret_cast<const float4*>(mb);
+        const float4 m1 = *reinterpret_cast<const float4*>(mb + 4);
+        out[0] += m0.x; out[1] += m0.y; out[2] += m0.z; out[3] += m0.w;
+        out[4] += m1.x; out[5] += m1.y; out[6] += m1.z; out[7] += m1.w;
+        const int tile_u0 = t * p.n_kb, tile_u1 = tile_u0 + p.n_kb;
+        if (u0 <= tile_u0 && u1 >= tile_u1) {
+          gemv_epilogue_row(p, t, gw, lane, out, ar_half);
+        } else {
+          const int c_first = gemv_owner(tile_u0, units, grid);
+          const int c_last = gemv_owner(tile_u1 - 1, units, grid);
+          const int my_slot = 2 * cta + ((u0 / p.n_kb) == t ? 0 : 1);
+          float4* part = reinterpret_cast<float4*>(p.partial);
+          part[((my_slot * 4 + gw) * 32 + lane) * 2] = make_float4(out[0], out[1], out[2], out[3]);
+          part[((my_slot * 4 + gw) * 32 + lane) * 2 + 1] = make_float4(out[4], out[5], out[6], out[7]);
           __threadfence();
-          float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int cc = c_first; cc <= c_last; ++cc) {
-            const int cu0 = static_cast<int>(gemv_range_begin(units, grid, cc));
-            const int slot = 2 * cc + ((cu0 / p.n_kb) == t ? 0 : 1);
-            const float4 v0 = __ldcg(&part[((slot * 4 + warp) * 32 + lane) * 2]);
-            const float4 v1 = __ldcg(&part[((slot * 4 + warp) * 32 + lane) * 2 + 1]);
-            sum[0] += v0.x; sum[1] += v0.y; sum[2] += v0.z; sum[3] += v0.w;
-            sum[4] += v1.x; sum[5] += v1.y; sum[6] += v1.z; sum[7] += v1.w;
+          __syncwarp();
+          int prev = 0;
+          if (lane == 0) prev = atomicAdd(&p.counters[t * 8 + gw], 1);
+          prev = __shfl_sync(0xffffffffu, prev, 0);
+          if (prev == c_last - c_first) {
+            __threadfence();
+            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int cc = c_first; cc <= c_last; ++cc) {
+              const int cu0 = static_cast<int>(gemv_range_begin(units, grid, cc));
+              const int slot = 2 * cc + ((cu0 / p.n_kb) == t ? 0 : 1);
+              const float4 v0 = __ldcg(&part[((slot * 4 + gw) * 32 + lane) * 2]);
+              const float4 v1 = __ldcg(&part[((slot * 4 + gw) * 32 + lane) * 2 + 1]);
+              sum[0] += v0.x; sum[1] += v0.y; sum[2] += v0.z; sum[3] += v0.w;
+              sum[4] += v1.x; sum[5] += v1.y; sum[6] += v1.z; sum[7] += v1.w;
+            }
+            if (lane == 0) p.counters[t * 8 + gw] = 0;
+            gemv_epilogue_row(p, t, gw, lane, sum, ar_half);
           }
-          if (lane == 0) p.counters[t * 8 + warp] = 0;
-          gemv_epilogue_row(p, t, warp, lane, sum, ar_half);
         }
       }
 #pragma unroll
@@ -563,58 +652,54 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     };
 
     int kb = u0 < u1 ? u0 % p.n_kb : 0, t = u0 < u1 ? u0 / p.n_kb : 0;
+    int s = 0;
+    uint32_t ph = 0;
     for (int u = u0; u < u1; ++u, ++kb) {
       if (kb == p.n_kb) {
         kb = 0;
         ++t;
       }
-      const int i = u - u0;
-      const int s = i % kGemvStages, a = i % kGemvAccs;
-      // every decision below is made warp-uniform: tcgen05.ld needs the whole warp
-      if (__all_sync(0xffffffffu, ok && !*cta_error)) {
+      // every decision below is warp-uniform: tcgen05.ld needs the whole warp
+      if (((u - u0) & 1) == eg && ok) {
         const long long c0 = p.prof != nullptr ? clock64() : 0;
-        if (!__all_sync(0xffffffffu, mbar_wait(&full[s], static_cast<uint32_t>(i / kGemvStages) & 1))) {
+        // acc_full[s] completes after the unit's MMAs, which were issued after full[s] completed:
+        // the slot's scales are in shared memory by then.
+        if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[s], ph, cta_error))) {
           set_status(p.status, ST_WAIT_FULL_TIMEOUT);
           *cta_error = 1;
           ok = false;
         } else {
+          const long long c1 = p.prof != nullptr ? clock64() : 0;
           if (u == u0 && warp == 0 && lane == 0) gemv_stamp(p, kGemvProfFirstData);
-          const uint8_t* sw = smem + s * TB_STAGE_BYTES;
-          const float ws = *reinterpret_cast<const float*>(sw + TB_WBLK_DATA + ((warp * 32 + lane) >> 3) * 4);
-          const float4 cs0 = *reinterpret_cast<const float4*>(sw + TB_WBLK_BYTES + TB_XBLK_DATA);
-          const float4 cs1 = *reinterpret_cast<const float4*>(sw + TB_WBLK_BYTES + TB_XBLK_DATA + 16);
+          tc_fence_after();
+          uint32_t dr[8];
+          tmem_ld8_issue(tmem_base + lane_base + static_cast<uint32_t>(s * kGemvAccCols), dr);
+          const uint8_t* sw = smem + s * kGemvSlotStride;
+          const float ws = *reinterpret_cast<const float*>(sw + TB_WBLK_DATA + ((gw * 32 + lane) >> 3) * 4);
+          const float4 cs0 = *reinterpret_cast<const float4*>(sw + kGemvSlotXOff + TB_XBLK_DATA);
+          const float4 cs1 = *reinterpret_cast<const float4*>(sw + kGemvSlotXOff + TB_XBLK_DATA + 16);
+          tmem_ld_wait(dr);
+          tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&empty[s]);
-          if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[a], static_cast<uint32_t>(i / kGemvAccs) & 1))) {
-            set_status(p.status, ST_WAIT_FULL_TIMEOUT);
-            *cta_error = 1;
-            ok = false;
-          } else {
-            const long long c1 = p.prof != nullptr ? clock64() : 0;
-            tc_fence_after();
-            float d[8];
-            tmem_ld8(tmem_base + lane_base + static_cast<uint32_t>(a * kGemvAccCols), d);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[a]);
-            out[0] = fmaf(d[0], ws * cs0.x, out[0]);
-            out[1] = fmaf(d[1], ws * cs0.y, out[1]);
-            out[2] = fmaf(d[2], ws * cs0.z, out[2]);
-            out[3] = fmaf(d[3], ws * cs0.w, out[3]);
-            out[4] = fmaf(d[4], ws * cs1.x, out[4]);
-            out[5] = fmaf(d[5], ws * cs1.y, out[5]);
-            out[6] = fmaf(d[6], ws * cs1.z, out[6]);
-            out[7] = fmaf(d[7], ws * cs1.w, out[7]);
-            if (p.prof != nullptr) {
-              prof_wait += c1 - c0;
-              prof_math += clock64() - c1;
-              ++prof_units;
-            }
+          out[0] = fmaf(__uint_as_float(dr[0]), ws * cs0.x, out[0]);
+          out[1] = fmaf(__uint_as_float(dr[1]), ws * cs0.y, out[1]);
+          out[2] = fmaf(__uint_as_float(dr[2]), ws * cs0.z, out[2]);
+          out[3] = fmaf(__uint_as_float(dr[3]), ws * cs0.w, out[3]);
+          out[4] = fmaf(__uint_as_float(dr[4]), ws * cs1.x, out[4]);
+          out[5] = fmaf(__uint_as_float(dr[5]), ws * cs1.y, out[5]);
+          out[6] = fmaf(__uint_as_float(dr[6]), ws * cs1.z, out[6]);
+          out[7] = fmaf(__uint_as_float(dr[7]), ws * cs1.w, out[7]);
+          if (p.prof != nullptr) {
+            prof_wait += c1 - c0;
+            prof_math += clock64() - c1;
+            ++prof_units;
           }
         }
       }
-      else {
-        ok = false;
+      if (++s == kGemvStages) {
+        s = 0;
+        ph ^= 1u;
       }
       if (kb == p.n_kb - 1 || u == u1 - 1) {
         if (u == u1 - 1 && warp == 0 && lane == 0) gemv_stamp(p, kGemvProfLastUnit);
@@ -630,13 +715,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       }
     }
 
-    if (p.ar.world > 1) {
-      // ---- one-shot all-reduce over peer memory, fused behind the streaming loop ----
+    if (p.ar.world > 1 && eg == 0) {
+      // ---- one-shot all-reduce over peer memory, fused behind the streaming loop (group 0) ----
       AllReduceState* self = p.ar.state[p.ar.rank];
       // 1. this CTA's peer stores are done: publish them.  The last CTA of the rank to get here
       //    tells every rank (itself included) that this rank's partial has landed.
       __threadfence_system();
-      asm volatile("bar.sync 1, %0;" ::"n"(kGemvEpilogueThreads) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemvGroupThreads) : "memory");
       if (threadIdx.x == 0) {
         const unsigned int prev = atomicAdd(&self->local_arrive, 1u);
         if (prev == static_cast<unsigned int>(grid) - 1u) {
@@ -660,14 +745,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           __nanosleep(32);
         }
       }
-      asm volatile("bar.sync 1, %0;" ::"n"(kGemvEpilogueThreads) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemvGroupThreads) : "memory");
       // 3. reduce the world's slots for this CTA's share of rows, add the residual, store.
       if (!*cta_error) {
         const float* mine = p.ar.recv[p.ar.rank];
         const int total = p.n_tokens * p.n_rows;
         const int e0 = static_cast<int>(static_cast<long long>(total) * cta / grid);
         const int e1 = static_cast<int>(static_cast<long long>(total) * (cta + 1) / grid);
-        for (int e = e0 + static_cast<int>(threadIdx.x); e < e1; e += kGemvEpilogueThreads) {
+        for (int e = e0 + static_cast<int>(threadIdx.x); e < e1; e += kGemvGroupThreads) {
           const int tok = e / p.n_rows, row = e % p.n_rows;
           float v = 0.f;
           for (int r = 0; r < p.ar.world; ++r)
@@ -676,7 +761,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         }
       }
       // 4. the last CTA to finish opens the next call (flips the buffer half).
-      asm volatile("bar.sync 1, %0;" ::"n"(kGemvEpilogueThreads) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemvGroupThreads) : "memory");
       if (threadIdx.x == 0) {
         const unsigned int prev = atomicAdd(&self->local_done, 1u);
         if (prev == static_cast<unsigned int>(grid) - 1u) {
@@ -692,7 +777,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
   // ---- common tail: every warp arrives here on every path; then the tensor memory is returned ----
   tc_fence_before();
   __syncthreads();
-  if (warp == kGemvMmaWarp) {
+  if (warp == kGemvFirstMmaWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kGemvTmemCols)
                  : "memory");
