@@ -216,6 +216,37 @@ def run_ours(args) -> None:
         graph.replay()
     barrier()
 
+    if args.trace_step:
+        # one eager step with every streaming launch traced into its own record
+        import ctypes
+        n_rec = 16
+        trace = torch.zeros(n_rec, 256, 16, dtype=torch.int64, device=dev)
+        ctx = ctypes.c_void_p(tilert_b200.tilert_init(local))
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        tilert_b200.check(lib.tilert_b200_set_profile_ring(ctx, ctypes.c_void_p(trace.data_ptr()), n_rec))
+        step()
+        torch.cuda.synchronize()
+        tilert_b200.check(lib.tilert_b200_set_profile(ctx, None))
+        tr = trace.cpu().double()
+        tr = tr[:, :148]
+        used = [r for r in range(n_rec) if tr[r, :, 0].max() > 0]
+        t_step0 = min(tr[r, :, 0][tr[r, :, 0] > 0].min() for r in used)
+        rows = []
+        for r in used:
+            m = tr[r, :, 0] > 0
+            ent, rdy, fd, lu, td, ex = (tr[r, m, i] for i in (0, 1, 2, 3, 4, 7))
+            k0 = ent.min()
+            rows.append({"launch": r, "ctas": int(m.sum()), "start_us": round(float(k0 - t_step0) / 1e3, 2),
+                         "first_data_med": round(float((fd - k0).median()) / 1e3, 2),
+                         "last_unit_min_med_max": [round(float(v) / 1e3, 2) for v in
+                                                   ((lu - k0).min(), (lu - k0).median(), (lu - k0).max())],
+                         "exit_max": round(float((ex - k0).max()) / 1e3, 2)})
+        print(json.dumps({"mode": "trace-step", "launches": rows}), flush=True)
+        if comm is not None:
+            comm.close()
+        return
+
     # ---- device-timed steps: L2 flushed (untimed) before each step ----
     sampler = ClockSampler(local)
     if rank == 0:
@@ -390,6 +421,8 @@ def run_profile_gemv(args) -> None:
     launch()
     torch.cuda.synchronize()
     tilert_b200.check(tilert_b200.lib().tilert_b200_set_profile(ctx, None))
+    if os.environ.get("TB_TRACE_DUMP"):
+        torch.save(trace.cpu(), os.environ["TB_TRACE_DUMP"] + ".full")
     tr = trace[:148].cpu().double()
     t0 = tr[:, 0].min()
     rel = (tr[:, :8] - t0) / 1e3
@@ -419,6 +452,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: no clock-sampling loop, no CPU baseline")
+    ap.add_argument("--trace-step", action="store_true",
+                    help="print the per-launch phase stamps of the streaming products of one step")
     ap.add_argument("--gemv-k", type=int, default=32768)
     ap.add_argument("--gemv-packed", action="store_true", help="profile-gemv: activations packed beforehand")
     ap.add_argument("--profile-gemv", action="store_true",

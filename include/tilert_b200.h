@@ -64,6 +64,9 @@ long long tilert_b200_launch_count(void);
  * %globaltimer stamps (entry, ready, first data, last unit, tiles done, first conversion, copies
  * issued, exit) and three counters of its first consumer warp (cycles waiting, cycles consuming, units).  NULL switches tracing off. */
 int tilert_b200_set_profile(TbContext* ctx, unsigned long long* trace);
+/* Same with room for several launches: `trace` is u64 [n_records][256][16] and the k-th streaming
+ * launch after this call writes record k % n_records (one decode step = one record per product). */
+int tilert_b200_set_profile_ring(TbContext* ctx, unsigned long long* trace, int n_records);
 
 /* ---- peer-to-peer plumbing for the fused all-reduce ------------------------------------ */
 /* The reference exchanges raw buffer addresses between its per-GPU threads
@@ -229,16 +232,18 @@ int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const void* q_pe, 
  * cudaMalloc from plug-ins, or a serving loop with a frozen memory budget in which an allocation
  * would synchronise the device.  It takes no TbContext (creating one allocates) and calls no
  * cudaMalloc, cudaFree or allocating library routine.  Its scratch -- partial sums of row tiles
- * shared by two thread blocks, and their arrival counters -- is a fixed ~2.1 MB array inside the
- * library image, held by every GPU that loads the library until the process exits.
+ * shared by two thread blocks, their arrival counters, and the converted activation blocks with
+ * their ready flags -- is a fixed ~2.4 MB array inside the library image, held by every GPU that
+ * loads the library until the process exits.
  *
  *   x [tokens, k] bf16, w_packed for [n, k], residual [tokens, n] bf16 or NULL, out [tokens, n] bf16;
- *   tokens 1..4, k a multiple of 128, n at most 131072 rows (a larger n returns TB_EINVAL);
+ *   tokens 1..4, k a multiple of 128 and at most 32768, n at most 131072 rows (a larger k or n
+ *   returns TB_EINVAL);
  *   status_out_dev: optional device int that receives the kernel's status word (0 = completed).
  *
  * The first call on each device looks up the array's device address and sets a function
  * attribute; make that call outside any stream capture.  All calls on a device share the one
- * array: the counters are cleared at the start of every call, and two calls whose kernels overlap
+ * array: the counters and flags are cleared at the start of every call, and two calls whose kernels overlap
  * on the GPU (different streams) race on it -- serialise them. */
 int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_packed, const void* residual, int tokens, int k,
                                   int n, void* out, int* status_out_dev, void* stream);

@@ -66,6 +66,8 @@ constexpr int kMaxGrid = 256;                       // CTAs a GEMV launch may us
 constexpr size_t kPartialBytes = 2ull * kMaxGrid * 8 * 32 * 16;
 constexpr int kMaxCounters = 1 << 16;               // row tiles * 8
 constexpr size_t kXpackScratchBytes = 2ull << 20;   // activation blocks of the widest K (2048 blocks)
+constexpr int kMaxXBlocks = 1984;                   // X blocks one launch may convert (fits kXpackScratchBytes)
+constexpr size_t kXFlagBytes = (kMaxXBlocks + 64) * sizeof(unsigned);  // flags, then {epoch, done}
 constexpr size_t kSmallScratchBytes = 64ull << 10;  // slot ids / weights for routing
 
 }  // namespace
@@ -77,8 +79,12 @@ struct TbContext {
   int* counters = nullptr;
   int* status = nullptr;
   uint8_t* xpack = nullptr;
+  uint8_t* xshared = nullptr;  // X blocks converted inside a streaming launch, shared by its CTAs
+  unsigned* xflags = nullptr;  // their ready flags, then the launch-epoch state
   uint8_t* small = nullptr;
   unsigned long long* prof = nullptr;  // caller-owned trace buffer, see tilert_b200_set_profile
+  int prof_records = 1;                // records in the buffer; streaming launch k writes record k % prof_records
+  long long prof_next = 0;
 };
 
 struct TbComm {
@@ -110,7 +116,16 @@ int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
   p.partial = ctx->partial;
   p.counters = ctx->counters;
   p.status = ctx->status;
+  if (p.x_mode == X_BF16) {
+    const int n_xsegs = p.tiles_per_xseg > 0 ? p.n_tiles / p.tiles_per_xseg : 1;
+    TB_REQUIRE(p.tiles_per_xseg <= 0 || p.n_tiles % p.tiles_per_xseg == 0);
+    TB_REQUIRE(static_cast<long long>(n_xsegs) * p.n_kb <= kMaxXBlocks);
+    p.xs = ctx->xshared;
+    p.xflag = ctx->xflags;
+    p.xstate = ctx->xflags + kMaxXBlocks;
+  }
   p.prof = ctx->prof;
+  if (ctx->prof != nullptr) p.prof += (ctx->prof_next++ % ctx->prof_records) * (256 * 16);
   TB_CUDA(launch(wstream_gemv_kernel, dim3(grid), dim3(kGemvThreads), kGemvSmemBytes, st, p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
@@ -197,7 +212,7 @@ int pack_flat(const void* x, int tokens, int k, const float* seg_scale, int n_se
 extern "C" const char* tilert_b200_last_error(void) { return g_last_error.c_str(); }
 extern "C" int tilert_b200_dsa_temp_vars_size(void) { return 56; }
 extern "C" size_t tilert_b200_context_bytes(void) {
-  return kPartialBytes + kMaxCounters * sizeof(int) + 256 + kXpackScratchBytes + kSmallScratchBytes;
+  return kPartialBytes + kMaxCounters * sizeof(int) + 256 + 2 * kXpackScratchBytes + kXFlagBytes + kSmallScratchBytes;
 }
 extern "C" size_t tilert_b200_xpack_bytes(int dim) { return static_cast<size_t>(dim / TB_KBLOCK) * TB_XBLK_BYTES; }
 
@@ -217,6 +232,10 @@ extern "C" int tilert_b200_init(int device, TbContext** ctx_out) {
   TB_CUDA(cudaMalloc(&c->counters, kMaxCounters * sizeof(int)));
   TB_CUDA(cudaMalloc(&c->status, 256));
   TB_CUDA(cudaMalloc(&c->xpack, kXpackScratchBytes));
+  TB_CUDA(cudaMalloc(&c->xshared, kXpackScratchBytes));
+  TB_CUDA(cudaMalloc(&c->xflags, kXFlagBytes));
+  TB_CUDA(cudaMemset(c->xshared, 0, kXpackScratchBytes));
+  TB_CUDA(cudaMemset(c->xflags, 0, kXFlagBytes));
   TB_CUDA(cudaMalloc(&c->small, kSmallScratchBytes));
   TB_CUDA(cudaMemset(c->counters, 0, kMaxCounters * sizeof(int)));
   TB_CUDA(cudaMemset(c->status, 0, 256));
@@ -234,6 +253,8 @@ extern "C" int tilert_b200_destroy(TbContext* ctx) {
   cudaFree(ctx->counters);
   cudaFree(ctx->status);
   cudaFree(ctx->xpack);
+  cudaFree(ctx->xshared);
+  cudaFree(ctx->xflags);
   cudaFree(ctx->small);
   delete ctx;
   return TB_OK;
@@ -253,6 +274,15 @@ extern "C" long long tilert_b200_launch_count(void) { return g_launches; }
 extern "C" int tilert_b200_set_profile(TbContext* ctx, unsigned long long* trace) {
   TB_REQUIRE(ctx != nullptr);
   ctx->prof = trace;
+  ctx->prof_records = 1;
+  ctx->prof_next = 0;
+  return TB_OK;
+}
+extern "C" int tilert_b200_set_profile_ring(TbContext* ctx, unsigned long long* trace, int n_records) {
+  TB_REQUIRE(ctx != nullptr && n_records >= 1);
+  ctx->prof = trace;
+  ctx->prof_records = n_records;
+  ctx->prof_next = 0;
   return TB_OK;
 }
 extern "C" int tilert_b200_dev_alloc(size_t bytes, void** dev_ptr_out) {
@@ -835,12 +865,16 @@ extern "C" int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const v
 
 // ------------------------------------------------------------ allocation-free entry point
 // Scratch for tilert_b200_matvec_fp8_static: partial sums of row tiles that straddle two CTAs
-// (2 * kMaxGrid slots of 4 KB), one arrival counter per 16-row group, and a status word.  It lives
-// in the library image, so every GPU that loads the library holds these ~2.1 MB until exit.
+// (2 * kMaxGrid slots of 4 KB), one arrival counter per 16-row group, a status word, and the shared
+// X blocks of a launch with their ready flags.  It lives in the library image, so every GPU that
+// loads the library holds these ~2.4 MB until exit.
 namespace {
 constexpr int kStaticMaxTiles = 1024;                                   // rows <= 131072
 constexpr size_t kStaticCounterBytes = kStaticMaxTiles * 8 * sizeof(int);
-constexpr size_t kStaticScratchBytes = kPartialBytes + kStaticCounterBytes + 256;
+constexpr int kStaticMaxKBlocks = 256;                                  // k <= 32768
+constexpr size_t kStaticXBytes = static_cast<size_t>(kStaticMaxKBlocks) * TB_XBLK_BYTES;   // shared X blocks
+constexpr size_t kStaticXFlagBytes = (kStaticMaxKBlocks + 64) * sizeof(unsigned);           // flags + epoch state
+constexpr size_t kStaticScratchBytes = kPartialBytes + kStaticCounterBytes + 256 + kStaticXFlagBytes + kStaticXBytes;
 }  // namespace
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
@@ -860,6 +894,8 @@ extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_pac
   const int n_tiles = (n + TB_TILE_ROWS - 1) / TB_TILE_ROWS;
   if (n_tiles > kStaticMaxTiles)
     return fail(TB_EINVAL, "tilert_b200_matvec_fp8_static: n exceeds the static scratch (at most 131072 rows)%s");
+  if (k / TB_KBLOCK > kStaticMaxKBlocks)
+    return fail(TB_EINVAL, "tilert_b200_matvec_fp8_static: k exceeds the static scratch (at most 32768)%s");
   TB_REQUIRE(static_cast<long long>(n_tiles) * (k / TB_KBLOCK) < (1ll << 30));
   int device = 0;
   TB_CUDA(cudaGetDevice(&device));
@@ -882,7 +918,10 @@ extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_pac
   int* status = reinterpret_cast<int*>(view.base + kPartialBytes + kStaticCounterBytes);
   // The array keeps whatever the previous call left: the arrival counters and the status word must
   // start at zero (a call that was cut short would otherwise leave them counting).
-  TB_CUDA(cudaMemsetAsync(counters, 0, kStaticCounterBytes + 256, st));
+  // The same goes for the X-block flags and their epoch state, which follow the status word.
+  unsigned* xflags = reinterpret_cast<unsigned*>(view.base + kPartialBytes + kStaticCounterBytes + 256);
+  uint8_t* xshared = view.base + kPartialBytes + kStaticCounterBytes + 256 + kStaticXFlagBytes;
+  TB_CUDA(cudaMemsetAsync(counters, 0, kStaticCounterBytes + 256 + kStaticXFlagBytes, st));
   GemvParams p;
   gemv_defaults(p);
   p.w = w_packed;
@@ -898,6 +937,9 @@ extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_pac
   p.partial = partial;
   p.counters = counters;
   p.status = status;
+  p.xs = xshared;
+  p.xflag = xflags;
+  p.xstate = xflags + kStaticMaxKBlocks;
   const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
   int grid = view.num_sms < kMaxGrid ? view.num_sms : kMaxGrid;
   if (units < grid) grid = static_cast<int>(units);

@@ -72,6 +72,9 @@ struct GemvParams {
   const float* gamma;            // X_BF16: optional RMSNorm gain over the whole vector (n_kb * 128 long)
   float eps;
   const float* seg_scale;        // X_BF16: optional [tokens, n_kb / kb_per_kseg] multipliers (routing weights)
+  uint8_t* xs;                   // X_BF16 scratch: the launch's X blocks [x segments * n_kb], written by all CTAs
+  unsigned* xflag;               // X_BF16 scratch: per X block, the launch epoch + 1 once the block is written
+  unsigned* xstate;              // X_BF16 scratch: {epoch = completed X_BF16 launches, CTAs done}, self-maintained
   int n_tiles;
   int n_kb;
   const int* nseg_ids;
@@ -121,6 +124,14 @@ __device__ __forceinline__ void gemv_stamp(const GemvParams& p, int slot) {
   if (p.prof != nullptr) p.prof[blockIdx.x * 16 + slot] = globaltimer_ns();
 }
 
+// Per-unit timeline of CTA 0 (SM cycle counter), rows 148.. of the trace: event e of unit i in
+// [kGemvTimelineFirst, +16) goes to prof[(148 + e) * 16 + i - kGemvTimelineFirst].
+constexpr int kGemvTimelineFirst = 96;
+__device__ __forceinline__ void gemv_timeline(const GemvParams& p, int ev, int i) {
+  if (p.prof != nullptr && blockIdx.x == 0 && i >= kGemvTimelineFirst && i < kGemvTimelineFirst + 16)
+    p.prof[(148 + ev) * 16 + i - kGemvTimelineFirst] = static_cast<unsigned long long>(clock64());
+}
+
 #ifndef TB_GEMV_STAGES
 #define TB_GEMV_STAGES 12
 #endif
@@ -162,7 +173,14 @@ __device__ __forceinline__ uint64_t umma_desc(const void* smem_ptr, uint32_t lbo
 // Instruction descriptor: D = f32, A = B = e4m3, both K-major, N = 16, M = 128.  Only 8 activation
 // columns exist: the B descriptor's 8-column group stride is 0, so columns 8-15 repeat columns 0-7
 // and are never read back.
+#ifdef TB_EXP_M64
+constexpr uint32_t kUmmaIdesc = (1u << 4) | (2u << 17) | (4u << 24);
+#else
 constexpr uint32_t kUmmaIdesc = (1u << 4) | (2u << 17) | (8u << 24);
+#endif
+#ifndef TB_EXP_NMMA
+#define TB_EXP_NMMA 4
+#endif
 __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -198,6 +216,26 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&d)[8]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 8; ++i) d[i] = __uint_as_float(r[i]);
+}
+
+// Bounded wait for a flag in global memory to reach `want` (set with st.release.gpu by another CTA).
+__device__ __forceinline__ bool flag_wait(const unsigned* flag, unsigned want, const volatile int* abort) {
+  unsigned v;
+#pragma unroll 1
+  for (int i = 0; i < 16; ++i) {
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v == want) return true;
+  }
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v == want) return true;
+      __nanosleep(64);
+    }
+    if (*abort != 0 || clock64() - t0 > kWaitBudgetCycles) return false;
+  }
 }
 
 __device__ __forceinline__ long long gemv_range_begin(long long units, int grid, int cta) {
@@ -276,6 +314,85 @@ __device__ __forceinline__ void gemv_epilogue_row(const GemvParams& p, int tile,
     if (t < ntok) gemv_store(p, row, t, val[t]);
 }
 
+// 1 / rms of each token's activation vector from the per-warp partial sums of squares (1 without a gain).
+__device__ __forceinline__ void gemv_rinv(const GemvParams& p, const float* norm_part, float (&rinv)[4]) {
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    rinv[t] = 1.f;
+    if (p.gamma != nullptr) {
+      float tot = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < kGemvHelperWarps; ++w2) tot += norm_part[w2 * 4 + t];
+      rinv[t] = rsqrtf(tot / static_cast<float>(p.n_kb * TB_KBLOCK) + p.eps);
+    }
+  }
+}
+
+// Converts X block `xb` (x segment xb / n_kb, k block xb % n_kb) of the launch's bf16 activations
+// into packed form at `blk` (shared or global memory): per token two e4m3 terms with power-of-two
+// scales, so the scaling is a multiplication and the residual x - hi*s is exact.  One warp.
+__device__ __forceinline__ void gemv_convert_xblock(const GemvParams& p, int xb, const float (&rinv)[4], uint8_t* blk,
+                                                    int lane) {
+  const int ntok = p.n_tokens;
+  const int kb = xb % p.n_kb;
+  const long long off = static_cast<long long>(xb) * TB_KBLOCK + lane * 4;  // x segments are contiguous
+  uint2 raw[4];
+#pragma unroll
+  for (int tk = 0; tk < 4; ++tk)
+    raw[tk] = tk < ntok ? *reinterpret_cast<const uint2*>(p.xb + tk * p.xb_stride + off) : make_uint2(0u, 0u);
+  const float4 g = p.gamma != nullptr ? *reinterpret_cast<const float4*>(p.gamma + kb * TB_KBLOCK + lane * 4)
+                                      : make_float4(1.f, 1.f, 1.f, 1.f);
+  const float g4[4] = {g.x, g.y, g.z, g.w};
+  const int c = lane >> 3, r = (lane >> 2) & 1, q4 = lane & 3;
+#pragma unroll
+  for (int tk = 0; tk < 4; ++tk) {
+    uint32_t whi = 0u, wlo = 0u;
+    float2 sc = make_float2(0.f, 0.f);
+    if (tk < ntok) {
+      const uint2 rw = raw[tk];
+      float x4[4] = {__uint_as_float(rw.x << 16), __uint_as_float(rw.x & 0xffff0000u), __uint_as_float(rw.y << 16),
+                     __uint_as_float(rw.y & 0xffff0000u)};
+      if (p.gamma != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x4[j] = bf2f(f2bf(x4[j] * rinv[tk] * g4[j]));
+      }
+      float amax = fmaxf(fmaxf(fabsf(x4[0]), fabsf(x4[1])), fmaxf(fabsf(x4[2]), fabsf(x4[3])));
+      amax = warp_max(amax);
+      // s_hi = 2^e: the power of two at or just above amax / 448 (at most one step higher when the
+      // product below rounds up); exponent clamped so that s_hi / 16 and 1 / s_hi stay normal
+      const uint32_t tb = __float_as_uint(amax * (1.0f / 448.0f));
+      int e = static_cast<int>(tb >> 23) + ((tb & 0x7fffffu) != 0u ? 1 : 0);
+      e = amax > 0.f ? min(max(e, 16), 240) : 127;
+      const float s_hi = __uint_as_float(static_cast<uint32_t>(e) << 23);
+      const float inv_hi = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);
+      const float s_lo = s_hi * 0.0625f, inv_lo = inv_hi * 16.f;
+      const __nv_fp8x2_storage_t h01 =
+          __nv_cvt_float2_to_fp8x2(make_float2(x4[0] * inv_hi, x4[1] * inv_hi), __NV_SATFINITE, __NV_E4M3);
+      const __nv_fp8x2_storage_t h23 =
+          __nv_cvt_float2_to_fp8x2(make_float2(x4[2] * inv_hi, x4[3] * inv_hi), __NV_SATFINITE, __NV_E4M3);
+      const __half2_raw hr01 = __nv_cvt_fp8x2_to_halfraw2(h01, __NV_E4M3);
+      const __half2_raw hr23 = __nv_cvt_fp8x2_to_halfraw2(h23, __NV_E4M3);
+      const float2 hf01 = __half22float2(*reinterpret_cast<const __half2*>(&hr01));
+      const float2 hf23 = __half22float2(*reinterpret_cast<const __half2*>(&hr23));
+      const float r0 = fmaf(-hf01.x, s_hi, x4[0]), r1 = fmaf(-hf01.y, s_hi, x4[1]);
+      const float r2 = fmaf(-hf23.x, s_hi, x4[2]), r3 = fmaf(-hf23.y, s_hi, x4[3]);
+      const __nv_fp8x2_storage_t l01 =
+          __nv_cvt_float2_to_fp8x2(make_float2(r0 * inv_lo, r1 * inv_lo), __NV_SATFINITE, __NV_E4M3);
+      const __nv_fp8x2_storage_t l23 =
+          __nv_cvt_float2_to_fp8x2(make_float2(r2 * inv_lo, r3 * inv_lo), __NV_SATFINITE, __NV_E4M3);
+      whi = static_cast<uint32_t>(h01) | (static_cast<uint32_t>(h23) << 16);
+      wlo = static_cast<uint32_t>(l01) | (static_cast<uint32_t>(l23) << 16);
+      float mlt = 1.f;
+      if (lane == 0 && p.seg_scale != nullptr) mlt = p.seg_scale[tk * (p.n_kb / p.kb_per_kseg) + kb / p.kb_per_kseg];
+      sc = make_float2(s_hi * mlt, s_lo * mlt);
+    }
+    // columns of absent tokens are written as zeros: the block is read whole by the tensor core
+    *reinterpret_cast<uint32_t*>(blk + c * 256 + r * 128 + (2 * tk) * 16 + q4 * 4) = whi;
+    *reinterpret_cast<uint32_t*>(blk + c * 256 + r * 128 + (2 * tk + 1) * 16 + q4 * 4) = wlo;
+    if (lane == 0) *reinterpret_cast<float2*>(blk + TB_XBLK_DATA + 8 * tk) = sc;
+  }
+}
+
 __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   float* merge = reinterpret_cast<float*>(smem + kGemvStages * kGemvSlotStride);  // [2][group threads][8]
@@ -300,7 +417,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
   if (threadIdx.x == 0) {
     gemv_stamp(p, kGemvProfEntry);
     for (int s = 0; s < kGemvStages; ++s) {
-      mbar_init(&full[s], p.x_mode == X_BF16 ? 2 : 1);  // producer (+ converter) arrive once per use
+      mbar_init(&full[s], p.x_mode == X_BF16 ? 2 : 1);  // producer (+ converter, or a second producer arrival)
       mbar_init(&empty[s], kGemvGroupWarps);            // the warps of the epilogue group that read the unit back
       mbar_init(&acc_full[s], 1);                       // completion of the unit's MMAs
     }
@@ -335,14 +452,24 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     const int hw = is_epilogue ? warp : warp - kGemvFirstConverterWarp + kGemvEpilogueWarps;
     const int n_chunks = p.n_kb * (TB_KBLOCK / 4);  // 8-byte chunks per token
     float ss[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int ch = hw * 32 + lane; ch < n_chunks; ch += kGemvHelperWarps * 32) {
+    // batches of independent loads: the whole vector is a few dependent-latency round trips otherwise
+    constexpr int kBatch = 8;
+    for (int ch0 = hw * 32 + lane; ch0 < n_chunks; ch0 += kBatch * kGemvHelperWarps * 32) {
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         if (t < p.n_tokens) {
-          const uint2 raw = *reinterpret_cast<const uint2*>(p.xb + t * p.xb_stride + ch * 4);
-          const float a0 = __uint_as_float(raw.x << 16), a1 = __uint_as_float(raw.x & 0xffff0000u);
-          const float a2 = __uint_as_float(raw.y << 16), a3 = __uint_as_float(raw.y & 0xffff0000u);
-          ss[t] += a0 * a0 + a1 * a1 + a2 * a2 + a3 * a3;
+          uint2 raw[kBatch];
+#pragma unroll
+          for (int j = 0; j < kBatch; ++j) {
+            const int ch = ch0 + j * kGemvHelperWarps * 32;
+            raw[j] = ch < n_chunks ? *reinterpret_cast<const uint2*>(p.xb + t * p.xb_stride + ch * 4) : make_uint2(0u, 0u);
+          }
+#pragma unroll
+          for (int j = 0; j < kBatch; ++j) {
+            const float a0 = __uint_as_float(raw[j].x << 16), a1 = __uint_as_float(raw[j].x & 0xffff0000u);
+            const float a2 = __uint_as_float(raw[j].y << 16), a3 = __uint_as_float(raw[j].y & 0xffff0000u);
+            ss[t] += a0 * a0 + a1 * a1 + a2 * a2 + a3 * a3;
+          }
         }
       }
     }
@@ -357,24 +484,18 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
   if (is_producer) {
     // ------------------------------------------------------------ producers
     // One issuing thread per warp; unit i of the CTA's range is copied by producer i % 4 into ring
-    // slot i % kGemvStages.
+    // slot i % kGemvStages: the W block from the weight tensor and the X block either from the
+    // caller's packed activations (X_PACKED) or from the launch's shared X blocks (X_BF16), which
+    // the converter warps of all CTAs are writing meanwhile -- a per-block flag says when.
     if (lane == 0) {
       const int pw = warp - kGemvFirstProducerWarp;
       const uint64_t pol = policy_evict_first();
+      const bool shared_x = p.x_mode == X_BF16;
       int last_i = -1;
       long long pw_wait = 0;
-      int t = (u0 + pw) / p.n_kb, kb = (u0 + pw) % p.n_kb;
-      int s = pw;
-      uint32_t ph_empty = 1;  // parity of the previous use's release
-      for (int u = u0 + pw; u < u1; u += kGemvProducerWarps) {
-        const int i = u - u0;
-        const long long w0 = p.prof != nullptr ? clock64() : 0;
-        if (i >= kGemvStages && !mbar_wait(&empty[s], ph_empty, cta_error)) {
-          set_status(p.status, ST_WAIT_EMPTY_TIMEOUT);
-          *cta_error = 1;
-          break;
-        }
-        if (p.prof != nullptr) pw_wait += clock64() - w0;
+      bool failed = false;
+
+      auto w_src = [&](int t, int kb) -> const uint8_t* {
         long long eid = 0;
         int tl = t, kbl = kb;
         if (p.nseg_ids != nullptr) {
@@ -385,19 +506,64 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           eid = p.kseg_ids[kb / p.kb_per_kseg];
           kbl = kb % p.kb_per_kseg;
         }
-        const uint8_t* wsrc =
-            p.w + eid * p.expert_stride + (static_cast<long long>(tl) * p.w_kb_per_tile + kbl) * TB_WBLK_BYTES;
-        uint8_t* dst = smem + s * kGemvSlotStride;
-        if (p.x_mode == X_PACKED) {
-          const int xseg = p.tiles_per_xseg > 0 ? t / p.tiles_per_xseg : 0;
-          const uint8_t* xsrc = p.x + (static_cast<long long>(xseg) * p.n_kb + kb) * TB_XBLK_BYTES;
-          mbar_expect_tx(&full[s], TB_WBLK_BYTES + TB_XBLK_BYTES);
-          bulk_g2s_stream(dst, wsrc, TB_WBLK_BYTES, &full[s], pol);
-          bulk_g2s(dst + kGemvSlotXOff, xsrc, TB_XBLK_BYTES, &full[s]);
-        } else {
+        return p.w + eid * p.expert_stride + (static_cast<long long>(tl) * p.w_kb_per_tile + kbl) * TB_WBLK_BYTES;
+      };
+      auto x_block = [&](int t, int kb) -> int {
+        const int xseg = p.tiles_per_xseg > 0 ? t / p.tiles_per_xseg : 0;
+        return xseg * p.n_kb + kb;
+      };
+      // X block of a unit from the shared blocks: wait (bounded) for its flag, then copy.
+      auto x_from_shared = [&](int s, int xb, unsigned want) -> bool {
+        if (!flag_wait(p.xflag + xb, want, cta_error)) return false;
+        // the block was written with ordinary stores by another CTA and is read by the copy engine
+        asm volatile("fence.proxy.async;" ::: "memory");
+        bulk_g2s(smem + s * kGemvSlotStride + kGemvSlotXOff, p.xs + static_cast<long long>(xb) * TB_XBLK_BYTES,
+                 TB_XBLK_BYTES, &full[s]);
+        return true;
+      };
+
+      int u = u0 + pw;
+      unsigned want = 0;
+      if (shared_x) {
+        // The first pass over the ring: weights only, which need nothing from the predecessor (the
+        // converter warps write these units' X blocks into the slots).  Only then wait for the
+        // predecessor; later units take their X blocks from the launch's shared blocks.
+        for (; u < u1 && u - u0 < kGemvStages; u += kGemvProducerWarps) {
+          const int s = u - u0;
           mbar_expect_tx(&full[s], TB_WBLK_BYTES);
-          bulk_g2s_stream(dst, wsrc, TB_WBLK_BYTES, &full[s], pol);
+          bulk_g2s_stream(smem + s * kGemvSlotStride, w_src(u / p.n_kb, u % p.n_kb), TB_WBLK_BYTES, &full[s], pol);
+          gemv_timeline(p, 1, s);
+          last_i = s;
         }
+        pdl_wait();
+        want = *reinterpret_cast<const volatile unsigned*>(p.xstate) + 1u;
+      }
+      int t = u < u1 ? u / p.n_kb : 0, kb = u < u1 ? u % p.n_kb : 0;
+      int s = (u - u0) % kGemvStages;
+      uint32_t ph_empty = (((u - u0) / kGemvStages) & 1) ^ 1;  // parity of the previous use's release
+      for (; u < u1 && !failed; u += kGemvProducerWarps) {
+        const int i = u - u0;
+        const long long w0 = p.prof != nullptr ? clock64() : 0;
+        if (i >= kGemvStages && !mbar_wait(&empty[s], ph_empty, cta_error)) {
+          failed = true;
+          break;
+        }
+        if (p.prof != nullptr) pw_wait += clock64() - w0;
+        gemv_timeline(p, 0, i);
+        uint8_t* dst = smem + s * kGemvSlotStride;
+        mbar_expect_tx(&full[s], TB_WBLK_BYTES + TB_XBLK_BYTES);
+        bulk_g2s_stream(dst, w_src(t, kb), TB_WBLK_BYTES, &full[s], pol);
+        if (shared_x) {
+          mbar_arrive(&full[s]);  // stands in for the converter's arrival of the first pass
+          if (!x_from_shared(s, x_block(t, kb), want)) {
+            failed = true;
+            break;
+          }
+        } else {
+          bulk_g2s(dst + kGemvSlotXOff, p.x + static_cast<long long>(x_block(t, kb)) * TB_XBLK_BYTES, TB_XBLK_BYTES,
+                   &full[s]);
+        }
+        gemv_timeline(p, 1, i);
         last_i = i;
         kb += kGemvProducerWarps;
         while (kb >= p.n_kb) {
@@ -410,130 +576,57 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           ph_empty ^= 1u;
         }
       }
+      if (failed) {
+        set_status(p.status, ST_WAIT_EMPTY_TIMEOUT);
+        *cta_error = 1;
+      }
+      if (shared_x) {
+        // This producer reads no more X flags.  The last producer of the launch to say so opens the
+        // next epoch, which makes every flag of this launch stale.
+        const unsigned prev = atomicAdd(p.xstate + 1, 1u);
+        if (prev == static_cast<unsigned>(grid * kGemvProducerWarps) - 1u) {
+          p.xstate[1] = 0u;
+          __threadfence();
+          *reinterpret_cast<volatile unsigned*>(p.xstate) = want;
+        }
+      }
       if (pw == 0) {
         gemv_stamp(p, kGemvProfIssued);
         if (p.prof != nullptr) p.prof[blockIdx.x * 16 + kGemvProfProdWait] = pw_wait;
       }
       // Do not leave the CTA while this thread's copies may still be landing in its shared memory:
       // wait (bounded) for the last use it issued into each of its ring slots.  On the normal path
-      // these have completed already, because the consumers waited on the same phases.
+      // these have completed already, because the consumers waited on the same phases.  (After a
+      // failed flag wait a slot may be short of its X block; that wait then runs into the abort flag.)
       for (int back = 0; back < kGemvStages && last_i - back >= 0; back += kGemvProducerWarps) {
         const int i = last_i - back;
-        mbar_wait(&full[i % kGemvStages], static_cast<uint32_t>(i / kGemvStages) & 1);
+        mbar_wait(&full[i % kGemvStages], static_cast<uint32_t>(i / kGemvStages) & 1, cta_error);
       }
     }
   } else if (is_converter) {
     // ------------------------------------------------- activation converters (X_BF16 only)
-    // Two warps take alternate units.  Each converts the 128 activations of its unit, for every
-    // token, into the two-term e4m3 X block of the stage: power-of-two scales, so the scaling is a
-    // multiplication and the residual x - hi*s is exact.
+    // The X blocks of a launch are the same for every CTA, so the CTAs share the conversion (the
+    // epilogue warps do this CTA's share before their loop; producers copy the shared blocks into
+    // the ring once their flags are up).  That round trip through global memory takes several
+    // microseconds, so the units of the first pass over the ring get their X blocks converted here,
+    // straight into the slots, by the two converter warps taking alternate units.
     const int cw = warp - kGemvFirstConverterWarp;  // 0 or 1
-    if (p.x_mode == X_BF16 && u0 + cw < u1) {
-      const int ntok = p.n_tokens;
-      float rinv[4] = {1.f, 1.f, 1.f, 1.f};
-      if (p.gamma != nullptr) {
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          float tot = 0.f;
-#pragma unroll
-          for (int w2 = 0; w2 < kGemvHelperWarps; ++w2) tot += norm_part[w2 * 4 + t];
-          rinv[t] = rsqrtf(tot / static_cast<float>(p.n_kb * TB_KBLOCK) + p.eps);
-        }
-      }
-      const long long xk = static_cast<long long>(p.n_kb) * TB_KBLOCK;  // activations per x segment
-      struct XRaw {
-        uint2 v[4];
-        float4 g;
-      };
-      auto fetch = [&](int u) {
-        XRaw o;
+    if (p.x_mode == X_BF16) {
+      float rinv[4];
+      gemv_rinv(p, norm_part, rinv);
+      for (int u = u0 + cw; u < u1 && u - u0 < kGemvStages; u += kGemvConverterWarps) {
+        const int s = u - u0;
         const int t = u / p.n_kb, kb = u % p.n_kb;
         const int xseg = p.tiles_per_xseg > 0 ? t / p.tiles_per_xseg : 0;
-        const long long off = xseg * xk + static_cast<long long>(kb) * TB_KBLOCK + lane * 4;
-#pragma unroll
-        for (int tk = 0; tk < 4; ++tk)
-          o.v[tk] = tk < ntok ? *reinterpret_cast<const uint2*>(p.xb + tk * p.xb_stride + off) : make_uint2(0, 0);
-        o.g = p.gamma != nullptr ? *reinterpret_cast<const float4*>(p.gamma + kb * TB_KBLOCK + lane * 4)
-                                 : make_float4(1.f, 1.f, 1.f, 1.f);
-        return o;
-      };
-      // software pipeline over this warp's units (u, u+2, u+4, ...): two requests in flight
-      const int ub = u0 + cw;
-      long long conv_cycles = 0;
-      XRaw x0 = fetch(ub), x1 = x0, x2 = x0;
-      if (ub + 2 < u1) x1 = fetch(ub + 2);
-      const int c = lane >> 3, r = (lane >> 2) & 1, q4 = lane & 3;
-      for (int u = ub; u < u1; u += kGemvConverterWarps) {
-        const int i = u - u0;
-        const int s = i % kGemvStages;
-        const uint32_t use = static_cast<uint32_t>(i / kGemvStages);
-        if (u + 4 < u1) x2 = fetch(u + 4);
-        if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1, cta_error)) {
-          set_status(p.status, ST_WAIT_EMPTY_TIMEOUT);
-          *cta_error = 1;
-          break;
-        }
-        const long long v0 = p.prof != nullptr ? clock64() : 0;
-        uint8_t* blk = smem + s * kGemvSlotStride + kGemvSlotXOff;
-        const int kb = u % p.n_kb;
-        const float g4[4] = {x0.g.x, x0.g.y, x0.g.z, x0.g.w};
-#pragma unroll
-        for (int tk = 0; tk < 4; ++tk) {
-          if (tk < ntok) {
-            const uint2 rw = x0.v[tk];
-            float x4[4] = {__uint_as_float(rw.x << 16), __uint_as_float(rw.x & 0xffff0000u),
-                           __uint_as_float(rw.y << 16), __uint_as_float(rw.y & 0xffff0000u)};
-            if (p.gamma != nullptr) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) x4[j] = bf2f(f2bf(x4[j] * rinv[tk] * g4[j]));
-            }
-            float amax = fmaxf(fmaxf(fabsf(x4[0]), fabsf(x4[1])), fmaxf(fabsf(x4[2]), fabsf(x4[3])));
-            amax = warp_max(amax);
-            // s_hi = 2^e: the power of two at or just above amax / 448 (at most one step higher when the
-            // product below rounds up); exponent clamped so that s_hi / 16 and 1 / s_hi stay normal
-            const uint32_t tb = __float_as_uint(amax * (1.0f / 448.0f));
-            int e = static_cast<int>(tb >> 23) + ((tb & 0x7fffffu) != 0u ? 1 : 0);
-            e = amax > 0.f ? min(max(e, 16), 240) : 127;
-            const float s_hi = __uint_as_float(static_cast<uint32_t>(e) << 23);
-            const float inv_hi = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);
-            const float s_lo = s_hi * 0.0625f, inv_lo = inv_hi * 16.f;
-            const __nv_fp8x2_storage_t h01 =
-                __nv_cvt_float2_to_fp8x2(make_float2(x4[0] * inv_hi, x4[1] * inv_hi), __NV_SATFINITE, __NV_E4M3);
-            const __nv_fp8x2_storage_t h23 =
-                __nv_cvt_float2_to_fp8x2(make_float2(x4[2] * inv_hi, x4[3] * inv_hi), __NV_SATFINITE, __NV_E4M3);
-            const __half2_raw hr01 = __nv_cvt_fp8x2_to_halfraw2(h01, __NV_E4M3);
-            const __half2_raw hr23 = __nv_cvt_fp8x2_to_halfraw2(h23, __NV_E4M3);
-            const float2 hf01 = __half22float2(*reinterpret_cast<const __half2*>(&hr01));
-            const float2 hf23 = __half22float2(*reinterpret_cast<const __half2*>(&hr23));
-            const float r0 = fmaf(-hf01.x, s_hi, x4[0]), r1 = fmaf(-hf01.y, s_hi, x4[1]);
-            const float r2 = fmaf(-hf23.x, s_hi, x4[2]), r3 = fmaf(-hf23.y, s_hi, x4[3]);
-            const __nv_fp8x2_storage_t l01 =
-                __nv_cvt_float2_to_fp8x2(make_float2(r0 * inv_lo, r1 * inv_lo), __NV_SATFINITE, __NV_E4M3);
-            const __nv_fp8x2_storage_t l23 =
-                __nv_cvt_float2_to_fp8x2(make_float2(r2 * inv_lo, r3 * inv_lo), __NV_SATFINITE, __NV_E4M3);
-            const uint32_t whi = static_cast<uint32_t>(h01) | (static_cast<uint32_t>(h23) << 16);
-            const uint32_t wlo = static_cast<uint32_t>(l01) | (static_cast<uint32_t>(l23) << 16);
-            *reinterpret_cast<uint32_t*>(blk + c * 256 + r * 128 + (2 * tk) * 16 + q4 * 4) = whi;
-            *reinterpret_cast<uint32_t*>(blk + c * 256 + r * 128 + (2 * tk + 1) * 16 + q4 * 4) = wlo;
-            if (lane == 0) {
-              float mlt = 1.f;
-              if (p.seg_scale != nullptr) mlt = p.seg_scale[tk * (p.n_kb / p.kb_per_kseg) + kb / p.kb_per_kseg];
-              *reinterpret_cast<float2*>(blk + TB_XBLK_DATA + 8 * tk) = make_float2(s_hi * mlt, s_lo * mlt);
-            }
-          }
-        }
-        // the X block was written through the generic proxy and is read by the tensor core (async proxy)
+        gemv_convert_xblock(p, xseg * p.n_kb + kb, rinv, smem + s * kGemvSlotStride + kGemvSlotXOff, lane);
+        // written through the generic proxy, read by the tensor core (async proxy)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(&full[s]);
           if (u == u0) gemv_stamp(p, kGemvProfFirstConvert);
         }
-        x0 = x1;
-        x1 = x2;
-        if (p.prof != nullptr) conv_cycles += clock64() - v0;
       }
-      if (cw == 0 && lane == 0 && p.prof != nullptr) p.prof[blockIdx.x * 16 + kGemvProfConvCycles] = conv_cycles;
     }
   } else if (is_mma) {
     // ------------------------------------------------------------ tensor-core issue
@@ -559,14 +652,16 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           break;
         }
         const long long m1 = p.prof != nullptr ? clock64() : 0;
+        gemv_timeline(p, 3, u - u0);
         tc_fence_after();
         const uint32_t wa = smem16 + static_cast<uint32_t>(s) * (kGemvSlotStride >> 4);
         const uint32_t xa = wa + (kGemvSlotXOff >> 4);
         const uint32_t d = tmem_base + static_cast<uint32_t>(s * kGemvAccCols);
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < TB_EXP_NMMA; ++c)
           umma_f8(d, desc_a_hi | (wa + c * (4096 >> 4)), desc_b_hi | (xa + c * (256 >> 4)), c > 0 ? 1u : 0u);
         umma_commit(&acc_full[s]);
+        gemv_timeline(p, 4, u - u0);
         if (p.prof != nullptr) {
           pf_full += m1 - m0;
           pf_issue += clock64() - m1;
@@ -595,12 +690,60 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     if (p.ar.world > 1) ar_epoch = *reinterpret_cast<volatile unsigned long long*>(&p.ar.state[p.ar.rank]->epoch);
     const int ar_half = static_cast<int>(ar_epoch & 1ull);
     const uint32_t lane_base = static_cast<uint32_t>(gw * 32) << 16;
+    if (p.x_mode == X_BF16) {
+      // This CTA's share of the launch's X blocks, while the ring fills: block c, c + grid, ...,
+      // spread over the eight epilogue warps; each block's flag is raised behind its stores.
+      const unsigned want = *reinterpret_cast<const volatile unsigned*>(p.xstate) + 1u;
+      const int n_xsegs = p.tiles_per_xseg > 0 ? p.n_tiles / p.tiles_per_xseg : 1;
+      const int n_xblocks = n_xsegs * p.n_kb;
+      float rinv[4];
+      gemv_rinv(p, norm_part, rinv);
+      for (int xb = cta + warp * grid; xb < n_xblocks; xb += kGemvEpilogueWarps * grid) {
+        gemv_convert_xblock(p, xb, rinv, p.xs + static_cast<long long>(xb) * TB_XBLK_BYTES, lane);
+        // ordinary stores that the copy engines of other CTAs will read
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.xflag + xb), "r"(want) : "memory");
+      }
+    }
     float out[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) out[c] = 0.f;
     bool ok = true;
     long long prof_wait = 0, prof_math = 0, prof_units = 0;
     int merge_buf = 0;
+
+    // A tile whose k blocks are spread over several CTAs (group 0 only): publish this CTA's partial
+    // sums; the last CTA to arrive adds all partials in CTA order and finishes the tile.
+    auto split_tile = [&](int t, const float (&v)[8]) {
+      const int tile_u0 = t * p.n_kb, tile_u1 = tile_u0 + p.n_kb;
+      const int c_first = gemv_owner(tile_u0, units, grid);
+      const int c_last = gemv_owner(tile_u1 - 1, units, grid);
+      const int my_slot = 2 * cta + ((u0 / p.n_kb) == t ? 0 : 1);
+      float4* part = reinterpret_cast<float4*>(p.partial);
+      part[((my_slot * 4 + gw) * 32 + lane) * 2] = make_float4(v[0], v[1], v[2], v[3]);
+      part[((my_slot * 4 + gw) * 32 + lane) * 2 + 1] = make_float4(v[4], v[5], v[6], v[7]);
+      // the warp's partials are ordered before lane 0's release by the warp barrier; the acquire half
+      // of the same atomic orders the last arriver's loads behind every other CTA's release
+      __syncwarp();
+      int prev = 0;
+      if (lane == 0)
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(&p.counters[t * 8 + gw]) : "memory");
+      prev = __shfl_sync(0xffffffffu, prev, 0);
+      if (prev == c_last - c_first) {
+        float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int cc = c_first; cc <= c_last; ++cc) {
+          const int cu0 = static_cast<int>(gemv_range_begin(units, grid, cc));
+          const int slot = 2 * cc + ((cu0 / p.n_kb) == t ? 0 : 1);
+          const float4 v0 = __ldcg(&part[((slot * 4 + gw) * 32 + lane) * 2]);
+          const float4 v1 = __ldcg(&part[((slot * 4 + gw) * 32 + lane) * 2 + 1]);
+          sum[0] += v0.x; sum[1] += v0.y; sum[2] += v0.z; sum[3] += v0.w;
+          sum[4] += v1.x; sum[5] += v1.y; sum[6] += v1.z; sum[7] += v1.w;
+        }
+        if (lane == 0) p.counters[t * 8 + gw] = 0;
+        gemv_epilogue_row(p, t, gw, lane, sum, ar_half);
+      }
+    };
 
     auto finish_tile = [&](int t) {
       // ---- merge the two groups' sums (every epilogue warp gets here for every tile, on every path) ----
@@ -620,31 +763,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         if (u0 <= tile_u0 && u1 >= tile_u1) {
           gemv_epilogue_row(p, t, gw, lane, out, ar_half);
         } else {
-          const int c_first = gemv_owner(tile_u0, units, grid);
-          const int c_last = gemv_owner(tile_u1 - 1, units, grid);
-          const int my_slot = 2 * cta + ((u0 / p.n_kb) == t ? 0 : 1);
-          float4* part = reinterpret_cast<float4*>(p.partial);
-          part[((my_slot * 4 + gw) * 32 + lane) * 2] = make_float4(out[0], out[1], out[2], out[3]);
-          part[((my_slot * 4 + gw) * 32 + lane) * 2 + 1] = make_float4(out[4], out[5], out[6], out[7]);
-          __threadfence();
-          __syncwarp();
-          int prev = 0;
-          if (lane == 0) prev = atomicAdd(&p.counters[t * 8 + gw], 1);
-          prev = __shfl_sync(0xffffffffu, prev, 0);
-          if (prev == c_last - c_first) {
-            __threadfence();
-            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int cc = c_first; cc <= c_last; ++cc) {
-              const int cu0 = static_cast<int>(gemv_range_begin(units, grid, cc));
-              const int slot = 2 * cc + ((cu0 / p.n_kb) == t ? 0 : 1);
-              const float4 v0 = __ldcg(&part[((slot * 4 + gw) * 32 + lane) * 2]);
-              const float4 v1 = __ldcg(&part[((slot * 4 + gw) * 32 + lane) * 2 + 1]);
-              sum[0] += v0.x; sum[1] += v0.y; sum[2] += v0.z; sum[3] += v0.w;
-              sum[4] += v1.x; sum[5] += v1.y; sum[6] += v1.z; sum[7] += v1.w;
-            }
-            if (lane == 0) p.counters[t * 8 + gw] = 0;
-            gemv_epilogue_row(p, t, gw, lane, sum, ar_half);
-          }
+          split_tile(t, out);
         }
       }
 #pragma unroll
@@ -662,6 +781,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       // every decision below is warp-uniform: tcgen05.ld needs the whole warp
       if (((u - u0) & 1) == eg && ok) {
         const long long c0 = p.prof != nullptr ? clock64() : 0;
+        if (gw == 0 && lane == 0) gemv_timeline(p, 7, u - u0);
         // acc_full[s] completes after the unit's MMAs, which were issued after full[s] completed:
         // the slot's scales are in shared memory by then.
         if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[s], ph, cta_error))) {
@@ -671,6 +791,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         } else {
           const long long c1 = p.prof != nullptr ? clock64() : 0;
           if (u == u0 && warp == 0 && lane == 0) gemv_stamp(p, kGemvProfFirstData);
+          if (gw == 0 && lane == 0) gemv_timeline(p, 5, u - u0);
           tc_fence_after();
           uint32_t dr[8];
           tmem_ld8_issue(tmem_base + lane_base + static_cast<uint32_t>(s * kGemvAccCols), dr);
@@ -682,6 +803,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&empty[s]);
+          if (gw == 0 && lane == 0) gemv_timeline(p, 6, u - u0);
           out[0] = fmaf(__uint_as_float(dr[0]), ws * cs0.x, out[0]);
           out[1] = fmaf(__uint_as_float(dr[1]), ws * cs0.y, out[1]);
           out[2] = fmaf(__uint_as_float(dr[2]), ws * cs0.z, out[2]);
