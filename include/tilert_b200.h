@@ -200,6 +200,19 @@ int tilert_rotate_op(TbContext* ctx, const void* in, void* out, int heads, int r
 int tilert_layernorm_rope_rotate_op(TbContext* ctx, const void* in, const int* cur_pos, void* k_cache,
                                     const float* weight, const float* bias, const float* freqs, int rope,
                                     int tokens, void* stream);
+/* proj_w_op + rmsnorm_kv_op + qkv_rope_op + rotate_op + layernorm_rope_rotate_op in one launch (the five
+ * operators above, ops/projx_wis.py:21-40, ops/rmsnorm_kv.py:20-43, ops/qkv_rope.py:21-50,
+ * ops/rotate.py:61-105, ops/layernorm_rope_rotate.py:23-83): they are independent of one another, and
+ * separately each costs a kernel boundary on the critical path of a decode step.  Arguments and
+ * results are those of the five operators: x [tokens, dim] raw hidden state with its input-norm gain,
+ * w_is [idx_heads, dim] bf16 -> idx_w_out [tokens, idx_heads] bf16; kv [tokens, kv_dim] -> kv_cache row;
+ * q_pe [tokens, heads, rope] and the pe_cache row rotated in place; iq [tokens, idx_heads, 128] ->
+ * iq_out; ki [tokens, 128] -> ki_cache row.  Results are bit-identical to the separate operators. */
+int tilert_attn_prep_op(TbContext* ctx, const void* x, const float* in_gamma, float eps, const void* w_is,
+                        int idx_heads, int dim, void* idx_w_out, const void* kv, const float* kv_gamma, int kv_dim,
+                        void* kv_cache, void* q_pe, int heads, int rope, void* pe_cache, const void* iq, void* iq_out,
+                        const void* ki, void* ki_cache, const float* ln_w, const float* ln_b, const float* freqs,
+                        const int* cur_pos, int tokens, void* stream);
 
 /* ---- DSA indexer and sparse attention ---------------------------------------------------- */
 

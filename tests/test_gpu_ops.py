@@ -222,6 +222,48 @@ def test_vector_ops(env):
           cos_min=0.99999, l2_max=6e-3)
 
 
+@pytest.mark.parametrize("tokens", [1, 2, 4])
+def test_attn_prep_equals_the_separate_operators(env, tokens):
+    """The fused launch must give bit-identical results to the five operators it replaces."""
+    ops, a, fc = env["ops"], env["a"], env["fc"]
+    g = torch.Generator().manual_seed(43 + tokens)
+    pos = 77
+    cur = torch.tensor([pos], dtype=I32, device="cuda")
+    fr = torch.view_as_real(fc[pos: pos + tokens]).contiguous().cuda()
+    x = rn(g, 1, tokens, a.dim).cuda()
+    in_gamma = (torch.rand(a.dim, generator=g) + 0.5).cuda()
+    w_is = (torch.randn(a.index_n_heads, a.dim, generator=g) * 0.05).to(BF16).cuda()
+    kv = rn(g, 1, tokens, a.kv_lora_rank).cuda()
+    kv_gamma = (torch.rand(a.kv_lora_rank, generator=g) + 0.5).cuda()
+    q_pe = rn(g, 1, tokens, a.n_heads, a.qk_rope_head_dim).cuda()
+    k_pe = rn(g, 1, tokens, a.qk_rope_head_dim).cuda()
+    iq = rn(g, 1, tokens, a.index_n_heads, a.index_head_dim).cuda()
+    ki = rn(g, 1, tokens, a.index_head_dim).cuda()
+    lw = (torch.rand(128, generator=g) + 0.5).cuda()
+    lb = (torch.randn(128, generator=g) * 0.1).cuda()
+
+    def buffers():
+        pe = torch.zeros(1, 128, a.qk_rope_head_dim, dtype=BF16, device="cuda")
+        pe[:, pos: pos + tokens] = k_pe
+        return dict(idx_w=torch.zeros(1, tokens, a.index_n_heads, dtype=BF16, device="cuda"),
+                    kvc=torch.zeros(1, 128, a.kv_lora_rank, dtype=BF16, device="cuda"), q=q_pe.clone(), pe=pe,
+                    iq_rt=torch.zeros_like(iq), kc=torch.zeros(1, 128, a.index_head_dim, dtype=BF16, device="cuda"))
+
+    r = buffers()
+    ops.projx_wis(x, w_is, r["idx_w"], gamma=in_gamma, eps=a.eps)
+    ops.rmsnorm_kv(kv, kv_gamma, cur, r["kvc"], eps=a.eps)
+    ops.qkv_rope(r["q"], r["pe"], fr, cur)
+    ops.rotate(iq, r["iq_rt"], fr)
+    ops.layernorm_rope_rotate(ki, cur, r["kc"], lw, lb, fr)
+    f = buffers()
+    ops.attn_prep(x, in_gamma, w_is, f["idx_w"], kv, kv_gamma, f["kvc"], f["q"], f["pe"], iq, f["iq_rt"], ki, f["kc"],
+                  lw, lb, fr, cur, eps=a.eps)
+    torch.cuda.synchronize()
+    for k in r:
+        assert torch.equal(r[k], f[k]), k
+    assert r["idx_w"].float().abs().max() > 0
+
+
 # ---------------------------------------------------------------------- indexer and top-k
 @pytest.mark.parametrize("heads,t_len,tokens", [(16, 300, 1), (64, 1000, 2), (32, 64, 1)])
 def test_indexer_logits(env, heads, t_len, tokens):

@@ -11,6 +11,7 @@
 #include "actpack.cuh"
 #include "elementwise.cuh"
 #include "gemv_bf16.cuh"
+#include "attn_prep.cuh"
 #include "indexer.cuh"
 #include "sparse_mla.cuh"
 #include "wstream_gemv.cuh"
@@ -776,6 +777,77 @@ extern "C" int tilert_layernorm_rope_rotate_op(TbContext* ctx, const void* in, c
   rotate128_kernel<<<(tokens + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(k_cache), 1, rope, freqs, weight,
       bias, cur_pos, tokens);
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+extern "C" int tilert_attn_prep_op(TbContext* ctx, const void* x, const float* in_gamma, float eps, const void* w_is,
+                                   int idx_heads, int dim, void* idx_w_out, const void* kv, const float* kv_gamma,
+                                   int kv_dim, void* kv_cache, void* q_pe, int heads, int rope, void* pe_cache,
+                                   const void* iq, void* iq_out, const void* ki, void* ki_cache, const float* ln_w,
+                                   const float* ln_b, const float* freqs, const int* cur_pos, int tokens,
+                                   void* stream) {
+  TB_REQUIRE(ctx != nullptr && x != nullptr && w_is != nullptr && idx_w_out != nullptr && kv != nullptr);
+  TB_REQUIRE(kv_gamma != nullptr && kv_cache != nullptr && q_pe != nullptr && pe_cache != nullptr && iq != nullptr);
+  TB_REQUIRE(iq_out != nullptr && ki != nullptr && ki_cache != nullptr && ln_w != nullptr && ln_b != nullptr);
+  TB_REQUIRE(freqs != nullptr && cur_pos != nullptr && tokens >= 1 && tokens <= 4 && rope == 64);
+  TB_REQUIRE(dim % 256 == 0 && dim <= 8192);
+  AttnPrepParams p{};
+  p.wis.gamma = in_gamma;
+  p.wis.eps = eps;
+  p.wis.w = w_is;
+  p.wis.n = idx_heads;
+  p.wis.k = dim;
+  p.wis.x = reinterpret_cast<const __nv_bfloat16*>(x);
+  p.wis.x_stride = dim;
+  p.wis.n_tokens = tokens;
+  p.wis.out = idx_w_out;
+  p.wis.out_bf16 = 1;
+  p.wis.out_stride = idx_heads;
+  constexpr int kWarps = kAttnPrepThreads / 32;
+  p.wis_blocks = (idx_heads + kGemvBf16SmallRows - 1) / kGemvBf16SmallRows;
+  p.kv = reinterpret_cast<const __nv_bfloat16*>(kv);
+  p.kv_stride = kv_dim;
+  p.kv_gamma = kv_gamma;
+  p.kv_eps = eps;
+  p.kv_dim = kv_dim;
+  p.kv_cache = reinterpret_cast<__nv_bfloat16*>(kv_cache);
+  p.kv_blocks = (tokens + kWarps - 1) / kWarps;
+  p.q_pe = reinterpret_cast<__nv_bfloat16*>(q_pe);
+  p.heads = heads;
+  p.rope = rope;
+  p.pe_cache = reinterpret_cast<__nv_bfloat16*>(pe_cache);
+  p.rope_blocks = (tokens * (heads + 1) * (rope / 2) + kAttnPrepThreads - 1) / kAttnPrepThreads;
+  p.iq = reinterpret_cast<const __nv_bfloat16*>(iq);
+  p.iq_out = reinterpret_cast<__nv_bfloat16*>(iq_out);
+  p.idx_heads = idx_heads;
+  p.iq_blocks = (tokens * idx_heads + kWarps - 1) / kWarps;
+  p.ki = reinterpret_cast<const __nv_bfloat16*>(ki);
+  p.ki_cache = reinterpret_cast<__nv_bfloat16*>(ki_cache);
+  p.ln_w = ln_w;
+  p.ln_b = ln_b;
+  p.ki_blocks = (tokens + kWarps - 1) / kWarps;
+  p.pos = cur_pos;
+  p.freqs = freqs;
+  p.n_tokens = tokens;
+  static bool attr_set[64] = {};
+  if (!attr_set[ctx->device & 63]) {
+    TB_CUDA(cudaFuncSetAttribute(attn_prep_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    TB_CUDA(cudaFuncSetAttribute(attn_prep_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    TB_CUDA(cudaFuncSetAttribute(attn_prep_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_set[ctx->device & 63] = true;
+  }
+  const int grid = p.wis_blocks + p.kv_blocks + p.rope_blocks + p.iq_blocks + p.ki_blocks;
+  const int tok = tokens == 1 ? 1 : (tokens == 2 ? 2 : 4);
+  const size_t smem = static_cast<size_t>(tok) * dim * sizeof(float);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (tok == 1)
+    TB_CUDA(launch(attn_prep_kernel<1>, dim3(grid), dim3(kAttnPrepThreads), smem, st, p));
+  else if (tok == 2)
+    TB_CUDA(launch(attn_prep_kernel<2>, dim3(grid), dim3(kAttnPrepThreads), smem, st, p));
+  else
+    TB_CUDA(launch(attn_prep_kernel<4>, dim3(grid), dim3(kAttnPrepThreads), smem, st, p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;

@@ -8,12 +8,10 @@
 namespace tb {
 
 // kv [tokens, dim] -> cache[pos + t, dim] = bf16(rmsnorm(kv) * gamma).   One warp per token.
-__global__ void rmsnorm_kv_kernel(const __nv_bfloat16* __restrict__ kv, long long kv_stride,
-                                  const float* __restrict__ gamma, float eps, int dim, const int* __restrict__ pos,
-                                  __nv_bfloat16* __restrict__ cache, int n_tokens) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+__device__ __forceinline__ void rmsnorm_kv_warp(int tok, const __nv_bfloat16* __restrict__ kv, long long kv_stride,
+                                                const float* __restrict__ gamma, float eps, int dim,
+                                                const int* __restrict__ pos, __nv_bfloat16* __restrict__ cache,
+                                                int n_tokens) {
   const int lane = threadIdx.x & 31;
   if (tok >= n_tokens) return;
   const __nv_bfloat16* x = kv + tok * kv_stride;
@@ -27,17 +25,22 @@ __global__ void rmsnorm_kv_kernel(const __nv_bfloat16* __restrict__ kv, long lon
   __nv_bfloat16* dst = cache + static_cast<long long>(*pos + tok) * dim;
   for (int i = lane; i < dim; i += 32) dst[i] = f2bf(bf2f(x[i]) * rinv * gamma[i]);
 }
+__global__ void rmsnorm_kv_kernel(const __nv_bfloat16* __restrict__ kv, long long kv_stride,
+                                  const float* __restrict__ gamma, float eps, int dim, const int* __restrict__ pos,
+                                  __nv_bfloat16* __restrict__ cache, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  rmsnorm_kv_warp(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), kv, kv_stride, gamma, eps, dim, pos, cache,
+                  n_tokens);
+}
 
 // Interleaved RoPE (pairs (x[2i], x[2i+1])) applied in place to q_pe [tokens, heads, rope] and to the
 // cached key rows pe_cache[pos + t, rope].  freqs: [tokens, rope/2, 2] = (cos, sin).
-__global__ void qkv_rope_kernel(__nv_bfloat16* __restrict__ q_pe, int heads, int rope,
-                                __nv_bfloat16* __restrict__ pe_cache, const int* __restrict__ pos,
-                                const float* __restrict__ freqs, int n_tokens) {
-  pdl_launch_dependents();
-  pdl_wait();
+__device__ __forceinline__ void qkv_rope_thread(int idx, __nv_bfloat16* __restrict__ q_pe, int heads, int rope,
+                                                __nv_bfloat16* __restrict__ pe_cache, const int* __restrict__ pos,
+                                                const float* __restrict__ freqs, int n_tokens) {
   const int half = rope / 2;
   const int per_tok = (heads + 1) * half;
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_tokens * per_tok) return;
   const int tok = idx / per_tok, rem = idx % per_tok;
   const int h = rem / half, i = rem % half;
@@ -50,6 +53,13 @@ __global__ void qkv_rope_kernel(__nv_bfloat16* __restrict__ q_pe, int heads, int
   const float a = bf2f(v[0]), b = bf2f(v[1]);
   v[0] = f2bf(a * c - b * s);
   v[1] = f2bf(a * s + b * c);
+}
+__global__ void qkv_rope_kernel(__nv_bfloat16* __restrict__ q_pe, int heads, int rope,
+                                __nv_bfloat16* __restrict__ pe_cache, const int* __restrict__ pos,
+                                const float* __restrict__ freqs, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  qkv_rope_thread(blockIdx.x * blockDim.x + threadIdx.x, q_pe, heads, rope, pe_cache, pos, freqs, n_tokens);
 }
 
 // 128-point Walsh-Hadamard transform of a warp-distributed vector: lane l holds elements
@@ -74,12 +84,11 @@ __device__ __forceinline__ void hadamard128(float (&v)[4]) {
 // `rope` of 128 dims (pairs (x[i], x[i + rope/2])), then Hadamard-128 scaled by 128^-1/2.  Every
 // stage rounds to bf16 as the reference's bf16 tensor pipeline does.  One warp per 128-vector.
 //   in  [tokens, heads, 128];  out: either [tokens, heads, 128] or cache[pos + t, 128] (heads == 1)
-__global__ void rotate128_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int heads,
-                                 int rope, const float* __restrict__ freqs, const float* __restrict__ ln_w,
-                                 const float* __restrict__ ln_b, const int* __restrict__ pos, int n_tokens) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int vec = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+__device__ __forceinline__ void rotate128_warp(int vec, const __nv_bfloat16* __restrict__ in,
+                                               __nv_bfloat16* __restrict__ out, int heads, int rope,
+                                               const float* __restrict__ freqs, const float* __restrict__ ln_w,
+                                               const float* __restrict__ ln_b, const int* __restrict__ pos,
+                                               int n_tokens) {
   const int lane = threadIdx.x & 31;
   if (vec >= n_tokens * heads) return;
   const int tok = vec / heads;
@@ -119,6 +128,14 @@ __global__ void rotate128_kernel(const __nv_bfloat16* __restrict__ in, __nv_bflo
   const float scale = 0.08838834764831845f;  // 128^-1/2 (a Python scalar in the reference: not rounded to bf16)
 #pragma unroll
   for (int j = 0; j < 4; ++j) dst[lane * 4 + j] = f2bf(bf2f(f2bf(v[j])) * scale);
+}
+__global__ void rotate128_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int heads,
+                                 int rope, const float* __restrict__ freqs, const float* __restrict__ ln_w,
+                                 const float* __restrict__ ln_b, const int* __restrict__ pos, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  rotate128_warp(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), in, out, heads, rope, freqs, ln_w, ln_b, pos,
+                 n_tokens);
 }
 
 // MoE routing (sigmoid scores + bias, optional group limiting, top-k, renormalise, scale).

@@ -128,14 +128,37 @@ __global__ void __launch_bounds__(kGemvBf16Threads) gemv_bf16_kernel(const GemvB
 constexpr int kGemvBf16SmallThreads = 256;
 constexpr int kGemvBf16SmallRows = 2;
 
+// `block` = index of the row pair; `xs` = [TOK][k] floats of shared memory.  The weights of the
+// block's two rows are requested before the wait for the predecessor kernel: they are static, and
+// their DRAM latency then overlaps the activation staging and the normalisation.
 template <int TOK>
-__global__ void __launch_bounds__(kGemvBf16SmallThreads) gemv_bf16_ksplit_kernel(const GemvBf16Params p) {
-  pdl_launch_dependents();
-  pdl_wait();
-  extern __shared__ __align__(16) float xs[];  // [TOK][k]
+__device__ __forceinline__ void gemv_bf16_ksplit_body(const GemvBf16Params& p, int block, float* xs) {
   __shared__ float red[TOK][8];
   __shared__ float part[kGemvBf16SmallRows][TOK][8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kslice = p.k / 8;  // per warp; multiple of 8 elements (k % 256 == 0); at most 1024 (k <= 8192)
+  uint4 wpre[kGemvBf16SmallRows][4][2];  // [row][iteration][bf16: .0 only | f32: two halves]
+#pragma unroll
+  for (int r = 0; r < kGemvBf16SmallRows; ++r) {
+    const int row = block * kGemvBf16SmallRows + r;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int k0 = warp * kslice + lane * 8 + it * 256;
+      wpre[r][it][0] = make_uint4(0u, 0u, 0u, 0u);
+      wpre[r][it][1] = make_uint4(0u, 0u, 0u, 0u);
+      if (row < p.n && k0 < (warp + 1) * kslice) {
+        if (p.w_is_f32) {
+          const float* wr = reinterpret_cast<const float*>(p.w) + static_cast<long long>(row) * p.k + k0;
+          wpre[r][it][0] = __ldg(reinterpret_cast<const uint4*>(wr));
+          wpre[r][it][1] = __ldg(reinterpret_cast<const uint4*>(wr + 4));
+        } else {
+          const __nv_bfloat16* wr = reinterpret_cast<const __nv_bfloat16*>(p.w) + static_cast<long long>(row) * p.k + k0;
+          wpre[r][it][0] = __ldg(reinterpret_cast<const uint4*>(wr));
+        }
+      }
+    }
+  }
+  pdl_wait();
   float ss[TOK];
 #pragma unroll
   for (int t = 0; t < TOK; ++t) ss[t] = 0.f;
@@ -190,7 +213,7 @@ __global__ void __launch_bounds__(kGemvBf16SmallThreads) gemv_bf16_ksplit_kernel
             for (int j = 0; j < 4; ++j) o[j] = bf2f(f2bf(o[j]));
           }
           *reinterpret_cast<float4*>(&xs[t * p.k + i]) = make_float4(o[0], o[1], o[2], o[3]);
-          if (p.xnorm_out != nullptr && blockIdx.x == 0 && t < p.n_tokens) {
+          if (p.xnorm_out != nullptr && block == 0 && t < p.n_tokens) {
             uint2 ob;
             ob.x = pack_bf16x2(o[0], o[1]);
             ob.y = pack_bf16x2(o[2], o[3]);
@@ -202,36 +225,39 @@ __global__ void __launch_bounds__(kGemvBf16SmallThreads) gemv_bf16_ksplit_kernel
   }
   __syncthreads();
 
-  const int kslice = p.k / 8;  // per warp; multiple of 8 elements (k % 256 == 0)
 #pragma unroll
   for (int r = 0; r < kGemvBf16SmallRows; ++r) {
-    const int row = blockIdx.x * kGemvBf16SmallRows + r;
+    const int row = block * kGemvBf16SmallRows + r;
     float acc[TOK];
 #pragma unroll
     for (int t = 0; t < TOK; ++t) acc[t] = 0.f;
     if (row < p.n) {
-      for (int k0 = warp * kslice + lane * 8; k0 < (warp + 1) * kslice; k0 += 256) {
-        float wf[8];
-        if (p.w_is_f32) {
-          const float* wr = reinterpret_cast<const float*>(p.w) + static_cast<long long>(row) * p.k + k0;
-          const float4 w0 = __ldg(reinterpret_cast<const float4*>(wr)), w1 = __ldg(reinterpret_cast<const float4*>(wr + 4));
-          wf[0] = w0.x; wf[1] = w0.y; wf[2] = w0.z; wf[3] = w0.w; wf[4] = w1.x; wf[5] = w1.y; wf[6] = w1.z; wf[7] = w1.w;
-        } else {
-          const __nv_bfloat16* wr = reinterpret_cast<const __nv_bfloat16*>(p.w) + static_cast<long long>(row) * p.k + k0;
-          const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wr));
-          const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            wf[2 * j] = __uint_as_float(ww[j] << 16);
-            wf[2 * j + 1] = __uint_as_float(ww[j] & 0xffff0000u);
+      for (int it = 0; it < 4; ++it) {
+        const int k0 = warp * kslice + lane * 8 + it * 256;
+        if (k0 < (warp + 1) * kslice) {
+          float wf[8];
+          if (p.w_is_f32) {
+            const uint4 w0 = wpre[r][it][0], w1 = wpre[r][it][1];
+            wf[0] = __uint_as_float(w0.x); wf[1] = __uint_as_float(w0.y); wf[2] = __uint_as_float(w0.z);
+            wf[3] = __uint_as_float(w0.w); wf[4] = __uint_as_float(w1.x); wf[5] = __uint_as_float(w1.y);
+            wf[6] = __uint_as_float(w1.z); wf[7] = __uint_as_float(w1.w);
+          } else {
+            const uint4 wv = wpre[r][it][0];
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              wf[2 * j] = __uint_as_float(ww[j] << 16);
+              wf[2 * j + 1] = __uint_as_float(ww[j] & 0xffff0000u);
+            }
           }
-        }
 #pragma unroll
-        for (int t = 0; t < TOK; ++t) {
-          const float4 xa = *reinterpret_cast<const float4*>(&xs[t * p.k + k0]);
-          const float4 xb = *reinterpret_cast<const float4*>(&xs[t * p.k + k0 + 4]);
-          acc[t] += wf[0] * xa.x + wf[1] * xa.y + wf[2] * xa.z + wf[3] * xa.w + wf[4] * xb.x + wf[5] * xb.y +
-                    wf[6] * xb.z + wf[7] * xb.w;
+          for (int t = 0; t < TOK; ++t) {
+            const float4 xa = *reinterpret_cast<const float4*>(&xs[t * p.k + k0]);
+            const float4 xb = *reinterpret_cast<const float4*>(&xs[t * p.k + k0 + 4]);
+            acc[t] += wf[0] * xa.x + wf[1] * xa.y + wf[2] * xa.z + wf[3] * xa.w + wf[4] * xb.x + wf[5] * xb.y +
+                      wf[6] * xb.z + wf[7] * xb.w;
+          }
         }
       }
     }
@@ -244,7 +270,7 @@ __global__ void __launch_bounds__(kGemvBf16SmallThreads) gemv_bf16_ksplit_kernel
   __syncthreads();
   if (threadIdx.x < kGemvBf16SmallRows * TOK) {
     const int r = threadIdx.x / TOK, t = threadIdx.x % TOK;
-    const int row = blockIdx.x * kGemvBf16SmallRows + r;
+    const int row = block * kGemvBf16SmallRows + r;
     if (row < p.n && t < p.n_tokens) {
       float s = 0.f;
 #pragma unroll
@@ -255,6 +281,13 @@ __global__ void __launch_bounds__(kGemvBf16SmallThreads) gemv_bf16_ksplit_kernel
         reinterpret_cast<float*>(p.out)[t * p.out_stride + row] = s;
     }
   }
+}
+
+template <int TOK>
+__global__ void __launch_bounds__(kGemvBf16SmallThreads) gemv_bf16_ksplit_kernel(const GemvBf16Params p) {
+  extern __shared__ __align__(16) float xs[];  // [TOK][k]
+  pdl_launch_dependents();
+  gemv_bf16_ksplit_body<TOK>(p, blockIdx.x, xs);
 }
 
 }  // namespace tb

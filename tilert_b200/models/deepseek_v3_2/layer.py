@@ -199,20 +199,21 @@ class DecoderLayer:
         a, w = self.args, self.w
         s = x.shape[1]
         v = lambda t: t[:, :s]  # noqa: E731
+        # The three FP8 products of the query path are issued back to back: each one's weight prefetch
+        # overlaps its predecessor's tail (programmatic dependent launch), and none of them needs the
+        # small per-token kernels that follow.
         ops.rmsnorm_projx_wqkva(x, w.in_norm, w.w_qkva, cur_pos, v(self.q_a), v(self.kv), self.pe_cache, v(self.ki),
                                 eps=a.eps)
-        ops.projx_wis(x, w.wis, v(self.idx_w), gamma=w.in_norm, eps=a.eps)
-        ops.rmsnorm_kv(v(self.kv), w.kv_norm, cur_pos, self.kv_cache, eps=a.eps)
         ops.rmsnorm_proj_q(v(self.q_a), w.q_norm, w.w_qb, v(self.q_nope), v(self.q_pe), v(self.iq), eps=a.eps)
-        ops.qkv_rope(v(self.q_pe), self.pe_cache, freqs, cur_pos)
-        ops.rotate(v(self.iq), v(self.iq_rt), freqs, rope=a.qk_rope_head_dim)
-        ops.layernorm_rope_rotate(v(self.ki), cur_pos, self.ki_cache, w.k_norm_w, w.k_norm_b, freqs,
-                                  rope=a.qk_rope_head_dim)
+        ops.projq_wqb(v(self.q_nope), w.w_absorb, None, v(self.q_lat))
+        # indexer head weights, latent norm into the cache, RoPE, indexer rotations: one launch
+        ops.attn_prep(x, w.in_norm, w.wis, v(self.idx_w), v(self.kv), w.kv_norm, self.kv_cache, v(self.q_pe),
+                      self.pe_cache, v(self.iq), v(self.iq_rt), v(self.ki), self.ki_cache, w.k_norm_w, w.k_norm_b,
+                      freqs, cur_pos, eps=a.eps, rope=a.qk_rope_head_dim)
         ops.sparse_index_topk(v(self.iq_rt), self.ki_cache, v(self.idx_w), self.idx_logits, v(self.sel), cur_pos,
                               n_keys=n_keys)
         if self.injected_sel is not None:
             v(self.sel).copy_(self.injected_sel)
-        ops.projq_wqb(v(self.q_nope), w.w_absorb, None, v(self.q_lat))
         ops.flash_sparse_mla(v(self.q_lat), v(self.q_pe), self.kv_cache, self.pe_cache, v(self.sel), cur_pos,
                              v(self.o_lat), softmax_scale=self.scale, split_size=64, out_acc=self.o_acc,
                              lse=self.lse, lse_acc=self.lse_acc)

@@ -334,6 +334,28 @@ def layernorm_rope_rotate(x_in, cur_pos, k_cache, weight, bias, freqs, profile_l
                                                         _p(bias), _p(freqs), rope, x_in.shape[-2], _stream()))
 
 
+def attn_prep(x, in_gamma, w_is, idx_w_out, kv, kv_gamma, kv_cache, q_pe, pe_cache, iq, iq_out, ki, ki_cache,
+              ln_weight, ln_bias, freqs, cur_pos, *, eps=1e-6, rope=64):
+    """projx_wis + rmsnorm_kv + qkv_rope + rotate + layernorm_rope_rotate in one launch
+    (ops/projx_wis.py:21-40, ops/rmsnorm_kv.py:20-43, ops/qkv_rope.py:21-50, ops/rotate.py:61-105,
+    ops/layernorm_rope_rotate.py:23-83); same arguments and bit-identical results."""
+    for t, nm in ((x, "x"), (w_is, "w_is"), (idx_w_out, "idx_w_out"), (kv, "kv"), (kv_cache, "kv_cache"),
+                  (q_pe, "q_pe"), (pe_cache, "pe_cache"), (iq, "iq"), (iq_out, "iq_out"), (ki, "ki"),
+                  (ki_cache, "ki_cache")):
+        _need(t, BF16, nm)
+    for t, nm in ((in_gamma, "in_gamma"), (kv_gamma, "kv_gamma"), (ln_weight, "ln_weight"), (ln_bias, "ln_bias"),
+                  (freqs, "freqs")):
+        _need(t, F32, nm)
+    _need(cur_pos, I32, "cur_pos")
+    if iq.shape[-1] != 128 or ki.shape[-1] != 128:
+        raise ValueError("dim must be 128")
+    tokens, heads = q_pe.shape[-3], q_pe.shape[-2]
+    _tb.check(_tb.lib().tilert_attn_prep_op(
+        _ctx(x), _p(x), _p(in_gamma), eps, _p(w_is), w_is.shape[0], w_is.shape[1], _p(idx_w_out), _p(kv), _p(kv_gamma),
+        kv.shape[-1], _p(kv_cache), _p(q_pe), heads, rope, _p(pe_cache), _p(iq), _p(iq_out), _p(ki), _p(ki_cache),
+        _p(ln_weight), _p(ln_bias), _p(freqs), _p(cur_pos), tokens, _stream()))
+
+
 # ------------------------------------------------------------ indexer and sparse attention
 def sparse_index(q, kv, weights, logits, cur_pos, profile_logs=None, compute_kernel_type="bf16", *,
                  model_arch="deepseek_v3_2", n_keys=None):
