@@ -533,11 +533,15 @@ extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (slot_ids == nullptr) slot_ids = reinterpret_cast<int*>(ctx->small);
   if (slot_w == nullptr) slot_w = reinterpret_cast<float*>(ctx->small + 4096);
-  TB_CUDA(launch(expert_select_kernel, dim3((tokens + 3) / 4), dim3(128), 0, st, scores, bias, n_experts, n_groups, n_limited_groups, top_k,
-                                                         route_scale, n_experts, probs_out, idx_out, slot_ids,
-                                                         slot_w, tokens));
-  ++g_launches;
-  TB_CUDA(cudaGetLastError());
+  // One token: the product launch routes the token itself.  Several tokens: a routing launch first,
+  // then one product launch per token (each token has its own expert list).
+  const bool route_in_kernel = tokens == 1;
+  if (!route_in_kernel) {
+    TB_CUDA(launch(expert_select_kernel, dim3((tokens + 3) / 4), dim3(128), 0, st, scores, bias, n_experts, n_groups,
+                   n_limited_groups, top_k, route_scale, n_experts, probs_out, idx_out, slot_ids, slot_w, tokens));
+    ++g_launches;
+    TB_CUDA(cudaGetLastError());
+  }
   const int n_slots = top_k + 1;
   for (int t = 0; t < tokens; ++t) {
     GemvParams p;
@@ -548,7 +552,22 @@ extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* 
     p.n_tiles = n_slots * p.tiles_per_nseg;
     p.n_kb = dim / TB_KBLOCK;
     p.w_kb_per_tile = p.n_kb;
-    p.nseg_ids = slot_ids + t * n_slots;
+    if (route_in_kernel) {
+      p.route.scores = scores;
+      p.route.bias = bias;
+      p.route.n_experts = n_experts;
+      p.route.n_groups = n_groups;
+      p.route.n_limited = n_limited_groups;
+      p.route.top_k = top_k;
+      p.route.route_scale = route_scale;
+      p.route.shared_id = n_experts;
+      p.route.probs = probs_out;
+      p.route.ids = idx_out;
+      p.route.slot_ids = slot_ids;
+      p.route.slot_w = slot_w;
+    } else {
+      p.nseg_ids = slot_ids + t * n_slots;
+    }
     p.expert_stride = expert_stride;
     p.n_tokens = tokens;
     p.only_token = tokens > 1 ? t : -1;

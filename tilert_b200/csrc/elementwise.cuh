@@ -142,22 +142,19 @@ __global__ void rotate128_kernel(const __nv_bfloat16* __restrict__ in, __nv_bflo
 // One warp per token; n_experts <= 256 (8 per lane).
 //   scores [tokens, n_experts] f32  ->  probs [tokens, top_k] f32, ids [tokens, top_k] i32,
 //   slot_ids [tokens, top_k + 1] i32 = (shared-expert id, ids...), slot_w [tokens, top_k + 1] = (1, probs...)
-__global__ void expert_select_kernel(const float* __restrict__ scores, const float* __restrict__ bias,
-                                     int n_experts, int n_groups, int n_limited, int top_k, float route_scale,
-                                     int shared_id, float* __restrict__ probs, int* __restrict__ ids,
-                                     int* __restrict__ slot_ids, float* __restrict__ slot_w, int n_tokens) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+// Routing of one token by one warp.  On return lane k (< top_k) holds the k-th selected expert in
+// `my_id` and its renormalised, scaled weight in `my_w`.
+__device__ __forceinline__ void expert_select_warp(const float* __restrict__ scores, const float* __restrict__ bias,
+                                                   int n_experts, int n_groups, int n_limited, int top_k,
+                                                   float route_scale, int& my_id, float& my_w) {
   const int lane = threadIdx.x & 31;
-  if (tok >= n_tokens) return;
   const int per_lane = (n_experts + 31) / 32;  // experts e = lane*per_lane + j  (contiguous per lane)
   float orig[8], sel[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int e = lane * per_lane + j;
     if (j < per_lane && e < n_experts) {
-      const float s = 1.0f / (1.0f + expf(-scores[tok * n_experts + e]));
+      const float s = 1.0f / (1.0f + expf(-scores[e]));
       orig[j] = s;
       sel[j] = bias != nullptr ? s + bias[e] : s;
     } else {
@@ -194,8 +191,8 @@ __global__ void expert_select_kernel(const float* __restrict__ scores, const flo
     }
   }
   float wsum = 0.f;
-  float my_w = 0.f;
-  int my_id = 0;
+  my_w = 0.f;
+  my_id = 0;
   for (int k = 0; k < top_k; ++k) {
     // arg-max over the warp, ties to the lower expert index
     float best = -INFINITY;
@@ -220,17 +217,40 @@ __global__ void expert_select_kernel(const float* __restrict__ scores, const flo
     wsum += w;
     if (lane == k) { my_w = w; my_id = best_e; }
   }
+  my_w = my_w / wsum * route_scale;
+}
+
+// Stores one token's routing in the forms the callers read: probs / ids [top_k], and the slot lists
+// [top_k + 1] = (shared expert, weight 1) followed by the selected experts.
+__device__ __forceinline__ void expert_select_store(int my_id, float my_w, int top_k, int shared_id,
+                                                    float* __restrict__ probs, int* __restrict__ ids,
+                                                    int* __restrict__ slot_ids, float* __restrict__ slot_w) {
+  const int lane = threadIdx.x & 31;
   if (lane < top_k) {
-    const float pr = my_w / wsum * route_scale;
-    probs[tok * top_k + lane] = pr;
-    ids[tok * top_k + lane] = my_id;
-    slot_ids[tok * (top_k + 1) + 1 + lane] = my_id;
-    slot_w[tok * (top_k + 1) + 1 + lane] = pr;
+    probs[lane] = my_w;
+    ids[lane] = my_id;
+    slot_ids[1 + lane] = my_id;
+    slot_w[1 + lane] = my_w;
   }
   if (lane == 0) {
-    slot_ids[tok * (top_k + 1)] = shared_id;
-    slot_w[tok * (top_k + 1)] = 1.0f;
+    slot_ids[0] = shared_id;
+    slot_w[0] = 1.0f;
   }
+}
+
+__global__ void expert_select_kernel(const float* __restrict__ scores, const float* __restrict__ bias,
+                                     int n_experts, int n_groups, int n_limited, int top_k, float route_scale,
+                                     int shared_id, float* __restrict__ probs, int* __restrict__ ids,
+                                     int* __restrict__ slot_ids, float* __restrict__ slot_w, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (tok >= n_tokens) return;
+  int my_id;
+  float my_w;
+  expert_select_warp(scores + tok * n_experts, bias, n_experts, n_groups, n_limited, top_k, route_scale, my_id, my_w);
+  expert_select_store(my_id, my_w, top_k, shared_id, probs + tok * top_k, ids + tok * top_k,
+                      slot_ids + tok * (top_k + 1), slot_w + tok * (top_k + 1));
 }
 
 }  // namespace tb

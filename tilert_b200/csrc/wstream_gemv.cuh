@@ -21,6 +21,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "elementwise.cuh"
 #include "formats.h"
 
 namespace tb {
@@ -63,6 +64,21 @@ enum XMode : int {
                  // splits them into two e4m3 terms and writes the X block of each stage itself
 };
 
+// Expert routing done inside the product launch (single-token launches): every producer warp routes
+// the token itself from the router scores, so the weight addresses need no separate routing launch;
+// CTA 0 also stores the result for the caller and for the down projection that follows.
+struct RouteParams {
+  const float* scores;  // [n_experts] router logits; nullptr = off (slot ids come from GemvParams::nseg_ids)
+  const float* bias;
+  int n_experts, n_groups, n_limited, top_k;
+  float route_scale;
+  int shared_id;        // slot 0: the shared expert's index in the packed expert array
+  float* probs;         // [top_k]
+  int* ids;             // [top_k]
+  int* slot_ids;        // [top_k + 1]
+  float* slot_w;        // [top_k + 1]
+};
+
 struct GemvParams {
   const uint8_t* w;
   const uint8_t* x;              // X_PACKED: packed blocks
@@ -78,6 +94,7 @@ struct GemvParams {
   int n_tiles;
   int n_kb;
   const int* nseg_ids;
+  RouteParams route;
   int tiles_per_nseg;
   const int* kseg_ids;
   int kb_per_kseg;
@@ -160,8 +177,9 @@ constexpr int kGemvSlotXOff = 16512;
 constexpr int kGemvSlotStride = 17664;
 constexpr int kGemvBarBytes = 3 * kGemvStages * 8;
 constexpr int kGemvMergeBytes = 2 * kGemvGroupThreads * 8 * 4;  // double-buffered sums of epilogue group 1
-constexpr int kGemvSmemBytes =
-    kGemvStages * kGemvSlotStride + kGemvMergeBytes + kGemvBarBytes + 16 + kGemvHelperWarps * 4 * 4 + 32;
+constexpr int kGemvRouteSlots = 32;  // slot ids per producer warp (top_k + 1 <= 32)
+constexpr int kGemvSmemBytes = kGemvStages * kGemvSlotStride + kGemvMergeBytes + kGemvBarBytes + 16 +
+                               kGemvHelperWarps * 4 * 4 + kGemvProducerWarps * kGemvRouteSlots * 4 + 32;
 
 // ---- tcgen05 helpers ----
 // Shared-memory operand descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; `lbo` =
@@ -402,6 +420,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
   volatile int* cta_error = reinterpret_cast<volatile int*>(acc_full + kGemvStages);
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(const_cast<int*>(cta_error) + 1);
   float* norm_part = reinterpret_cast<float*>(const_cast<int*>(cta_error) + 4);  // [helper warps][4 tokens]
+  int* route_ids = reinterpret_cast<int*>(norm_part + kGemvHelperWarps * 4);    // [producer warps][kGemvRouteSlots]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grid = gridDim.x, cta = blockIdx.x;
@@ -444,7 +463,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
   const bool is_converter = warp >= kGemvFirstConverterWarp;
   // Producers stream weights, which no kernel of the step writes; they wait for the predecessor only
   // when their addresses depend on it (routing ids) or when they also copy packed activations.
-  if (!is_producer || p.x_mode == X_PACKED || p.nseg_ids != nullptr || p.kseg_ids != nullptr) pdl_wait();
+  if (!is_producer || p.x_mode == X_PACKED || p.nseg_ids != nullptr || p.kseg_ids != nullptr ||
+      p.route.scores != nullptr)
+    pdl_wait();
 
   if (p.x_mode == X_BF16 && p.gamma != nullptr && (is_epilogue || is_converter)) {
     // RMSNorm statistics of the activation vector(s): the epilogue and converter warps split the
@@ -487,6 +508,22 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     // slot i % kGemvStages: the W block from the weight tensor and the X block either from the
     // caller's packed activations (X_PACKED) or from the launch's shared X blocks (X_BF16), which
     // the converter warps of all CTAs are writing meanwhile -- a per-block flag says when.
+    const int* my_nseg_ids = p.nseg_ids;
+    if (p.route.scores != nullptr) {
+      // route the token with the whole warp; keep the slot list where this warp's issuing lane reads it
+      int my_id;
+      float my_w;
+      expert_select_warp(p.route.scores, p.route.bias, p.route.n_experts, p.route.n_groups, p.route.n_limited,
+                         p.route.top_k, p.route.route_scale, my_id, my_w);
+      int* mine = route_ids + (warp - kGemvFirstProducerWarp) * kGemvRouteSlots;
+      if (lane < p.route.top_k) mine[1 + lane] = my_id;
+      if (lane == 0) mine[0] = p.route.shared_id;
+      if (cta == 0 && warp == kGemvFirstProducerWarp)
+        expert_select_store(my_id, my_w, p.route.top_k, p.route.shared_id, p.route.probs, p.route.ids,
+                            p.route.slot_ids, p.route.slot_w);
+      __syncwarp();
+      my_nseg_ids = mine;
+    }
     if (lane == 0) {
       const int pw = warp - kGemvFirstProducerWarp;
       const uint64_t pol = policy_evict_first();
@@ -498,8 +535,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       auto w_src = [&](int t, int kb) -> const uint8_t* {
         long long eid = 0;
         int tl = t, kbl = kb;
-        if (p.nseg_ids != nullptr) {
-          eid = p.nseg_ids[t / p.tiles_per_nseg];
+        if (my_nseg_ids != nullptr) {
+          eid = my_nseg_ids[t / p.tiles_per_nseg];
           tl = t % p.tiles_per_nseg;
         }
         if (p.kseg_ids != nullptr) {
