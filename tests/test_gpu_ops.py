@@ -294,6 +294,9 @@ def test_topk_exact_random(env):
     g = torch.Generator().manual_seed(7)
     _topk_case(env, torch.randn(1, 2, 5000, generator=g), 5000, 256)
     _topk_case(env, torch.randn(1, 1, 20000, generator=g), 19990, 2048)
+    # row lengths on both sides of the register-resident kernels' limits (4096 and 8192 entries)
+    for n in (4095, 4096, 4097, 8191, 8192, 8193):
+        _topk_case(env, torch.randn(1, 2, n, generator=g), n, 2048)
 
 
 def test_topk_ties_infs_and_short_rows(env):

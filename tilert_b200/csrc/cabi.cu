@@ -898,8 +898,17 @@ extern "C" int tilert_sparse_index_op(TbContext* ctx, const void* q, const void*
 extern "C" int tilert_topk_accurate_op(TbContext* ctx, const float* logits, long long logits_stride, int rows, int n,
                                        int k, int* indices, void* stream) {
   TB_REQUIRE(ctx != nullptr && logits != nullptr && indices != nullptr && rows >= 1 && n >= 0 && k >= 1);
-  topk_radix_kernel<<<rows, kTopkThreads, 0, static_cast<cudaStream_t>(stream)>>>(logits, logits_stride, n, k,
-                                                                                  indices, k);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long out_stride = k;
+  if (n <= kTopkThreads * 4)
+    TB_CUDA(launch(topk_radix_reg_kernel<4>, dim3(rows), dim3(kTopkThreads), 0, st, logits, logits_stride, n, k, indices,
+                   out_stride));
+  else if (n <= kTopkThreads * 8)
+    TB_CUDA(launch(topk_radix_reg_kernel<8>, dim3(rows), dim3(kTopkThreads), 0, st, logits, logits_stride, n, k, indices,
+                   out_stride));
+  else
+    TB_CUDA(launch(topk_radix_kernel, dim3(rows), dim3(kTopkThreads), 0, st, logits, logits_stride, n, k, indices,
+                   out_stride));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;

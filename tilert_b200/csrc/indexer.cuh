@@ -266,4 +266,141 @@ __global__ void __launch_bounds__(kTopkThreads) topk_radix_kernel(const float* _
   for (int i = n_sel + tid; i < k; i += kTopkThreads) dst[i] = -1;
 }
 
+// Same selection for rows of at most kTopkThreads * ITEMS entries: every thread keeps its ITEMS
+// consecutive keys in registers, so the row is read from memory once instead of once per pass.
+template <int ITEMS>
+__global__ void __launch_bounds__(kTopkThreads) topk_radix_reg_kernel(const float* __restrict__ logits,
+                                                                      long long logits_stride, int n, int k,
+                                                                      int* __restrict__ out, long long out_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int hist[256];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_remaining;
+  __shared__ int s_warp_gt[32], s_warp_eq[32];
+  const float* row = logits + blockIdx.x * logits_stride;
+  int* dst = out + blockIdx.x * out_stride;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int i0 = tid * ITEMS;
+
+  uint32_t key[ITEMS];
+  int cnt = 0;
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) {
+    key[j] = i0 + j < n ? f32_order_key(row[i0 + j]) : 0u;  // 0 is below the key of -inf: never eligible
+    cnt += key[j] > kNegInfKey;
+  }
+  if (tid < 256) hist[tid] = 0;
+  if (tid == 0) { s_prefix = 0; s_remaining = 0; }
+  __syncthreads();
+  {
+    int wsum = cnt;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+    if (lane == 0 && wsum != 0) atomicAdd(&s_remaining, wsum);
+  }
+  __syncthreads();
+  const int n_eligible = s_remaining;
+  __syncthreads();
+
+  uint32_t thr = kNegInfKey + 1;  // select everything eligible
+  int need_eq = 0x7fffffff;       // how many entries equal to thr to take
+  const bool take_all = n_eligible <= k;
+  if (!take_all) {
+    if (tid == 0) s_remaining = k;
+    uint32_t prefix = 0, mask = 0;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      // hist is zero here (initially, and re-zeroed by warp 0 after each pass's scan)
+#pragma unroll
+      for (int j = 0; j < ITEMS; ++j)
+        if (key[j] > kNegInfKey && (key[j] & mask) == prefix) atomicAdd(&hist[(key[j] >> shift) & 0xff], 1);
+      __syncthreads();
+      if (warp == 0) {
+        // find the digit where the count of larger-or-equal digits reaches the remaining quota:
+        // lane l owns bins 8l .. 8l+7; suffix sums across lanes, then a short scan inside one lane
+        const int rem = s_remaining;
+        int b[8], ssum = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          b[j] = hist[lane * 8 + j];
+          hist[lane * 8 + j] = 0;
+          ssum += b[j];
+        }
+        int suf = ssum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_down_sync(0xffffffffu, suf, o);
+          if (lane + o < 32) suf += v;
+        }
+        int suf_next = __shfl_down_sync(0xffffffffu, suf, 1);
+        if (lane == 31) suf_next = 0;
+        if (suf >= rem && suf_next < rem) {
+          int r = rem - suf_next, d = 0;
+          bool found = false;
+#pragma unroll
+          for (int j = 7; j >= 0; --j) {
+            if (!found) {
+              if (b[j] >= r || j == 0) {
+                d = j;
+                found = true;
+              } else {
+                r -= b[j];
+              }
+            }
+          }
+          s_remaining = r;
+          s_prefix = prefix | (static_cast<uint32_t>(lane * 8 + d) << shift);
+        }
+      }
+      __syncthreads();
+      prefix = s_prefix;
+      mask |= 0xffu << shift;
+    }
+    thr = prefix;
+    need_eq = s_remaining;
+  }
+
+  // ordered compaction of the one chunk
+  uint32_t gt_mask = 0, eq_mask = 0;
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) {
+    if (key[j] > kNegInfKey) {
+      if (take_all || key[j] > thr) gt_mask |= 1u << j;
+      else if (key[j] == thr) eq_mask |= 1u << j;
+    }
+  }
+  const int my_gt = __popc(gt_mask), my_eq = __popc(eq_mask);
+  int sc_gt = my_gt, sc_eq = my_eq;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, sc_gt, o), b = __shfl_up_sync(0xffffffffu, sc_eq, o);
+    if (lane >= o) { sc_gt += a; sc_eq += b; }
+  }
+  if (lane == 31) { s_warp_gt[warp] = sc_gt; s_warp_eq[warp] = sc_eq; }
+  __syncthreads();
+  int pre_gt = 0, pre_eq = 0, tot_gt = 0, tot_eq = 0;
+  for (int w2 = 0; w2 < 32; ++w2) {
+    const int a = s_warp_gt[w2], b = s_warp_eq[w2];
+    if (w2 < warp) { pre_gt += a; pre_eq += b; }
+    tot_gt += a; tot_eq += b;
+  }
+  int eq_before = pre_eq + sc_eq - my_eq;                 // ties before this thread, in index order
+  int w = pre_gt + sc_gt - my_gt + min(eq_before, need_eq);  // entries selected before this thread
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) {
+    if (gt_mask & (1u << j)) {
+      if (w < k) dst[w] = i0 + j;
+      ++w;
+    } else if (eq_mask & (1u << j)) {
+      if (eq_before < need_eq) {
+        if (w < k) dst[w] = i0 + j;
+        ++w;
+      }
+      ++eq_before;
+    }
+  }
+  const int n_sel = tot_gt + min(tot_eq, need_eq);
+  for (int i = n_sel + tid; i < k; i += kTopkThreads) dst[i] = -1;
+}
+
 }  // namespace tb
