@@ -241,9 +241,14 @@ def run_ours(args) -> None:
         for r in used:
             m = tr[r, :, 0] > 0
             ent, rdy, fd, lu, td, ex = (tr[r, m, i] for i in (0, 1, 2, 3, 4, 7))
+            fc = tr[r, m, 5]
             k0 = ent.min()
             rows.append({"launch": r, "ctas": int(m.sum()), "start_us": round(float(k0 - t_step0) / 1e3, 2),
+                         "entry_max": round(float((ent - k0).max()) / 1e3, 2),
+                         "ready_med": round(float((rdy - k0).median()) / 1e3, 2),
+                         "first_convert_med": round(float((fc[fc > 0] - k0).median()) / 1e3, 2) if (fc > 0).any() else None,
                          "first_data_med": round(float((fd - k0).median()) / 1e3, 2),
+                         "tiles_done_max": round(float((td - k0).max()) / 1e3, 2),
                          "last_unit_min_med_max": [round(float(v) / 1e3, 2) for v in
                                                    ((lu - k0).min(), (lu - k0).median(), (lu - k0).max())],
                          "exit_max": round(float((ex - k0).max()) / 1e3, 2)})

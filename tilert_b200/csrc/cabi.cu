@@ -102,6 +102,16 @@ size_t comm_state_offset(int world, int max_rows) {
   return (b + 255) / 256 * 256;
 }
 
+// Short rows (few k blocks per tile) with many tiles: whole tiles per CTA when the busiest CTA then
+// has at most 20 % more than the average; otherwise equal shares of units with split-tile fix-up.
+void set_partition(GemvParams& p, int grid) {
+  const int max_tiles = (p.n_tiles + grid - 1) / grid;
+  p.whole_tiles = (p.n_kb <= 16 && p.n_tiles >= grid / 2 &&
+                   static_cast<long long>(max_tiles) * grid * 5 <= static_cast<long long>(p.n_tiles) * 6)
+                      ? 1
+                      : 0;
+}
+
 int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
   static bool attr_set[64] = {};
   if (!attr_set[ctx->device & 63]) {
@@ -114,6 +124,7 @@ int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
   TB_REQUIRE(units < (1ll << 30));
   int grid = ctx->num_sms < kMaxGrid ? ctx->num_sms : kMaxGrid;
   if (units < grid) grid = static_cast<int>(units);
+  set_partition(p, grid);
   p.partial = ctx->partial;
   p.counters = ctx->counters;
   p.status = ctx->status;
@@ -1043,6 +1054,7 @@ extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_pac
   const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
   int grid = view.num_sms < kMaxGrid ? view.num_sms : kMaxGrid;
   if (units < grid) grid = static_cast<int>(units);
+  set_partition(p, grid);
   TB_CUDA(launch(wstream_gemv_kernel, dim3(grid), dim3(kGemvThreads), kGemvSmemBytes, st, p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());

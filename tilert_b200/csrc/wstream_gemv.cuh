@@ -102,6 +102,7 @@ struct GemvParams {
   int w_kb_per_tile;
   int tiles_per_xseg;
   int n_tokens;
+  int whole_tiles;       // 1: CTAs take whole row tiles (set by the host when that balances within 20 %)
   int only_token;        // >= 0: store only this token's results (per-token expert lists)
   int cols_per_token;
   int epi;
@@ -427,8 +428,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
   const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
   // unit indices fit 32 bits (checked on the host); all per-stage index arithmetic is 32-bit --
   // 64-bit divisions in these loops cost more than the stage's data movement
-  const int u0 = static_cast<int>(gemv_range_begin(units, grid, cta));
-  const int u1 = static_cast<int>(gemv_range_begin(units, grid, cta + 1));
+  // Ranges: equal shares of units (row tiles may then be split between CTAs and need a fix-up
+  // through global memory), or, when the host found that whole row tiles balance well enough,
+  // equal shares of tiles (no tile is ever split).
+  const int u0 = p.whole_tiles ? static_cast<int>(gemv_range_begin(p.n_tiles, grid, cta)) * p.n_kb
+                               : static_cast<int>(gemv_range_begin(units, grid, cta));
+  const int u1 = p.whole_tiles ? static_cast<int>(gemv_range_begin(p.n_tiles, grid, cta + 1)) * p.n_kb
+                               : static_cast<int>(gemv_range_begin(units, grid, cta + 1));
 
   // The successor may start right away.  Weight prefetch does not depend on the predecessor, so only
   // threads that read activations / routing ids / residuals or write results wait for it (below).
@@ -727,7 +733,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     if (p.ar.world > 1) ar_epoch = *reinterpret_cast<volatile unsigned long long*>(&p.ar.state[p.ar.rank]->epoch);
     const int ar_half = static_cast<int>(ar_epoch & 1ull);
     const uint32_t lane_base = static_cast<uint32_t>(gw * 32) << 16;
-    if (p.x_mode == X_BF16) {
+    if (p.x_mode == X_BF16 && units > static_cast<long long>(kGemvStages) * grid) {
+      // (Skipped when no CTA has more units than ring slots: the converter warps cover those.)
       // This CTA's share of the launch's X blocks, while the ring fills: block c, c + grid, ...,
       // spread over the eight epilogue warps; each block's flag is raised behind its stores.
       const unsigned want = *reinterpret_cast<const volatile unsigned*>(p.xstate) + 1u;
@@ -769,13 +776,30 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       prev = __shfl_sync(0xffffffffu, prev, 0);
       if (prev == c_last - c_first) {
         float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int cc = c_first; cc <= c_last; ++cc) {
-          const int cu0 = static_cast<int>(gemv_range_begin(units, grid, cc));
-          const int slot = 2 * cc + ((cu0 / p.n_kb) == t ? 0 : 1);
-          const float4 v0 = __ldcg(&part[((slot * 4 + gw) * 32 + lane) * 2]);
-          const float4 v1 = __ldcg(&part[((slot * 4 + gw) * 32 + lane) * 2 + 1]);
-          sum[0] += v0.x; sum[1] += v0.y; sum[2] += v0.z; sum[3] += v0.w;
-          sum[4] += v1.x; sum[5] += v1.y; sum[6] += v1.z; sum[7] += v1.w;
+        // batches of independent loads (a plain loop would pay one L2 round trip per CTA), added in CTA order
+        constexpr int kBatch = 8;
+        for (int cb = c_first; cb <= c_last; cb += kBatch) {
+          float4 v0[kBatch], v1[kBatch];
+#pragma unroll
+          for (int j = 0; j < kBatch; ++j) {
+            const int cc = cb + j;
+            if (cc <= c_last) {
+              const int cu0 = static_cast<int>(gemv_range_begin(units, grid, cc));
+              const int slot = 2 * cc + ((cu0 / p.n_kb) == t ? 0 : 1);
+              v0[j] = __ldcg(&part[((slot * 4 + gw) * 32 + lane) * 2]);
+              v1[j] = __ldcg(&part[((slot * 4 + gw) * 32 + lane) * 2 + 1]);
+            } else {
+              v0[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+              v1[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < kBatch; ++j) {
+            if (cb + j <= c_last) {
+              sum[0] += v0[j].x; sum[1] += v0[j].y; sum[2] += v0[j].z; sum[3] += v0[j].w;
+              sum[4] += v1[j].x; sum[5] += v1[j].y; sum[6] += v1[j].z; sum[7] += v1[j].w;
+            }
+          }
         }
         if (lane == 0) p.counters[t * 8 + gw] = 0;
         gemv_epilogue_row(p, t, gw, lane, sum, ar_half);
