@@ -183,6 +183,18 @@ int tilert_rmsnorm_expert_proj_op(TbContext* ctx, const void* x, const float* ga
 int tilert_rmsnorm_head_proj_op(TbContext* ctx, const void* x, const float* gamma, float eps, const void* w,
                                 int tokens, int dim, int vocab, void* x_norm_out, float* logits_out, void* stream);
 
+/* eh_proj_allreduce_op (ops/eh_proj_allreduce.py:23-60; golden :252-277): out[t, :] = W_eh[dim, 2*dim] .
+ * concat(e_norm[t], h_norm[t])   (bf16 in, bf16 weights, bf16 out).  Every rank computes the whole
+ * product: the reference's K-sharding + all-reduce of this 205 MB bf16 weight is not reproduced. */
+int tilert_eh_proj_allreduce_op(TbContext* ctx, const void* e_norm, const void* h_norm, const void* w, int tokens,
+                                int dim, void* out, void* stream);
+/* mtp_preprocess_layer (modules/mtp_preprocess.py:20-28; golden :197-229) for already embedded tokens:
+ * e_norm = RMSNorm(e) * gamma_e, h_norm = RMSNorm(h) * gamma_h (both rounded to bf16 and optionally
+ * written out), then eh_proj as above, in one launch per two tokens. */
+int tilert_mtp_preprocess_op(TbContext* ctx, const void* e, const void* h, const float* gamma_e,
+                             const float* gamma_h, float eps, const void* w, int tokens, int dim, void* e_norm_out,
+                             void* h_norm_out, void* out, void* stream);
+
 /* ---- per-token vector operators -------------------------------------------------------- */
 
 /* rmsnorm_kv_op (ops/rmsnorm_kv.py:20-43): kv_cache[*cur_pos + t] = bf16(RMSNorm(kv[t]) * gamma). */

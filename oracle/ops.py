@@ -340,3 +340,22 @@ def dense_down(vec, w_down, n_split):
 def rmsnorm_head_proj(x, gamma, w_head, eps):
     """RMSNormHeadProj.golden_forward, ops/rmsnorm_head_proj.py:253-273.  f32 logits."""
     return rms_norm_f32(x, gamma, eps) @ w_head.float().T
+
+
+def eh_proj(e_norm, h_norm, w_eh):
+    """EHProjAllReduce.golden_forward, ops/eh_proj_allreduce.py:252-277, summed over devices: the
+    concatenated normalised embedding and hidden state through eh_proj [dim, 2*dim] (bf16 in, bf16 out)."""
+    cat = torch.cat([e_norm, h_norm], dim=-1)
+    return cat @ w_eh.T  # a bf16 matmul, as in the reference
+
+
+def mtp_preprocess(e, h, gamma_e, gamma_h, w_eh, eps=1e-6):
+    """MTPPreprocessLayer.golden_forward, modules/mtp_preprocess.py:197-229: enorm(embedding),
+    hnorm(previous hidden state), concatenate, eh_proj.  The reference golden keeps the two
+    normalised vectors in f32 and multiplies them with the bf16 weight, which its own ``linear``
+    rejects on CPU (dtype mismatch); its kernel path hands bf16 vectors to eh_proj_allreduce_op
+    (ops/eh_proj_allreduce.py:40), and that is what is restated here.  Returns (e_norm, h_norm, out)."""
+    e_norm = rmsnorm_bf16(e, gamma_e, eps)
+    h_norm = rmsnorm_bf16(h, gamma_h, eps)
+    return e_norm, h_norm, eh_proj(e_norm, h_norm, w_eh)
+

@@ -41,6 +41,9 @@ def pin_inputs(seed: int = 1234) -> dict[str, torch.Tensor]:
         "hidden": rn(1, 1, a.dim),
         "ffn_hidden": rn(1, 1, 1 + a.n_activated_experts, a.moe_inter_dim, scale=0.1),
         "dense_hidden": rn(1, 1, a.inter_dim, scale=0.1),
+        "e_norm": rn(1, 2, a.dim),
+        "h_norm": rn(1, 2, a.dim),
+        "w_eh": rn(a.dim, 2 * a.dim, scale=0.03),
     }
 
 
@@ -84,6 +87,7 @@ def oracle_results(inp: dict[str, torch.Tensor] | None = None) -> dict[str, list
     r["expert_down"] = [oo.expert_down(inp["ffn_hidden"], [[w1.expert(n)[2] for n in names2]], probs2)]
     r["dense_down"] = [oo.dense_down(inp["dense_hidden"], w0.w_down, a.inter_dim // a.moe_inter_dim)]
     r["head"] = [oo.rmsnorm_head_proj(inp["hidden"], sd["model.norm.weight"], sd["lm_head.weight"], a.eps)]
+    r["eh_proj"] = [oo.eh_proj(inp["e_norm"], inp["h_norm"], inp["w_eh"])]
     return r
 
 

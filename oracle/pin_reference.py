@@ -245,6 +245,12 @@ def main(ref_root: str, out_path: str) -> None:
         check("head", op.golden_forward(inp["hidden"]).float(),
               oo.rmsnorm_head_proj(inp["hidden"], sd_full["model.norm.weight"], sd_full["lm_head.weight"], a.eps))
 
+    def t_eh_proj():
+        op = rops.EHProjAllReduce(margs, num_devices=1)
+        op.init_reference_weights({"eh_proj.weight": inp["w_eh"]}, None, 0)
+        check("eh_proj", op.golden_forward(inp["e_norm"], inp["h_norm"], 0),
+              oo.eh_proj(inp["e_norm"], inp["h_norm"], inp["w_eh"]))
+
     for name, fn in list(locals().items()):
         if name.startswith("t_") and isinstance(fn, types.FunctionType):
             attempt(name[2:], fn)

@@ -462,6 +462,25 @@ def test_head(env):
           cos_min=0.99999, l2_max=2e-3)
 
 
+@pytest.mark.parametrize("tokens", [1, 2, 4])
+def test_mtp_preprocess_and_eh_proj(env, tokens):
+    ops, a = env["ops"], env["a"]
+    g = torch.Generator().manual_seed(91 + tokens)
+    e, h = rn(g, 1, tokens, a.dim), rn(g, 1, tokens, a.dim, scale=2.0)
+    ge, gh = torch.rand(a.dim, generator=g) + 0.5, torch.rand(a.dim, generator=g) + 0.5
+    w = rn(g, a.dim, 2 * a.dim, scale=0.03)
+    e_ref, h_ref, out_ref = oo.mtp_preprocess(e, h, ge, gh, w, a.eps)
+    out = torch.zeros(1, tokens, a.dim, dtype=BF16, device="cuda")
+    en, hn = torch.zeros_like(out), torch.zeros_like(out)
+    ops.mtp_preprocess(e.cuda(), h.cuda(), ge.cuda(), gh.cuda(), w.cuda(), out, eps=a.eps, e_norm_out=en, h_norm_out=hn)
+    close("mtp.enorm", e_ref, en, cos_min=0.99999, l2_max=4e-3)
+    close("mtp.hnorm", h_ref, hn, cos_min=0.99999, l2_max=4e-3)
+    close("mtp.out", out_ref, out, cos_min=0.9999, l2_max=8e-3)
+    out2 = torch.zeros_like(out)
+    ops.eh_proj_allreduce(e_ref.cuda(), h_ref.cuda(), w.cuda(), 0, out2)
+    close("eh_proj", oo.eh_proj(e_ref, h_ref, w), out2, cos_min=0.9999, l2_max=8e-3)
+
+
 def test_bad_arguments_raise(env):
     ops = env["ops"]
     with pytest.raises(ValueError):

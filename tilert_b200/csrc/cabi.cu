@@ -674,7 +674,7 @@ int launch_gemv_bf16(TbContext* ctx, GemvBf16Params& p, cudaStream_t st) {
     attr_set = true;
   }
   TB_REQUIRE(smem <= 200 * 1024);
-  if (p.n <= 2048 && p.k <= 8192) {
+  if (p.n <= 2048 && p.k <= 8192 && p.x2 == nullptr) {
     static bool attr2_set = false;
     if (!attr2_set) {
       TB_CUDA(cudaFuncSetAttribute(gemv_bf16_ksplit_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
@@ -760,6 +760,59 @@ extern "C" int tilert_rmsnorm_head_proj_op(TbContext* ctx, const void* x, const 
   p.out = logits_out;
   p.out_stride = vocab;
   return launch_gemv_bf16(ctx, p, static_cast<cudaStream_t>(stream));
+}
+
+// Multi-token-prediction input: (optionally enorm / hnorm, then) concat and eh_proj [dim, 2*dim] bf16.
+// At most two tokens fit the kernel's shared memory at 2*dim = 14336; more tokens take two launches.
+namespace {
+int launch_eh_proj(TbContext* ctx, const void* e, const void* h, const float* gamma_e, const float* gamma_h, float eps,
+                   const void* w, int tokens, int dim, void* e_norm_out, void* h_norm_out, void* out,
+                   cudaStream_t st) {
+  TB_REQUIRE(tokens >= 1 && tokens <= 4 && dim % 128 == 0);
+  for (int t0 = 0; t0 < tokens; t0 += 2) {
+    const int nt = tokens - t0 < 2 ? tokens - t0 : 2;
+    GemvBf16Params p{};
+    p.w = w;
+    p.n = dim;
+    p.k = 2 * dim;
+    p.k1 = dim;
+    p.x = reinterpret_cast<const __nv_bfloat16*>(e) + static_cast<long long>(t0) * dim;
+    p.x_stride = dim;
+    p.x2 = reinterpret_cast<const __nv_bfloat16*>(h) + static_cast<long long>(t0) * dim;
+    p.x2_stride = dim;
+    p.n_tokens = nt;
+    p.gamma = gamma_e;
+    p.gamma2 = gamma_h;
+    p.eps = eps;
+    p.round_norm_bf16 = 1;
+    if (e_norm_out != nullptr) p.xnorm_out = reinterpret_cast<__nv_bfloat16*>(e_norm_out) + static_cast<long long>(t0) * dim;
+    p.xnorm_stride = dim;
+    if (h_norm_out != nullptr) p.xnorm2_out = reinterpret_cast<__nv_bfloat16*>(h_norm_out) + static_cast<long long>(t0) * dim;
+    p.xnorm2_stride = dim;
+    p.out = reinterpret_cast<__nv_bfloat16*>(out) + static_cast<long long>(t0) * dim;
+    p.out_bf16 = 1;
+    p.out_stride = dim;
+    const int rc = launch_gemv_bf16(ctx, p, st);
+    if (rc != TB_OK) return rc;
+  }
+  return TB_OK;
+}
+}  // namespace
+
+extern "C" int tilert_eh_proj_allreduce_op(TbContext* ctx, const void* e_norm, const void* h_norm, const void* w,
+                                           int tokens, int dim, void* out, void* stream) {
+  TB_REQUIRE(ctx != nullptr && e_norm != nullptr && h_norm != nullptr && w != nullptr && out != nullptr);
+  return launch_eh_proj(ctx, e_norm, h_norm, nullptr, nullptr, 0.f, w, tokens, dim, nullptr, nullptr, out,
+                        static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tilert_mtp_preprocess_op(TbContext* ctx, const void* e, const void* h, const float* gamma_e,
+                                        const float* gamma_h, float eps, const void* w, int tokens, int dim,
+                                        void* e_norm_out, void* h_norm_out, void* out, void* stream) {
+  TB_REQUIRE(ctx != nullptr && e != nullptr && h != nullptr && gamma_e != nullptr && gamma_h != nullptr);
+  TB_REQUIRE(w != nullptr && out != nullptr);
+  return launch_eh_proj(ctx, e, h, gamma_e, gamma_h, eps, w, tokens, dim, e_norm_out, h_norm_out, out,
+                        static_cast<cudaStream_t>(stream));
 }
 
 // -------------------------------------------------------------------- per-token vector operators

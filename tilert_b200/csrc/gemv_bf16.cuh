@@ -20,6 +20,14 @@ struct GemvBf16Params {
   int round_norm_bf16;           // 1: normalised activations are rounded to bf16 before the product
   __nv_bfloat16* xnorm_out;      // optional [tokens, k] (written by CTA 0)
   long long xnorm_stride;
+  // Optional second segment (row-per-warp kernel only): activations [k1, k) come from x2 and are
+  // normalised on their own with gamma2 -- the MTP input "concat(enorm(e), hnorm(h))".
+  const __nv_bfloat16* x2;       // [tokens, k - k1]; nullptr = one segment
+  long long x2_stride;
+  int k1;
+  const float* gamma2;
+  __nv_bfloat16* xnorm2_out;     // optional [tokens, k - k1] (written by CTA 0)
+  long long xnorm2_stride;
   void* out;                     // [tokens, n] f32 (out_bf16 = 0) or bf16 (out_bf16 = 1)
   int out_bf16;
   long long out_stride;
@@ -36,40 +44,54 @@ __global__ void __launch_bounds__(kGemvBf16Threads) gemv_bf16_kernel(const GemvB
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nwarps = blockDim.x >> 5;
 
-  // stage (and normalise) the activations
-  float ss[TOK];
+  // stage (and normalise) the activations; with a second segment each half has its own statistics
+  const int k1 = p.x2 != nullptr ? p.k1 : p.k;
+  float ss[TOK], ss2[TOK];
 #pragma unroll
-  for (int t = 0; t < TOK; ++t) ss[t] = 0.f;
+  for (int t = 0; t < TOK; ++t) ss[t] = ss2[t] = 0.f;
   for (int i = threadIdx.x; i < p.k; i += blockDim.x) {
 #pragma unroll
     for (int t = 0; t < TOK; ++t) {
-      const float v = t < p.n_tokens ? bf2f(p.x[t * p.x_stride + i]) : 0.f;
+      float v = 0.f;
+      if (t < p.n_tokens) v = i < k1 ? bf2f(p.x[t * p.x_stride + i]) : bf2f(p.x2[t * p.x2_stride + i - k1]);
       xs[t * p.k + i] = v;
-      ss[t] += v * v;
+      if (i < k1) ss[t] += v * v; else ss2[t] += v * v;
     }
   }
   if (p.gamma != nullptr) {
+    __shared__ float red2[TOK][32];
 #pragma unroll
     for (int t = 0; t < TOK; ++t) {
-      const float s = warp_sum(ss[t]);
-      if (lane == 0) red[t][warp] = s;
+      const float s = warp_sum(ss[t]), s2 = warp_sum(ss2[t]);
+      if (lane == 0) {
+        red[t][warp] = s;
+        red2[t][warp] = s2;
+      }
     }
     __syncthreads();
-    float rinv[TOK];
+    float rinv[TOK], rinv2[TOK];
 #pragma unroll
     for (int t = 0; t < TOK; ++t) {
-      float tot = lane < nwarps ? red[t][lane] : 0.f;
+      float tot = lane < nwarps ? red[t][lane] : 0.f, tot2 = lane < nwarps ? red2[t][lane] : 0.f;
       tot = warp_sum(tot);
-      rinv[t] = rsqrtf(tot / static_cast<float>(p.k) + p.eps);
+      tot2 = warp_sum(tot2);
+      rinv[t] = rsqrtf(tot / static_cast<float>(k1) + p.eps);
+      rinv2[t] = rsqrtf(tot2 / static_cast<float>(p.k - k1 > 0 ? p.k - k1 : 1) + p.eps);
     }
     for (int i = threadIdx.x; i < p.k; i += blockDim.x) {
-      const float g = p.gamma[i];
+      const float g = i < k1 ? p.gamma[i] : p.gamma2[i - k1];
 #pragma unroll
       for (int t = 0; t < TOK; ++t) {
-        float v = xs[t * p.k + i] * rinv[t] * g;
+        float v = xs[t * p.k + i] * (i < k1 ? rinv[t] : rinv2[t]) * g;
         if (p.round_norm_bf16) v = bf2f(f2bf(v));
         xs[t * p.k + i] = v;
-        if (p.xnorm_out != nullptr && blockIdx.x == 0 && t < p.n_tokens) p.xnorm_out[t * p.xnorm_stride + i] = f2bf(v);
+        if (blockIdx.x == 0 && t < p.n_tokens) {
+          if (i < k1) {
+            if (p.xnorm_out != nullptr) p.xnorm_out[t * p.xnorm_stride + i] = f2bf(v);
+          } else if (p.xnorm2_out != nullptr) {
+            p.xnorm2_out[t * p.xnorm2_stride + i - k1] = f2bf(v);
+          }
+        }
       }
     }
   }

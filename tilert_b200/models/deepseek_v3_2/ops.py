@@ -287,6 +287,34 @@ def rmsnorm_head_proj(x, gamma, w, x_norm_out, logits_out, profile_logs=None, *,
 
 
 # ------------------------------------------------------------- per-token vector operators
+def eh_proj_allreduce(vec_in_enorm, vec_in_hnorm, w, flag, hidden_out, profile_logs=None, *,
+                      model_arch="deepseek_v3_2"):
+    """ops/eh_proj_allreduce.py:23-60.  ``w`` is eh_proj.weight [dim, 2*dim] bf16; ``flag`` is unused."""
+    _need(vec_in_enorm, BF16, "vec_in_enorm")
+    _need(vec_in_hnorm, BF16, "vec_in_hnorm")
+    _need(w, BF16, "w")
+    _need(hidden_out, BF16, "hidden_out")
+    tokens, dim = vec_in_enorm.shape[-2], vec_in_enorm.shape[-1]
+    _tb.check(_tb.lib().tilert_eh_proj_allreduce_op(_ctx(w), _p(vec_in_enorm), _p(vec_in_hnorm), _p(w), tokens, dim,
+                                                    _p(hidden_out), _stream()))
+
+
+def mtp_preprocess(e, h, gamma_e, gamma_h, w, hidden_out, profile_logs=None, *, model_arch="deepseek_v3_2", eps=1e-6,
+                   e_norm_out=None, h_norm_out=None):
+    """modules/mtp_preprocess.py:20-28 for already embedded tokens: enorm, hnorm, concat, eh_proj."""
+    _need(e, BF16, "e")
+    _need(h, BF16, "h")
+    _need(gamma_e, F32, "gamma_e")
+    _need(gamma_h, F32, "gamma_h")
+    _need(w, BF16, "w")
+    _need(hidden_out, BF16, "hidden_out")
+    _need(e_norm_out, BF16, "e_norm_out", optional=True)
+    _need(h_norm_out, BF16, "h_norm_out", optional=True)
+    tokens, dim = e.shape[-2], e.shape[-1]
+    _tb.check(_tb.lib().tilert_mtp_preprocess_op(_ctx(w), _p(e), _p(h), _p(gamma_e), _p(gamma_h), eps, _p(w), tokens,
+                                                 dim, _p(e_norm_out), _p(h_norm_out), _p(hidden_out), _stream()))
+
+
 def rmsnorm_kv(kv, gamma, cur_pos, kv_cache, profile_logs=None, *, model_arch="deepseek_v3_2", eps=1e-6):
     """ops/rmsnorm_kv.py:20-43."""
     _need(kv, BF16, "kv")
