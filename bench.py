@@ -242,10 +242,12 @@ def run_ours(args) -> None:
             m = tr[r, :, 0] > 0
             ent, rdy, fd, lu, td, ex = (tr[r, m, i] for i in (0, 1, 2, 3, 4, 7))
             fc = tr[r, m, 5]
+            nd = tr[r, m, 13]
             k0 = ent.min()
             rows.append({"launch": r, "ctas": int(m.sum()), "start_us": round(float(k0 - t_step0) / 1e3, 2),
                          "entry_max": round(float((ent - k0).max()) / 1e3, 2),
                          "ready_med": round(float((rdy - k0).median()) / 1e3, 2),
+                         "norm_done_med": round(float((nd[nd > 0] - k0).median()) / 1e3, 2) if (nd > 0).any() else None,
                          "first_convert_med": round(float((fc[fc > 0] - k0).median()) / 1e3, 2) if (fc > 0).any() else None,
                          "first_data_med": round(float((fd - k0).median()) / 1e3, 2),
                          "tiles_done_max": round(float((td - k0).max()) / 1e3, 2),
@@ -433,8 +435,6 @@ def run_profile_gemv(args) -> None:
     launch()
     torch.cuda.synchronize()
     tilert_b200.check(tilert_b200.lib().tilert_b200_set_profile(ctx, None))
-    if os.environ.get("TB_TRACE_DUMP"):
-        torch.save(trace.cpu(), os.environ["TB_TRACE_DUMP"] + ".full")
     tr = trace[:148].cpu().double()
     t0 = tr[:, 0].min()
     rel = (tr[:, :8] - t0) / 1e3
@@ -447,8 +447,6 @@ def run_profile_gemv(args) -> None:
     for idx, nm in ((11, "mma0_wait_full_x2"), (12, "mma0_issue_x2"), (14, "prod0_wait_empty_x4"),
                     (15, "conv0_cycles_x2")):
         phases[nm + "_per_unit"] = round(float((tr[:, idx] / units).median()), 1)
-    if os.environ.get("TB_TRACE_DUMP"):
-        torch.save(tr, os.environ["TB_TRACE_DUMP"])
     print(json.dumps({"trace_us_min_med_max": phases}))
     print(json.dumps({"mode": "profile-gemv", "n": n, "k": k, "weight_bytes": w.numel(), "ms_per_launch": ms,
                       "gbs": w.numel() / ms / 1e6, "torch_sum_read_gbs": read_gbs,

@@ -62,7 +62,9 @@ long long tilert_b200_launch_count(void);
 /* Tracing, the role of the reference's `profile_logs` argument (tilert/utils.py:18-45): while
  * `trace` (device memory, u64 [256][16]) is set, every weight-streaming launch records per CTA eight
  * %globaltimer stamps (entry, ready, first data, last unit, tiles done, first conversion, copies
- * issued, exit) and three counters of its first consumer warp (cycles waiting, cycles consuming, units).  NULL switches tracing off. */
+ * issued, exit) and counters of its first epilogue, MMA, producer and converter warps (cycles waiting /
+ * working, units); rows 148-155 hold a per-unit timeline of CTA 0 (units 96-111, SM cycles).  NULL
+ * switches tracing off. */
 int tilert_b200_set_profile(TbContext* ctx, unsigned long long* trace);
 /* Same with room for several launches: `trace` is u64 [n_records][256][16] and the k-th streaming
  * launch after this call writes record k % n_records (one decode step = one record per product). */

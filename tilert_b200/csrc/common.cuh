@@ -74,25 +74,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // counted on the SM's cycle counter, read only after a batch of failed polls: reading %globaltimer
 // costs about as much as a whole pipeline stage, and a waiting consumer is the normal state of a
 // bandwidth-bound kernel.
-#ifdef TB_WAIT_SLEEP_NS
-#define TB_WAIT_BACKOFF() __nanosleep(TB_WAIT_SLEEP_NS)
-#else
-#define TB_WAIT_BACKOFF()
-#endif
 constexpr long long kWaitBudgetCycles = 4000000000ll;  // about two seconds at ~2 GHz
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 #pragma unroll 1
-  for (int i = 0; i < 32; ++i) {
+  for (int i = 0; i < 32; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-    TB_WAIT_BACKOFF();
-  }
   const long long t0 = clock64();
   while (true) {
 #pragma unroll 1
-    for (int i = 0; i < 256; ++i) {
+    for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-      TB_WAIT_BACKOFF();
-    }
     if (clock64() - t0 > kWaitBudgetCycles) return false;
   }
 }
@@ -102,17 +93,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 // read only on the slow path.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort) {
 #pragma unroll 1
-  for (int i = 0; i < 32; ++i) {
+  for (int i = 0; i < 32; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-    TB_WAIT_BACKOFF();
-  }
   const long long t0 = clock64();
   while (true) {
 #pragma unroll 1
-    for (int i = 0; i < 256; ++i) {
+    for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-      TB_WAIT_BACKOFF();
-    }
     if (*abort != 0 || clock64() - t0 > kWaitBudgetCycles) return false;
   }
 }

@@ -134,7 +134,7 @@ enum GemvProfSlot : int {
   kGemvProfUnits = 10,        // consumer 0: number of units it consumed
   kGemvProfMmaWaitFull = 11,  // MMA warp 0: cycles waiting for its slots to fill
   kGemvProfMmaIssue = 12,     // MMA warp 0: cycles issuing MMAs and their commit
-  kGemvProfUnused13 = 13,
+  kGemvProfNormDone = 13,     // converter 0: RMSNorm statistics of the activations are ready (%globaltimer)
   kGemvProfProdWait = 14,     // producer 0: cycles waiting for free slots
   kGemvProfConvCycles = 15,   // converter 0: cycles converting (excluding waits)
 };
@@ -142,18 +142,18 @@ __device__ __forceinline__ void gemv_stamp(const GemvParams& p, int slot) {
   if (p.prof != nullptr) p.prof[blockIdx.x * 16 + slot] = globaltimer_ns();
 }
 
-// Per-unit timeline of CTA 0 (SM cycle counter), rows 148.. of the trace: event e of unit i in
-// [kGemvTimelineFirst, +16) goes to prof[(148 + e) * 16 + i - kGemvTimelineFirst].
+// Per-unit timeline of CTA 0 (SM cycle counter), rows 148.. of the trace (free when the grid has at
+// most 148 CTAs): event e of unit i in [kGemvTimelineFirst, +16) goes to
+// prof[(148 + e) * 16 + i - kGemvTimelineFirst].  Events: 0 producer saw the slot free, 1 copy issued,
+// 3 MMA thread saw the slot full, 4 MMAs committed, 7 epilogue reached the unit, 5 epilogue saw the
+// accumulator, 6 epilogue released the slot.
 constexpr int kGemvTimelineFirst = 96;
 __device__ __forceinline__ void gemv_timeline(const GemvParams& p, int ev, int i) {
-  if (p.prof != nullptr && blockIdx.x == 0 && i >= kGemvTimelineFirst && i < kGemvTimelineFirst + 16)
+  if (p.prof != nullptr && blockIdx.x == 0 && gridDim.x <= 148 && i >= kGemvTimelineFirst && i < kGemvTimelineFirst + 16)
     p.prof[(148 + ev) * 16 + i - kGemvTimelineFirst] = static_cast<unsigned long long>(clock64());
 }
 
-#ifndef TB_GEMV_STAGES
-#define TB_GEMV_STAGES 12
-#endif
-constexpr int kGemvStages = TB_GEMV_STAGES;  // ring slots; a multiple of every role's warp count
+constexpr int kGemvStages = 12;         // ring slots; a multiple of every role's warp count
 constexpr int kGemvAccCols = 16;        // TMEM columns per accumulator: N = 16 is the smallest N at M = 128
 constexpr int kGemvTmemCols = 256;      // one accumulator per slot; a power of two >= kGemvStages * kGemvAccCols
 constexpr int kGemvEpilogueGroups = 2;  // unit i is read back by group i % 2
@@ -192,14 +192,7 @@ __device__ __forceinline__ uint64_t umma_desc(const void* smem_ptr, uint32_t lbo
 // Instruction descriptor: D = f32, A = B = e4m3, both K-major, N = 16, M = 128.  Only 8 activation
 // columns exist: the B descriptor's 8-column group stride is 0, so columns 8-15 repeat columns 0-7
 // and are never read back.
-#ifdef TB_EXP_M64
-constexpr uint32_t kUmmaIdesc = (1u << 4) | (2u << 17) | (4u << 24);
-#else
 constexpr uint32_t kUmmaIdesc = (1u << 4) | (2u << 17) | (8u << 24);
-#endif
-#ifndef TB_EXP_NMMA
-#define TB_EXP_NMMA 4
-#endif
 __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -257,11 +250,22 @@ __device__ __forceinline__ bool flag_wait(const unsigned* flag, unsigned want, c
   }
 }
 
+// Equal shares: CTA c owns units [begin(c), begin(c+1)), begin(c) = floor(units * c / grid).  Written
+// with 32-bit operations only (units < 2^30, grid <= 256): a 64-bit division is a long subroutine,
+// and these run at the two moments of a launch when nothing else hides them -- its first and its
+// last microsecond.  floor((q g + r) c / g) = q c + floor(r c / g).
 __device__ __forceinline__ long long gemv_range_begin(long long units, int grid, int cta) {
-  return units * cta / grid;
+  const unsigned u = static_cast<unsigned>(units), g = static_cast<unsigned>(grid), c = static_cast<unsigned>(cta);
+  const unsigned q = u / g, r = u - q * g;
+  return static_cast<long long>(q * c + (r * c) / g);
 }
+// The CTA whose range holds `unit`: a float estimate, corrected with the exact range bounds.
 __device__ __forceinline__ int gemv_owner(long long unit, long long units, int grid) {
-  return static_cast<int>(((unit + 1) * grid - 1) / units);
+  int c = static_cast<int>((static_cast<float>(unit) + 0.5f) * __fdividef(static_cast<float>(grid), static_cast<float>(units)));
+  c = c < 0 ? 0 : (c > grid - 1 ? grid - 1 : c);
+  while (c > 0 && gemv_range_begin(units, grid, c) > unit) --c;
+  while (c < grid - 1 && gemv_range_begin(units, grid, c + 1) <= unit) ++c;
+  return c;
 }
 
 __device__ __forceinline__ void gemv_store(const GemvParams& p, int row, int token, float v) {
@@ -308,7 +312,7 @@ __device__ __forceinline__ void gemv_epilogue_row(const GemvParams& p, int tile,
         const float up = __shfl_xor_sync(0xffffffffu, val[t], 8);
         if ((lane & 8) == 0) {
           const float gate = val[t];
-          gemv_store(p, n16 * 8 + (lane & 7), t, gate / (1.0f + __expf(-gate)) * up);
+          gemv_store(p, n16 * 8 + (lane & 7), t, __fdividef(gate, 1.0f + __expf(-gate)) * up);
         }
       }
     }
@@ -342,7 +346,7 @@ __device__ __forceinline__ void gemv_rinv(const GemvParams& p, const float* norm
       float tot = 0.f;
 #pragma unroll
       for (int w2 = 0; w2 < kGemvHelperWarps; ++w2) tot += norm_part[w2 * 4 + t];
-      rinv[t] = rsqrtf(tot / static_cast<float>(p.n_kb * TB_KBLOCK) + p.eps);
+      rinv[t] = rsqrtf(__fdividef(tot, static_cast<float>(p.n_kb * TB_KBLOCK)) + p.eps);
     }
   }
 }
@@ -467,6 +471,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
   const bool is_mma = warp >= kGemvFirstMmaWarp && warp < kGemvFirstProducerWarp;
   const bool is_producer = warp >= kGemvFirstProducerWarp && warp < kGemvFirstConverterWarp;
   const bool is_converter = warp >= kGemvFirstConverterWarp;
+  if (is_converter && p.x_mode == X_BF16 && p.gamma != nullptr) {
+    // the norm gain is a weight: pull it into L2 now, so that the conversions that follow the
+    // statistics do not start with a DRAM round trip
+    const int n_lines = p.n_kb * (TB_KBLOCK * 4 / 128);
+    for (int l = (warp - kGemvFirstConverterWarp) * 32 + lane; l < n_lines; l += kGemvConverterWarps * 32)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.gamma) + l * 128));
+  }
   // Producers stream weights, which no kernel of the step writes; they wait for the predecessor only
   // when their addresses depend on it (routing ids) or when they also copy packed activations.
   if (!is_producer || p.x_mode == X_PACKED || p.nseg_ids != nullptr || p.kseg_ids != nullptr ||
@@ -506,6 +517,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       if (lane == 0) norm_part[hw * 4 + t] = v;
     }
     asm volatile("bar.sync 2, %0;" ::"n"(kGemvHelperWarps * 32) : "memory");
+    if (warp == kGemvFirstConverterWarp && lane == 0) gemv_stamp(p, kGemvProfNormDone);
   }
 
   if (is_producer) {
@@ -701,7 +713,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         const uint32_t xa = wa + (kGemvSlotXOff >> 4);
         const uint32_t d = tmem_base + static_cast<uint32_t>(s * kGemvAccCols);
 #pragma unroll
-        for (int c = 0; c < TB_EXP_NMMA; ++c)
+        for (int c = 0; c < 4; ++c)
           umma_f8(d, desc_a_hi | (wa + c * (4096 >> 4)), desc_b_hi | (xa + c * (256 >> 4)), c > 0 ? 1u : 0u);
         umma_commit(&acc_full[s]);
         gemv_timeline(p, 4, u - u0);
