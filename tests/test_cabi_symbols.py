@@ -83,3 +83,19 @@ def test_activation_split_is_exact_for_bf16():
     rec = pack.reference_xpack(x)
     rel = (rec - x.float()).abs() / x.float().abs().amax(-1, keepdim=True)
     assert float(rel.max()) < 2 ** -18
+
+
+def test_torch_ops_namespace_registers_reference_names():
+    """The dispatcher names the reference's wrappers call exist after register() (no GPU work here)."""
+    import torch
+
+    from tilert_b200 import torch_ops
+
+    torch_ops.register()
+    torch_ops.register()  # idempotent
+    for name in torch_ops.op_names():
+        assert hasattr(torch.ops.tilert, name), name
+    assert torch.ops.tilert.dsa_temp_vars_size() == 56
+    schema = str(torch.ops.tilert.rmsnorm_kv_op.default._schema)
+    assert schema.startswith("tilert::rmsnorm_kv_op(Tensor kv, Tensor gamma, Tensor cur_pos, Tensor(a!) kv_cache")
+
