@@ -1,0 +1,69 @@
+"""Checkpoint converter: an HF-format FP8 safetensors checkpoint -> per-rank packed files (CPU only)."""
+
+import json
+
+import torch
+
+from tilert_b200 import convert, synthetic
+from tilert_b200.models.deepseek_v3_2.layer import LayerWeights
+from tilert_b200.models.deepseek_v3_2.model_args import toy_model_args
+
+
+def _toy_checkpoint(tmp_path, a):
+    """Two-shard HF-style checkpoint of toy layers 0 (dense) and 1 (MoE) with an index file."""
+    from safetensors.torch import save_file
+
+    sd = {}
+    for li in (0, 1):
+        sd.update(synthetic.random_layer_state_dict(a, li, "cpu", seed=3))
+    g = torch.Generator().manual_seed(5)
+    sd["model.embed_tokens.weight"] = torch.randn(a.vocab_size, a.dim, generator=g).to(torch.bfloat16)
+    sd["model.norm.weight"] = torch.rand(a.dim, generator=g) + 0.5
+    sd["lm_head.weight"] = torch.randn(a.vocab_size, a.dim, generator=g).to(torch.bfloat16)
+    keys = sorted(sd)
+    shards = {"model-00001-of-00002.safetensors": keys[: len(keys) // 2],
+              "model-00002-of-00002.safetensors": keys[len(keys) // 2:]}
+    weight_map = {}
+    for fname, ks in shards.items():
+        save_file({k: sd[k].contiguous() for k in ks}, str(tmp_path / fname))
+        weight_map.update({k: fname for k in ks})
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
+    return sd
+
+
+def test_convert_round_trip_matches_direct_packing(tmp_path):
+    a = toy_model_args()
+    hf = tmp_path / "hf"
+    hf.mkdir()
+    sd = _toy_checkpoint(hf, a)
+    out = tmp_path / "packed"
+    files = convert.convert(str(hf), str(out), a, world=2, layers=[0, 1])
+    assert len(files) == 2 * 3 and (out / "manifest.json").exists()
+    for rank in (0, 1):
+        for li in (0, 1):
+            direct = LayerWeights(a, sd, li, "cpu", 2, rank)
+            loaded = convert.load_layer(out / f"rank{rank}" / f"layer_{li:03d}.safetensors", "cpu")
+            assert loaded.dense == direct.dense and loaded.inter_local == direct.inter_local
+            names = convert._COMMON + (() if direct.dense else convert._MOE_ONLY)
+            for n in names:
+                x, y = getattr(direct, n), getattr(loaded, n)
+                assert x.dtype == y.dtype and x.shape == y.shape, n
+                assert torch.equal(x.view(torch.uint8) if x.dtype == torch.uint8 else x, y), n
+        head = convert.load_head(out / f"rank{rank}" / "head.safetensors", "cpu")
+        v_l = a.vocab_size // 2
+        assert torch.equal(head["head"], sd["lm_head.weight"][rank * v_l:(rank + 1) * v_l])
+        assert torch.equal(head["embed"], sd["model.embed_tokens.weight"])
+
+
+def test_lazy_checkpoint_reader(tmp_path):
+    a = toy_model_args()
+    sd = _toy_checkpoint(tmp_path, a)
+    ck = convert.HFCheckpoint(tmp_path)
+    k = "model.layers.1.self_attn.o_proj.weight"
+    assert k in ck and torch.equal(ck[k].view(torch.uint8), sd[k].view(torch.uint8))
+    try:
+        ck["missing.key"]
+    except KeyError:
+        pass
+    else:
+        raise AssertionError("KeyError expected")
