@@ -18,7 +18,7 @@
  *   - a context owns scratch memory used by the calls made with it: use one context per stream.
  *
  * Weight operands named `*_packed` are in the library's block format (128x128 e4m3 tiles in
- * tensor-core fragment order followed by their scales, see tilert_b200/csrc/formats.h); they are
+ * the tensor core's shared-memory operand order followed by their scales, see tilert_b200/csrc/formats.h); they are
  * produced from HF-format tensors (e4m3 weight + f32 `weight_scale_inv` per 128x128 block) by
  * `tilert_b200.pack`.  Activation operands named `xpack` are in the matching activation block
  * format, produced by the rmsnorm/pack operators below.
@@ -250,6 +250,26 @@ int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const void* q_pe, 
                                const int* indices, int topk, const int* cur_pos, int heads, int tokens, int n_cache,
                                float softmax_scale, int split_size, void* out, float* out_acc, float* lse,
                                float* lse_acc, void* stream);
+
+/* ---- sampling --------------------------------------------------------------------------- */
+
+/* The sampling step the reference runs inside its driver (configuration and outputs visible in
+ * modules/end2end.py:253-311, 665-703: SAMPLING_CONFIG = (temperature, top_p, top_k, use_top_p),
+ * TOP_N_LOG_PROBS / TOP_N_INDICES [.., 256], TOP_P_SCORES = log-probability of the sampled token;
+ * the algorithm itself is inside its binary and is restated here in the standard form).
+ *   logits [tokens, logits_stride] f32 (first `vocab` entries of a row are used);
+ *   config_dev: 4 floats in device memory; temperature 0 = greedy arg-max (ties to the lower id);
+ *   candidates are the 1024 largest logits; top_k in [1, 1024] keeps the first top_k, any other value
+ *   all 1024; with use_top_p the shortest prefix reaching top_p of the temperature-scaled softmax mass
+ *   of the whole vocabulary is kept; one uniform number from (seed, step, token index) picks a token.
+ *   step_dev: optional device state of two u64 {step, scratch}, zero before first use: the launch reads
+ *   the step and its last block increments it (so a replayed CUDA graph draws new numbers); NULL uses
+ *   step_value.  token_logprob_out / topn_* may be NULL; log-probabilities are those of the unscaled
+ *   softmax over the whole vocabulary, top-n sorted by descending probability. */
+int tilert_sample_op(TbContext* ctx, const float* logits, long long logits_stride, int tokens, int vocab,
+                     const float* config_dev, unsigned long long seed, unsigned long long* step_dev,
+                     unsigned long long step_value, int* token_out, float* token_logprob_out, float* topn_logprob_out,
+                     int* topn_index_out, void* stream);
 
 /* ---- allocation-free product ------------------------------------------------------------ */
 

@@ -359,3 +359,39 @@ def mtp_preprocess(e, h, gamma_e, gamma_h, w_eh, eps=1e-6):
     h_norm = rmsnorm_bf16(h, gamma_h, eps)
     return e_norm, h_norm, eh_proj(e_norm, h_norm, w_eh)
 
+
+def sample_uniform(seed: int, step: int, tok: int) -> float:
+    """The sampler's uniform number for (seed, step, token index): a splitmix64 finaliser, top 24 bits."""
+    mask = (1 << 64) - 1
+    z = (seed + 0x9E3779B97F4A7C15 * (step + 1) + 0xD1B54A32D192ED03 * (tok + 1)) & mask
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+    z ^= z >> 31
+    return float(z >> 40) / 16777216.0
+
+
+def sample_intervals(logits_row, temperature, top_p, top_k, use_top_p, n_candidates=1024):
+    """Restatement of the sampling rule -- NO reference golden exists (the rule lives in the reference's
+    binary; only its configuration and outputs are visible, modules/end2end.py:253-311, 665-703); parity
+    unpinned.  Standard temperature / top-k / top-p sampling over the ``n_candidates`` largest logits:
+    returns (token ids in sampling order, cumulative upper bounds in [0, 1] of each kept token,
+    log-probabilities of the unscaled softmax for all candidates).  A uniform number u selects the first
+    token whose bound exceeds u.  Computed in float64."""
+    x = logits_row.double()
+    order = torch.argsort(-x, stable=True)[:n_candidates]  # value descending, ties to the lower id
+    vals = x[order]
+    lse1 = torch.logsumexp(x, 0)
+    logp = vals - lse1
+    if temperature <= 0:
+        return order[:1], torch.ones(1, dtype=torch.float64), logp
+    pt = torch.exp((vals - x.max()) / temperature) / torch.exp((x - x.max()) / temperature).sum()
+    k_eff = top_k if 1 <= top_k <= n_candidates else n_candidates
+    k_eff = min(k_eff, order.numel())
+    cum = torch.cumsum(pt[:k_eff], 0)
+    n_keep = k_eff
+    if use_top_p:
+        reach = torch.nonzero(cum >= top_p)
+        if reach.numel():
+            n_keep = min(int(reach[0]) + 1, k_eff)
+    return order[:n_keep], cum[:n_keep] / cum[n_keep - 1], logp
+

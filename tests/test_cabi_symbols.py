@@ -43,7 +43,7 @@ def test_ops_refuse_cpu_tensors():
                        torch.zeros(1, 8, 512, dtype=torch.bfloat16))
 
 
-def test_weight_pack_round_trip_and_fragment_map():
+def test_weight_pack_round_trip_and_byte_map():
     g = torch.Generator().manual_seed(0)
     w = torch.randint(0, 255, (576, 1024), generator=g, dtype=torch.uint8)
     s = torch.rand(5, 8, generator=g) + 0.1

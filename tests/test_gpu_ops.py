@@ -538,6 +538,59 @@ def test_torch_ops_namespace_calls_reach_the_kernels(env):
     assert torch.equal(idx.cpu(), oo.topk_indices(logits.cpu(), 256).view(1, 256))
 
 
+def test_sampling_matches_the_restated_rule(env):
+    """Greedy, top-k, top-p and plain temperature sampling over a vocabulary-sized row: the kernel's
+    token must be the one the float64 restatement assigns to the same uniform number (a token whose
+    cumulative interval the number misses by less than 1e-4 is accepted: f32 vs f64 sums)."""
+    ops = env["ops"]
+    g = torch.Generator().manual_seed(404)
+    vocab, tokens = 129280, 3
+    logits = (torch.randn(tokens, vocab, generator=g) * 2.5)
+    logits[0, 777] = 30.0                                  # a dominant token
+    logits[1, 5] = logits[1, 9] = logits[1].max() + 1.0    # an exact tie at the top
+    dev_logits = logits.cuda()
+    tok = torch.zeros(tokens, dtype=I32, device="cuda")
+    lp = torch.zeros(tokens, dtype=F32, device="cuda")
+    tn_lp = torch.zeros(tokens, 256, dtype=F32, device="cuda")
+    tn_ix = torch.zeros(tokens, 256, dtype=I32, device="cuda")
+    for cfg, seed, step in [((0.0, 1.0, 0.0, 0.0), 1, 0), ((1.0, 1.0, 50.0, 0.0), 2, 3), ((0.7, 0.9, 0.0, 1.0), 3, 11),
+                            ((1.3, 0.5, 40.0, 1.0), 4, 12345), ((1.0, 1.0, 0.0, 0.0), 5, 7)]:
+        config = torch.tensor(cfg, dtype=F32, device="cuda")
+        ops.sample(dev_logits, config, tok, seed=seed, step_value=step, token_logprob=lp, topn_logprobs=tn_lp,
+                   topn_indices=tn_ix)
+        torch.cuda.synchronize()
+        for t in range(tokens):
+            ids, bounds, logp = oo.sample_intervals(logits[t], cfg[0], cfg[1], int(cfg[2]), cfg[3] != 0)
+            got = int(tok[t])
+            if cfg[0] == 0.0:
+                assert got == int(ids[0]), (cfg, t)
+            else:
+                u = oo.sample_uniform(seed, step, t)
+                pos = (ids == got).nonzero()
+                assert pos.numel() == 1, (cfg, t, got)
+                j = int(pos[0])
+                lo = float(bounds[j - 1]) if j > 0 else 0.0
+                assert lo - 1e-4 <= u < float(bounds[j]) + 1e-4, (cfg, t, got, u, lo, float(bounds[j]))
+            order = torch.argsort(-logits[t].double(), stable=True)
+            assert torch.equal(tn_ix[t].cpu().long(), order[:256])
+            assert torch.allclose(tn_lp[t].cpu().double(), logp[:256], atol=2e-4)
+            assert abs(float(lp[t]) - float(logp[(order[:1024] == got).nonzero()[0]])) < 2e-4
+    # a device step counter makes identical launches draw different numbers (what a replayed graph needs)
+    step = torch.zeros(2, dtype=torch.int64, device="cuda")
+    config = torch.tensor((1.0, 1.0, 0.0, 0.0), dtype=F32, device="cuda")
+    flat = torch.zeros(1, 4096, dtype=F32, device="cuda")  # uniform distribution: the token tracks u
+    seen = set()
+    one = torch.zeros(1, dtype=I32, device="cuda")
+    for i in range(6):
+        ops.sample(flat, config, one, seed=9, step=step)
+        torch.cuda.synchronize()
+        assert int(step[0]) == i + 1 and int(step[1]) == 0
+        expect = int(oo.sample_uniform(9, i, 0) * 1024)  # candidates = ids 0..1023, each 1/1024
+        assert abs(int(one[0]) - expect) <= 1
+        seen.add(int(one[0]))
+    assert len(seen) >= 5
+
+
 def test_bad_arguments_raise(env):
     ops = env["ops"]
     with pytest.raises(ValueError):

@@ -14,6 +14,7 @@
 #include "attn_prep.cuh"
 #include "indexer.cuh"
 #include "sparse_mla.cuh"
+#include "sampler.cuh"
 #include "wstream_gemv.cuh"
 
 using namespace tb;
@@ -1022,6 +1023,32 @@ extern "C" int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const v
   TB_CUDA(cudaGetLastError());
   TB_CUDA(launch(sparse_mla_combine_kernel, dim3(dim3(heads, tokens)), dim3(128), 0, st, out_acc, lse_acc, p.n_splits,
                                                                  reinterpret_cast<__nv_bfloat16*>(out), lse));
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+// ------------------------------------------------------------------------------ sampling
+extern "C" int tilert_sample_op(TbContext* ctx, const float* logits, long long logits_stride, int tokens, int vocab,
+                                const float* config_dev, unsigned long long seed, unsigned long long* step_dev,
+                                unsigned long long step_value, int* token_out, float* token_logprob_out,
+                                float* topn_logprob_out, int* topn_index_out, void* stream) {
+  TB_REQUIRE(ctx != nullptr && logits != nullptr && config_dev != nullptr && token_out != nullptr);
+  TB_REQUIRE(tokens >= 1 && vocab >= 1 && logits_stride >= vocab);
+  TB_REQUIRE((topn_logprob_out == nullptr) == (topn_index_out == nullptr));
+  SampleParams p{};
+  p.logits = logits;
+  p.stride = logits_stride;
+  p.vocab = vocab;
+  p.config = config_dev;
+  p.seed = seed;
+  p.step = step_dev;
+  p.step_value = step_value;
+  p.token = token_out;
+  p.token_logprob = token_logprob_out;
+  p.topn_logprob = topn_logprob_out;
+  p.topn_index = topn_index_out;
+  TB_CUDA(launch(sample_kernel, dim3(tokens), dim3(kTopkThreads), 0, static_cast<cudaStream_t>(stream), p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;

@@ -110,18 +110,13 @@ constexpr int kTopkItems = 8;  // consecutive elements per thread in the ordered
 
 // One CTA per row.  Selects the k largest logits among [0, n) (entries equal to -inf are skipped),
 // ties by lower index, and writes their indices in ascending order; unused slots get -1.
-__global__ void __launch_bounds__(kTopkThreads) topk_radix_kernel(const float* __restrict__ logits,
-                                                                  long long logits_stride, int n, int k,
-                                                                  int* __restrict__ out, long long out_stride) {
-  pdl_launch_dependents();
-  pdl_wait();
+// The selection for one row by one CTA of kTopkThreads threads; `dst` may be shared or global memory.
+__device__ __forceinline__ void topk_radix_row(const float* __restrict__ row, int n, int k, int* dst) {
   __shared__ int hist[256];
   __shared__ uint32_t s_prefix;
   __shared__ int s_remaining;
   __shared__ int s_warp_gt[32], s_warp_eq[32];
   __shared__ int s_base_sel, s_base_eq;
-  const float* row = logits + blockIdx.x * logits_stride;
-  int* dst = out + blockIdx.x * out_stride;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   // count eligible entries
@@ -264,6 +259,13 @@ __global__ void __launch_bounds__(kTopkThreads) topk_radix_kernel(const float* _
   }
   const int n_sel = s_base_sel;
   for (int i = n_sel + tid; i < k; i += kTopkThreads) dst[i] = -1;
+}
+__global__ void __launch_bounds__(kTopkThreads) topk_radix_kernel(const float* __restrict__ logits,
+                                                                  long long logits_stride, int n, int k,
+                                                                  int* __restrict__ out, long long out_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  topk_radix_row(logits + blockIdx.x * logits_stride, n, k, out + blockIdx.x * out_stride);
 }
 
 // Same selection for rows of at most kTopkThreads * ITEMS entries: every thread keeps its ITEMS

@@ -60,30 +60,10 @@ __global__ void __launch_bounds__(kMlaThreads) sparse_mla_kernel(const MlaParams
     mbar_init(bar, 1);
     mbar_fence_init();
   }
-  // stage the 16 query heads: [512 latent | 64 rope]
-  for (int i = tid; i < kMlaHeads * 72; i += kMlaThreads) {
-    const int r = i / 72, c = i % 72;
-    const int head = hg * kMlaHeads + r;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (head < p.heads) {
-      const long long th = static_cast<long long>(tok) * p.heads + head;
-      v = c < 64 ? *reinterpret_cast<const uint4*>(p.q_lat + th * kMlaDV + c * 8)
-                 : *reinterpret_cast<const uint4*>(p.q_pe + th * kMlaDR + (c - 64) * 8);
-    }
-    *reinterpret_cast<uint4*>(sQ + r * kMlaPitch + c * 8) = v;
-  }
-  __syncthreads();
-
-  uint32_t phase = 0;  // completed phases of `bar` (a block without valid rows issues no copy)
-  float m_run[2] = {-INFINITY, -INFINITY};
-  float l_run[2] = {0.f, 0.f};
-  float o[16][4];
-#pragma unroll
-  for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-
-  for (int blk = 0; blk < p.blocks_per_split; ++blk) {
+  // Gather of one block of 64 selected rows: one bulk copy per row and part, all completing on `bar`.
+  // Returns the number of valid rows (a block without valid rows issues no copy).
+  auto issue_gather = [&](int blk) -> int {
     const int key_base = (split * p.blocks_per_split + blk) * kMlaKeys;
-    // ---- gather 64 selected rows ----
     int my_idx = -1;
     bool valid = false;
     if (tid < kMlaKeys) {
@@ -106,6 +86,34 @@ __global__ void __launch_bounds__(kMlaThreads) sparse_mla_kernel(const MlaParams
         for (int c = 0; c < 72; ++c) *reinterpret_cast<uint4*>(row + c * 8) = make_uint4(0, 0, 0, 0);
       }
     }
+    return n_valid;
+  };
+  // the first block's rows are requested before the queries are staged: the two latencies overlap
+  int n_valid = p.blocks_per_split > 0 ? issue_gather(0) : 0;
+  // stage the 16 query heads: [512 latent | 64 rope]
+  for (int i = tid; i < kMlaHeads * 72; i += kMlaThreads) {
+    const int r = i / 72, c = i % 72;
+    const int head = hg * kMlaHeads + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (head < p.heads) {
+      const long long th = static_cast<long long>(tok) * p.heads + head;
+      v = c < 64 ? *reinterpret_cast<const uint4*>(p.q_lat + th * kMlaDV + c * 8)
+                 : *reinterpret_cast<const uint4*>(p.q_pe + th * kMlaDR + (c - 64) * 8);
+    }
+    *reinterpret_cast<uint4*>(sQ + r * kMlaPitch + c * 8) = v;
+  }
+  __syncthreads();
+
+  uint32_t phase = 0;  // completed phases of `bar` (a block without valid rows issues no copy)
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  float o[16][4];
+#pragma unroll
+  for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+  for (int blk = 0; blk < p.blocks_per_split; ++blk) {
+    // ---- 64 selected rows (block 0 was requested before the loop) ----
+    if (blk > 0) n_valid = issue_gather(blk);
     if (n_valid > 0) {
       if (!mbar_wait(bar, phase & 1)) set_status(p.status, ST_WAIT_FULL_TIMEOUT);
       ++phase;
@@ -259,14 +267,34 @@ __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float* __
       s_mx = mx;
     }
   }
-  __syncthreads();
+  // partial outputs in batches of 16 independent loads; the first batch is requested before the
+  // barrier, so it overlaps the weights' own load and reductions
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   const float* src = o_acc + th * n_splits * kMlaDV + threadIdx.x * 4;
-#pragma unroll 8
-  for (int i = 0; i < n_splits; ++i) {
-    const float4 v = __ldcs(reinterpret_cast<const float4*>(src + static_cast<long long>(i) * kMlaDV));
-    const float wgt = s_w[i];
-    acc[0] += wgt * v.x; acc[1] += wgt * v.y; acc[2] += wgt * v.z; acc[3] += wgt * v.w;
+  constexpr int kBatch = 16;
+  float4 v[kBatch];
+#pragma unroll
+  for (int j = 0; j < kBatch; ++j)
+    v[j] = j < n_splits ? __ldcs(reinterpret_cast<const float4*>(src + static_cast<long long>(j) * kMlaDV))
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+  __syncthreads();
+  for (int i0 = 0; i0 < n_splits; i0 += kBatch) {
+    float4 nxt[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int i = i0 + kBatch + j;
+      nxt[j] = i < n_splits ? __ldcs(reinterpret_cast<const float4*>(src + static_cast<long long>(i) * kMlaDV))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (i0 + j < n_splits) {
+        const float wgt = s_w[i0 + j];
+        acc[0] += wgt * v[j].x; acc[1] += wgt * v[j].y; acc[2] += wgt * v[j].z; acc[3] += wgt * v[j].w;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) v[j] = nxt[j];
   }
   const float den = s_den;
   const float inv = den > 0.f ? 1.f / den : 0.f;

@@ -60,7 +60,7 @@ struct AllReduce {
 // Where the activations of a launch come from.
 enum XMode : int {
   X_PACKED = 0,  // X blocks prepared beforehand in global memory (bulk-copied with the weights)
-  X_BF16 = 1,    // bf16 vectors in global memory; a converter warp normalises (optional RMSNorm),
+  X_BF16 = 1,    // bf16 vectors in global memory; the kernel normalises them (optional RMSNorm),
                  // splits them into two e4m3 terms and writes the X block of each stage itself
 };
 
@@ -123,15 +123,15 @@ struct GemvParams {
 enum GemvProfSlot : int {
   kGemvProfEntry = 0,         // kernel entry
   kGemvProfReady = 1,         // barriers initialised
-  kGemvProfFirstData = 2,     // consumer 0: its first unit's data is in shared memory
-  kGemvProfLastUnit = 3,      // consumer 0: its last unit is consumed
-  kGemvProfTilesDone = 4,     // consumer 0: all its tile reductions / epilogues are done
+  kGemvProfFirstData = 2,     // epilogue warp 0: the accumulator of the CTA's first unit is complete
+  kGemvProfLastUnit = 3,      // epilogue warp 0: the CTA's last unit is read back
+  kGemvProfTilesDone = 4,     // epilogue warp 0: all its tile reductions / epilogues are done
   kGemvProfFirstConvert = 5,  // converter 0: first X block written
   kGemvProfIssued = 6,        // producer 0: all its copies issued
-  kGemvProfExit = 7,          // consumer 0: end of kernel (after the all-reduce, if any)
-  kGemvProfWaitCycles = 8,    // consumer 0: SM cycles spent waiting for data, summed over its units
-  kGemvProfMathCycles = 9,    // consumer 0: SM cycles spent consuming, summed over its units
-  kGemvProfUnits = 10,        // consumer 0: number of units it consumed
+  kGemvProfExit = 7,          // epilogue warp 0: end of kernel (after the all-reduce, if any)
+  kGemvProfWaitCycles = 8,    // epilogue warp 0: SM cycles spent waiting for accumulators, summed over its units
+  kGemvProfMathCycles = 9,    // epilogue warp 0: SM cycles spent reading back and scaling, summed over its units
+  kGemvProfUnits = 10,        // epilogue warp 0: number of units it read back
   kGemvProfMmaWaitFull = 11,  // MMA warp 0: cycles waiting for its slots to fill
   kGemvProfMmaIssue = 12,     // MMA warp 0: cycles issuing MMAs and their commit
   kGemvProfNormDone = 13,     // converter 0: RMSNorm statistics of the activations are ready (%globaltimer)
@@ -651,7 +651,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       }
       // Do not leave the CTA while this thread's copies may still be landing in its shared memory:
       // wait (bounded) for the last use it issued into each of its ring slots.  On the normal path
-      // these have completed already, because the consumers waited on the same phases.  (After a
+      // these have completed already, because the MMA-issuing threads waited on the same phases.  (After a
       // failed flag wait a slot may be short of its X block; that wait then runs into the abort flag.)
       for (int back = 0; back < kGemvStages && last_i - back >= 0; back += kGemvProducerWarps) {
         const int i = last_i - back;

@@ -451,3 +451,27 @@ def flash_sparse_mla(q, q_pe, kv, k_pe, indices, cur_pos, output, profile_logs=N
                                                    _p(cur_pos), heads, tokens, kv.shape[-2], softmax_scale,
                                                    split_size, _p(output), _p(out_acc), _p(lse), _p(lse_acc),
                                                    _stream()))
+
+
+# ------------------------------------------------------------------------------ sampling
+def sample(logits, config, token_out, *, seed=0, step=None, step_value=0, token_logprob=None, topn_logprobs=None,
+           topn_indices=None, vocab=None):
+    """The driver's sampling step (modules/end2end.py:253-311, 665-703): ``config`` is the f32
+    ``SAMPLING_CONFIG`` tensor (temperature, top_p, top_k, use_top_p); ``step`` an optional int64[2] device
+    tensor that makes replayed CUDA graphs draw new numbers; outputs as ``TOP_P_SCORES`` /
+    ``TOP_N_LOG_PROBS`` / ``TOP_N_INDICES``."""
+    _need(logits, F32, "logits")
+    _need(config, F32, "config")
+    _need(token_out, I32, "token_out")
+    _need(token_logprob, F32, "token_logprob", optional=True)
+    _need(topn_logprobs, F32, "topn_logprobs", optional=True)
+    _need(topn_indices, I32, "topn_indices", optional=True)
+    if step is not None and (step.dtype != torch.int64 or step.numel() < 2 or not step.is_cuda):
+        raise ValueError("step must be an int64 CUDA tensor of two elements")
+    rows = logits.numel() // logits.shape[-1]
+    n = logits.shape[-1] if vocab is None else vocab
+    seed &= (1 << 63) - 1
+    _tb.check(_tb.lib().tilert_sample_op(_ctx(logits), _p(logits), logits.shape[-1], rows, n, _p(config), seed, _p(step),
+                                         step_value, _p(token_out), _p(token_logprob), _p(topn_logprobs),
+                                         _p(topn_indices), _stream()))
+
