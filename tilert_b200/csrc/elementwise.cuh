@@ -15,6 +15,52 @@ __device__ __forceinline__ void rmsnorm_kv_warp(int tok, const __nv_bfloat16* __
   const int lane = threadIdx.x & 31;
   if (tok >= n_tokens) return;
   const __nv_bfloat16* x = kv + tok * kv_stride;
+  __nv_bfloat16* dst = cache + static_cast<long long>(*pos + tok) * dim;
+  if (dim % 256 == 0 && dim <= 1024 && (kv_stride % 8) == 0) {
+    // every load of the lane up front (8 bf16 per 16-byte load, lane-contiguous), one pass
+    constexpr int kMaxV = 4;
+    const int nv = dim / 256;
+    uint4 raw[kMaxV];
+    float4 g0[kMaxV], g1[kMaxV];
+#pragma unroll
+    for (int v = 0; v < kMaxV; ++v) {
+      if (v < nv) {
+        const int e = (v * 32 + lane) * 8;
+        raw[v] = *reinterpret_cast<const uint4*>(x + e);
+        g0[v] = *reinterpret_cast<const float4*>(gamma + e);
+        g1[v] = *reinterpret_cast<const float4*>(gamma + e + 4);
+      }
+    }
+    float ss = 0.f;
+    float f[kMaxV][8];
+#pragma unroll
+    for (int v = 0; v < kMaxV; ++v) {
+      if (v < nv) {
+        const uint32_t w4[4] = {raw[v].x, raw[v].y, raw[v].z, raw[v].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          f[v][2 * j] = __uint_as_float(w4[j] << 16);
+          f[v][2 * j + 1] = __uint_as_float(w4[j] & 0xffff0000u);
+          ss += f[v][2 * j] * f[v][2 * j] + f[v][2 * j + 1] * f[v][2 * j + 1];
+        }
+      }
+    }
+    ss = warp_sum(ss);
+    const float rinv = rsqrtf(ss / static_cast<float>(dim) + eps);
+#pragma unroll
+    for (int v = 0; v < kMaxV; ++v) {
+      if (v < nv) {
+        const float gg[8] = {g0[v].x, g0[v].y, g0[v].z, g0[v].w, g1[v].x, g1[v].y, g1[v].z, g1[v].w};
+        uint4 o;
+        o.x = pack_bf16x2(f[v][0] * rinv * gg[0], f[v][1] * rinv * gg[1]);
+        o.y = pack_bf16x2(f[v][2] * rinv * gg[2], f[v][3] * rinv * gg[3]);
+        o.z = pack_bf16x2(f[v][4] * rinv * gg[4], f[v][5] * rinv * gg[5]);
+        o.w = pack_bf16x2(f[v][6] * rinv * gg[6], f[v][7] * rinv * gg[7]);
+        *reinterpret_cast<uint4*>(dst + (v * 32 + lane) * 8) = o;
+      }
+    }
+    return;
+  }
   float ss = 0.f;
   for (int i = lane; i < dim; i += 32) {
     const float v = bf2f(x[i]);
@@ -22,7 +68,6 @@ __device__ __forceinline__ void rmsnorm_kv_warp(int tok, const __nv_bfloat16* __
   }
   ss = warp_sum(ss);
   const float rinv = rsqrtf(ss / static_cast<float>(dim) + eps);
-  __nv_bfloat16* dst = cache + static_cast<long long>(*pos + tok) * dim;
   for (int i = lane; i < dim; i += 32) dst[i] = f2bf(bf2f(x[i]) * rinv * gamma[i]);
 }
 __global__ void rmsnorm_kv_kernel(const __nv_bfloat16* __restrict__ kv, long long kv_stride,

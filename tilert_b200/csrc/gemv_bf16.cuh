@@ -184,18 +184,31 @@ __device__ __forceinline__ void gemv_bf16_ksplit_body(const GemvBf16Params& p, i
   float ss[TOK];
 #pragma unroll
   for (int t = 0; t < TOK; ++t) ss[t] = 0.f;
-  for (int i = threadIdx.x * 8; i < p.k; i += kGemvBf16SmallThreads * 8) {
+  // all of this thread's activation loads first (k <= 8192: at most four per token), then the staging:
+  // a plain loop would pay one memory round trip per iteration
+  uint4 xraw[4][TOK];
 #pragma unroll
-    for (int t = 0; t < TOK; ++t) {
-      uint4 raw = make_uint4(0, 0, 0, 0);
-      if (t < p.n_tokens) raw = *reinterpret_cast<const uint4*>(p.x + t * p.x_stride + i);
-      const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+  for (int it = 0; it < 4; ++it) {
+    const int i = (it * kGemvBf16SmallThreads + threadIdx.x) * 8;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float a = __uint_as_float(wv[j] << 16), b = __uint_as_float(wv[j] & 0xffff0000u);
-        xs[t * p.k + i + 2 * j] = a;
-        xs[t * p.k + i + 2 * j + 1] = b;
-        ss[t] += a * a + b * b;
+    for (int t = 0; t < TOK; ++t)
+      xraw[it][t] = (i < p.k && t < p.n_tokens) ? *reinterpret_cast<const uint4*>(p.x + t * p.x_stride + i)
+                                                : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int i = (it * kGemvBf16SmallThreads + threadIdx.x) * 8;
+    if (i < p.k) {
+#pragma unroll
+      for (int t = 0; t < TOK; ++t) {
+        const uint32_t wv[4] = {xraw[it][t].x, xraw[it][t].y, xraw[it][t].z, xraw[it][t].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float a = __uint_as_float(wv[j] << 16), b = __uint_as_float(wv[j] & 0xffff0000u);
+          xs[t * p.k + i + 2 * j] = a;
+          xs[t * p.k + i + 2 * j + 1] = b;
+          ss[t] += a * a + b * b;
+        }
       }
     }
   }

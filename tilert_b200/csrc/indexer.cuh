@@ -37,21 +37,36 @@ __global__ void __launch_bounds__(kIdxWarps * 32) indexer_logits_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int key0 = blockIdx.x * (kIdxWarps * kIdxKeysPerWarp);
 
-  // stage q (H x 128) and this CTA's 64 keys with 16-byte loads
-  for (int i = threadIdx.x; i < H * 16; i += blockDim.x) {
+  // stage q (H x 128) and this CTA's 64 keys with 16-byte loads: all loads of a thread are requested
+  // before the first is stored (a load-store loop would pay one memory round trip per iteration)
+  constexpr int kThreads = kIdxWarps * 32;
+  constexpr int kQIters = H * 16 / kThreads, kKIters = 64 * 16 / kThreads;
+  uint4 qv[kQIters], kv[kKIters];
+#pragma unroll
+  for (int it = 0; it < kKIters; ++it) {
+    const int i = it * kThreads + threadIdx.x;
     const int r = i >> 4, c = i & 15;
-    *reinterpret_cast<uint4*>(sq + r * kIdxPitch + c * 8) =
-        *reinterpret_cast<const uint4*>(q + (static_cast<long long>(tok) * H + r) * 128 + c * 8);
-  }
-  for (int i = threadIdx.x; i < 64 * 16; i += blockDim.x) {
-    const int r = i >> 4, c = i & 15;
-    uint4 v = make_uint4(0, 0, 0, 0);
+    kv[it] = make_uint4(0, 0, 0, 0);
     if (key0 + r < n_keys) {
       asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                   : "=r"(kv[it].x), "=r"(kv[it].y), "=r"(kv[it].z), "=r"(kv[it].w)
                    : "l"(kcache + static_cast<long long>(key0 + r) * 128 + c * 8));
     }
-    *reinterpret_cast<uint4*>(sk + r * kIdxPitch + c * 8) = v;
+  }
+#pragma unroll
+  for (int it = 0; it < kQIters; ++it) {
+    const int i = it * kThreads + threadIdx.x;
+    qv[it] = *reinterpret_cast<const uint4*>(q + (static_cast<long long>(tok) * H + (i >> 4)) * 128 + (i & 15) * 8);
+  }
+#pragma unroll
+  for (int it = 0; it < kKIters; ++it) {
+    const int i = it * kThreads + threadIdx.x;
+    *reinterpret_cast<uint4*>(sk + (i >> 4) * kIdxPitch + (i & 15) * 8) = kv[it];
+  }
+#pragma unroll
+  for (int it = 0; it < kQIters; ++it) {
+    const int i = it * kThreads + threadIdx.x;
+    *reinterpret_cast<uint4*>(sq + (i >> 4) * kIdxPitch + (i & 15) * 8) = qv[it];
   }
   for (int i = threadIdx.x; i < H; i += blockDim.x) sw[i] = bf2f(w[tok * H + i]);
   __syncthreads();

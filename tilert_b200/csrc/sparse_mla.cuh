@@ -90,17 +90,26 @@ __global__ void __launch_bounds__(kMlaThreads) sparse_mla_kernel(const MlaParams
   };
   // the first block's rows are requested before the queries are staged: the two latencies overlap
   int n_valid = p.blocks_per_split > 0 ? issue_gather(0) : 0;
-  // stage the 16 query heads: [512 latent | 64 rope]
-  for (int i = tid; i < kMlaHeads * 72; i += kMlaThreads) {
+  // stage the 16 query heads: [512 latent | 64 rope]; all of a thread's loads are requested before the
+  // first is stored (a load-store loop would pay one memory round trip per iteration)
+  constexpr int kQIters = kMlaHeads * 72 / kMlaThreads;  // 9
+  uint4 qv[kQIters];
+#pragma unroll
+  for (int it = 0; it < kQIters; ++it) {
+    const int i = it * kMlaThreads + tid;
     const int r = i / 72, c = i % 72;
     const int head = hg * kMlaHeads + r;
-    uint4 v = make_uint4(0, 0, 0, 0);
+    qv[it] = make_uint4(0, 0, 0, 0);
     if (head < p.heads) {
       const long long th = static_cast<long long>(tok) * p.heads + head;
-      v = c < 64 ? *reinterpret_cast<const uint4*>(p.q_lat + th * kMlaDV + c * 8)
-                 : *reinterpret_cast<const uint4*>(p.q_pe + th * kMlaDR + (c - 64) * 8);
+      qv[it] = c < 64 ? *reinterpret_cast<const uint4*>(p.q_lat + th * kMlaDV + c * 8)
+                      : *reinterpret_cast<const uint4*>(p.q_pe + th * kMlaDR + (c - 64) * 8);
     }
-    *reinterpret_cast<uint4*>(sQ + r * kMlaPitch + c * 8) = v;
+  }
+#pragma unroll
+  for (int it = 0; it < kQIters; ++it) {
+    const int i = it * kMlaThreads + tid;
+    *reinterpret_cast<uint4*>(sQ + (i / 72) * kMlaPitch + (i % 72) * 8) = qv[it];
   }
   __syncthreads();
 
