@@ -435,6 +435,8 @@ def run_profile_gemv(args) -> None:
     launch()
     torch.cuda.synchronize()
     tilert_b200.check(tilert_b200.lib().tilert_b200_set_profile(ctx, None))
+    if os.environ.get("TB_TIMELINE_OUT"):
+        torch.save(trace.cpu(), os.environ["TB_TIMELINE_OUT"])
     tr = trace[:148].cpu().double()
     t0 = tr[:, 0].min()
     rel = (tr[:, :8] - t0) / 1e3

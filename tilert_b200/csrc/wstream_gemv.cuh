@@ -147,7 +147,10 @@ __device__ __forceinline__ void gemv_stamp(const GemvParams& p, int slot) {
 // prof[(148 + e) * 16 + i - kGemvTimelineFirst].  Events: 0 producer saw the slot free, 1 copy issued,
 // 3 MMA thread saw the slot full, 4 MMAs committed, 7 epilogue reached the unit, 5 epilogue saw the
 // accumulator, 6 epilogue released the slot.
-constexpr int kGemvTimelineFirst = 96;
+#ifndef TB_TIMELINE_FIRST
+#define TB_TIMELINE_FIRST 96
+#endif
+constexpr int kGemvTimelineFirst = TB_TIMELINE_FIRST;
 __device__ __forceinline__ void gemv_timeline(const GemvParams& p, int ev, int i) {
   if (p.prof != nullptr && blockIdx.x == 0 && gridDim.x <= 148 && i >= kGemvTimelineFirst && i < kGemvTimelineFirst + 16)
     p.prof[(148 + ev) * 16 + i - kGemvTimelineFirst] = static_cast<unsigned long long>(clock64());
@@ -570,8 +573,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       // X block of a unit from the shared blocks: wait (bounded) for its flag, then copy.
       auto x_from_shared = [&](int s, int xb, unsigned want) -> bool {
         if (!flag_wait(p.xflag + xb, want, cta_error)) return false;
-        // the block was written with ordinary stores by another CTA and is read by the copy engine
-        asm volatile("fence.proxy.async;" ::: "memory");
+        // the block was written with ordinary stores by another CTA and is read by the copy engine:
+        // order the flag's acquire before the async-proxy read of global memory
+        asm volatile("fence.proxy.async.global;" ::: "memory");
         bulk_g2s(smem + s * kGemvSlotStride + kGemvSlotXOff, p.xs + static_cast<long long>(xb) * TB_XBLK_BYTES,
                  TB_XBLK_BYTES, &full[s]);
         return true;
@@ -756,8 +760,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       gemv_rinv(p, norm_part, rinv);
       for (int xb = cta + warp * grid; xb < n_xblocks; xb += kGemvEpilogueWarps * grid) {
         gemv_convert_xblock(p, xb, rinv, p.xs + static_cast<long long>(xb) * TB_XBLK_BYTES, lane);
-        // ordinary stores that the copy engines of other CTAs will read
-        asm volatile("fence.proxy.async;" ::: "memory");
+        // ordinary stores that the copy engines of other CTAs will read: the readers fence between
+        // their acquire of the flag and their copy, the writer only has to release
         __syncwarp();
         if (lane == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.xflag + xb), "r"(want) : "memory");
       }
