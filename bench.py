@@ -40,8 +40,8 @@ WORKLOAD = ("C1: one full-shape DeepSeek-V3.2 MoE decoder layer, batch 1, 1 toke
 
 
 # DRAM traffic per algorithmic byte of the streaming kernel, from one ncu capture of
-# `bench.py --profile-gemv` (dram__bytes_read.sum + dram__bytes_write.sum = 239.63 MB for 235.80 MB of weights).
-NCU_TRAFFIC_RATIO = 239.63 / 235.80
+# `bench.py --profile-gemv` (dram__bytes_read.sum + dram__bytes_write.sum = 239.50 MB for 235.80 MB of weights).
+NCU_TRAFFIC_RATIO = 239.50 / 235.80
 
 
 def forced_scores(n_experts: int, top_k: int) -> torch.Tensor:
@@ -356,7 +356,7 @@ def run_ours(args) -> None:
                          "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
                          "peak_source": peak_src, "traffic": upgate_bytes * NCU_TRAFFIC_RATIO,
                          "traffic_source": "ncu dram read+write of the same kernel on a 235.8 MB weight "
-                                           "(239.6 MB per launch), scaled by bytes streamed",
+                                           "(239.5 MB per launch), scaled by bytes streamed",
                          "bytes_per_launch": upgate_bytes, "launch_ms": upgate_ms},
             "step_roofline": {"bytes_per_step_this_gpu": step_bytes, "achieved": step_bytes / (ms_per_step * 1e-3) / 1e9,
                               "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak_gbs, "unit": "GB/s"},
