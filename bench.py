@@ -178,7 +178,15 @@ def run_ours(args) -> None:
     tilert_b200.tilert_init(local)
     lib = tilert_b200.lib()
 
-    a = full_layer_args(max_seq_len=CACHE_LEN)
+    # --tokens 4 --cache-rows 16384: the speculative-decoding verify step (four rows per pass) instead
+    # of the headline workload; one GPU only (multi-token expert reductions are per-token launches)
+    S, cache_len = args.tokens, args.cache_rows
+    if S > 1 and world > 1:
+        raise SystemExit("--tokens > 1 runs on one GPU")
+    workload = WORKLOAD if (S, cache_len) == (1, CACHE_LEN) else (
+        f"C4-style verify step: one full-shape DeepSeek-V3.2 MoE decoder layer, batch 1, {S} tokens/step, "
+        f"{cache_len}-row latent KV cache, FP8 e4m3 weights with 128x128 block scales")
+    a = full_layer_args(max_seq_len=cache_len)
     comm = None
     if world > 1:
         from tilert_b200.comm import Comm
@@ -188,19 +196,21 @@ def run_ours(args) -> None:
     weights = L.LayerWeights(a, sd, 0, dev, world, rank)
     del sd
     torch.cuda.empty_cache()
-    layer = L.DecoderLayer(a, weights, dev, CACHE_LEN, 1, world, None if comm is None else comm.handle)
+    layer = L.DecoderLayer(a, weights, dev, cache_len, S, world, None if comm is None else comm.handle)
+    if args.mla_split:
+        layer.mla_split = args.mla_split
     g = torch.Generator(device=dev).manual_seed(2)
     for t in (layer.kv_cache, layer.pe_cache, layer.ki_cache):
         t.copy_(torch.randn(t.shape, generator=g, dtype=torch.float32, device=dev).to(torch.bfloat16))
-    layer.forced_scores = forced_scores(a.n_routed_experts, a.n_activated_experts).to(dev)
-    x_host = torch.randn(1, 1, a.dim, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).pin_memory()
-    out_host = torch.empty(1, 1, a.dim, dtype=torch.bfloat16).pin_memory()
+    layer.forced_scores = forced_scores(a.n_routed_experts, a.n_activated_experts).expand(1, S, -1).contiguous().to(dev)
+    x_host = torch.randn(1, S, a.dim, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).pin_memory()
+    out_host = torch.empty(1, S, a.dim, dtype=torch.bfloat16).pin_memory()
     x = x_host.to(dev)
-    cur = torch.tensor([CACHE_LEN - 1], dtype=torch.int32, device=dev)
-    freqs = L.precompute_freqs(a)[CACHE_LEN - 1: CACHE_LEN].contiguous().to(dev)
+    cur = torch.tensor([cache_len - S], dtype=torch.int32, device=dev)
+    freqs = L.precompute_freqs(a)[cache_len - S: cache_len].contiguous().to(dev)
 
     def step():
-        return layer.forward(x, cur, freqs, CACHE_LEN)
+        return layer.forward(x, cur, freqs, cache_len)
 
     # warm-up outside capture, then capture one step in a CUDA graph
     step()
@@ -336,18 +346,18 @@ def run_ours(args) -> None:
     if rank == 0:
         ms_per_step = dev_ms / args.steps
         step_bytes = weights.weight_bytes(a) + a.index_topk * (a.kv_lora_rank + a.qk_rope_head_dim) * 2 \
-            + CACHE_LEN * a.index_head_dim * 2
+            + cache_len * a.index_head_dim * 2
         achieved = upgate_bytes / (upgate_ms * 1e-3) / 1e9
         line = {
-            "metric": METRIC, "value": 1000.0 / ms_per_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "metric": METRIC, "value": 1000.0 * S / ms_per_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
             "dtype": "fp8_e4m3 (weights and activations as two e4m3 terms), f32 accumulate", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "parallelism": f"tp{world}", "cache_rows": CACHE_LEN,
+            "config": {"workload": workload, "parallelism": f"tp{world}", "cache_rows": cache_len, "tokens_per_step": S,
                        "l2": "256 MB buffer written before every timed step (untimed); per-step weights (>=75 MB "
                              "per GPU) are streamed with an evict-first policy",
                        "timing": "CUDA events around each CUDA-graph replay of the step, summed over steps, max over ranks"},
-            "e2e": {"value": args.steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
+            "e2e": {"value": args.steps * S / e2e_s, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2},
             "gpu_launches": int(launches_per_step * args.steps),
             "launches_per_step": int(launches_per_step),
@@ -362,7 +372,11 @@ def run_ours(args) -> None:
                               "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak_gbs, "unit": "GB/s"},
             "device_status": int(status),
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if S > 1:
+            # every row is verified; on average `accept` of them are emitted per step
+            line["speculative"] = {"rows_per_step": S, "assumed_mean_accepted": 3.2,
+                                   "emitted_tokens_per_s": 1000.0 * min(3.2, S) / ms_per_step}
+        if world == 1 and S == 1 and not args.no_cpu_baseline:
             try:
                 dt, desc = cpu_reference_steps(2, 1)
                 line["cpu_baseline"] = {"value": 1.0 / dt, "unit": UNIT, **desc}
@@ -461,6 +475,10 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=1, choices=[1, 2, 4],
+                    help="rows per step (4 = the speculative-decoding verify step); default 1, the headline workload")
+    ap.add_argument("--cache-rows", type=int, default=CACHE_LEN, help="rows of the latent caches (context length)")
+    ap.add_argument("--mla-split", type=int, default=0, help="keys per attention split (multiple of 64); 0 = the layer's choice")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: no clock-sampling loop, no CPU baseline")

@@ -271,6 +271,23 @@ int tilert_sample_op(TbContext* ctx, const float* logits, long long logits_strid
                      unsigned long long step_value, int* token_out, float* token_logprob_out, float* topn_logprob_out,
                      int* topn_index_out, void* stream);
 
+/* ---- greedy token over a vocabulary split across ranks ----------------------------------- */
+
+/* The arg-max that follows rmsnorm_head_proj_op when every rank holds vocab / world rows of the head
+ * (the reference keeps LOGITS_OUT as f32[1, 4, vocab / 8] per device and leaves PREDICTED_TOKENS,
+ * tilert/models/deepseek_v3_2/modules/end2end.py:617-651, temp_var_indices.py:15-76; the exchange
+ * itself is inside its native library).  Every rank takes the arg-max of its slice, stores the
+ * (value, global index) pair into every rank's receive slot over peer memory and, once all ranks
+ * have arrived (bounded wait, status word on time-out), picks the largest value, lowest index on ties.
+ * It is one call in the communicator's sequence, like a fused all-reduce: every rank must issue it
+ * at the same point of its stream.
+ *
+ *   logits [tokens, logits_stride] f32, of which n_local entries per row are this rank's slice,
+ *   entry 0 being global index index_offset; tokens 1..4; comm NULL or of world 1: local arg-max only;
+ *   token_out [tokens] int64; value_out [tokens] f32 or NULL. */
+int tilert_argmax_exchange_op(TbContext* ctx, const float* logits, long long logits_stride, int tokens, int n_local,
+                              int index_offset, TbComm* comm, long long* token_out, float* value_out, void* stream);
+
 /* ---- allocation-free product ------------------------------------------------------------ */
 
 /* No counterpart in the reference.  out[t, :] = W . x[t, :] (+ residual[t, :]) with the same FP8

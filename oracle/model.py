@@ -81,15 +81,19 @@ def _fp8_linear(gen, n, k, std, out, key):
 
 
 def random_state_dict(args: Args, seed: int = 0, std: float = 0.02,
-                      expert_ids: list[int] | None = None) -> dict[str, torch.Tensor]:
+                      expert_ids: list[int] | None = None, with_mtp: bool = False) -> dict[str, torch.Tensor]:
     """HF-keyed random checkpoint: N(0, std) -> e4m3 + 128x128 f32 scales, norm gains 1,
     router bias 0.  ``expert_ids`` limits which routed experts are materialised (the full
-    layer has 256 of them; a one-step check touches 8)."""
+    layer has 256 of them; a one-step check touches 8).  ``with_mtp`` appends the multi-token
+    prediction layer under ``model.layers.{n_layers}`` (an MoE layer plus ``enorm``, ``hnorm``,
+    ``eh_proj`` and ``shared_head.norm``; embedding and head are the main model's), drawn after
+    everything else so that the other tensors do not depend on the switch."""
     gen = torch.Generator().manual_seed(seed)
     sd: dict[str, torch.Tensor] = {}
     a = args
     sd["model.embed_tokens.weight"] = (torch.randn(a.vocab_size, a.dim, generator=gen, dtype=torch.float32) * std).to(BF16)
-    for li in range(a.n_layers):
+
+    def layer(li: int, dense: bool) -> None:
         p = f"model.layers.{li}"
         sd[f"{p}.input_layernorm.weight"] = torch.ones(a.dim, dtype=torch.float32)
         sd[f"{p}.post_attention_layernorm.weight"] = torch.ones(a.dim, dtype=torch.float32)
@@ -110,7 +114,7 @@ def random_state_dict(args: Args, seed: int = 0, std: float = 0.02,
         sd[f"{at}.indexer.weights_proj.weight"] = (
             torch.randn(a.index_n_heads, a.dim, generator=gen, dtype=torch.float32) * std).to(BF16)
         m = f"{p}.mlp"
-        if li < a.n_dense_layers:
+        if dense:
             _fp8_linear(gen, a.inter_dim, a.dim, std, sd, f"{m}.gate_proj")
             _fp8_linear(gen, a.inter_dim, a.dim, std, sd, f"{m}.up_proj")
             _fp8_linear(gen, a.dim, a.inter_dim, std, sd, f"{m}.down_proj")
@@ -123,8 +127,18 @@ def random_state_dict(args: Args, seed: int = 0, std: float = 0.02,
                 _fp8_linear(gen, a.moe_inter_dim, a.dim, std, sd, f"{m}.{nm}.gate_proj")
                 _fp8_linear(gen, a.moe_inter_dim, a.dim, std, sd, f"{m}.{nm}.up_proj")
                 _fp8_linear(gen, a.dim, a.moe_inter_dim, std, sd, f"{m}.{nm}.down_proj")
+
+    for li in range(a.n_layers):
+        layer(li, li < a.n_dense_layers)
     sd["model.norm.weight"] = torch.ones(a.dim, dtype=torch.float32)
     sd["lm_head.weight"] = (torch.randn(a.vocab_size, a.dim, generator=gen, dtype=torch.float32) * std).to(BF16)
+    if with_mtp:
+        p = f"model.layers.{a.n_layers}"
+        layer(a.n_layers, False)
+        sd[f"{p}.enorm.weight"] = torch.ones(a.dim, dtype=torch.float32)
+        sd[f"{p}.hnorm.weight"] = torch.ones(a.dim, dtype=torch.float32)
+        sd[f"{p}.eh_proj.weight"] = (torch.randn(a.dim, 2 * a.dim, generator=gen, dtype=torch.float32) * std).to(BF16)
+        sd[f"{p}.shared_head.norm.weight"] = torch.ones(a.dim, dtype=torch.float32)
     return sd
 
 
@@ -283,3 +297,104 @@ class Model:
             toks.append(nxt)
             lgs.append(lg)
         return toks, lgs
+
+
+class MtpModel(Model):
+    """Greedy speculative decoding with the multi-token-prediction layer drafting three tokens.
+
+    The reference runs this inside its native library (``dsa_mtp_e2e_show_hands``); Python only
+    sees the interface: a step takes four draft tokens at the current position and leaves
+    ``PREDICTED_TOKENS``, ``ACCEPTED_TOKENS`` (1..4 of them) and ``NEXT_DRAFT_TOKENS``
+    (tilert/models/deepseek_v3_2/modules/end2end.py:598-651), and the host loop advances the position
+    by the accepted count (generator.py:336-375).  The rule inside is not stated anywhere in the
+    reference, so the standard one is used and **parity is unpinned** for it:
+
+    * ``draft[0]`` is the last known token, ``draft[1:4]`` are guesses.  The main model runs the four
+      tokens at positions ``p .. p+3`` in one pass; ``predicted[j]`` is the arg-max after row ``j``.
+    * accepted count ``n`` = 1 + the number of leading guesses with ``draft[j+1] == predicted[j]``;
+      ``predicted[:n]`` are emitted.
+    * The prediction layer pairs the hidden state of position ``q`` (the last block's output, before
+      the final norm) with the embedding of the token at ``q+1``: ``eh_proj([enorm(e), hnorm(h)])``
+      -> one MoE decoder layer with its own caches -> ``shared_head.norm`` -> the main head
+      (modules/mtp_preprocess.py:197-229, modules/mtp.py:28-50).  One four-row pass at ``p .. p+3``
+      with the tokens ``predicted[0:4]`` yields guess 1 from row ``n-1``; two single-row passes at
+      ``p+n`` and ``p+n+1`` chain the layer's own hidden state and the previous guess into guesses 2, 3.
+    * ``next_draft = [predicted[n-1], guess 1, guess 2, guess 3]``.  Rows written past ``p+n-1`` by
+      either model hold rejected tokens; the next step starts at ``p+n`` and rewrites them first.
+    """
+
+    N_TOKENS = 4
+
+    def __init__(self, args: Args, sd: dict[str, torch.Tensor], cache_len: int | None = None):
+        super().__init__(args, sd, cache_len)
+        p = f"model.layers.{args.n_layers}"
+        self.mtp_w = LayerWeights(args, sd, args.n_layers)
+        self.mtp_cache = Caches(args, cache_len or args.max_seq_len)
+        self.enorm, self.hnorm = sd[f"{p}.enorm.weight"], sd[f"{p}.hnorm.weight"]
+        self.w_eh = sd[f"{p}.eh_proj.weight"]
+        self.mtp_norm = sd[f"{p}.shared_head.norm.weight"]
+
+    def main_pass(self, tokens: list[int], pos: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """The main model over ``tokens`` at ``pos ..``: (hidden [1, S, dim] bf16, logits [S, vocab] f32)."""
+        x = self.embed[torch.tensor(tokens)].view(1, len(tokens), -1)
+        for w, c in zip(self.layers, self.caches):
+            x = layer_step(self.args, w, c, x, pos, self.freqs_cis)
+        return x, ops.rmsnorm_head_proj(x, self.final_norm, self.head, self.args.eps).view(len(tokens), -1)
+
+    def mtp_pass(self, next_tokens: list[int], h: torch.Tensor, pos: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """The prediction layer over rows at ``pos ..``: row j pairs ``h[:, j]`` with the embedding of
+        ``next_tokens[j]``.  Returns (its hidden [1, S, dim] bf16, logits [S, vocab] f32)."""
+        e = self.embed[torch.tensor(next_tokens)].view(1, len(next_tokens), -1)
+        _, _, x = ops.mtp_preprocess(e, h, self.enorm, self.hnorm, self.w_eh, self.args.eps)
+        x = layer_step(self.args, self.mtp_w, self.mtp_cache, x, pos, self.freqs_cis)
+        return x, ops.rmsnorm_head_proj(x, self.mtp_norm, self.head, self.args.eps).view(len(next_tokens), -1)
+
+    def prefill_chunk(self, tokens: list[int], extra_token: int) -> None:
+        """Four prompt tokens at the current position through both models; ``extra_token`` is the prompt
+        token that follows the chunk (generator.py:297-328).  Does not move the position."""
+        h, _ = self.main_pass(tokens, self.pos)
+        self.mtp_pass(tokens[1:] + [extra_token], h, self.pos)
+
+    def verify_step(self, draft: list[int]) -> dict:
+        """One speculative step at the current position; advances it by the accepted count."""
+        n_tok, p = self.N_TOKENS, self.pos
+        assert len(draft) == n_tok
+        h, logits = self.main_pass(draft, p)
+        predicted = [int(t) for t in torch.argmax(logits, dim=-1)]
+        n = 1
+        while n < n_tok and draft[n] == predicted[n - 1]:
+            n += 1
+        mh, mlog = self.mtp_pass(predicted, h, p)
+        guesses, glogits = [int(torch.argmax(mlog[n - 1]))], [mlog[n - 1]]
+        hh = mh[:, n - 1: n]
+        for i in range(1, n_tok - 1):
+            hh, gl = self.mtp_pass([guesses[-1]], hh, p + n - 1 + i)
+            guesses.append(int(torch.argmax(gl[0])))
+            glogits.append(gl[0])
+        self.pos = p + n
+        return {"predicted": predicted, "n_accepted": n, "next_draft": [predicted[n - 1]] + guesses,
+                "logits": logits, "guess_logits": torch.stack(glogits)}
+
+    def generate_mtp(self, prompt: list[int], n_new: int) -> tuple[list[int], list[int]]:
+        """Chunked prefill, then speculative steps until ``n_new`` tokens are out
+        (generator.py:267-417).  Returns (tokens, accepted count of every step)."""
+        n_tok, plen = self.N_TOKENS, len(prompt)
+        self.pos = 0
+        while self.pos < plen - 1:
+            end = min(self.pos + n_tok, plen)
+            chunk = prompt[self.pos: end]
+            valid = len(chunk)
+            chunk = chunk + [chunk[-1]] * (n_tok - valid)
+            extra = prompt[self.pos + n_tok] if self.pos + n_tok < plen else prompt[end - 1]
+            self.prefill_chunk(chunk, extra)
+            self.pos += valid
+        self.pos = plen - 1
+        draft = [prompt[-1]] * n_tok
+        out: list[int] = []
+        counts: list[int] = []
+        while len(out) < n_new:
+            r = self.verify_step(draft)
+            out += r["predicted"][: r["n_accepted"]]
+            counts.append(r["n_accepted"])
+            draft = r["next_draft"]
+        return out[:n_new], counts

@@ -3,7 +3,8 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 tests/multi_gpu_check.py
 
 Every rank runs its shard of both toy layers (heads / N, expert intermediate / N) with the fused
-peer-memory all-reduce; every rank's output must match the CPU oracle's unsharded layer (cosine
+peer-memory all-reduce, then the whole toy model with the vocabulary head split across ranks and the
+greedy token exchanged over peer memory; every rank's output must match the CPU oracle's unsharded layer (cosine
 >= 0.999, rel-L2 <= 2e-2) and all ranks must hold bit-identical results.  Several steps are run
 back to back so that both halves of the receive buffers and the epoch bookkeeping are exercised.
 """
@@ -71,6 +72,29 @@ def main() -> int:
                           flush=True)
                 if not (cos >= 0.999 and l2 <= 2e-2 and same):
                     failures.append((li, tokens, step, cos, l2, same))
+    # The whole toy model with the vocabulary head split across ranks: the greedy token comes from the
+    # (value, index) exchange over peer memory and must be the arg-max of the gathered logits on every
+    # rank; graph replay is on, so the exchange's device-resident epoch is exercised too.
+    from tilert_b200.models.deepseek_v3_2.model import DsaModel
+    toks = torch.randint(0, a.vocab_size, (10,), generator=torch.Generator().manual_seed(3)).tolist()
+    dm = DsaModel(margs, sd, dev, cache_len=256, world=world, rank=rank, comm=comm.handle)
+    ref = om.Model(a, sd, cache_len=256)
+    for pos, t in enumerate(toks):
+        dm.forward(t, pos)
+        torch.cuda.synchronize()
+        _, rl = ref.step(t)
+        parts = [torch.empty_like(dm.logits) for _ in range(world)]
+        dist.all_gather(parts, dm.logits)
+        full = torch.cat([p.view(-1) for p in parts]).float().cpu()
+        l2 = (torch.norm(rl.float() - full) / torch.norm(rl.float())).item()
+        picked = [torch.empty_like(dm.token_out) for _ in range(world)]
+        dist.all_gather(picked, dm.token_out)
+        picked = [int(p) for p in picked]
+        expected = int(torch.argmax(full))
+        if rank == 0:
+            print(f"model pos {pos}: logits rel_l2 {l2:.3e} token {picked} expected {expected}", flush=True)
+        if not (l2 <= 2e-2 and all(p == expected for p in picked)):
+            failures.append(("model", pos, l2, picked, expected))
     status = tilert_b200.device_status(local)
     if status != 0:
         failures.append(("device_status", status))

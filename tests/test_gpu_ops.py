@@ -452,6 +452,19 @@ def test_router_and_expert_path(env):
     rdown = oo.expert_down(hid.cpu(), dl, probs.cpu())
     close("experts.down+res", (rdown.float() + h.float()).to(BF16), out)
 
+    # the same pair through the reference's dispatcher names and argument order: identical bytes; the down
+    # product rebuilds the slot table from the routed indices and weights the reference passes
+    from tilert_b200 import torch_ops
+
+    torch_ops.register()
+    hid2, probs2, eidx2, out2 = torch.zeros_like(hid), torch.zeros_like(probs), torch.zeros_like(eidx), torch.zeros_like(out)
+    torch.ops.tilert.expert_select_up_gate_silu_op(hn, scores, gw.router_bias, gw.w_gu, hid2, probs2, eidx2, None,
+                                                   "deepseek_v3_2", "fp8mma", 1, 1, a.route_scale)
+    assert torch.equal(hid, hid2) and torch.equal(eidx, eidx2) and torch.equal(probs, probs2)
+    torch.ops.tilert.expert_down_allreduce_op(hid2, gw.w_down, None, eidx2, probs2, h.cuda(), 0, out2, None,
+                                              "deepseek_v3_2", "fp8mma")
+    assert torch.equal(out, out2)
+
 
 def test_grouped_routing_full_shape(env):
     """256 experts in 8 groups, 4 groups kept, top-8 -- checked through the up/gate operator with a
@@ -589,6 +602,22 @@ def test_sampling_matches_the_restated_rule(env):
         assert abs(int(one[0]) - expect) <= 1
         seen.add(int(one[0]))
     assert len(seen) >= 5
+
+
+def test_argmax_exchange_single_rank_is_exact(env):
+    """Without a communicator the exchange operator is a plain arg-max: exact, lowest index on ties,
+    offset added (the cross-rank part is checked by the multi-GPU run)."""
+    ops = env["ops"]
+    g = torch.Generator().manual_seed(91)
+    for vocab, tokens in ((4096, 1), (129280, 4), (1000, 2)):
+        logits = torch.randn(1, tokens, vocab, generator=g, dtype=F32)
+        logits[0, 0, 17] = logits[0, 0, vocab - 5] = 9.5          # a tie at the maximum
+        tok = torch.zeros(tokens, dtype=torch.int64, device="cuda")
+        val = torch.zeros(tokens, dtype=F32, device="cuda")
+        ops.argmax_exchange(logits.cuda(), 1000, tok, val)
+        ref = torch.argmax(logits[0], dim=-1)
+        assert tok.cpu().tolist() == (ref + 1000).tolist() and int(tok[0]) == 1017
+        assert torch.equal(val.cpu(), logits[0].max(dim=-1).values)
 
 
 def test_bad_arguments_raise(env):

@@ -16,6 +16,7 @@
 #include "sparse_mla.cuh"
 #include "sampler.cuh"
 #include "wstream_gemv.cuh"
+#include "argmax_exchange.cuh"
 
 using namespace tb;
 
@@ -103,14 +104,16 @@ size_t comm_state_offset(int world, int max_rows) {
   return (b + 255) / 256 * 256;
 }
 
-// Short rows (few k blocks per tile) with many tiles: whole tiles per CTA when the busiest CTA then
-// has at most 20 % more than the average; otherwise equal shares of units with split-tile fix-up.
+// Whole tiles per CTA when that balances well enough -- short rows (few k blocks per tile) with many
+// tiles when the busiest CTA then has at most 20 % more than the average, any row length at 4 % --
+// otherwise equal shares of units with split-tile fix-up.
 void set_partition(GemvParams& p, int grid) {
   const int max_tiles = (p.n_tiles + grid - 1) / grid;
-  p.whole_tiles = (p.n_kb <= 16 && p.n_tiles >= grid / 2 &&
-                   static_cast<long long>(max_tiles) * grid * 5 <= static_cast<long long>(p.n_tiles) * 6)
-                      ? 1
-                      : 0;
+  const long long busiest = static_cast<long long>(max_tiles) * grid, all = p.n_tiles;
+  const bool short_rows = p.n_kb <= 16 && p.n_tiles >= grid / 2 && busiest * 5 <= all * 6;
+  // Long rows too when whole tiles balance within 4 %: the fix-up of split tiles costs more than that.
+  const bool balanced = p.n_tiles >= grid / 2 && busiest * 25 <= all * 26;
+  p.whole_tiles = (short_rows || balanced) ? 1 : 0;
 }
 
 int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
@@ -1049,6 +1052,39 @@ extern "C" int tilert_sample_op(TbContext* ctx, const float* logits, long long l
   p.topn_logprob = topn_logprob_out;
   p.topn_index = topn_index_out;
   TB_CUDA(launch(sample_kernel, dim3(tokens), dim3(kTopkThreads), 0, static_cast<cudaStream_t>(stream), p));
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+// ------------------------------------------------------------------ greedy token across ranks
+extern "C" int tilert_argmax_exchange_op(TbContext* ctx, const float* logits, long long logits_stride, int tokens,
+                                         int n_local, int index_offset, TbComm* comm, long long* token_out,
+                                         float* value_out, void* stream) {
+  TB_REQUIRE(ctx != nullptr && logits != nullptr && token_out != nullptr);
+  TB_REQUIRE(tokens >= 1 && tokens <= 4 && n_local >= 1 && logits_stride >= n_local && index_offset >= 0);
+  ArgmaxParams p{};
+  p.logits = logits;
+  p.stride = logits_stride;
+  p.n_local = n_local;
+  p.index_offset = index_offset;
+  p.n_tokens = tokens;
+  p.token_out = token_out;
+  p.value_out = value_out;
+  p.status = ctx->status;
+  p.ar.world = 1;
+  if (comm != nullptr && comm->world > 1) {
+    TB_REQUIRE(comm->max_rows >= 2);
+    p.slot_rows = comm->max_rows;
+    p.ar.world = comm->world;
+    p.ar.rank = comm->rank;
+    const size_t off = comm_state_offset(comm->world, comm->max_rows);
+    for (int r = 0; r < comm->world; ++r) {
+      p.ar.recv[r] = reinterpret_cast<float*>(comm->buffers[r]);
+      p.ar.state[r] = reinterpret_cast<AllReduceState*>(reinterpret_cast<uint8_t*>(comm->buffers[r]) + off);
+    }
+  }
+  TB_CUDA(launch(argmax_exchange_kernel, dim3(1), dim3(kArgmaxThreads), 0, static_cast<cudaStream_t>(stream), p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;

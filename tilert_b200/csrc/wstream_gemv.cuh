@@ -41,14 +41,43 @@ struct OutRegion {
 };
 
 // Device-resident state of one rank's all-reduce endpoint.  Everything a call needs (which half
-// of the receive buffer to use, what the arrival counter must reach) is derived from `epoch` on
-// the device, so a captured CUDA graph can be replayed.
+// of the receive buffer to use, what the arrival counters must reach) is derived from the counters
+// on the device, so a captured CUDA graph can be replayed.  One counter per source rank: a call is
+// complete here when EVERY source has added kArUnit for it (spread over the source's CTAs), so a
+// fast rank's next call can never stand in for a slow rank's missing arrival.
 struct AllReduceState {
-  unsigned long long epoch;         // completed all-reduce calls on this rank
-  unsigned long long arrive;        // incremented once per rank per call, by every rank (peer-written)
-  unsigned int local_arrive;        // CTAs of this rank that have pushed their partials (self-resetting)
-  unsigned int local_done;          // CTAs of this rank that have finished the call (self-resetting)
+  unsigned long long arrive_from[8];  // peer-written: arrive_from[r] is added to by rank r only
 };
+constexpr unsigned long long kArUnit = 1ull << 20;
+
+// Completed exchanges on this endpoint: this rank's own counter on itself.  When a launch starts
+// (its predecessor has completed) every earlier call of this rank is whole, so the counter is an
+// exact multiple of kArUnit.
+__device__ __forceinline__ unsigned long long ar_epoch_of(const AllReduceState* self, int rank) {
+  return *reinterpret_cast<const volatile unsigned long long*>(&self->arrive_from[rank]) / kArUnit;
+}
+
+// Bounded wait until every source rank has arrived for call `epoch`; then an acquire fence orders
+// the reads of the receive slots behind the counters.  Returns false when the budget ran out.
+__device__ __forceinline__ bool ar_wait_all(const AllReduceState* self, int world, unsigned long long epoch) {
+  const unsigned long long target = (epoch + 1ull) * kArUnit;
+  const long long t0 = clock64();
+  for (;;) {
+    bool done = true;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      if (r < world) {
+        unsigned long long seen;
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(&self->arrive_from[r]) : "memory");
+        done = done && seen >= target;
+      }
+    }
+    if (done) break;
+    if (clock64() - t0 > kWaitBudgetCycles) return false;
+  }
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
+  return true;
+}
 
 struct AllReduce {
   int world;                  // 1 = off
@@ -102,7 +131,7 @@ struct GemvParams {
   int w_kb_per_tile;
   int tiles_per_xseg;
   int n_tokens;
-  int whole_tiles;       // 1: CTAs take whole row tiles (set by the host when that balances within 20 %)
+  int whole_tiles;       // 1: CTAs take whole row tiles (set by the host when that balances well enough)
   int only_token;        // >= 0: store only this token's results (per-token expert lists)
   int cols_per_token;
   int epi;
@@ -746,7 +775,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     // shared memory; group 0 finishes the tile.
     const int eg = warp / kGemvGroupWarps, gw = warp % kGemvGroupWarps;
     unsigned long long ar_epoch = 0;
-    if (p.ar.world > 1) ar_epoch = *reinterpret_cast<volatile unsigned long long*>(&p.ar.state[p.ar.rank]->epoch);
+    if (p.ar.world > 1) ar_epoch = ar_epoch_of(p.ar.state[p.ar.rank], p.ar.rank);
     const int ar_half = static_cast<int>(ar_epoch & 1ull);
     const uint32_t lane_base = static_cast<uint32_t>(gw * 32) << 16;
     if (p.x_mode == X_BF16 && units > static_cast<long long>(kGemvStages) * grid) {
@@ -917,31 +946,22 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     if (p.ar.world > 1 && eg == 0) {
       // ---- one-shot all-reduce over peer memory, fused behind the streaming loop (group 0) ----
       AllReduceState* self = p.ar.state[p.ar.rank];
-      // 1. this CTA's peer stores are done: publish them.  The last CTA of the rank to get here
-      //    tells every rank (itself included) that this rank's partial has landed.
-      __threadfence_system();
+      // 1. this CTA's peer stores are done (the barrier collects the group's; the fence below
+      //    orders them, cumulatively, before the counts): tell every rank, itself included.  The CTAs
+      //    of a rank add kArUnit between them to the rank's counter on every endpoint.
       asm volatile("bar.sync 1, %0;" ::"n"(kGemvGroupThreads) : "memory");
       if (threadIdx.x == 0) {
-        const unsigned int prev = atomicAdd(&self->local_arrive, 1u);
-        if (prev == static_cast<unsigned int>(grid) - 1u) {
-          self->local_arrive = 0u;
-          __threadfence_system();
-          for (int pr = 0; pr < p.ar.world; ++pr)
-            asm volatile("red.release.sys.global.add.u64 [%0], 1;" ::"l"(&p.ar.state[pr]->arrive) : "memory");
-        }
-        // 2. wait (bounded) until every rank has arrived for this call.
-        const unsigned long long target = (ar_epoch + 1ull) * static_cast<unsigned long long>(p.ar.world);
-        const unsigned long long t0 = globaltimer_ns();
-        unsigned long long seen = 0;
-        while (ok) {
-          asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(&self->arrive) : "memory");
-          if (seen >= target) break;
-          if (globaltimer_ns() - t0 > kWaitBudgetNs) {
-            set_status(p.status, ST_PEER_TIMEOUT);
-            *cta_error = 1;
-            break;
-          }
-          __nanosleep(32);
+        const unsigned long long share = kArUnit / static_cast<unsigned long long>(grid);
+        const unsigned long long mine_w = cta < grid - 1 ? share : kArUnit - share * static_cast<unsigned long long>(grid - 1);
+        // one system-scope fence for all the counts (a release per count would wait for the
+        // previous count's round trip over the link)
+        __threadfence_system();
+        for (int pr = 0; pr < p.ar.world; ++pr)
+          asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(&p.ar.state[pr]->arrive_from[p.ar.rank]), "l"(mine_w) : "memory");
+        // 2. wait (bounded) until every CTA of every rank has arrived for this call.
+        if (ok && !ar_wait_all(self, p.ar.world, ar_epoch)) {
+          set_status(p.status, ST_PEER_TIMEOUT);
+          *cta_error = 1;
         }
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kGemvGroupThreads) : "memory");
@@ -957,16 +977,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           for (int r = 0; r < p.ar.world; ++r)
             v += __ldcg(&mine[((static_cast<long long>(ar_half) * p.ar.world + r) * 4 + tok) * p.n_rows + row]);
           gemv_store(p, row, tok, v);
-        }
-      }
-      // 4. the last CTA to finish opens the next call (flips the buffer half).
-      asm volatile("bar.sync 1, %0;" ::"n"(kGemvGroupThreads) : "memory");
-      if (threadIdx.x == 0) {
-        const unsigned int prev = atomicAdd(&self->local_done, 1u);
-        if (prev == static_cast<unsigned int>(grid) - 1u) {
-          self->local_done = 0u;
-          __threadfence();
-          *reinterpret_cast<volatile unsigned long long*>(&self->epoch) = ar_epoch + 1ull;
         }
       }
     }

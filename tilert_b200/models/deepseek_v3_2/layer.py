@@ -168,6 +168,7 @@ class DecoderLayer:
         self.sel = torch.full((1, s, a.index_topk), -1, dtype=I32, device=dev)
         self.q_lat = z(1, s, self.hl, a.kv_lora_rank)
         self.o_lat = z(1, s, self.hl, a.kv_lora_rank)
+        self.mla_split = 64  # keys per attention split (a multiple of 64): splits x groups of 16 heads x tokens CTAs
         self.n_splits = (a.index_topk + 63) // 64
         self.o_acc = z(1, s, self.hl, self.n_splits, a.kv_lora_rank, dtype=F32)
         self.lse = z(1, s, self.hl, dtype=F32)
@@ -215,7 +216,7 @@ class DecoderLayer:
         if self.injected_sel is not None:
             v(self.sel).copy_(self.injected_sel)
         ops.flash_sparse_mla(v(self.q_lat), v(self.q_pe), self.kv_cache, self.pe_cache, v(self.sel), cur_pos,
-                             v(self.o_lat), softmax_scale=self.scale, split_size=64, out_acc=self.o_acc,
+                             v(self.o_lat), softmax_scale=self.scale, split_size=self.mla_split, out_acc=self.o_acc,
                              lse=self.lse, lse_acc=self.lse_acc)
         ops.projo_wkvb(v(self.o_lat), w.w_v, None, v(self.o))
         ops.unproj_o_allreduce(v(self.o), w.w_o, None, x, 0, v(self.h), comm=self.comm)

@@ -20,7 +20,7 @@ class DsaModel:
     def __init__(self, args: ModelArgs, sd: dict[str, torch.Tensor], device="cuda", cache_len: int | None = None,
                  world: int = 1, rank: int = 0, comm: int | None = None, use_graph: bool = True):
         self.args, self.device = args, torch.device(device)
-        self.world, self.rank = world, rank
+        self.world, self.rank, self.comm = world, rank, comm
         dev = self.device
         self.cache_len = cache_len or args.max_seq_len
         self.embed = sd["model.embed_tokens.weight"].to(dev, BF16)
@@ -52,7 +52,11 @@ class DsaModel:
         for layer in self.layers:
             x = layer.forward(x, self.cur_pos, fr, n_keys)
         ops.rmsnorm_head_proj(x, self.final_norm, self.head, None, self.logits, eps=self.args.eps)
-        self.token_out.copy_(torch.argmax(self.logits.view(-1)))
+        if self.world > 1:
+            # every rank holds vocab / world rows of the head: exchange (value, index) pairs over peer memory
+            ops.argmax_exchange(self.logits, self.rank * self.logits.shape[-1], self.token_out, comm=self.comm)
+        else:
+            self.token_out.copy_(torch.argmax(self.logits.view(-1)))
         self.cur_pos += 1
 
     def _bucket(self, pos: int) -> int:

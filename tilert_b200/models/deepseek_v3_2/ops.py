@@ -286,6 +286,20 @@ def rmsnorm_head_proj(x, gamma, w, x_norm_out, logits_out, profile_logs=None, *,
                                                     w.shape[0], _p(x_norm_out), _p(logits_out), _stream()))
 
 
+def argmax_exchange(logits, index_offset, token_out, value_out=None, *, comm=None):
+    """Greedy token over a vocabulary split across ranks (the arg-max behind the reference's
+    ``PREDICTED_TOKENS``, modules/end2end.py:617-651): ``logits`` [..., S, vocab / world] f32 is this rank's
+    slice starting at global index ``index_offset``; ``token_out`` int64 [S] receives the same token on
+    every rank.  Without ``comm`` it is a local arg-max."""
+    _need(logits, F32, "logits")
+    _need(token_out, torch.int64, "token_out")
+    _need(value_out, F32, "value_out", optional=True)
+    tokens = logits.shape[-2]
+    _tb.check(_tb.lib().tilert_argmax_exchange_op(_ctx(logits), _p(logits), logits.stride(-2), tokens, logits.shape[-1],
+                                                  index_offset, None if comm is None else ctypes.c_void_p(comm),
+                                                  _p(token_out), _p(value_out), _stream()))
+
+
 # ------------------------------------------------------------- per-token vector operators
 def eh_proj_allreduce(vec_in_enorm, vec_in_hnorm, w, flag, hidden_out, profile_logs=None, *,
                       model_arch="deepseek_v3_2"):
