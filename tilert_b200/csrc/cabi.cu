@@ -601,7 +601,6 @@ extern "C" int tilert_expert_down_allreduce_op(TbContext* ctx, const void* vec, 
                                                void* out, TbComm* comm, void* stream) {
   TB_REQUIRE(ctx != nullptr && vec != nullptr && w_packed != nullptr && out != nullptr);
   TB_REQUIRE(inter % TB_KBLOCK == 0);
-  TB_REQUIRE(comm == nullptr || comm->world == 1 || tokens == 1);  // per-token launches share one reduction slot
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (slot_ids == nullptr) slot_ids = reinterpret_cast<const int*>(ctx->small);
   if (slot_w == nullptr) slot_w = reinterpret_cast<const float*>(ctx->small + 4096);
