@@ -1,7 +1,7 @@
 // Greedy token over a vocabulary that is split across ranks: every rank finds the arg-max of its
 // own slice of the f32 logits, pushes the (value, global index) pair into every rank's receive
 // slot with plain peer stores, and picks the best pair once all ranks have arrived -- the same
-// one-shot exchange (receive-buffer halves, arrival counter, bounded wait) as the all-reduce fused
+// one-shot exchange (receive-buffer halves, words tagged with the call number, bounded wait) as the all-reduce fused
 // into the streaming products (wstream_gemv.cuh), so it takes its place in the same call sequence.
 // Ties go to the lowest index, on one rank and between ranks.
 #pragma once
@@ -87,40 +87,46 @@ __global__ void __launch_bounds__(kArgmaxThreads, 1) argmax_exchange_kernel(cons
     }
     return;
   }
-  // ---- exchange: slot of rank r, token t = rows 0 (value) and 1 (index bits) of [half][r][t][slot_rows] ----
+  // ---- exchange: slot of rank r, token t = words 0 (value) and 1 (index bits) of [half][r][t][slot_rows],
+  //      each tagged with the call number like the all-reduce's partial sums ----
   if (threadIdx.x == 0) {
-    AllReduceState* self = p.ar.state[p.ar.rank];
-    const unsigned long long epoch = ar_epoch_of(self, p.ar.rank);
+    const unsigned long long epoch = ar_epoch_of(p.ar.state);
+    const uint32_t tag = ar_tag(epoch);
     const long long half = static_cast<long long>(epoch & 1ull);
     for (int t = 0; t < p.n_tokens; ++t) {
       const long long idx = ((half * p.ar.world + p.ar.rank) * 4 + t) * p.slot_rows;
       for (int pr = 0; pr < p.ar.world; ++pr) {
-        p.ar.recv[pr][idx] = s_best_val[t];
-        p.ar.recv[pr][idx + 1] = __int_as_float(s_best_idx[t]);
+        ar_push(&p.ar.recv[pr][idx], tag, s_best_val[t]);
+        ar_push(&p.ar.recv[pr][idx + 1], tag, __int_as_float(s_best_idx[t]));
       }
     }
-    __threadfence_system();
-    for (int pr = 0; pr < p.ar.world; ++pr)
-      asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(&p.ar.state[pr]->arrive_from[p.ar.rank]), "l"(kArUnit) : "memory");
-    const bool ok = ar_wait_all(self, p.ar.world, epoch);
-    if (!ok) set_status(p.status, ST_PEER_TIMEOUT);
-    if (ok) {
-      const float* mine = p.ar.recv[p.ar.rank];
-      for (int t = 0; t < p.n_tokens; ++t) {
-        float bv = -INFINITY;
-        int bi = 0x7fffffff;
-        for (int r = 0; r < p.ar.world; ++r) {
-          const long long idx = ((half * p.ar.world + r) * 4 + t) * p.slot_rows;
-          const float v = __ldcg(&mine[idx]);
-          const int i = __float_as_int(__ldcg(&mine[idx + 1]));
-          if (argmax_better(v, i, bv, bi)) {
-            bv = v;
-            bi = i;
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(&p.ar.state->calls), "l"(kArUnit) : "memory");
+    const unsigned long long* mine = p.ar.recv[p.ar.rank];
+    const long long t0 = clock64();
+    for (int t = 0; t < p.n_tokens; ++t) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int r = 0; r < p.ar.world; ++r) {
+        const long long idx = ((half * p.ar.world + r) * 4 + t) * p.slot_rows;
+        unsigned long long wv, wi;
+        for (;;) {
+          wv = ar_peek(&mine[idx]);
+          wi = ar_peek(&mine[idx + 1]);
+          if (static_cast<uint32_t>(wv >> 32) == tag && static_cast<uint32_t>(wi >> 32) == tag) break;
+          if (clock64() - t0 > kWaitBudgetCycles) {
+            set_status(p.status, ST_PEER_TIMEOUT);
+            return;
           }
         }
-        p.token_out[t] = bi;
-        if (p.value_out != nullptr) p.value_out[t] = bv;
+        const float v = __uint_as_float(static_cast<uint32_t>(wv));
+        const int i = static_cast<int>(static_cast<uint32_t>(wi));
+        if (argmax_better(v, i, bv, bi)) {
+          bv = v;
+          bi = i;
+        }
       }
+      p.token_out[t] = bi;
+      if (p.value_out != nullptr) p.value_out[t] = bv;
     }
   }
 }

@@ -99,8 +99,8 @@ struct TbComm {
 namespace {
 
 size_t comm_state_offset(int world, int max_rows) {
-  // [2 halves][world][4 tokens][max_rows] f32, then the endpoint state
-  size_t b = 2ull * world * 4 * max_rows * sizeof(float);
+  // [2 halves][world][4 tokens][max_rows] 64-bit words {call number, f32}, then the endpoint state
+  size_t b = 2ull * world * 4 * max_rows * sizeof(unsigned long long);
   return (b + 255) / 256 * 256;
 }
 
@@ -174,10 +174,8 @@ int set_comm(GemvParams& p, TbComm* comm, int n_rows) {
   p.ar.world = comm->world;
   p.ar.rank = comm->rank;
   const size_t off = comm_state_offset(comm->world, comm->max_rows);
-  for (int r = 0; r < comm->world; ++r) {
-    p.ar.recv[r] = reinterpret_cast<float*>(comm->buffers[r]);
-    p.ar.state[r] = reinterpret_cast<AllReduceState*>(reinterpret_cast<uint8_t*>(comm->buffers[r]) + off);
-  }
+  for (int r = 0; r < comm->world; ++r) p.ar.recv[r] = reinterpret_cast<unsigned long long*>(comm->buffers[r]);
+  p.ar.state = reinterpret_cast<AllReduceState*>(reinterpret_cast<uint8_t*>(comm->buffers[comm->rank]) + off);
   return TB_OK;
 }
 
@@ -1078,10 +1076,8 @@ extern "C" int tilert_argmax_exchange_op(TbContext* ctx, const float* logits, lo
     p.ar.world = comm->world;
     p.ar.rank = comm->rank;
     const size_t off = comm_state_offset(comm->world, comm->max_rows);
-    for (int r = 0; r < comm->world; ++r) {
-      p.ar.recv[r] = reinterpret_cast<float*>(comm->buffers[r]);
-      p.ar.state[r] = reinterpret_cast<AllReduceState*>(reinterpret_cast<uint8_t*>(comm->buffers[r]) + off);
-    }
+    for (int r = 0; r < comm->world; ++r) p.ar.recv[r] = reinterpret_cast<unsigned long long*>(comm->buffers[r]);
+    p.ar.state = reinterpret_cast<AllReduceState*>(reinterpret_cast<uint8_t*>(comm->buffers[comm->rank]) + off);
   }
   TB_CUDA(launch(argmax_exchange_kernel, dim3(1), dim3(kArgmaxThreads), 0, static_cast<cudaStream_t>(stream), p));
   ++g_launches;

@@ -40,51 +40,50 @@ struct OutRegion {
   const int* pos_ptr;        // optional device int: destination starts at token index *pos_ptr
 };
 
-// Device-resident state of one rank's all-reduce endpoint.  Everything a call needs (which half
-// of the receive buffer to use, what the arrival counters must reach) is derived from the counters
-// on the device, so a captured CUDA graph can be replayed.  One counter per source rank: a call is
-// complete here when EVERY source has added kArUnit for it (spread over the source's CTAs), so a
-// fast rank's next call can never stand in for a slow rank's missing arrival.
+// All-reduce endpoint of one rank.  A partial sum travels as one 64-bit word {call number, f32 bits}
+// written with a single store, so a word that carries the current call number IS the arrival of its
+// value: no fence, no counter and no second trip over the link between the data and a flag (a
+// naturally aligned 64-bit access is single-copy atomic).  The receive buffer has two halves used
+// by alternate calls: a rank can only start call n+2 after every rank has pushed call n+1, which a
+// rank does after it has finished reading call n, so a half is never overwritten while it is read.
+// The call number is device-resident -- every CTA of a launch adds its share of kArUnit to `calls`
+// after it has read it -- so nothing on the host changes between calls and a captured CUDA graph
+// can be replayed.
 struct AllReduceState {
-  unsigned long long arrive_from[8];  // peer-written: arrive_from[r] is added to by rank r only
+  unsigned long long calls;  // local only: kArUnit per completed exchange of this rank
 };
 constexpr unsigned long long kArUnit = 1ull << 20;
 
-// Completed exchanges on this endpoint: this rank's own counter on itself.  When a launch starts
-// (its predecessor has completed) every earlier call of this rank is whole, so the counter is an
-// exact multiple of kArUnit.
-__device__ __forceinline__ unsigned long long ar_epoch_of(const AllReduceState* self, int rank) {
-  return *reinterpret_cast<const volatile unsigned long long*>(&self->arrive_from[rank]) / kArUnit;
-}
-
-// Bounded wait until every source rank has arrived for call `epoch`; then an acquire fence orders
-// the reads of the receive slots behind the counters.  Returns false when the budget ran out.
-__device__ __forceinline__ bool ar_wait_all(const AllReduceState* self, int world, unsigned long long epoch) {
-  const unsigned long long target = (epoch + 1ull) * kArUnit;
-  const long long t0 = clock64();
-  for (;;) {
-    bool done = true;
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      if (r < world) {
-        unsigned long long seen;
-        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(&self->arrive_from[r]) : "memory");
-        done = done && seen >= target;
-      }
-    }
-    if (done) break;
-    if (clock64() - t0 > kWaitBudgetCycles) return false;
-  }
-  asm volatile("fence.acq_rel.sys;" ::: "memory");
-  return true;
-}
-
 struct AllReduce {
-  int world;                  // 1 = off
+  int world;                      // 1 = off
   int rank;
-  float* recv[8];             // recv[p]: rank p's receive buffer [2 halves][world][4 tokens][n_rows] f32
-  AllReduceState* state[8];   // state[p]: rank p's endpoint state (state[rank] is local memory)
+  unsigned long long* recv[8];    // recv[p]: rank p's receive buffer [2 halves][world][4 tokens][n_rows] words
+  AllReduceState* state;          // this rank's state (local memory)
 };
+
+// Completed exchanges on this endpoint.  When a launch starts (its predecessor has completed) every
+// earlier call is whole, and no CTA of this launch can complete the current one before all of them
+// have read the counter (each adds its share only afterwards).
+__device__ __forceinline__ unsigned long long ar_epoch_of(const AllReduceState* self) {
+  return *reinterpret_cast<const volatile unsigned long long*>(&self->calls) / kArUnit;
+}
+__device__ __forceinline__ uint32_t ar_tag(unsigned long long epoch) {
+  return static_cast<uint32_t>(epoch) + 1u;  // never the zero the buffers start with (wraps after 2^32 calls)
+}
+__device__ __forceinline__ void ar_push(unsigned long long* dst, uint32_t tag, float v) {
+  const unsigned long long word = (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(v);
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(word) : "memory");
+}
+__device__ __forceinline__ unsigned long long ar_peek(const unsigned long long* src) {
+  unsigned long long word;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(src) : "memory");
+  return word;
+}
+// Share of kArUnit that CTA `cta` of `grid` adds to the call counter.
+__device__ __forceinline__ unsigned long long ar_share(int cta, int grid) {
+  const unsigned long long share = kArUnit / static_cast<unsigned long long>(grid);
+  return cta < grid - 1 ? share : kArUnit - share * static_cast<unsigned long long>(grid - 1);
+}
 
 // Where the activations of a launch come from.
 enum XMode : int {
@@ -322,7 +321,7 @@ __device__ __forceinline__ void gemv_store(const GemvParams& p, int row, int tok
 // Final values of one weight row (8 accumulator columns) of row tile `tile`; the calling warp holds
 // rows 32*warp .. 32*warp+31 of the tile, one per lane.
 __device__ __forceinline__ void gemv_epilogue_row(const GemvParams& p, int tile, int warp, int lane,
-                                                  const float (&v)[8], int ar_half) {
+                                                  const float (&v)[8], unsigned long long ar_epoch) {
   const int row_in_tile = warp * 32 + lane;
   float val[8];
   int ntok;
@@ -357,8 +356,8 @@ __device__ __forceinline__ void gemv_epilogue_row(const GemvParams& p, int tile,
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
         if (t < ntok && t < p.n_tokens) {
-          const long long idx = ((static_cast<long long>(ar_half) * p.ar.world + p.ar.rank) * 4 + t) * p.n_rows + row;
-          for (int pr = 0; pr < p.ar.world; ++pr) p.ar.recv[pr][idx] = val[t];
+          const long long idx = ((static_cast<long long>(ar_epoch & 1ull) * p.ar.world + p.ar.rank) * 4 + t) * p.n_rows + row;
+          for (int pr = 0; pr < p.ar.world; ++pr) ar_push(&p.ar.recv[pr][idx], ar_tag(ar_epoch), val[t]);
         }
       }
     }
@@ -775,8 +774,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     // shared memory; group 0 finishes the tile.
     const int eg = warp / kGemvGroupWarps, gw = warp % kGemvGroupWarps;
     unsigned long long ar_epoch = 0;
-    if (p.ar.world > 1) ar_epoch = ar_epoch_of(p.ar.state[p.ar.rank], p.ar.rank);
-    const int ar_half = static_cast<int>(ar_epoch & 1ull);
+    if (p.ar.world > 1) ar_epoch = ar_epoch_of(p.ar.state);
     const uint32_t lane_base = static_cast<uint32_t>(gw * 32) << 16;
     if (p.x_mode == X_BF16 && units > static_cast<long long>(kGemvStages) * grid) {
       // (Skipped when no CTA has more units than ring slots: the converter warps cover those.)
@@ -847,7 +845,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           }
         }
         if (lane == 0) p.counters[t * 8 + gw] = 0;
-        gemv_epilogue_row(p, t, gw, lane, sum, ar_half);
+        gemv_epilogue_row(p, t, gw, lane, sum, ar_epoch);
       }
     };
 
@@ -867,7 +865,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         out[4] += m1.x; out[5] += m1.y; out[6] += m1.z; out[7] += m1.w;
         const int tile_u0 = t * p.n_kb, tile_u1 = tile_u0 + p.n_kb;
         if (u0 <= tile_u0 && u1 >= tile_u1) {
-          gemv_epilogue_row(p, t, gw, lane, out, ar_half);
+          gemv_epilogue_row(p, t, gw, lane, out, ar_epoch);
         } else {
           split_tile(t, out);
         }
@@ -945,39 +943,46 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
 
     if (p.ar.world > 1 && eg == 0) {
       // ---- one-shot all-reduce over peer memory, fused behind the streaming loop (group 0) ----
-      AllReduceState* self = p.ar.state[p.ar.rank];
-      // 1. this CTA's peer stores are done (the barrier collects the group's; the fence below
-      //    orders them, cumulatively, before the counts): tell every rank, itself included.  The CTAs
-      //    of a rank add kArUnit between them to the rank's counter on every endpoint.
-      asm volatile("bar.sync 1, %0;" ::"n"(kGemvGroupThreads) : "memory");
-      if (threadIdx.x == 0) {
-        const unsigned long long share = kArUnit / static_cast<unsigned long long>(grid);
-        const unsigned long long mine_w = cta < grid - 1 ? share : kArUnit - share * static_cast<unsigned long long>(grid - 1);
-        // one system-scope fence for all the counts (a release per count would wait for the
-        // previous count's round trip over the link)
-        __threadfence_system();
-        for (int pr = 0; pr < p.ar.world; ++pr)
-          asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(&p.ar.state[pr]->arrive_from[p.ar.rank]), "l"(mine_w) : "memory");
-        // 2. wait (bounded) until every CTA of every rank has arrived for this call.
-        if (ok && !ar_wait_all(self, p.ar.world, ar_epoch)) {
-          set_status(p.status, ST_PEER_TIMEOUT);
-          *cta_error = 1;
+      // This CTA's partials are on their way (every word carries the call number).  Count the CTA
+      // towards the call -- a local add, nothing waits on it -- then sum, in rank order, the words of
+      // this CTA's share of rows as they arrive, add the residual and store.
+      if (threadIdx.x == 0)
+        asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(&p.ar.state->calls), "l"(ar_share(cta, grid)) : "memory");
+      const unsigned long long* mine = p.ar.recv[p.ar.rank];
+      const uint32_t tag = ar_tag(ar_epoch);
+      const long long half_base = static_cast<long long>(ar_epoch & 1ull) * p.ar.world;
+      const int total = p.n_tokens * p.n_rows;
+      const int e0 = static_cast<int>(static_cast<long long>(total) * cta / grid);
+      const int e1 = static_cast<int>(static_cast<long long>(total) * (cta + 1) / grid);
+      const long long t0 = clock64();
+      bool alive = ok && !*cta_error;
+      for (int e = e0 + static_cast<int>(threadIdx.x); e < e1 && alive; e += kGemvGroupThreads) {
+        const int tok = e / p.n_rows, row = e % p.n_rows;
+        float v = 0.f;
+        unsigned pending = (1u << p.ar.world) - 1u;
+        float part[8];
+        while (pending != 0u) {
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            if (r < p.ar.world && (pending >> r) & 1u) {
+              const unsigned long long word = ar_peek(&mine[((half_base + r) * 4 + tok) * p.n_rows + row]);
+              if (static_cast<uint32_t>(word >> 32) == tag) {
+                part[r] = __uint_as_float(static_cast<uint32_t>(word));
+                pending &= ~(1u << r);
+              }
+            }
+          }
+          if (pending != 0u && clock64() - t0 > kWaitBudgetCycles) {
+            set_status(p.status, ST_PEER_TIMEOUT);
+            alive = false;
+            break;
+          }
         }
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(kGemvGroupThreads) : "memory");
-      // 3. reduce the world's slots for this CTA's share of rows, add the residual, store.
-      if (!*cta_error) {
-        const float* mine = p.ar.recv[p.ar.rank];
-        const int total = p.n_tokens * p.n_rows;
-        const int e0 = static_cast<int>(static_cast<long long>(total) * cta / grid);
-        const int e1 = static_cast<int>(static_cast<long long>(total) * (cta + 1) / grid);
-        for (int e = e0 + static_cast<int>(threadIdx.x); e < e1; e += kGemvGroupThreads) {
-          const int tok = e / p.n_rows, row = e % p.n_rows;
-          float v = 0.f;
-          for (int r = 0; r < p.ar.world; ++r)
-            v += __ldcg(&mine[((static_cast<long long>(ar_half) * p.ar.world + r) * 4 + tok) * p.n_rows + row]);
-          gemv_store(p, row, tok, v);
-        }
+        if (!alive) break;
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < p.ar.world) v += part[r];
+        gemv_store(p, row, tok, v);
       }
     }
     if (warp == 0 && lane == 0) gemv_stamp(p, kGemvProfExit);
