@@ -283,19 +283,35 @@ def run_ours(args) -> None:
         ends[i].record()
     barrier()
     dev_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
-    # keep sampling clocks through a longer loaded stretch so the median is meaningful
-    t_end = time.time() + (0.0 if args.profile else 1.0)
-    while time.time() < t_end:
+    # keep sampling clocks through a longer loaded stretch (about a second) so the median is meaningful.
+    # Every rank must replay the step the SAME number of times -- a rank that did one more would wait
+    # for partial sums nobody sends -- so the count is agreed on, not decided by each rank's clock.
+    reps = torch.tensor([0 if args.profile else int(1000.0 * args.steps / max(dev_ms, 1e-3))], dtype=torch.int64,
+                        device=dev)
+    if world > 1:
+        dist.all_reduce(reps, op=dist.ReduceOp.MIN)
+    for _ in range(int(reps.item())):
         graph.replay()
     torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
+
+    def phase_status(name: str) -> int:
+        """Device status word after a phase, worst over ranks (0 = every wait in every kernel was met)."""
+        st = torch.tensor([tilert_b200.device_status(local)], dtype=torch.int64, device=dev)
+        if world > 1:
+            dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        if rank == 0 and int(st.item()) != 0:
+            print(f"bench: device status {int(st.item())} after {name}", file=sys.stderr, flush=True)
+        return int(st.item())
+
+    healthy = phase_status("the timed steps and the load loop") == 0
 
     # ---- the same layer four times per replay, each pass fed by the previous one: what a layer costs
     # inside a model, where its first launch overlaps the previous layer's tail instead of a cold start
     # (the weights are 4-8x the L2, so every pass still streams them from HBM) ----
     n_chain = 4
     chain_ms = None
-    if not args.profile:
+    if not args.profile and healthy:
         def chain():
             y = x
             for _ in range(n_chain):
@@ -318,6 +334,7 @@ def run_ours(args) -> None:
             c1[i].record()
         barrier()
         chain_ms = sum(a_.elapsed_time(b_) for a_, b_ in zip(c0, c1)) / 10 / n_chain
+        phase_status("the chained passes")
 
     # ---- end to end: host buffers, H2D + step + D2H inside the timed region ----
     barrier()

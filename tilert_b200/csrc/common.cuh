@@ -74,7 +74,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // counted on the SM's cycle counter, read only after a batch of failed polls: reading %globaltimer
 // costs about as much as a whole pipeline stage, and a waiting consumer is the normal state of a
 // bandwidth-bound kernel.
-constexpr long long kWaitBudgetCycles = 4000000000ll;  // about two seconds at ~2 GHz
+constexpr long long kWaitBudgetCycles = 1000000000ll;  // about half a second at ~2 GHz
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 #pragma unroll 1
   for (int i = 0; i < 32; ++i)
