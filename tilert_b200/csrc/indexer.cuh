@@ -121,15 +121,6 @@ __device__ __forceinline__ uint32_t f32_order_key(float v) {
 constexpr uint32_t kNegInfKey = 0x007fffffu;  // order key of -inf: never selected
 
 constexpr int kTopkThreads = 1024;
-
-// One histogram count per group of lanes with the same digit: indexer scores share their top bytes,
-// so in the first passes nearly every lane of a warp hits the same bin, and 32 same-address shared
-// atomics serialise.  Must be reached by all 32 lanes of the warp.
-__device__ __forceinline__ void topk_hist_add(int* hist, bool active, uint32_t digit) {
-  const uint32_t d = active ? digit : 256u;
-  const uint32_t peers = __match_any_sync(0xffffffffu, d);
-  if (active && (threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[d], __popc(peers));
-}
 constexpr int kTopkItems = 8;  // consecutive elements per thread in the ordered compaction
 
 // One CTA per row.  Selects the k largest logits among [0, n) (entries equal to -inf are skipped),
@@ -169,10 +160,9 @@ __device__ __forceinline__ void topk_radix_row(const float* __restrict__ row, in
     for (int shift = 24; shift >= 0; shift -= 8) {
       if (tid < 256) hist[tid] = 0;
       __syncthreads();
-      for (int i0 = 0; i0 < n; i0 += kTopkThreads) {  // warp-uniform trip count (topk_hist_add needs the whole warp)
-        const int i = i0 + tid;
-        const uint32_t key = i < n ? f32_order_key(row[i]) : 0u;
-        topk_hist_add(hist, key > kNegInfKey && (key & mask) == prefix, (key >> shift) & 0xff);
+      for (int i = tid; i < n; i += kTopkThreads) {
+        const uint32_t key = f32_order_key(row[i]);
+        if (key > kNegInfKey && (key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1);
       }
       __syncthreads();
       if (warp == 0) {
@@ -340,7 +330,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_radix_reg_kernel(const floa
       // hist is zero here (initially, and re-zeroed by warp 0 after each pass's scan)
 #pragma unroll
       for (int j = 0; j < ITEMS; ++j)
-        topk_hist_add(hist, key[j] > kNegInfKey && (key[j] & mask) == prefix, (key[j] >> shift) & 0xff);
+        if (key[j] > kNegInfKey && (key[j] & mask) == prefix) atomicAdd(&hist[(key[j] >> shift) & 0xff], 1);
       __syncthreads();
       if (warp == 0) {
         // find the digit where the count of larger-or-equal digits reaches the remaining quota:
