@@ -95,6 +95,47 @@ def main() -> int:
             print(f"model pos {pos}: logits rel_l2 {l2:.3e} token {picked} expected {expected}", flush=True)
         if not (l2 <= 2e-2 and all(p == expected for p in picked)):
             failures.append(("model", pos, l2, picked, expected))
+    # Speculative decoding across ranks: chunked prefill, then verify steps fed with the oracle's drafts
+    # (the second one with the true continuation, so several drafts are accepted).  The four rows' logits,
+    # gathered over the vocabulary slices, must match the oracle's; the predicted tokens must be the arg-max
+    # of the gathered logits and, like the accepted count and the next drafts, the same on every rank.
+    from tilert_b200.models.deepseek_v3_2.mtp import MtpDsaModel
+    sd_mtp = om.random_state_dict(a, seed=0, with_mtp=True)
+    prompt = torch.randint(0, a.vocab_size, (21,), generator=torch.Generator().manual_seed(11)).tolist()
+    plain, _ = om.Model(a, sd_mtp, cache_len=256).generate(prompt, 8)
+    ref = om.MtpModel(a, sd_mtp, cache_len=256)
+    ref.generate_mtp(prompt, 0)
+    spec = MtpDsaModel(margs, sd_mtp, dev, cache_len=256, world=world, rank=rank, comm=comm.handle)
+    spec.generate(prompt, 0)
+    draft = [prompt[-1]] * 4
+    for step in range(3):
+        if step == 1:
+            k = ref.pos - (len(prompt) - 1)
+            draft = [draft[0]] + plain[k: k + 3]
+        r = ref.verify_step(list(draft))
+        spec.forward(draft)
+        torch.cuda.synchronize()
+        parts = [torch.empty_like(spec.logits) for _ in range(world)]
+        dist.all_gather(parts, spec.logits)
+        full = torch.cat(parts, dim=-1)[0].float().cpu()
+        l2 = (torch.norm(r["logits"] - full) / torch.norm(r["logits"])).item()
+        mine = torch.cat([spec.predicted, spec.n_accepted, spec.next_draft])
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        same = all(torch.equal(everyone[0], t) for t in everyone)
+        pred = spec.predicted.cpu().tolist()
+        exact = pred == torch.argmax(full, dim=-1).tolist()
+        n_dev = spec.get_num_accepted()
+        if rank == 0:
+            print(f"speculative step {step}: logits rel_l2 {l2:.3e} predicted {pred} oracle {r['predicted']} "
+                  f"accepted {n_dev} oracle {r['n_accepted']} ranks_identical {same}", flush=True)
+        if not (l2 <= 2e-2 and same and exact):
+            failures.append(("speculative", step, l2, same, exact))
+        if pred != r["predicted"]:
+            break  # an arg-max tie fell the other way: the sequences part ways here
+        if n_dev != r["n_accepted"] or (step == 1 and n_dev < 2):
+            failures.append(("speculative accepted", step, n_dev, r["n_accepted"]))
+        draft = r["next_draft"]
     status = tilert_b200.device_status(local)
     if status != 0:
         failures.append(("device_status", status))

@@ -36,25 +36,31 @@ N_TOKENS = 4  # rows per step: the reference's ``forward_max_seq_len`` (end2end.
 
 
 class MtpDsaModel:
-    """Main model + prediction layer on one rank.  ``sd`` is an HF-keyed FP8 state dict whose
-    prediction layer sits under ``model.layers.{n_layers}``."""
+    """Main model + prediction layer on one rank of ``world`` (tensor parallel like ``DsaModel``: heads,
+    expert slices and vocabulary rows per rank, fused all-reduces, ``comm`` from ``tilert_b200.comm``).
+    ``sd`` is an HF-keyed FP8 state dict whose prediction layer sits under ``model.layers.{n_layers}``."""
 
     def __init__(self, args: ModelArgs, sd: dict[str, torch.Tensor], device="cuda", cache_len: int | None = None,
-                 use_graph: bool = True):
+                 use_graph: bool = True, world: int = 1, rank: int = 0, comm: int | None = None):
         self.args, self.device = args, torch.device(device)
+        self.world, self.rank, self.comm = world, rank, comm
         dev, s = self.device, N_TOKENS
         self.cache_len = cache_len or args.max_seq_len
         p = f"model.layers.{args.n_layers}"
         self.embed = sd["model.embed_tokens.weight"].to(dev, BF16)
         self.final_norm = sd["model.norm.weight"].to(dev, F32)
-        self.head = sd["lm_head.weight"].to(dev, BF16).contiguous()
+        # with several ranks every rank holds vocab / world rows of the head (shared by both models) and
+        # the greedy tokens come from the (value, index) exchange over peer memory
+        v_l = args.vocab_size // world
+        self.head = sd["lm_head.weight"][rank * v_l:(rank + 1) * v_l].to(dev, BF16).contiguous()
         self.enorm = sd[f"{p}.enorm.weight"].to(dev, F32)
         self.hnorm = sd[f"{p}.hnorm.weight"].to(dev, F32)
         self.w_eh = sd[f"{p}.eh_proj.weight"].to(dev, BF16).contiguous()
         self.mtp_norm = sd[f"{p}.shared_head.norm.weight"].to(dev, F32)
-        self.layers = [DecoderLayer(args, LayerWeights(args, sd, li, dev), dev, self.cache_len, s)
+        self.layers = [DecoderLayer(args, LayerWeights(args, sd, li, dev, world, rank), dev, self.cache_len, s, world, comm)
                        for li in range(args.n_layers)]
-        self.mtp_layer = DecoderLayer(args, LayerWeights(args, sd, args.n_layers, dev), dev, self.cache_len, s)
+        self.mtp_layer = DecoderLayer(args, LayerWeights(args, sd, args.n_layers, dev, world, rank), dev,
+                                      self.cache_len, s, world, comm)
         self.freqs = precompute_freqs(args).to(dev)
         z = lambda *shape, dtype: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
         self.cur_pos = z(1, dtype=I32)
@@ -64,17 +70,18 @@ class MtpDsaModel:
         self.extra_token = z(1, dtype=I64)      # prefill only: the prompt token after the chunk
         self.valid = z(1, dtype=I32)            # prefill only: rows of the chunk that are real
         # step results (the reference's PREDICTED_TOKENS / ACCEPTED_TOKENS / NEXT_DRAFT_TOKENS)
-        self.logits = z(1, s, args.vocab_size, dtype=F32)
+        self.logits = z(1, s, v_l, dtype=F32)                  # this rank's slice of the vocabulary
         self.predicted = z(s, dtype=I64)
         self.n_accepted = z(1, dtype=I64)
         self.next_draft = z(s, dtype=I64)
-        self.guess_logits = z(s - 1, args.vocab_size, dtype=F32)
+        self.guess_logits = z(s - 1, v_l, dtype=F32)
         # scratch
         self.mtp_in = z(1, s, args.dim, dtype=BF16)
-        self.mtp_logits = z(1, s, args.vocab_size, dtype=F32)
+        self.mtp_logits = z(1, s, v_l, dtype=F32)
         self.chain_pos = z(1, dtype=I32)
         self.chain_in = z(1, 1, args.dim, dtype=BF16)
-        self.chain_logits = z(1, 1, args.vocab_size, dtype=F32)
+        self.chain_logits = z(1, 1, v_l, dtype=F32)
+        self.guess = z(1, dtype=I64)
         self.use_graph = use_graph
         self._graphs: dict[tuple[str, int], torch.cuda.CUDAGraph] = {}
         self.pos = 0  # host copy of the position
@@ -101,6 +108,13 @@ class MtpDsaModel:
 
     def get_next_draft_tokens(self) -> torch.Tensor:
         return self.next_draft
+
+    def _argmax(self, logits: torch.Tensor, out: torch.Tensor) -> None:
+        """Greedy tokens of ``logits`` [1, S, vocab / world] into ``out`` int64 [S], the same on every rank."""
+        if self.world > 1:
+            ops.argmax_exchange(logits, self.rank * logits.shape[-1], out, comm=self.comm)
+        else:
+            out.copy_(torch.argmax(logits.view(out.numel(), -1), dim=-1))
 
     # -- the passes --
     def _main_pass(self, tokens: torch.Tensor, n_keys: int) -> torch.Tensor:
@@ -131,22 +145,22 @@ class MtpDsaModel:
     def _verify_ops(self, n_keys: int) -> None:
         s = N_TOKENS
         h = self._main_pass(self.draft, n_keys)
-        self.predicted.copy_(torch.argmax(self.logits.view(s, -1), dim=-1))
+        self._argmax(self.logits, self.predicted)
         match = (self.draft[1:] == self.predicted[:-1]).to(I64)
         self.n_accepted.copy_(1 + torch.cumprod(match, 0).sum().view(1))
         last = self.n_accepted - 1                                   # row of the last accepted token
         mh = self._mtp_pass(self.predicted, h, self.cur_pos, n_keys, self.mtp_in, self.mtp_logits)
         self.guess_logits[0].copy_(self.mtp_logits.view(s, -1).index_select(0, last).view(-1))
-        guess = torch.argmax(self.guess_logits[0]).view(1)
+        self._argmax(self.guess_logits[0].view(1, 1, -1), self.guess)
         self.next_draft[0:1].copy_(self.predicted.index_select(0, last))
-        self.next_draft[1:2].copy_(guess)
+        self.next_draft[1:2].copy_(self.guess)
         hh = mh.index_select(1, last).clone()
         for i in range(1, s - 1):
             self.chain_pos.copy_(self.cur_pos + (last + i).to(I32))
-            hh = self._mtp_pass(guess, hh, self.chain_pos, n_keys, self.chain_in, self.chain_logits).clone()
+            hh = self._mtp_pass(self.guess, hh, self.chain_pos, n_keys, self.chain_in, self.chain_logits).clone()
             self.guess_logits[i].copy_(self.chain_logits.view(-1))
-            guess = torch.argmax(self.guess_logits[i]).view(1)
-            self.next_draft[i + 1: i + 2].copy_(guess)
+            self._argmax(self.guess_logits[i].view(1, 1, -1), self.guess)
+            self.next_draft[i + 1: i + 2].copy_(self.guess)
         self.cur_pos += self.n_accepted.to(I32)
 
     def _bucket(self) -> int:
