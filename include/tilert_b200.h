@@ -271,6 +271,23 @@ int tilert_sample_op(TbContext* ctx, const float* logits, long long logits_strid
                      unsigned long long step_value, int* token_out, float* token_logprob_out, float* topn_logprob_out,
                      int* topn_index_out, void* stream);
 
+/* ---- latent caches from an external prefill, FP8 wire format -------------------------------- */
+
+/* The decode side of prefill / decode disaggregation: tilert/pd_vllm/profiles/mla_nsa.py:16-41 (layout),
+ * :186-232 (_dequant_kv, _dequant_ki) followed by DSAv32Generator.inject_cache
+ * (tilert/models/deepseek_v3_2/generator.py:419-484), as one launch per layer.
+ *
+ *   kv_raw   [seq_len, 528] bytes: 512 e4m3 latent values + 4 f32 scales (one per 128 values);
+ *   pe_raw   [seq_len, 128] bytes: 64 bf16 rope values;
+ *   ki_pages [ceil(seq_len / 64), 8448] bytes: 64 x 128 e4m3 indexer-key values, then 64 f32 scales;
+ *   rows start_pos .. start_pos + seq_len - 1 of kv_cache [cache_rows, 512], pe_cache [cache_rows, 64] and
+ *   ki_cache [cache_rows, 128] (bf16) are written: latent = e4m3 * scale rounded to bf16; indexer key =
+ *   e4m3 * scale rounded to bf16, then Hadamard-128 scaled by 128^-1/2.  A plane and its cache may both be
+ *   NULL to skip it.  kv_raw and kv_cache must be 16-byte aligned, the other planes 4-byte aligned. */
+int tilert_inject_cache_fp8_op(TbContext* ctx, const uint8_t* kv_raw, const uint8_t* pe_raw, const uint8_t* ki_pages,
+                               int seq_len, int start_pos, int cache_rows, void* kv_cache, void* pe_cache,
+                               void* ki_cache, void* stream);
+
 /* ---- greedy token over a vocabulary split across ranks ----------------------------------- */
 
 /* The arg-max that follows rmsnorm_head_proj_op when every rank holds vocab / world rows of the head

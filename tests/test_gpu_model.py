@@ -270,3 +270,82 @@ def test_full_shape_moe_layer_matches_oracle(tb):
         cos, l2 = _m(r, d.view(r.shape))
         _log({"name": f"full.{name}", "cos": cos, "rel_l2": l2})
         assert cos >= 0.999 and l2 <= 2e-2, (name, cos, l2)
+
+
+def test_model_driver_sampling(tb):
+    """The driver's sampling switch: temperature 0 reproduces greedy decoding through the sampling
+    operator; a seeded temperature-1 run is reproducible, and the reported log-probability is the
+    log-softmax of the step's logits at the sampled token."""
+    from tilert_b200.models.deepseek_v3_2.model import DsaModel
+    from tilert_b200.models.deepseek_v3_2.model_args import toy_model_args
+
+    a = om.toy_args()
+    sd = om.random_state_dict(a, seed=0)
+    prompt = torch.randint(0, a.vocab_size, (9,), generator=torch.Generator().manual_seed(4)).tolist()
+    dev = DsaModel(toy_model_args(), sd, "cuda", cache_len=256)
+    greedy = dev.generate(prompt, 8)
+    dev.set_sampling(temperature=0.0)
+    assert dev.generate(prompt, 8) == greedy
+
+    def run(seed):
+        dev.set_sampling(temperature=1.0, top_p=0.95, top_k=64, use_top_p=True, seed=seed)
+        dev.sample_step.zero_()
+        return dev.generate(prompt, 8)
+
+    first, again, other = run(7), run(7), run(8)
+    assert first == again
+    assert first != greedy or other != greedy  # 64 candidates at temperature 1: sampling moves off the arg-max
+    # after the last step: logits and the sampled token of that step
+    lp = torch.log_softmax(dev.logits.view(-1).double(), dim=-1)
+    assert abs(float(lp[int(dev.token_out)]) - float(dev.token_logprob)) < 2e-4
+    assert torch.equal(dev.topn_indices[0].long().cpu(), torch.argsort(-dev.logits.view(-1).double(), stable=True)[:256].cpu())
+
+
+def test_injected_caches_continue_a_sequence(tb):
+    """Prefill/decode disaggregation: a model that receives the caches of a prompt (bf16, as
+    DSAv32Generator.inject_cache takes them) continues exactly like the model that computed them itself;
+    through the FP8 wire format the continuation's logits stay within the format's quantisation error."""
+    from oracle import cache_format as cf
+    from tilert_b200.models.deepseek_v3_2.model import DsaModel
+    from tilert_b200.models.deepseek_v3_2.model_args import toy_model_args
+
+    a = om.toy_args()
+    sd = om.random_state_dict(a, seed=0)
+    prompt = torch.randint(0, a.vocab_size, (40,), generator=torch.Generator().manual_seed(6)).tolist()
+    src = DsaModel(toy_model_args(), sd, "cuda", cache_len=256)
+    src.reset_sequence()
+    for pos, t in enumerate(prompt[:-1]):
+        src.forward(t, pos)
+    n = len(prompt) - 1
+    caches = [(ly.ki_cache[0, :n].clone(), ly.kv_cache[0, :n].clone(), ly.pe_cache[0, :n].clone()) for ly in src.layers]
+    src.forward(prompt[-1], n)
+    torch.cuda.synchronize()
+    want = src.logits.view(-1).clone()
+
+    dst = DsaModel(toy_model_args(), sd, "cuda", cache_len=256)
+    dst.inject_cache(caches, start_pos=0)
+    dst.set_cur_pos(n)
+    dst.forward(prompt[-1], n)
+    torch.cuda.synchronize()
+    assert torch.equal(dst.logits.view(-1), want)
+
+    # FP8 wire format.  The indexer keys travel un-rotated (the receiver applies the Hadamard rotation, which
+    # is its own inverse up to the scale): rotate the cache rows back to make the wire input.
+    h = oo.hadamard_matrix(128) * 128 ** -0.5
+    planes = []
+    for ki, kv, pe in caches:
+        ki_plain = (ki.float().cpu() @ h).to(BF16)
+        planes.append((cf.quant_kv(kv.cpu()), pe.cpu().contiguous().view(torch.uint8).view(n, 128), cf.quant_ki_pages(ki_plain)))
+    dq = DsaModel(toy_model_args(), sd, "cuda", cache_len=256)
+    dq.inject_cache(planes, start_pos=0, end_pos=n)
+    dq.set_cur_pos(n)
+    dq.forward(prompt[-1], n)
+    torch.cuda.synchronize()
+    cos, l2 = _m(want, dq.logits.view(-1))
+    _log({"name": "inject.fp8.logits", "cos": cos, "rel_l2": l2})
+    assert cos >= 0.95, (cos, l2)  # e4m3 caches: per cent-level noise, and room for one router near-tie
+    for (ki, kv, pe), ly in zip(caches, dq.layers):
+        c, _ = _m(kv, ly.kv_cache[0, :n])
+        assert c >= 0.999, c
+        c, _ = _m(ki, ly.ki_cache[0, :n])
+        assert c >= 0.998, c

@@ -620,6 +620,40 @@ def test_argmax_exchange_single_rank_is_exact(env):
         assert torch.equal(val.cpu(), logits[0].max(dim=-1).values)
 
 
+def test_inject_cache_fp8_wire_format(env):
+    """Caches injected from the FP8 wire format: the latent rows are bit-exact against the oracle (and so
+    against the reference's dequantiser, which the oracle is pinned to), the rope rows are copied, the
+    indexer keys match after the Hadamard rotation (f32 butterfly here, f32 matrix product there); rows
+    outside [start_pos, start_pos + seq) stay untouched; ragged lengths and an empty injection work."""
+    from oracle import cache_format as cf
+
+    ops = env["ops"]
+    g = torch.Generator().manual_seed(33)
+    for seq, start in ((150, 0), (64, 7), (1, 300), (0, 5)):
+        kv = (torch.randn(seq, 512, generator=g) * 1.7).to(BF16)
+        pe = torch.randn(seq, 64, generator=g).to(BF16)
+        ki = torch.randn(seq, 128, generator=g).to(BF16)
+        kv_raw, ki_pages = cf.quant_kv(kv), cf.quant_ki_pages(ki)
+        pe_raw = pe.contiguous().view(torch.uint8).view(seq, 128)
+        rows = 512
+        kc = torch.full((1, rows, 512), 3.0, dtype=BF16, device="cuda")
+        pc = torch.full((1, rows, 64), 3.0, dtype=BF16, device="cuda")
+        ic = torch.full((1, rows, 128), 3.0, dtype=BF16, device="cuda")
+        ops.inject_cache_fp8(kv_raw.cuda(), pe_raw.cuda(), ki_pages.cuda(), seq, start, kc, pc, ic)
+        torch.cuda.synchronize()
+        if seq:
+            assert torch.equal(kc[0, start: start + seq].cpu().view(torch.int16), cf.dequant_kv(kv_raw, seq).view(torch.int16))
+            assert torch.equal(pc[0, start: start + seq].cpu().view(torch.int16), pe.view(torch.int16))
+            ref_ki = cf.dequant_ki(ki_pages, seq).float()
+            got_ki = ic[0, start: start + seq].float().cpu()
+            assert (got_ki - ref_ki).abs().max() <= 2.0 ** -7 * ref_ki.abs().max()
+        for c in (kc, pc, ic):
+            assert (c[0, :start] == 3.0).all() and (c[0, start + seq:] == 3.0).all()
+    with pytest.raises(env["tb"].TilertError):
+        ops.inject_cache_fp8(torch.zeros(4, 528, dtype=torch.uint8, device="cuda"), None, None, 4, 510,
+                             torch.zeros(1, 512, 512, dtype=BF16, device="cuda"), None, None)
+
+
 def test_bad_arguments_raise(env):
     ops = env["ops"]
     with pytest.raises(ValueError):

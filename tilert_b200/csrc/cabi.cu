@@ -17,6 +17,7 @@
 #include "sampler.cuh"
 #include "wstream_gemv.cuh"
 #include "argmax_exchange.cuh"
+#include "cache_inject.cuh"
 
 using namespace tb;
 
@@ -1049,6 +1050,32 @@ extern "C" int tilert_sample_op(TbContext* ctx, const float* logits, long long l
   p.topn_logprob = topn_logprob_out;
   p.topn_index = topn_index_out;
   TB_CUDA(launch(sample_kernel, dim3(tokens), dim3(kTopkThreads), 0, static_cast<cudaStream_t>(stream), p));
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+// ------------------------------------------------------------------ cache injection (FP8 wire format)
+extern "C" int tilert_inject_cache_fp8_op(TbContext* ctx, const uint8_t* kv_raw, const uint8_t* pe_raw,
+                                          const uint8_t* ki_pages, int seq_len, int start_pos, int cache_rows,
+                                          void* kv_cache, void* pe_cache, void* ki_cache, void* stream) {
+  TB_REQUIRE(ctx != nullptr && seq_len >= 0 && start_pos >= 0 && start_pos + seq_len <= cache_rows);
+  TB_REQUIRE((kv_raw == nullptr) == (kv_cache == nullptr) && (pe_raw == nullptr) == (pe_cache == nullptr) &&
+             (ki_pages == nullptr) == (ki_cache == nullptr));
+  TB_REQUIRE(reinterpret_cast<uintptr_t>(kv_raw) % 16 == 0 && reinterpret_cast<uintptr_t>(pe_raw) % 4 == 0 &&
+             reinterpret_cast<uintptr_t>(ki_pages) % 4 == 0 && reinterpret_cast<uintptr_t>(kv_cache) % 16 == 0);
+  if (seq_len == 0) return TB_OK;
+  CacheInjectParams p{};
+  p.kv_raw = kv_raw;
+  p.pe_raw = pe_raw;
+  p.ki_pages = ki_pages;
+  p.seq_len = seq_len;
+  p.start_pos = start_pos;
+  p.kv_cache = reinterpret_cast<__nv_bfloat16*>(kv_cache);
+  p.pe_cache = reinterpret_cast<__nv_bfloat16*>(pe_cache);
+  p.ki_cache = reinterpret_cast<__nv_bfloat16*>(ki_cache);
+  const int grid = (seq_len + kInjectWarps - 1) / kInjectWarps;
+  TB_CUDA(launch(cache_inject_fp8_kernel, dim3(grid), dim3(kInjectWarps * 32), 0, static_cast<cudaStream_t>(stream), p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;

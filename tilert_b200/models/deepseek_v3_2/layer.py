@@ -194,6 +194,26 @@ class DecoderLayer:
         self.injected_sel: torch.Tensor | None = None
         self.scale = softmax_scale(a)
 
+    def inject_cache(self, ki: torch.Tensor, kv: torch.Tensor, pe: torch.Tensor, start_pos: int = 0) -> None:
+        """Rows ``start_pos ..`` of the three caches from bf16 tensors [seq, 128 / 512 / 64] computed by an
+        external prefill (one layer of DSAv32Generator.inject_cache, generator.py:419-484; the caches are
+        replicated on every rank)."""
+        n = ki.shape[0]
+        if not (kv.shape[0] == pe.shape[0] == n) or start_pos < 0 or start_pos + n > self.cache_len:
+            raise ValueError("inject_cache: the three tensors must hold the same rows and fit the caches")
+        dev = self.kv_cache.device
+        self.ki_cache[0, start_pos: start_pos + n].copy_(ki.to(dev, BF16))
+        self.kv_cache[0, start_pos: start_pos + n].copy_(kv.to(dev, BF16))
+        self.pe_cache[0, start_pos: start_pos + n].copy_(pe.to(dev, BF16))
+
+    def inject_cache_fp8(self, kv_raw: torch.Tensor, pe_raw: torch.Tensor, ki_pages: torch.Tensor, seq_len: int,
+                         start_pos: int = 0) -> None:
+        """The same from the FP8 wire format (uint8 planes [seq, 528], [seq, 128], [pages, 8448];
+        pd_vllm/profiles/mla_nsa.py:16-41), dequantised on the device in one launch."""
+        dev = self.kv_cache.device
+        ops.inject_cache_fp8(kv_raw.to(dev).contiguous(), pe_raw.to(dev).contiguous(), ki_pages.to(dev).contiguous(),
+                             seq_len, start_pos, self.kv_cache, self.pe_cache, self.ki_cache)
+
     def forward(self, x: torch.Tensor, cur_pos: torch.Tensor, freqs: torch.Tensor, n_keys: int) -> torch.Tensor:
         """``x`` [1, S, dim] bf16, ``cur_pos`` int32[1] (position of token 0), ``freqs`` f32 [S, rope/2, 2],
         ``n_keys`` = number of cache rows the indexer scans (>= cur_pos + S).  Returns [1, S, dim] bf16."""

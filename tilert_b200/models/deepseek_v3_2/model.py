@@ -38,6 +38,16 @@ class DsaModel:
         self.token_out = torch.zeros(1, dtype=torch.int64, device=dev)
         self.use_graph = use_graph
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        # sampling state (the reference's SAMPLING_CONFIG / TOP_P_SCORES / TOP_N_LOG_PROBS / TOP_N_INDICES
+        # temp vars, temp_var_indices.py:64-73): greedy until set_sampling is called
+        self.sampling_config = torch.tensor([0.0, 1.0, 0.0, 0.0], dtype=F32, device=dev)  # temperature, top_p, top_k, use_top_p
+        self.sampling_seed = 0
+        self.sampling = False
+        self.sample_step = torch.zeros(2, dtype=torch.int64, device=dev)  # advanced by every launch (graph replay safe)
+        self.sampled = torch.zeros(1, dtype=I32, device=dev)
+        self.token_logprob = torch.zeros(1, dtype=F32, device=dev)
+        self.topn_logprobs = torch.zeros(1, 256, dtype=F32, device=dev)
+        self.topn_indices = torch.zeros(1, 256, dtype=I32, device=dev)
 
     # -- reference driver controls (end2end.py:551-577) --
     def reset_sequence(self) -> None:
@@ -45,6 +55,42 @@ class DsaModel:
 
     def set_cur_pos(self, pos: int) -> None:
         self.cur_pos.fill_(pos)
+
+    def set_sampling(self, temperature: float = 0.0, top_p: float = 1.0, top_k: int = 0, use_top_p: bool = False,
+                     seed: int | None = None) -> None:
+        """Sample the next token instead of taking the arg-max (end2end.py:253-311: temperature, top-p, top-k
+        per request; ``set_sampling_seed``).  Temperature 0 with no seed change returns to greedy decoding.
+        The token's log-probability and the top-256 log-probabilities / ids are left in ``token_logprob``,
+        ``topn_logprobs`` and ``topn_indices`` after every step."""
+        if self.world > 1:
+            raise ValueError("sampling needs the whole vocabulary on one rank; the split head decodes greedily")
+        self.sampling_config.copy_(torch.tensor([temperature, top_p, float(top_k), 1.0 if use_top_p else 0.0]))
+        if seed is not None and seed != self.sampling_seed:
+            self.sampling_seed = seed
+            self._graphs.clear()  # the seed is a launch argument
+        if not self.sampling:
+            self.sampling = True
+            self._graphs.clear()
+
+    def set_sampling_seed(self, seed: int) -> None:
+        """end2end.py:120-134."""
+        if seed != self.sampling_seed:
+            self.sampling_seed = seed
+            self._graphs.clear()
+
+    def inject_cache(self, layer_caches, start_pos: int = 0, end_pos: int | None = None) -> None:
+        """``layer_caches``: one (ki, kv, pe) bf16 triple per layer from an external prefill
+        (DSAv32Generator.inject_cache, generator.py:419-484); follow with ``set_cur_pos``.  A triple of
+        uint8 planes (kv_raw [seq, 528], pe_raw [seq, 128], ki_pages [pages, 8448]) is taken as the FP8 wire
+        format of pd_vllm/profiles/mla_nsa.py and needs ``end_pos`` (the pages do not tell the length)."""
+        for layer, (c0, c1, c2) in zip(self.layers, layer_caches):
+            if c0.dtype == torch.uint8:
+                if end_pos is None:
+                    raise ValueError("inject_cache: end_pos is needed with FP8 planes")
+                layer.inject_cache_fp8(c0, c1, c2, end_pos - start_pos, start_pos)
+            else:
+                n = c0.shape[0] if end_pos is None else end_pos - start_pos
+                layer.inject_cache(c0[:n], c1[:n], c2[:n], start_pos)
 
     def _step_ops(self, n_keys: int) -> None:
         x = self.embed[self.token].view(1, 1, -1)
@@ -55,6 +101,11 @@ class DsaModel:
         if self.world > 1:
             # every rank holds vocab / world rows of the head: exchange (value, index) pairs over peer memory
             ops.argmax_exchange(self.logits, self.rank * self.logits.shape[-1], self.token_out, comm=self.comm)
+        elif self.sampling:
+            ops.sample(self.logits.view(1, -1), self.sampling_config, self.sampled, seed=self.sampling_seed,
+                       step=self.sample_step, token_logprob=self.token_logprob, topn_logprobs=self.topn_logprobs,
+                       topn_indices=self.topn_indices)
+            self.token_out.copy_(self.sampled)
         else:
             self.token_out.copy_(torch.argmax(self.logits.view(-1)))
         self.cur_pos += 1
@@ -75,12 +126,11 @@ class DsaModel:
             self._step_ops(n_keys)
             return
         if n_keys not in self._graphs:
-            saved = self.cur_pos.clone()
-            for ly in self.layers:  # warm-up outside capture (lazy function attributes, allocator)
-                pass
-            self._step_ops(n_keys)
+            saved, saved_step = self.cur_pos.clone(), self.sample_step.clone()
+            self._step_ops(n_keys)  # warm-up outside capture (lazy function attributes, allocator)
             torch.cuda.synchronize()
             self.cur_pos.copy_(saved)
+            self.sample_step.copy_(saved_step)  # the warm-up drew a number: give it back
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 self._step_ops(n_keys)

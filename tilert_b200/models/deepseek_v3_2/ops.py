@@ -286,6 +286,28 @@ def rmsnorm_head_proj(x, gamma, w, x_norm_out, logits_out, profile_logs=None, *,
                                                     w.shape[0], _p(x_norm_out), _p(logits_out), _stream()))
 
 
+def inject_cache_fp8(kv_raw, pe_raw, ki_pages, seq_len, start_pos, kv_cache, pe_cache, ki_cache):
+    """Latent caches of one layer from an external prefill in the FP8 wire format (pd_vllm/profiles/mla_nsa.py:
+    16-41, 186-232, then generator.py:419-484): ``kv_raw`` uint8 [seq, 528], ``pe_raw`` uint8 [seq, 128],
+    ``ki_pages`` uint8 [ceil(seq / 64), 8448] are dequantised into rows ``start_pos ..`` of the bf16 caches
+    (the indexer keys also get their Hadamard rotation).  A plane may be None together with its cache."""
+    for t, name in ((kv_raw, "kv_raw"), (pe_raw, "pe_raw"), (ki_pages, "ki_pages")):
+        _need(t, torch.uint8, name, optional=True)
+    for t, name in ((kv_cache, "kv_cache"), (pe_cache, "pe_cache"), (ki_cache, "ki_cache")):
+        _need(t, BF16, name, optional=True)
+    if seq_len == 0:
+        return
+    ref = next(t for t in (kv_cache, pe_cache, ki_cache) if t is not None)
+    if kv_raw is not None and (kv_raw.numel() < seq_len * 528 or kv_cache is None):
+        raise ValueError("kv_raw must hold seq_len rows of 528 bytes and come with kv_cache")
+    if pe_raw is not None and (pe_raw.numel() < seq_len * 128 or pe_cache is None):
+        raise ValueError("pe_raw must hold seq_len rows of 128 bytes and come with pe_cache")
+    if ki_pages is not None and (ki_pages.numel() < (seq_len + 63) // 64 * 8448 or ki_cache is None):
+        raise ValueError("ki_pages must hold ceil(seq_len / 64) pages of 8448 bytes and come with ki_cache")
+    _tb.check(_tb.lib().tilert_inject_cache_fp8_op(_ctx(ref), _p(kv_raw), _p(pe_raw), _p(ki_pages), seq_len, start_pos,
+                                                   ref.shape[-2], _p(kv_cache), _p(pe_cache), _p(ki_cache), _stream()))
+
+
 def argmax_exchange(logits, index_offset, token_out, value_out=None, *, comm=None):
     """Greedy token over a vocabulary split across ranks (the arg-max behind the reference's
     ``PREDICTED_TOKENS``, modules/end2end.py:617-651): ``logits`` [..., S, vocab / world] f32 is this rank's
