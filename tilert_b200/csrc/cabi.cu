@@ -67,7 +67,7 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
 }
 
 constexpr int kMaxGrid = 256;                       // CTAs a GEMV launch may use (>= SM count)
-constexpr size_t kPartialBytes = 2ull * kMaxGrid * 8 * 32 * 16;
+constexpr size_t kPartialBytes = 2ull * kMaxGrid * 8 * 32 * 16;  // = kMaxGrid slots x 4 warps x 32 lanes x 8 words x 8 bytes
 constexpr int kMaxCounters = 1 << 16;               // row tiles * 8
 constexpr size_t kXpackScratchBytes = 2ull << 20;   // activation blocks of the widest K (2048 blocks)
 constexpr int kMaxXBlocks = 1984;                   // X blocks one launch may convert (fits kXpackScratchBytes)
@@ -81,6 +81,7 @@ struct TbContext {
   int num_sms = 0;
   float* partial = nullptr;
   int* counters = nullptr;
+  unsigned long long* launch_calls = nullptr;  // device-resident launch number of the streaming kernel
   int* status = nullptr;
   uint8_t* xpack = nullptr;
   uint8_t* xshared = nullptr;  // X blocks converted inside a streaming launch, shared by its CTAs
@@ -132,6 +133,7 @@ int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
   set_partition(p, grid);
   p.partial = ctx->partial;
   p.counters = ctx->counters;
+  p.launch_calls = ctx->launch_calls;
   p.status = ctx->status;
   if (p.x_mode == X_BF16) {
     const int n_xsegs = p.tiles_per_xseg > 0 ? p.n_tiles / p.tiles_per_xseg : 1;
@@ -246,6 +248,8 @@ extern "C" int tilert_b200_init(int device, TbContext** ctx_out) {
   TB_CUDA(cudaMalloc(&c->partial, kPartialBytes));
   TB_CUDA(cudaMalloc(&c->counters, kMaxCounters * sizeof(int)));
   TB_CUDA(cudaMalloc(&c->status, 256));
+  TB_CUDA(cudaMalloc(&c->launch_calls, 256));
+  TB_CUDA(cudaMemset(c->launch_calls, 0, 256));
   TB_CUDA(cudaMalloc(&c->xpack, kXpackScratchBytes));
   TB_CUDA(cudaMalloc(&c->xshared, kXpackScratchBytes));
   TB_CUDA(cudaMalloc(&c->xflags, kXFlagBytes));
@@ -253,6 +257,7 @@ extern "C" int tilert_b200_init(int device, TbContext** ctx_out) {
   TB_CUDA(cudaMemset(c->xflags, 0, kXFlagBytes));
   TB_CUDA(cudaMalloc(&c->small, kSmallScratchBytes));
   TB_CUDA(cudaMemset(c->counters, 0, kMaxCounters * sizeof(int)));
+  TB_CUDA(cudaMemset(c->partial, 0, kPartialBytes));
   TB_CUDA(cudaMemset(c->status, 0, 256));
   TB_CUDA(cudaMemset(c->xpack, 0, kXpackScratchBytes));
   TB_CUDA(cudaMemset(c->small, 0, kSmallScratchBytes));
@@ -266,6 +271,7 @@ extern "C" int tilert_b200_destroy(TbContext* ctx) {
   cudaSetDevice(ctx->device);
   cudaFree(ctx->partial);
   cudaFree(ctx->counters);
+  cudaFree(ctx->launch_calls);
   cudaFree(ctx->status);
   cudaFree(ctx->xpack);
   cudaFree(ctx->xshared);
@@ -1113,17 +1119,19 @@ extern "C" int tilert_argmax_exchange_op(TbContext* ctx, const float* logits, lo
 }
 
 // ------------------------------------------------------------ allocation-free entry point
-// Scratch for tilert_b200_matvec_fp8_static: partial sums of row tiles that straddle two CTAs
-// (2 * kMaxGrid slots of 4 KB), one arrival counter per 16-row group, a status word, and the shared
-// X blocks of a launch with their ready flags.  It lives in the library image, so every GPU that
-// loads the library holds these ~2.4 MB until exit.
+// Scratch for tilert_b200_matvec_fp8_static: partial sums of row tiles shared by several CTAs
+// (kMaxGrid slots of 8 KB, every word tagged with the launch number), a counter area that is no
+// longer used, a status word, the shared X blocks of a launch with their ready flags, and the launch
+// number itself (last 256 bytes; never cleared, the kernel maintains it).  It lives in the library
+// image, so every GPU that loads the library holds these ~2.4 MB until exit.
 namespace {
 constexpr int kStaticMaxTiles = 1024;                                   // rows <= 131072
 constexpr size_t kStaticCounterBytes = kStaticMaxTiles * 8 * sizeof(int);
 constexpr int kStaticMaxKBlocks = 256;                                  // k <= 32768
 constexpr size_t kStaticXBytes = static_cast<size_t>(kStaticMaxKBlocks) * TB_XBLK_BYTES;   // shared X blocks
 constexpr size_t kStaticXFlagBytes = (kStaticMaxKBlocks + 64) * sizeof(unsigned);           // flags + epoch state
-constexpr size_t kStaticScratchBytes = kPartialBytes + kStaticCounterBytes + 256 + kStaticXFlagBytes + kStaticXBytes;
+constexpr size_t kStaticLaunchCallsOffset = kPartialBytes + kStaticCounterBytes + 256 + kStaticXFlagBytes + kStaticXBytes;
+constexpr size_t kStaticScratchBytes = kStaticLaunchCallsOffset + 256;  // + the launch number (never cleared)
 }  // namespace
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
@@ -1165,8 +1173,8 @@ extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_pac
   float* partial = reinterpret_cast<float*>(view.base);
   int* counters = reinterpret_cast<int*>(view.base + kPartialBytes);
   int* status = reinterpret_cast<int*>(view.base + kPartialBytes + kStaticCounterBytes);
-  // The array keeps whatever the previous call left: the arrival counters and the status word must
-  // start at zero (a call that was cut short would otherwise leave them counting).
+  // The array keeps whatever the previous call left: the status word must start at zero (the partial
+  // sums need no clearing: stale words carry an older launch number).
   // The same goes for the X-block flags and their epoch state, which follow the status word.
   unsigned* xflags = reinterpret_cast<unsigned*>(view.base + kPartialBytes + kStaticCounterBytes + 256);
   uint8_t* xshared = view.base + kPartialBytes + kStaticCounterBytes + 256 + kStaticXFlagBytes;
@@ -1185,6 +1193,7 @@ extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_pac
   set_region(p, 0, n, out, n);
   p.partial = partial;
   p.counters = counters;
+  p.launch_calls = reinterpret_cast<unsigned long long*>(view.base + kStaticLaunchCallsOffset);
   p.status = status;
   p.xs = xshared;
   p.xflag = xflags;

@@ -17,6 +17,7 @@ enum Status : int {
   ST_WAIT_EMPTY_TIMEOUT = 2,  // producer gave up waiting for a free ring slot
   ST_PEER_TIMEOUT = 3,        // all-reduce gave up waiting for a peer's arrival
   ST_BAD_ARGUMENT = 4,
+  ST_SPLIT_TIMEOUT = 5,       // a row tile's owner gave up waiting for another CTA's partial sums
 };
 
 // Upper bound for every spin-wait, in nanoseconds of %globaltimer.

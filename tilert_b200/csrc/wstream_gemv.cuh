@@ -139,8 +139,9 @@ struct GemvParams {
   OutRegion regions[TB_MAX_REGIONS];
   const __nv_bfloat16* residual;  // optional [tokens, n_rows]
   long long residual_stride;
-  float* partial;   // scratch: [2 * grid][8 warps][32 lanes] float4
-  int* counters;    // scratch: [n_tiles * 8], zero before the first launch, self-resetting
+  float* partial;   // scratch: [grid][4 warps][32 lanes][8] 64-bit words {launch number, f32 partial sum}
+  int* counters;    // scratch (unused by the kernel; kept for the layout of the callers' scratch areas)
+  unsigned long long* launch_calls;  // scratch: kArUnit per completed launch that used `partial` (self-maintained)
   int* status;
   unsigned long long* prof;  // optional trace: [grid][16] (see GemvProfSlot)
   AllReduce ar;
@@ -775,6 +776,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     const int eg = warp / kGemvGroupWarps, gw = warp % kGemvGroupWarps;
     unsigned long long ar_epoch = 0;
     if (p.ar.world > 1) ar_epoch = ar_epoch_of(p.ar.state);
+    // tag of this launch's split-tile partial sums (same scheme as the all-reduce's call number: every
+    // CTA adds its share to the counter at its end, after having read it here)
+    const uint32_t split_tag =
+        ar_tag(*reinterpret_cast<const volatile unsigned long long*>(p.launch_calls) / kArUnit);
     const uint32_t lane_base = static_cast<uint32_t>(gw * 32) << 16;
     if (p.x_mode == X_BF16 && units > static_cast<long long>(kGemvStages) * grid) {
       // (Skipped when no CTA has more units than ring slots: the converter warps cover those.)
@@ -800,53 +805,74 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     long long prof_wait = 0, prof_math = 0, prof_units = 0;
     int merge_buf = 0;
 
-    // A tile whose k blocks are spread over several CTAs (group 0 only): publish this CTA's partial
-    // sums; the last CTA to arrive adds all partials in CTA order and finishes the tile.
+    // A tile whose k blocks are spread over several CTAs (group 0 only).  The CTA that holds the tile's
+    // first unit owns it; every other CTA of the tile leaves its partial sums in its own slot as 64-bit
+    // words tagged with the launch number (a tagged word IS the arrival of its value: no fence, no
+    // counter), and the owner, which reaches the tile at the very end of its range, picks them up in
+    // CTA order -- so the result does not depend on timing -- and finishes the tile.  A CTA is a guest
+    // of at most one tile (the one its range starts inside), hence one slot per CTA.
     auto split_tile = [&](int t, const float (&v)[8]) {
       const int tile_u0 = t * p.n_kb, tile_u1 = tile_u0 + p.n_kb;
-      const int c_first = gemv_owner(tile_u0, units, grid);
-      const int c_last = gemv_owner(tile_u1 - 1, units, grid);
-      const int my_slot = 2 * cta + ((u0 / p.n_kb) == t ? 0 : 1);
-      float4* part = reinterpret_cast<float4*>(p.partial);
-      part[((my_slot * 4 + gw) * 32 + lane) * 2] = make_float4(v[0], v[1], v[2], v[3]);
-      part[((my_slot * 4 + gw) * 32 + lane) * 2 + 1] = make_float4(v[4], v[5], v[6], v[7]);
-      // the warp's partials are ordered before lane 0's release by the warp barrier; the acquire half
-      // of the same atomic orders the last arriver's loads behind every other CTA's release
-      __syncwarp();
-      int prev = 0;
-      if (lane == 0)
-        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(&p.counters[t * 8 + gw]) : "memory");
-      prev = __shfl_sync(0xffffffffu, prev, 0);
-      if (prev == c_last - c_first) {
-        float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        // batches of independent loads (a plain loop would pay one L2 round trip per CTA), added in CTA order
-        constexpr int kBatch = 8;
-        for (int cb = c_first; cb <= c_last; cb += kBatch) {
-          float4 v0[kBatch], v1[kBatch];
+      unsigned long long* part = reinterpret_cast<unsigned long long*>(p.partial);
+      if (u0 > tile_u0) {
+        unsigned long long* dst = part + (static_cast<long long>(cta * 4 + gw) * 32 + lane) * 8;
 #pragma unroll
-          for (int j = 0; j < kBatch; ++j) {
-            const int cc = cb + j;
-            if (cc <= c_last) {
-              const int cu0 = static_cast<int>(gemv_range_begin(units, grid, cc));
-              const int slot = 2 * cc + ((cu0 / p.n_kb) == t ? 0 : 1);
-              v0[j] = __ldcg(&part[((slot * 4 + gw) * 32 + lane) * 2]);
-              v1[j] = __ldcg(&part[((slot * 4 + gw) * 32 + lane) * 2 + 1]);
-            } else {
-              v0[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-              v1[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < 8; ++j) {
+          const unsigned long long word = (static_cast<unsigned long long>(split_tag) << 32) | __float_as_uint(v[j]);
+          asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(dst + j), "l"(word) : "memory");
+        }
+        return;
+      }
+      const int c_last = gemv_owner(tile_u1 - 1, units, grid);
+      float sum[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum[j] = v[j];
+      const long long t0 = clock64();
+      constexpr int kBatch = 4;  // guests read per round: independent loads, one L2 round trip
+      for (int cb = cta + 1; cb <= c_last && ok; cb += kBatch) {
+        unsigned long long w[kBatch][8];
+        unsigned pending = 0;
+#pragma unroll
+        for (int g = 0; g < kBatch; ++g)
+          if (cb + g <= c_last) pending |= 1u << g;
+        while (pending != 0u) {
+#pragma unroll
+          for (int g = 0; g < kBatch; ++g) {
+            if ((pending >> g) & 1u) {
+              const unsigned long long* src = part + (static_cast<long long>((cb + g) * 4 + gw) * 32 + lane) * 8;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w[g][j]) : "l"(src + j) : "memory");
             }
           }
 #pragma unroll
-          for (int j = 0; j < kBatch; ++j) {
-            if (cb + j <= c_last) {
-              sum[0] += v0[j].x; sum[1] += v0[j].y; sum[2] += v0[j].z; sum[3] += v0[j].w;
-              sum[4] += v1[j].x; sum[5] += v1[j].y; sum[6] += v1[j].z; sum[7] += v1[j].w;
+          for (int g = 0; g < kBatch; ++g) {
+            if ((pending >> g) & 1u) {
+              bool all = true;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) all = all && static_cast<uint32_t>(w[g][j] >> 32) == split_tag;
+              if (all) pending &= ~(1u << g);
             }
+          }
+          // the warp moves on together (tcgen05.ld later needs all its lanes)
+          pending = __reduce_or_sync(0xffffffffu, pending);
+          if (pending != 0u && (*cta_error != 0 || clock64() - t0 > kWaitBudgetCycles)) {
+            set_status(p.status, ST_SPLIT_TIMEOUT);
+            *cta_error = 1;
+            ok = false;
+            break;
           }
         }
-        if (lane == 0) p.counters[t * 8 + gw] = 0;
-        gemv_epilogue_row(p, t, gw, lane, sum, ar_epoch);
+        if (!ok) break;
+#pragma unroll
+        for (int g = 0; g < kBatch; ++g) {
+          if (cb + g <= c_last) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum[j] += __uint_as_float(static_cast<uint32_t>(w[g][j]));
+          }
+        }
       }
+      if (ok) gemv_epilogue_row(p, t, gw, lane, sum, ar_epoch);
     };
 
     auto finish_tile = [&](int t) {
@@ -940,6 +966,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         p.prof[blockIdx.x * 16 + kGemvProfUnits] = prof_units;
       }
     }
+
+    if (threadIdx.x == 0)
+      asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p.launch_calls), "l"(ar_share(cta, grid)) : "memory");
 
     if (p.ar.world > 1 && eg == 0) {
       // ---- one-shot all-reduce over peer memory, fused behind the streaming loop (group 0) ----
