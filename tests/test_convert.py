@@ -67,3 +67,42 @@ def test_lazy_checkpoint_reader(tmp_path):
         pass
     else:
         raise AssertionError("KeyError expected")
+
+
+def test_convert_writes_the_prediction_layer(tmp_path):
+    """A checkpoint with the multi-token-prediction layer: its decoder layer is packed like the others and its
+    norms / eh_proj land in mtp.safetensors on every rank."""
+    from safetensors.torch import save_file
+
+    a = toy_model_args()
+    hf = tmp_path / "hf"
+    hf.mkdir()
+    sd = _toy_checkpoint(hf, a)
+    li = a.n_layers
+    extra = synthetic.random_layer_state_dict(a, li, "cpu", seed=4)
+    g = torch.Generator().manual_seed(6)
+    p = f"model.layers.{li}"
+    extra[f"{p}.enorm.weight"] = torch.rand(a.dim, generator=g) + 0.5
+    extra[f"{p}.hnorm.weight"] = torch.rand(a.dim, generator=g) + 0.5
+    extra[f"{p}.shared_head.norm.weight"] = torch.rand(a.dim, generator=g) + 0.5
+    extra[f"{p}.eh_proj.weight"] = torch.randn(a.dim, 2 * a.dim, generator=g).to(torch.bfloat16)
+    save_file({k: v.contiguous() for k, v in extra.items()}, str(hf / "model-mtp.safetensors"))
+    index = json.loads((hf / "model.safetensors.index.json").read_text())
+    index["weight_map"].update({k: "model-mtp.safetensors" for k in extra})
+    (hf / "model.safetensors.index.json").write_text(json.dumps(index))
+    sd.update(extra)
+
+    out = tmp_path / "packed"
+    files = convert.convert(str(hf), str(out), a, world=2)
+    assert len(files) == 2 * (3 + 1 + 1)  # three decoder layers, mtp.safetensors, head per rank
+    assert json.loads((out / "manifest.json").read_text())["mtp_layer"] == li
+    for rank in (0, 1):
+        small = convert.load_mtp(out / f"rank{rank}" / "mtp.safetensors", "cpu")
+        assert torch.equal(small["eh_proj"], sd[f"{p}.eh_proj.weight"]) and small["enorm"].dtype == torch.float32
+        assert torch.equal(small["shared_head_norm"], sd[f"{p}.shared_head.norm.weight"])
+        direct = LayerWeights(a, sd, li, "cpu", 2, rank)
+        loaded = convert.load_layer(out / f"rank{rank}" / f"layer_{li:03d}.safetensors", "cpu")
+        assert not loaded.dense and torch.equal(loaded.w_o, direct.w_o) and torch.equal(loaded.w_gu, direct.w_gu)
+    # asking for specific layers leaves the prediction layer out unless it is named
+    files = convert.convert(str(hf), str(tmp_path / "some"), a, world=1, layers=[0], with_head=False)
+    assert len(files) == 1

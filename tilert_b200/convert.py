@@ -5,7 +5,8 @@ each operator's ``device_sharding``: read the HF tensors (e4m3 ``weight`` + f32 
 128x128 block, sharded ``*.safetensors`` with ``model.safetensors.index.json``), shard them for
 ``world`` ranks and write, for every rank, one safetensors file per layer holding the tensors exactly
 as the kernels stream them (``tilert_b200.pack`` formats), plus one file with the embedding, the final
-norm and the rank's slice of the vocabulary head.
+norm and the rank's slice of the vocabulary head.  A checkpoint that carries the multi-token-prediction
+layer (``model.layers.{n_layers}``) also gets that layer's decoder weights and a small ``mtp.safetensors``.
 
     python -m tilert_b200.convert --hf /path/to/DeepSeek-V3.2 --out /path/to/packed --world 8
 
@@ -110,6 +111,35 @@ def load_head(path: str | os.PathLike, device) -> dict[str, torch.Tensor]:
     return {k: v.to(device) for k, v in load_file(str(path)).items()}
 
 
+_MTP_KEYS = {"enorm": "enorm.weight", "hnorm": "hnorm.weight", "eh_proj": "eh_proj.weight",
+             "shared_head_norm": "shared_head.norm.weight"}
+
+
+def has_mtp_layer(ckpt, args: ModelArgs) -> bool:
+    """True when the checkpoint carries the multi-token-prediction layer (``model.layers.{n_layers}``)."""
+    return f"model.layers.{args.n_layers}.eh_proj.weight" in ckpt
+
+
+def save_mtp(sd, args: ModelArgs, path: str | os.PathLike) -> None:
+    """The prediction layer's own small tensors (the role of ``transform_mtp`` in the reference's converter,
+    tilert/models/preprocess/weight_converter.py:405-435): enorm / hnorm / shared_head.norm gains in f32 and
+    eh_proj in bf16, replicated on every rank.  Its decoder layer is written like any other layer; its
+    embedding and head are the main model's."""
+    from safetensors.torch import save_file
+
+    p = f"model.layers.{args.n_layers}"
+    tensors = {name: sd[f"{p}.{key}"].to(torch.bfloat16 if name == "eh_proj" else torch.float32).contiguous()
+               for name, key in _MTP_KEYS.items()}
+    Path(path).parent.mkdir(parents=True, exist_ok=True)
+    save_file(tensors, str(path), metadata={"format": FORMAT, "layer": str(args.n_layers)})
+
+
+def load_mtp(path: str | os.PathLike, device) -> dict[str, torch.Tensor]:
+    from safetensors.torch import load_file
+
+    return {k: v.to(device) for k, v in load_file(str(path)).items()}
+
+
 def convert(hf_dir, out_dir, args: ModelArgs, world: int = 1, layers: list[int] | None = None, device="cpu",
             with_head: bool = True) -> list[str]:
     """Convert ``layers`` (default: all of ``args.n_layers``) for every rank; returns the files written."""
@@ -117,6 +147,9 @@ def convert(hf_dir, out_dir, args: ModelArgs, world: int = 1, layers: list[int] 
     out = Path(out_dir)
     written: list[str] = []
     layer_ids = list(range(args.n_layers)) if layers is None else layers
+    mtp = has_mtp_layer(ckpt, args) and (layers is None or args.n_layers in layers)
+    if mtp and args.n_layers not in layer_ids:
+        layer_ids = layer_ids + [args.n_layers]  # the prediction layer's decoder layer
     for rank in range(world):
         for li in layer_ids:
             lw = LayerWeights(args, ckpt, li, device, world, rank)
@@ -124,11 +157,15 @@ def convert(hf_dir, out_dir, args: ModelArgs, world: int = 1, layers: list[int] 
             save_layer(lw, path)
             written.append(str(path))
             del lw
+        if mtp:
+            path = out / f"rank{rank}" / "mtp.safetensors"
+            save_mtp(ckpt, args, path)
+            written.append(str(path))
         if with_head and "lm_head.weight" in ckpt:
             path = out / f"rank{rank}" / "head.safetensors"
             save_head(ckpt, args, world, rank, path)
             written.append(str(path))
-    manifest = {"format": FORMAT, "world": world, "layers": layer_ids, "dim": args.dim, "n_heads": args.n_heads,
+    manifest = {"format": FORMAT, "world": world, "layers": layer_ids, "mtp_layer": args.n_layers if mtp else None, "dim": args.dim, "n_heads": args.n_heads,
                 "n_routed_experts": args.n_routed_experts}
     (out / "manifest.json").write_text(json.dumps(manifest, indent=1))
     return written
