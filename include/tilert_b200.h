@@ -84,7 +84,9 @@ int tilert_b200_ipc_import(const uint8_t handle[64], void** dev_ptr_out);
 int tilert_b200_ipc_close(void* dev_ptr);
 /* `buffers[r]` is rank r's communication buffer (own allocation for r == rank, imported mapping
  * otherwise), each `tilert_b200_comm_buffer_bytes(world, max_rows)` bytes and zero-filled before
- * any rank's first call. */
+ * any rank's first call.  Every rank must issue the same sequence of all-reduce / exchange operators on
+ * the communicator (same count, same order): a call that no peer matches waits for its bounded time,
+ * sets the status word to 3 and leaves the ranks' call numbers apart for good. */
 int tilert_b200_comm_create(TbContext* ctx, int world, int rank, void* const* buffers, int max_rows,
                             TbComm** comm_out);
 int tilert_b200_comm_destroy(TbComm* comm);
