@@ -69,6 +69,29 @@ int tilert_b200_set_profile(TbContext* ctx, unsigned long long* trace);
 /* Same with room for several launches: `trace` is u64 [n_records][256][16] and the k-th streaming
  * launch after this call writes record k % n_records (one decode step = one record per product). */
 int tilert_b200_set_profile_ring(TbContext* ctx, unsigned long long* trace, int n_records);
+/* Upper bound, in SM clock cycles, of every bounded wait in the library's kernels on the context's device
+ * (default 1e9, about half a second; cycles <= 0 restores it).  A wait that runs out makes its kernel
+ * return early with a status code (tilert_b200_status); tests use a short bound to exercise that path. */
+int tilert_b200_set_wait_budget(TbContext* ctx, long long cycles);
+
+/* ---- chained launches ------------------------------------------------------------------- */
+/* The reference runs a whole decode step as ONE native call (dsa_show_hands,
+ * tilert/models/deepseek_v3_2/modules/end2end.py:99-104,551-558).  Between chain_begin and chain_end the
+ * FP8 product operators below are recorded instead of launched, and chain_end launches them as the
+ * phases of one persistent kernel whose weight stream runs through the phase boundaries (activations of
+ * a phase wait on a grid-wide signal of the phases that produce them).  tilert_rmsnorm_expert_proj_op,
+ * tilert_proj_w_op and tilert_attn_prep_op may be recorded too: they run on spare warps at the start of
+ * the product recorded after them.  Any other operator returns TB_ESTATE while a chain is being recorded.
+ * Limits: 12 products and 3 such operators per chain.  Every CTA of the launch must be resident at once
+ * (as for the single products), so chained launches of different streams must not overlap on a device. */
+int tilert_b200_chain_begin(TbContext* ctx);
+int tilert_b200_chain_end(TbContext* ctx, void* stream);
+int tilert_b200_chain_abort(TbContext* ctx);
+/* Trace of chained launches: while `trace` (device memory, u64 [12][256][8], zeroed by the caller) is set,
+ * epilogue warp 0 of every CTA records per phase the %globaltimer at: dependencies met, norm statistics
+ * ready, hook done, first accumulator complete, last unit read back, tiles reduced, main signal raised;
+ * slot 7 = the CTA's units in the phase.  NULL switches it off. */
+int tilert_b200_set_chain_profile(TbContext* ctx, unsigned long long* trace);
 
 /* ---- peer-to-peer plumbing for the fused all-reduce ------------------------------------ */
 /* The reference exchanges raw buffer addresses between its per-GPU threads
@@ -145,13 +168,14 @@ int tilert_unproj_o_allreduce_op(TbContext* ctx, const void* vec, const uint8_t*
 /* expert_select_up_gate_silu_op (ops/expert_sel_up_gate_silu.py:23-48): routing (sigmoid + bias,
  * group-limited top-k, renormalise, scale) then SiLU(W1 x) * (W3 x) for the shared expert and the
  * selected routed experts.  hidden [tokens, dim] bf16 is the normalised post-attention state
- * (hidden_out of rmsnorm_expert_proj_op).  w_packed: [n_experts + 1] experts, `expert_stride` bytes apart, the
+ * (hidden_out of rmsnorm_expert_proj_op) when gamma == NULL; with gamma (f32 [dim]) it is the raw state
+ * and the RMSNorm (eps) runs inside the launch, so the product need not wait for the router's copy.  w_packed: [n_experts + 1] experts, `expert_stride` bytes apart, the
  * shared expert last; rows of each expert interleave gate and up in groups of 8.
  * hidden_out [tokens, top_k + 1, inter] bf16 (slot 0 = shared expert).
  * slot_ids / slot_w [tokens, top_k + 1]: expert id and weight per slot (inputs of the down op).
  * Under tensor parallelism every rank holds an `inter`-row slice of every expert. */
-int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* hidden, const float* scores,
-                                         const float* bias, const uint8_t* w_packed, long long expert_stride,
+int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* hidden, const float* gamma, float eps,
+                                         const float* scores, const float* bias, const uint8_t* w_packed, long long expert_stride,
                                          int tokens, int dim, int inter, int n_experts, int n_groups,
                                          int n_limited_groups, int top_k, float route_scale, void* hidden_out,
                                          float* probs_out, int* idx_out, int* slot_ids, float* slot_w,

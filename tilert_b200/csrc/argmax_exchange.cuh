@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(kArgmaxThreads, 1) argmax_exchange_kernel(cons
     asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(&p.ar.state->calls), "l"(kArUnit) : "memory");
     const unsigned long long* mine = p.ar.recv[p.ar.rank];
     const long long t0 = clock64();
+    const long long budget = kWaitBudgetCycles;
     for (int t = 0; t < p.n_tokens; ++t) {
       float bv = -INFINITY;
       int bi = 0x7fffffff;
@@ -113,7 +114,7 @@ __global__ void __launch_bounds__(kArgmaxThreads, 1) argmax_exchange_kernel(cons
           wv = ar_peek(&mine[idx]);
           wi = ar_peek(&mine[idx + 1]);
           if (static_cast<uint32_t>(wv >> 32) == tag && static_cast<uint32_t>(wi >> 32) == tag) break;
-          if (clock64() - t0 > kWaitBudgetCycles) {
+          if (clock64() - t0 > budget) {
             set_status(p.status, ST_PEER_TIMEOUT);
             return;
           }

@@ -7,6 +7,7 @@
 #include <cstring>
 #include <string>
 #include <utility>
+#include <vector>
 
 #include "actpack.cuh"
 #include "elementwise.cuh"
@@ -16,6 +17,7 @@
 #include "sparse_mla.cuh"
 #include "sampler.cuh"
 #include "wstream_gemv.cuh"
+#include "wstream_chain.cuh"
 #include "argmax_exchange.cuh"
 #include "cache_inject.cuh"
 
@@ -68,7 +70,7 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
 
 constexpr int kMaxGrid = 256;                       // CTAs a GEMV launch may use (>= SM count)
 constexpr size_t kPartialBytes = 2ull * kMaxGrid * 8 * 32 * 16;  // = kMaxGrid slots x 4 warps x 32 lanes x 8 words x 8 bytes
-constexpr int kMaxCounters = 1 << 16;               // row tiles * 8
+constexpr int kMaxTiles = 1 << 13;                  // row tiles of one streaming product
 constexpr size_t kXpackScratchBytes = 2ull << 20;   // activation blocks of the widest K (2048 blocks)
 constexpr int kMaxXBlocks = 1984;                   // X blocks one launch may convert (fits kXpackScratchBytes)
 constexpr size_t kXFlagBytes = (kMaxXBlocks + 64) * sizeof(unsigned);  // flags, then {epoch, done}
@@ -76,11 +78,32 @@ constexpr size_t kSmallScratchBytes = 64ull << 10;  // slot ids / weights for ro
 
 }  // namespace
 
+// Byte range written by a recorded phase (or its hook) and the signal that says it is complete.
+struct ChainRange {
+  const char* lo;
+  const char* hi;
+  int sig;
+};
+// Streaming products recorded between tilert_b200_chain_begin and tilert_b200_chain_end: they run as the
+// phases of one wstream_chain_kernel launch.
+struct ChainRecorder {
+  bool active = false;
+  ChainParams params;
+  int n_hooks = 0;
+  int pending_hook = -1;  // recorded hook that waits for the next product to attach to
+  int x_blocks = 0;       // shared X blocks handed out so far
+  int n_ar = 0;
+  std::vector<ChainRange> outs;
+};
+
 struct TbContext {
   int device = 0;
   int num_sms = 0;
   float* partial = nullptr;
-  int* counters = nullptr;
+  float* chain_partial = nullptr;      // split-tile slots of chained launches: one region per phase
+  unsigned* chain_signals = nullptr;   // signal counters of chained launches (self-clearing)
+  unsigned long long* chain_prof = nullptr;  // caller-owned trace of chained launches, see tilert_b200_set_chain_profile
+  ChainRecorder rec;
   unsigned long long* launch_calls = nullptr;  // device-resident launch number of the streaming kernel
   int* status = nullptr;
   uint8_t* xpack = nullptr;
@@ -118,21 +141,153 @@ void set_partition(GemvParams& p, int grid) {
   p.whole_tiles = (short_rows || balanced) ? 1 : 0;
 }
 
+// Most units any CTA takes under the launch's partition; decides whether the CTAs share the activation
+// conversion (a CTA converts only the X blocks of its first pass over the ring by itself).
+int max_cta_units(const GemvParams& p, int grid) {
+  if (p.whole_tiles) return (p.n_tiles + grid - 1) / grid * p.n_kb;
+  const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
+  return static_cast<int>((units + grid - 1) / grid);
+}
+
+const char* cptr(const void* p) { return reinterpret_cast<const char*>(p); }
+
+// Highest signal among the recorded outputs that overlap [ptr, ptr + bytes); -1 when nothing recorded writes there.
+int chain_dep(const ChainRecorder& r, const void* ptr, long long bytes) {
+  if (ptr == nullptr || bytes <= 0) return -1;
+  int best = -1;
+  for (const ChainRange& o : r.outs)
+    if (cptr(ptr) < o.hi && cptr(ptr) + bytes > o.lo && o.sig > best) best = o.sig;
+  return best;
+}
+void chain_out(ChainRecorder& r, const void* ptr, long long bytes, int sig) {
+  if (ptr != nullptr && bytes > 0) r.outs.push_back({cptr(ptr), cptr(ptr) + bytes, sig});
+}
+int imax(int a, int b) { return a > b ? a : b; }
+
+int chain_grid(const TbContext* ctx) { return ctx->num_sms < kMaxGrid ? ctx->num_sms : kMaxGrid; }
+
+// Appends a streaming product to the chain being recorded.  Dependencies come from the recorded outputs
+// that the product's inputs overlap: activations, residual and routing weights decide when the activation
+// side may start, slot ids and router scores when the producers may compute weight addresses.
+int record_phase(TbContext* ctx, GemvParams& p) {
+  ChainRecorder& r = ctx->rec;
+  if (r.params.n_phases >= kChainMaxPhases) return fail(TB_ESTATE, "chain: too many products in one chain%s");
+  if (p.x_mode != X_BF16) return fail(TB_EINVAL, "chain: only products on bf16 activations can be chained%s");
+  const int ph = r.params.n_phases;
+  const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
+  const int grid = chain_grid(ctx);
+  p.grid_eff = units < grid ? static_cast<int>(units) : grid;
+  set_partition(p, p.grid_eff);
+  p.shared_x = max_cta_units(p, p.grid_eff) > kGemvStages ? 1 : 0;
+  p.partial = ctx->chain_partial + static_cast<size_t>(ph) * (kPartialBytes / sizeof(float));
+  p.launch_calls = ctx->launch_calls;
+  p.status = ctx->status;
+  p.prof = nullptr;
+  const int n_xsegs = p.tiles_per_xseg > 0 ? p.n_tiles / p.tiles_per_xseg : 1;
+  TB_REQUIRE(p.tiles_per_xseg <= 0 || p.n_tiles % p.tiles_per_xseg == 0);
+  const int n_xblocks = n_xsegs * p.n_kb;
+  if (r.x_blocks + n_xblocks > kMaxXBlocks) return fail(TB_ESTATE, "chain: the chained products need too many X blocks%s");
+  p.xs = ctx->xshared + static_cast<size_t>(r.x_blocks) * TB_XBLK_BYTES;
+  p.xflag = ctx->xflags + r.x_blocks;
+  p.xstate = ctx->xflags + kMaxXBlocks;
+  r.x_blocks += n_xblocks;
+
+  ChainPhase& c = r.params.ph[ph];
+  c.hook = r.pending_hook;
+  r.pending_hook = -1;
+  c.ar_index = r.n_ar;
+  if (p.ar.world > 1) ++r.n_ar;
+  c.main_target = grid;
+
+  // a down projection that reads the slot list an earlier recorded product routes: route it here too, so
+  // that its weight addresses do not wait for that product to finish
+  if (p.kseg_ids != nullptr) {
+    for (int q = 0; q < ph; ++q) {
+      const RouteParams& rq = r.params.ph[q].g.route;
+      if (rq.scores != nullptr && rq.slot_ids == p.kseg_ids) {
+        p.route = rq;
+        p.route.for_kseg = 1;
+        p.route.slot_base = 0;
+        p.route.probs = nullptr;
+        p.kseg_ids = nullptr;
+        break;
+      }
+    }
+  }
+  // activation-side dependencies
+  int dep = chain_dep(r, p.xb, (static_cast<long long>(p.n_tokens - 1) * p.xb_stride + static_cast<long long>(n_xblocks) * TB_KBLOCK) * 2);
+  dep = imax(dep, chain_dep(r, p.residual, (static_cast<long long>(p.n_tokens - 1) * p.residual_stride + p.n_rows) * 2));
+  if (p.seg_scale != nullptr)
+    dep = imax(dep, chain_dep(r, p.seg_scale, static_cast<long long>(p.n_tokens) * (p.n_kb / p.kb_per_kseg) * 4));
+  if (c.hook >= 0) {
+    const ChainHook& h = r.params.hooks[c.hook];
+    if (h.kind == HOOK_ATTN_PREP) {
+      dep = imax(dep, 2 * ph - 2);  // reads cache rows and vectors of every earlier product
+    } else {
+      const GemvBf16Params& q = h.prep.wis;
+      dep = imax(dep, chain_dep(r, q.x, (static_cast<long long>(q.n_tokens - 1) * q.x_stride + q.k) * 2));
+    }
+  }
+  c.wait_sig = dep;
+  // weight-address dependencies
+  int wdep = -1;
+  if (p.nseg_ids != nullptr) wdep = imax(wdep, chain_dep(r, p.nseg_ids, 4ll * (p.n_tiles / p.tiles_per_nseg)));
+  if (p.kseg_ids != nullptr) wdep = imax(wdep, chain_dep(r, p.kseg_ids, 4ll * (p.n_kb / p.kb_per_kseg)));
+  if (p.route.scores != nullptr) {
+    wdep = imax(wdep, chain_dep(r, p.route.scores, 4ll * p.route.n_experts));
+    if (p.route.probs != nullptr) c.main_target = grid + 1;  // producer 0 of CTA 0 stores the routing results
+  }
+  c.w_sig = wdep;
+
+  // outputs
+  for (int i = 0; i < p.n_regions; ++i) {
+    const OutRegion& reg = p.regions[i];
+    if (reg.pos_ptr != nullptr) continue;  // cache rows: only hooks read them, and those wait for every earlier product
+    const long long esz = reg.dtype == 0 ? 2 : 4;
+    chain_out(r, reg.ptr, (static_cast<long long>(p.n_tokens - 1) * reg.token_stride + (reg.row_end - reg.row_begin)) * esz, 2 * ph);
+  }
+  if (p.route.scores != nullptr && p.route.probs != nullptr) {
+    chain_out(r, p.route.probs, 4ll * p.route.top_k, 2 * ph);
+    chain_out(r, p.route.ids, 4ll * p.route.top_k, 2 * ph);
+    chain_out(r, p.route.slot_ids, 4ll * (p.route.top_k + 1), 2 * ph);
+    chain_out(r, p.route.slot_w, 4ll * (p.route.top_k + 1), 2 * ph);
+  }
+  if (c.hook >= 0) {
+    const ChainHook& h = r.params.hooks[c.hook];
+    const GemvBf16Params& q = h.prep.wis;
+    if (q.w != nullptr) {
+      chain_out(r, q.out, (static_cast<long long>(q.n_tokens - 1) * q.out_stride + q.n) * (q.out_bf16 ? 2 : 4), 2 * ph + 1);
+      chain_out(r, q.xnorm_out, (static_cast<long long>(q.n_tokens - 1) * q.xnorm_stride + q.k) * 2, 2 * ph + 1);
+    }
+    if (h.kind == HOOK_ATTN_PREP) {
+      const AttnPrepParams& a = h.prep;
+      chain_out(r, a.q_pe, 2ll * a.n_tokens * a.heads * a.rope, 2 * ph + 1);
+      chain_out(r, a.iq_out, 2ll * a.n_tokens * a.idx_heads * 128, 2 * ph + 1);
+    }
+  }
+  c.g = p;
+  ++r.params.n_phases;
+  return TB_OK;
+}
+
 int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
   static bool attr_set[64] = {};
   if (!attr_set[ctx->device & 63]) {
     TB_CUDA(cudaFuncSetAttribute(wstream_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBytes));
+    TB_CUDA(cudaFuncSetAttribute(wstream_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChainSmemBytes));
     attr_set[ctx->device & 63] = true;
   }
   TB_REQUIRE(p.n_tiles > 0 && p.n_kb > 0);
-  TB_REQUIRE(p.n_tiles * 8 <= kMaxCounters);
+  TB_REQUIRE(p.n_tiles <= kMaxTiles);
   const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
   TB_REQUIRE(units < (1ll << 30));
+  if (ctx->rec.active) return record_phase(ctx, p);
   int grid = ctx->num_sms < kMaxGrid ? ctx->num_sms : kMaxGrid;
   if (units < grid) grid = static_cast<int>(units);
   set_partition(p, grid);
+  p.grid_eff = grid;
+  p.shared_x = max_cta_units(p, grid) > kGemvStages ? 1 : 0;
   p.partial = ctx->partial;
-  p.counters = ctx->counters;
   p.launch_calls = ctx->launch_calls;
   p.status = ctx->status;
   if (p.x_mode == X_BF16) {
@@ -150,6 +305,13 @@ int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
   TB_CUDA(cudaGetLastError());
   return TB_OK;
 }
+
+// Operators that cannot become part of a chained launch refuse to run while one is being recorded.
+#define TB_NOT_CHAINABLE(ctx)                                                                          \
+  do {                                                                                                 \
+    if ((ctx) != nullptr && (ctx)->rec.active)                                                         \
+      return fail(TB_ESTATE, "%s cannot be recorded into a chain (end the chain first)", __func__);    \
+  } while (0)
 
 void gemv_defaults(GemvParams& p) {
   memset(&p, 0, sizeof(p));
@@ -229,7 +391,7 @@ int pack_flat(const void* x, int tokens, int k, const float* seg_scale, int n_se
 extern "C" const char* tilert_b200_last_error(void) { return g_last_error.c_str(); }
 extern "C" int tilert_b200_dsa_temp_vars_size(void) { return 56; }
 extern "C" size_t tilert_b200_context_bytes(void) {
-  return kPartialBytes + kMaxCounters * sizeof(int) + 256 + 2 * kXpackScratchBytes + kXFlagBytes + kSmallScratchBytes;
+  return kPartialBytes * (1 + kChainMaxPhases) + 1024 + 2 * kXpackScratchBytes + kXFlagBytes + kSmallScratchBytes;
 }
 extern "C" size_t tilert_b200_xpack_bytes(int dim) { return static_cast<size_t>(dim / TB_KBLOCK) * TB_XBLK_BYTES; }
 
@@ -246,7 +408,10 @@ extern "C" int tilert_b200_init(int device, TbContext** ctx_out) {
   }
   c->num_sms = prop.multiProcessorCount;
   TB_CUDA(cudaMalloc(&c->partial, kPartialBytes));
-  TB_CUDA(cudaMalloc(&c->counters, kMaxCounters * sizeof(int)));
+  TB_CUDA(cudaMalloc(&c->chain_partial, kPartialBytes * kChainMaxPhases));
+  TB_CUDA(cudaMemset(c->chain_partial, 0, kPartialBytes * kChainMaxPhases));
+  TB_CUDA(cudaMalloc(&c->chain_signals, 256));
+  TB_CUDA(cudaMemset(c->chain_signals, 0, 256));
   TB_CUDA(cudaMalloc(&c->status, 256));
   TB_CUDA(cudaMalloc(&c->launch_calls, 256));
   TB_CUDA(cudaMemset(c->launch_calls, 0, 256));
@@ -256,7 +421,6 @@ extern "C" int tilert_b200_init(int device, TbContext** ctx_out) {
   TB_CUDA(cudaMemset(c->xshared, 0, kXpackScratchBytes));
   TB_CUDA(cudaMemset(c->xflags, 0, kXFlagBytes));
   TB_CUDA(cudaMalloc(&c->small, kSmallScratchBytes));
-  TB_CUDA(cudaMemset(c->counters, 0, kMaxCounters * sizeof(int)));
   TB_CUDA(cudaMemset(c->partial, 0, kPartialBytes));
   TB_CUDA(cudaMemset(c->status, 0, 256));
   TB_CUDA(cudaMemset(c->xpack, 0, kXpackScratchBytes));
@@ -270,7 +434,8 @@ extern "C" int tilert_b200_destroy(TbContext* ctx) {
   if (ctx == nullptr) return TB_OK;
   cudaSetDevice(ctx->device);
   cudaFree(ctx->partial);
-  cudaFree(ctx->counters);
+  cudaFree(ctx->chain_partial);
+  cudaFree(ctx->chain_signals);
   cudaFree(ctx->launch_calls);
   cudaFree(ctx->status);
   cudaFree(ctx->xpack);
@@ -286,7 +451,64 @@ extern "C" int tilert_b200_status(TbContext* ctx, int* status_out) {
   TB_CUDA(cudaSetDevice(ctx->device));
   TB_CUDA(cudaDeviceSynchronize());
   TB_CUDA(cudaMemcpy(status_out, ctx->status, sizeof(int), cudaMemcpyDeviceToHost));
-  if (*status_out != 0) TB_CUDA(cudaMemset(ctx->status, 0, sizeof(int)));
+  if (*status_out != 0) {
+    // a launch that gave up may have left signal counters of a chained launch half-way: start clean
+    TB_CUDA(cudaMemset(ctx->status, 0, sizeof(int)));
+    TB_CUDA(cudaMemset(ctx->chain_signals, 0, 256));
+  }
+  return TB_OK;
+}
+
+extern "C" int tilert_b200_set_wait_budget(TbContext* ctx, long long cycles) {
+  TB_REQUIRE(ctx != nullptr);
+  TB_CUDA(cudaSetDevice(ctx->device));
+  const long long v = cycles > 0 ? cycles : kDefaultWaitBudgetCycles;
+  TB_CUDA(cudaMemcpyToSymbol(g_wait_budget_cycles, &v, sizeof(v)));
+  return TB_OK;
+}
+
+// ------------------------------------------------------------------------------ chained launches
+extern "C" int tilert_b200_chain_begin(TbContext* ctx) {
+  TB_REQUIRE(ctx != nullptr);
+  if (ctx->rec.active) return fail(TB_ESTATE, "chain: a chain is already being recorded%s");
+  ChainRecorder& r = ctx->rec;
+  memset(&r.params, 0, sizeof(r.params));
+  r.n_hooks = 0;
+  r.pending_hook = -1;
+  r.x_blocks = 0;
+  r.n_ar = 0;
+  r.outs.clear();
+  r.active = true;
+  return TB_OK;
+}
+
+extern "C" int tilert_b200_chain_abort(TbContext* ctx) {
+  TB_REQUIRE(ctx != nullptr);
+  ctx->rec.active = false;
+  return TB_OK;
+}
+
+extern "C" int tilert_b200_chain_end(TbContext* ctx, void* stream) {
+  TB_REQUIRE(ctx != nullptr);
+  ChainRecorder& r = ctx->rec;
+  if (!r.active) return fail(TB_ESTATE, "chain: no chain is being recorded%s");
+  r.active = false;
+  if (r.pending_hook >= 0) return fail(TB_ESTATE, "chain: the last recorded operator needs a following product to attach to%s");
+  if (r.params.n_phases == 0) return TB_OK;
+  r.params.signals = ctx->chain_signals;
+  r.params.prof = ctx->chain_prof;
+  static_assert(sizeof(ChainParams) <= 24 * 1024, "kernel parameter space");
+  static_assert(kChainSignals + 1 <= 64, "signal area");
+  TB_CUDA(launch(wstream_chain_kernel, dim3(chain_grid(ctx)), dim3(kGemvThreads), kChainSmemBytes,
+                 static_cast<cudaStream_t>(stream), r.params));
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
+}
+
+extern "C" int tilert_b200_set_chain_profile(TbContext* ctx, unsigned long long* trace) {
+  TB_REQUIRE(ctx != nullptr);
+  ctx->chain_prof = trace;
   return TB_OK;
 }
 
@@ -367,6 +589,7 @@ extern "C" int tilert_b200_comm_destroy(TbComm* comm) {
 extern "C" int tilert_rmsnorm_quant_op(TbContext* ctx, const void* x, const float* gamma, float eps, int tokens,
                                        int dim, void* out, uint8_t* q_out, float* q_scale_out,
                                        const float* seg_scale, int n_seg, uint8_t* xpack, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && x != nullptr);
   TB_REQUIRE((q_out == nullptr) == (q_scale_out == nullptr));
   if (xpack == nullptr) xpack = ctx->xpack;  // caller only wants the bf16 / reference-format outputs
@@ -392,6 +615,7 @@ extern "C" int tilert_rmsnorm_quant_op(TbContext* ctx, const void* x, const floa
 
 extern "C" int tilert_xq_repack_op(TbContext* ctx, const uint8_t* x_q, const float* x_scale, int tokens, int dim,
                                    uint8_t* xpack, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && x_q != nullptr && x_scale != nullptr && xpack != nullptr);
   TB_REQUIRE(dim % TB_KBLOCK == 0 && tokens >= 1 && tokens <= 8);
   const int n_kb = dim / TB_KBLOCK;
@@ -540,8 +764,8 @@ extern "C" int tilert_unproj_o_allreduce_op(TbContext* ctx, const void* vec, con
   return launch_gemv(ctx, p, st);
 }
 
-extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* hidden, const float* scores,
-                                                    const float* bias, const uint8_t* w_packed,
+extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* hidden, const float* gamma, float eps,
+                                                    const float* scores, const float* bias, const uint8_t* w_packed,
                                                     long long expert_stride, int tokens, int dim, int inter,
                                                     int n_experts, int n_groups, int n_limited_groups, int top_k,
                                                     float route_scale, void* hidden_out, float* probs_out,
@@ -553,6 +777,59 @@ extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (slot_ids == nullptr) slot_ids = reinterpret_cast<int*>(ctx->small);
   if (slot_w == nullptr) slot_w = reinterpret_cast<float*>(ctx->small + 4096);
+  const int n_slots = top_k + 1;
+  auto base = [&](GemvParams& p) {
+    gemv_defaults(p);
+    p.w = w_packed;
+    set_x_bf16(p, hidden, dim, gamma, eps);
+    p.tiles_per_nseg = 2 * inter / TB_TILE_ROWS;
+    p.n_kb = dim / TB_KBLOCK;
+    p.w_kb_per_tile = p.n_kb;
+    p.expert_stride = expert_stride;
+    p.n_tokens = tokens;
+    p.epi = EPI_SILU_MUL;
+  };
+  auto route = [&](GemvParams& p, int t) {
+    p.route.scores = scores + static_cast<long long>(t) * n_experts;
+    p.route.bias = bias;
+    p.route.n_experts = n_experts;
+    p.route.n_groups = n_groups;
+    p.route.n_limited = n_limited_groups;
+    p.route.top_k = top_k;
+    p.route.route_scale = route_scale;
+    p.route.shared_id = n_experts;
+    p.route.probs = probs_out + t * top_k;
+    p.route.ids = idx_out + t * top_k;
+    p.route.slot_ids = slot_ids + t * n_slots;
+    p.route.slot_w = slot_w + t * n_slots;
+  };
+  if (ctx->rec.active) {
+    // Chained: the shared expert (static addresses, every token at once) is a phase of its own, so that
+    // the stream covers the routing; then one phase per token for its routed experts, each routed by the
+    // producer warps themselves.
+    GemvParams ps;
+    base(ps);
+    ps.w = w_packed + static_cast<long long>(n_experts) * expert_stride;
+    ps.tiles_per_nseg = 0;
+    ps.n_tiles = 2 * inter / TB_TILE_ROWS;
+    ps.n_rows = inter;
+    set_region(ps, 0, inter, hidden_out, static_cast<long long>(n_slots) * inter);
+    int rc = launch_gemv(ctx, ps, st);
+    if (rc != TB_OK) return rc;
+    for (int t = 0; t < tokens; ++t) {
+      GemvParams p;
+      base(p);
+      route(p, t);
+      p.route.slot_base = 1;
+      p.n_tiles = top_k * p.tiles_per_nseg;
+      p.only_token = tokens > 1 ? t : -1;
+      p.n_rows = top_k * inter;
+      set_region(p, 0, p.n_rows, reinterpret_cast<__nv_bfloat16*>(hidden_out) + inter, static_cast<long long>(n_slots) * inter);
+      rc = launch_gemv(ctx, p, st);
+      if (rc != TB_OK) return rc;
+    }
+    return TB_OK;
+  }
   // One token: the product launch routes the token itself.  Several tokens: a routing launch first,
   // then one product launch per token (each token has its own expert list).
   const bool route_in_kernel = tokens == 1;
@@ -562,36 +839,15 @@ extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* 
     ++g_launches;
     TB_CUDA(cudaGetLastError());
   }
-  const int n_slots = top_k + 1;
   for (int t = 0; t < tokens; ++t) {
     GemvParams p;
-    gemv_defaults(p);
-    p.w = w_packed;
-    set_x_bf16(p, hidden, dim);
-    p.tiles_per_nseg = 2 * inter / TB_TILE_ROWS;
+    base(p);
     p.n_tiles = n_slots * p.tiles_per_nseg;
-    p.n_kb = dim / TB_KBLOCK;
-    p.w_kb_per_tile = p.n_kb;
-    if (route_in_kernel) {
-      p.route.scores = scores;
-      p.route.bias = bias;
-      p.route.n_experts = n_experts;
-      p.route.n_groups = n_groups;
-      p.route.n_limited = n_limited_groups;
-      p.route.top_k = top_k;
-      p.route.route_scale = route_scale;
-      p.route.shared_id = n_experts;
-      p.route.probs = probs_out;
-      p.route.ids = idx_out;
-      p.route.slot_ids = slot_ids;
-      p.route.slot_w = slot_w;
-    } else {
+    if (route_in_kernel)
+      route(p, 0);
+    else
       p.nseg_ids = slot_ids + t * n_slots;
-    }
-    p.expert_stride = expert_stride;
-    p.n_tokens = tokens;
     p.only_token = tokens > 1 ? t : -1;
-    p.epi = EPI_SILU_MUL;
     p.n_rows = n_slots * inter;
     set_region(p, 0, p.n_rows, hidden_out, p.n_rows);
     int rc = launch_gemv(ctx, p, st);
@@ -665,9 +921,31 @@ extern "C" int tilert_down_allreduce_op(TbContext* ctx, const void* vec, const u
 
 // ------------------------------------------------------------------------------ bf16 products
 namespace {
+// Small per-token work recorded into a chain: it runs on the epilogue warps at the start of the next
+// recorded product, once that product's (and the hook's own) inputs are complete.
+int record_hook(TbContext* ctx, int kind, const AttnPrepParams& prep) {
+  ChainRecorder& r = ctx->rec;
+  if (r.pending_hook >= 0) return fail(TB_ESTATE, "chain: two hook operators in a row (a product must follow each)%s");
+  if (r.n_hooks >= kChainMaxHooks) return fail(TB_ESTATE, "chain: too many hook operators in one chain%s");
+  const GemvBf16Params& q = prep.wis;
+  if (q.w != nullptr) {
+    TB_REQUIRE(q.n_tokens >= 1 && q.n_tokens <= 4 && q.k % 256 == 0 && q.k <= 8192 && q.n <= 4096 && q.x2 == nullptr);
+  }
+  ChainHook& h = r.params.hooks[r.n_hooks];
+  h.kind = kind;
+  h.prep = prep;
+  r.pending_hook = r.n_hooks++;
+  return TB_OK;
+}
+
 int launch_gemv_bf16(TbContext* ctx, GemvBf16Params& p, cudaStream_t st) {
   TB_REQUIRE(p.n_tokens >= 1 && p.n_tokens <= 4);
   TB_REQUIRE(p.k % 256 == 0);
+  if (ctx->rec.active) {
+    AttnPrepParams prep{};
+    prep.wis = p;
+    return record_hook(ctx, HOOK_ROWS, prep);
+  }
   const int tok_t = p.n_tokens == 1 ? 1 : (p.n_tokens == 2 ? 2 : 4);
   const size_t smem = static_cast<size_t>(tok_t) * p.k * sizeof(float);
   const int warps = kGemvBf16Threads / 32;
@@ -826,6 +1104,7 @@ extern "C" int tilert_mtp_preprocess_op(TbContext* ctx, const void* e, const voi
 // -------------------------------------------------------------------- per-token vector operators
 extern "C" int tilert_rmsnorm_kv_op(TbContext* ctx, const void* kv, const float* gamma, float eps, int tokens,
                                     int dim, const int* cur_pos, void* kv_cache, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && kv != nullptr && gamma != nullptr && cur_pos != nullptr && kv_cache != nullptr);
   rmsnorm_kv_kernel<<<(tokens + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(kv), dim, gamma, eps, dim, cur_pos,
@@ -837,6 +1116,7 @@ extern "C" int tilert_rmsnorm_kv_op(TbContext* ctx, const void* kv, const float*
 
 extern "C" int tilert_qkv_rope_op(TbContext* ctx, void* q_pe, int heads, int rope, void* pe_cache,
                                   const int* cur_pos, const float* freqs, int tokens, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && q_pe != nullptr && pe_cache != nullptr && cur_pos != nullptr && freqs != nullptr);
   const int total = tokens * (heads + 1) * (rope / 2);
   qkv_rope_kernel<<<(total + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -849,6 +1129,7 @@ extern "C" int tilert_qkv_rope_op(TbContext* ctx, void* q_pe, int heads, int rop
 
 extern "C" int tilert_rotate_op(TbContext* ctx, const void* in, void* out, int heads, int rope, const float* freqs,
                                 int tokens, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && in != nullptr && out != nullptr && freqs != nullptr);
   TB_REQUIRE(rope == 64);
   const int vecs = tokens * heads;
@@ -863,6 +1144,7 @@ extern "C" int tilert_rotate_op(TbContext* ctx, const void* in, void* out, int h
 extern "C" int tilert_layernorm_rope_rotate_op(TbContext* ctx, const void* in, const int* cur_pos, void* k_cache,
                                                const float* weight, const float* bias, const float* freqs, int rope,
                                                int tokens, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && in != nullptr && cur_pos != nullptr && k_cache != nullptr);
   TB_REQUIRE(weight != nullptr && bias != nullptr && freqs != nullptr && rope == 64);
   rotate128_kernel<<<(tokens + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -929,6 +1211,13 @@ extern "C" int tilert_attn_prep_op(TbContext* ctx, const void* x, const float* i
     TB_CUDA(cudaFuncSetAttribute(attn_prep_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr_set[ctx->device & 63] = true;
   }
+  if (ctx->rec.active) {
+    // in a chain the rotary table and the epilogue warps' 256 threads stand in for the kernel's blocks
+    constexpr int kEpi = kGemvEpilogueThreads;
+    p.rope_blocks = (tokens * (heads + 1) * (rope / 2) + kEpi - 1) / kEpi;
+    static_assert(kGemvEpilogueThreads == kAttnPrepThreads, "hook blocks are sized like the kernel's");
+    return record_hook(ctx, HOOK_ATTN_PREP, p);
+  }
   const int grid = p.wis_blocks + p.kv_blocks + p.rope_blocks + p.iq_blocks + p.ki_blocks;
   const int tok = tokens == 1 ? 1 : (tokens == 2 ? 2 : 4);
   const size_t smem = static_cast<size_t>(tok) * dim * sizeof(float);
@@ -948,6 +1237,7 @@ extern "C" int tilert_attn_prep_op(TbContext* ctx, const void* x, const float* i
 extern "C" int tilert_sparse_index_op(TbContext* ctx, const void* q, const void* k_cache, const void* weights,
                                       float* logits, long long logits_stride, int heads, int tokens, int n_keys,
                                       const int* cur_pos, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && q != nullptr && k_cache != nullptr && weights != nullptr && logits != nullptr);
   TB_REQUIRE(cur_pos != nullptr && n_keys > 0 && (heads == 16 || heads == 32 || heads == 64));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -969,6 +1259,7 @@ extern "C" int tilert_sparse_index_op(TbContext* ctx, const void* q, const void*
 
 extern "C" int tilert_topk_accurate_op(TbContext* ctx, const float* logits, long long logits_stride, int rows, int n,
                                        int k, int* indices, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && logits != nullptr && indices != nullptr && rows >= 1 && n >= 0 && k >= 1);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long out_stride = k;
@@ -999,6 +1290,7 @@ extern "C" int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const v
                                           const void* k_pe, const int* indices, int topk, const int* cur_pos,
                                           int heads, int tokens, int n_cache, float softmax_scale, int split_size,
                                           void* out, float* out_acc, float* lse, float* lse_acc, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && q != nullptr && q_pe != nullptr && kv != nullptr && k_pe != nullptr);
   TB_REQUIRE(indices != nullptr && cur_pos != nullptr && out != nullptr && out_acc != nullptr && lse_acc != nullptr);
   TB_REQUIRE(split_size > 0 && split_size % kMlaKeys == 0 && topk > 0);
@@ -1040,6 +1332,7 @@ extern "C" int tilert_sample_op(TbContext* ctx, const float* logits, long long l
                                 const float* config_dev, unsigned long long seed, unsigned long long* step_dev,
                                 unsigned long long step_value, int* token_out, float* token_logprob_out,
                                 float* topn_logprob_out, int* topn_index_out, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && logits != nullptr && config_dev != nullptr && token_out != nullptr);
   TB_REQUIRE(tokens >= 1 && vocab >= 1 && logits_stride >= vocab);
   TB_REQUIRE((topn_logprob_out == nullptr) == (topn_index_out == nullptr));
@@ -1065,6 +1358,7 @@ extern "C" int tilert_sample_op(TbContext* ctx, const float* logits, long long l
 extern "C" int tilert_inject_cache_fp8_op(TbContext* ctx, const uint8_t* kv_raw, const uint8_t* pe_raw,
                                           const uint8_t* ki_pages, int seq_len, int start_pos, int cache_rows,
                                           void* kv_cache, void* pe_cache, void* ki_cache, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && seq_len >= 0 && start_pos >= 0 && start_pos + seq_len <= cache_rows);
   TB_REQUIRE((kv_raw == nullptr) == (kv_cache == nullptr) && (pe_raw == nullptr) == (pe_cache == nullptr) &&
              (ki_pages == nullptr) == (ki_cache == nullptr));
@@ -1091,6 +1385,7 @@ extern "C" int tilert_inject_cache_fp8_op(TbContext* ctx, const uint8_t* kv_raw,
 extern "C" int tilert_argmax_exchange_op(TbContext* ctx, const float* logits, long long logits_stride, int tokens,
                                          int n_local, int index_offset, TbComm* comm, long long* token_out,
                                          float* value_out, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && logits != nullptr && token_out != nullptr);
   TB_REQUIRE(tokens >= 1 && tokens <= 4 && n_local >= 1 && logits_stride >= n_local && index_offset >= 0);
   ArgmaxParams p{};
@@ -1120,17 +1415,16 @@ extern "C" int tilert_argmax_exchange_op(TbContext* ctx, const float* logits, lo
 
 // ------------------------------------------------------------ allocation-free entry point
 // Scratch for tilert_b200_matvec_fp8_static: partial sums of row tiles shared by several CTAs
-// (kMaxGrid slots of 8 KB, every word tagged with the launch number), a counter area that is no
-// longer used, a status word, the shared X blocks of a launch with their ready flags, and the launch
-// number itself (last 256 bytes; never cleared, the kernel maintains it).  It lives in the library
-// image, so every GPU that loads the library holds these ~2.4 MB until exit.
+// (kMaxGrid slots of 8 KB, every word tagged with the launch number), a status word, the ready flags
+// of a launch's shared X blocks with their epoch, the X blocks themselves, and the launch number
+// (last 256 bytes; never cleared, the kernel maintains it).  It lives in the library image, so every
+// GPU that loads the library holds these ~2.4 MB until exit.
 namespace {
 constexpr int kStaticMaxTiles = 1024;                                   // rows <= 131072
-constexpr size_t kStaticCounterBytes = kStaticMaxTiles * 8 * sizeof(int);
 constexpr int kStaticMaxKBlocks = 256;                                  // k <= 32768
 constexpr size_t kStaticXBytes = static_cast<size_t>(kStaticMaxKBlocks) * TB_XBLK_BYTES;   // shared X blocks
 constexpr size_t kStaticXFlagBytes = (kStaticMaxKBlocks + 64) * sizeof(unsigned);           // flags + epoch state
-constexpr size_t kStaticLaunchCallsOffset = kPartialBytes + kStaticCounterBytes + 256 + kStaticXFlagBytes + kStaticXBytes;
+constexpr size_t kStaticLaunchCallsOffset = kPartialBytes + 256 + kStaticXFlagBytes + kStaticXBytes;
 constexpr size_t kStaticScratchBytes = kStaticLaunchCallsOffset + 256;  // + the launch number (never cleared)
 }  // namespace
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
@@ -1171,14 +1465,13 @@ extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_pac
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* partial = reinterpret_cast<float*>(view.base);
-  int* counters = reinterpret_cast<int*>(view.base + kPartialBytes);
-  int* status = reinterpret_cast<int*>(view.base + kPartialBytes + kStaticCounterBytes);
+  int* status = reinterpret_cast<int*>(view.base + kPartialBytes);
   // The array keeps whatever the previous call left: the status word must start at zero (the partial
   // sums need no clearing: stale words carry an older launch number).
   // The same goes for the X-block flags and their epoch state, which follow the status word.
-  unsigned* xflags = reinterpret_cast<unsigned*>(view.base + kPartialBytes + kStaticCounterBytes + 256);
-  uint8_t* xshared = view.base + kPartialBytes + kStaticCounterBytes + 256 + kStaticXFlagBytes;
-  TB_CUDA(cudaMemsetAsync(counters, 0, kStaticCounterBytes + 256 + kStaticXFlagBytes, st));
+  unsigned* xflags = reinterpret_cast<unsigned*>(view.base + kPartialBytes + 256);
+  uint8_t* xshared = view.base + kPartialBytes + 256 + kStaticXFlagBytes;
+  TB_CUDA(cudaMemsetAsync(status, 0, 256 + kStaticXFlagBytes, st));
   GemvParams p;
   gemv_defaults(p);
   p.w = w_packed;
@@ -1192,7 +1485,6 @@ extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_pac
   p.residual_stride = n;
   set_region(p, 0, n, out, n);
   p.partial = partial;
-  p.counters = counters;
   p.launch_calls = reinterpret_cast<unsigned long long*>(view.base + kStaticLaunchCallsOffset);
   p.status = status;
   p.xs = xshared;
@@ -1202,6 +1494,8 @@ extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_pac
   int grid = view.num_sms < kMaxGrid ? view.num_sms : kMaxGrid;
   if (units < grid) grid = static_cast<int>(units);
   set_partition(p, grid);
+  p.grid_eff = grid;
+  p.shared_x = max_cta_units(p, grid) > kGemvStages ? 1 : 0;
   TB_CUDA(launch(wstream_gemv_kernel, dim3(grid), dim3(kGemvThreads), kGemvSmemBytes, st, p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());

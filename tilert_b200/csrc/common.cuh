@@ -18,10 +18,8 @@ enum Status : int {
   ST_PEER_TIMEOUT = 3,        // all-reduce gave up waiting for a peer's arrival
   ST_BAD_ARGUMENT = 4,
   ST_SPLIT_TIMEOUT = 5,       // a row tile's owner gave up waiting for another CTA's partial sums
+  ST_CHAIN_TIMEOUT = 6,       // a phase of a chained launch gave up waiting for an earlier phase's signal
 };
-
-// Upper bound for every spin-wait, in nanoseconds of %globaltimer.
-constexpr unsigned long long kWaitBudgetNs = 2000000000ull;
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
@@ -75,7 +73,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // counted on the SM's cycle counter, read only after a batch of failed polls: reading %globaltimer
 // costs about as much as a whole pipeline stage, and a waiting consumer is the normal state of a
 // bandwidth-bound kernel.
-constexpr long long kWaitBudgetCycles = 1000000000ll;  // about half a second at ~2 GHz
+constexpr long long kDefaultWaitBudgetCycles = 1000000000ll;  // about half a second at ~2 GHz
+// The budget lives in device memory so that a host call can shorten it (tilert_b200_set_wait_budget);
+// it is read only on the slow path of a wait, after a few hundred failed polls.
+__device__ long long g_wait_budget_cycles = kDefaultWaitBudgetCycles;
+__device__ __forceinline__ long long wait_budget_cycles() {
+  return *reinterpret_cast<const volatile long long*>(&g_wait_budget_cycles);
+}
+#define kWaitBudgetCycles (::tb::wait_budget_cycles())
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 #pragma unroll 1
   for (int i = 0; i < 32; ++i)
@@ -130,13 +135,6 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
 }
 
 // ---- warp MMA ----
-// D(16x8,f32) += A(16x32,e4m3,row) * B(32x8,e4m3,col)
-__device__ __forceinline__ void mma_e4m3_16832(float (&d)[4], const uint4& a, const uint2& b) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y));
-}
 // D(16x8,f32) += A(16x16,bf16,row) * B(16x8,bf16,col)
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile(
@@ -147,16 +145,6 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(smem_u32(smem_row)));
-}
-__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], const void* smem_row) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
-               : "=r"(r[0]), "=r"(r[1])
-               : "r"(smem_u32(smem_row)));
-}
-__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], const void* smem_row) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
-               : "=r"(r[0]), "=r"(r[1])
                : "r"(smem_u32(smem_row)));
 }
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {

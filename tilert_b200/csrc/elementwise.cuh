@@ -7,6 +7,13 @@
 
 namespace tb {
 
+// Activations may have been written earlier in the SAME launch by other thread blocks (the chained
+// streaming launch runs these routines between its products): they are read with L2-only loads, never
+// through the non-coherent path a `const __restrict__` pointer would allow.
+__device__ __forceinline__ float ld_act(const __nv_bfloat16* p) {
+  return bf16_bits_to_f32(__ldcg(reinterpret_cast<const unsigned short*>(p)));
+}
+
 // kv [tokens, dim] -> cache[pos + t, dim] = bf16(rmsnorm(kv) * gamma).   One warp per token.
 __device__ __forceinline__ void rmsnorm_kv_warp(int tok, const __nv_bfloat16* __restrict__ kv, long long kv_stride,
                                                 const float* __restrict__ gamma, float eps, int dim,
@@ -26,7 +33,7 @@ __device__ __forceinline__ void rmsnorm_kv_warp(int tok, const __nv_bfloat16* __
     for (int v = 0; v < kMaxV; ++v) {
       if (v < nv) {
         const int e = (v * 32 + lane) * 8;
-        raw[v] = *reinterpret_cast<const uint4*>(x + e);
+        raw[v] = __ldcg(reinterpret_cast<const uint4*>(x + e));
         g0[v] = *reinterpret_cast<const float4*>(gamma + e);
         g1[v] = *reinterpret_cast<const float4*>(gamma + e + 4);
       }
@@ -63,12 +70,12 @@ __device__ __forceinline__ void rmsnorm_kv_warp(int tok, const __nv_bfloat16* __
   }
   float ss = 0.f;
   for (int i = lane; i < dim; i += 32) {
-    const float v = bf2f(x[i]);
+    const float v = ld_act(x + i);
     ss += v * v;
   }
   ss = warp_sum(ss);
   const float rinv = rsqrtf(ss / static_cast<float>(dim) + eps);
-  for (int i = lane; i < dim; i += 32) dst[i] = f2bf(bf2f(x[i]) * rinv * gamma[i]);
+  for (int i = lane; i < dim; i += 32) dst[i] = f2bf(ld_act(x + i) * rinv * gamma[i]);
 }
 __global__ void rmsnorm_kv_kernel(const __nv_bfloat16* __restrict__ kv, long long kv_stride,
                                   const float* __restrict__ gamma, float eps, int dim, const int* __restrict__ pos,
@@ -140,7 +147,7 @@ __device__ __forceinline__ void rotate128_warp(int vec, const __nv_bfloat16* __r
   const __nv_bfloat16* x = in + static_cast<long long>(vec) * 128;
   float v[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) v[j] = bf2f(x[lane * 4 + j]);
+  for (int j = 0; j < 4; ++j) v[j] = ld_act(x + lane * 4 + j);
   if (ln_w != nullptr) {
     float s = warp_sum(v[0] + v[1] + v[2] + v[3]);
     const float mean = s * (1.0f / 128.0f);
@@ -199,7 +206,7 @@ __device__ __forceinline__ void expert_select_warp(const float* __restrict__ sco
   for (int j = 0; j < 8; ++j) {
     const int e = lane * per_lane + j;
     if (j < per_lane && e < n_experts) {
-      const float s = 1.0f / (1.0f + expf(-scores[e]));
+      const float s = 1.0f / (1.0f + expf(-__ldcg(scores + e)));
       orig[j] = s;
       sel[j] = bias != nullptr ? s + bias[e] : s;
     } else {

@@ -101,6 +101,8 @@ struct RouteParams {
   int n_experts, n_groups, n_limited, top_k;
   float route_scale;
   int shared_id;        // slot 0: the shared expert's index in the packed expert array
+  int slot_base;        // first slot of the list (shared expert, selected experts...) this launch's row segments use
+  int for_kseg;         // 1: the slot list indexes the K segments (down projection) instead of the row segments
   float* probs;         // [top_k]
   int* ids;             // [top_k]
   int* slot_ids;        // [top_k + 1]
@@ -131,6 +133,8 @@ struct GemvParams {
   int tiles_per_xseg;
   int n_tokens;
   int whole_tiles;       // 1: CTAs take whole row tiles (set by the host when that balances well enough)
+  int shared_x;          // X_BF16: 1 when some CTA has more units than ring slots, so the CTAs share the conversion
+  int grid_eff;          // chained launches: CTAs that take units of this phase (min(grid, units)); the rest idle through it
   int only_token;        // >= 0: store only this token's results (per-token expert lists)
   int cols_per_token;
   int epi;
@@ -140,7 +144,6 @@ struct GemvParams {
   const __nv_bfloat16* residual;  // optional [tokens, n_rows]
   long long residual_stride;
   float* partial;   // scratch: [grid][4 warps][32 lanes][8] 64-bit words {launch number, f32 partial sum}
-  int* counters;    // scratch (unused by the kernel; kept for the layout of the callers' scratch areas)
   unsigned long long* launch_calls;  // scratch: kArUnit per completed launch that used `partial` (self-maintained)
   int* status;
   unsigned long long* prof;  // optional trace: [grid][16] (see GemvProfSlot)
@@ -781,7 +784,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
     const uint32_t split_tag =
         ar_tag(*reinterpret_cast<const volatile unsigned long long*>(p.launch_calls) / kArUnit);
     const uint32_t lane_base = static_cast<uint32_t>(gw * 32) << 16;
-    if (p.x_mode == X_BF16 && units > static_cast<long long>(kGemvStages) * grid) {
+    if (p.x_mode == X_BF16 && p.shared_x) {
       // (Skipped when no CTA has more units than ring slots: the converter warps cover those.)
       // This CTA's share of the launch's X blocks, while the ring fills: block c, c + grid, ...,
       // spread over the eight epilogue warps; each block's flag is raised behind its stores.
@@ -828,6 +831,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
 #pragma unroll
       for (int j = 0; j < 8; ++j) sum[j] = v[j];
       const long long t0 = clock64();
+      const long long budget = kWaitBudgetCycles;
       constexpr int kBatch = 4;  // guests read per round: independent loads, one L2 round trip
       for (int cb = cta + 1; cb <= c_last && ok; cb += kBatch) {
         unsigned long long w[kBatch][8];
@@ -856,7 +860,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           }
           // the warp moves on together (tcgen05.ld later needs all its lanes)
           pending = __reduce_or_sync(0xffffffffu, pending);
-          if (pending != 0u && (*cta_error != 0 || clock64() - t0 > kWaitBudgetCycles)) {
+          if (pending != 0u && (*cta_error != 0 || clock64() - t0 > budget)) {
             set_status(p.status, ST_SPLIT_TIMEOUT);
             *cta_error = 1;
             ok = false;
@@ -984,6 +988,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       const int e0 = static_cast<int>(static_cast<long long>(total) * cta / grid);
       const int e1 = static_cast<int>(static_cast<long long>(total) * (cta + 1) / grid);
       const long long t0 = clock64();
+      const long long budget = kWaitBudgetCycles;
       bool alive = ok && !*cta_error;
       for (int e = e0 + static_cast<int>(threadIdx.x); e < e1 && alive; e += kGemvGroupThreads) {
         const int tok = e / p.n_rows, row = e % p.n_rows;
@@ -1001,7 +1006,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
               }
             }
           }
-          if (pending != 0u && clock64() - t0 > kWaitBudgetCycles) {
+          if (pending != 0u && clock64() - t0 > budget) {
             set_status(p.status, ST_PEER_TIMEOUT);
             alive = false;
             break;

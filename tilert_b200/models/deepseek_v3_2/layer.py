@@ -12,6 +12,7 @@ products (o_proj, down_proj) reduce inside their kernels.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -193,6 +194,8 @@ class DecoderLayer:
         # parity tests to separate the discrete selection from the floating-point path.
         self.injected_sel: torch.Tensor | None = None
         self.scale = softmax_scale(a)
+        # Products of a step run as two chained persistent launches (TILERT_B200_CHAIN=0: one launch each)
+        self.chained = os.environ.get("TILERT_B200_CHAIN", "1") != "0"
 
     def inject_cache(self, ki: torch.Tensor, kv: torch.Tensor, pe: torch.Tensor, start_pos: int = 0) -> None:
         """Rows ``start_pos ..`` of the three caches from bf16 tensors [seq, 128 / 512 / 64] computed by an
@@ -220,17 +223,18 @@ class DecoderLayer:
         a, w = self.args, self.w
         s = x.shape[1]
         v = lambda t: t[:, :s]  # noqa: E731
-        # The three FP8 products of the query path are issued back to back: each one's weight prefetch
-        # overlaps its predecessor's tail (programmatic dependent launch), and none of them needs the
-        # small per-token kernels that follow.
-        ops.rmsnorm_projx_wqkva(x, w.in_norm, w.w_qkva, cur_pos, v(self.q_a), v(self.kv), self.pe_cache, v(self.ki),
-                                eps=a.eps)
-        ops.rmsnorm_proj_q(v(self.q_a), w.q_norm, w.w_qb, v(self.q_nope), v(self.q_pe), v(self.iq), eps=a.eps)
-        ops.projq_wqb(v(self.q_nope), w.w_absorb, None, v(self.q_lat))
-        # indexer head weights, latent norm into the cache, RoPE, indexer rotations: one launch
-        ops.attn_prep(x, w.in_norm, w.wis, v(self.idx_w), v(self.kv), w.kv_norm, self.kv_cache, v(self.q_pe),
-                      self.pe_cache, v(self.iq), v(self.iq_rt), v(self.ki), self.ki_cache, w.k_norm_w, w.k_norm_b,
-                      freqs, cur_pos, eps=a.eps, rope=a.qk_rope_head_dim)
+        dev, chained = x.device, self.chained
+        # Launch 1: the three FP8 products of the query path and the small per-token work between them
+        # (indexer head weights, latent norm into the cache, RoPE, indexer rotations) as one persistent
+        # kernel; with ``chained = False`` the same operators run as separate launches.
+        with ops.chain(dev, chained):
+            ops.rmsnorm_projx_wqkva(x, w.in_norm, w.w_qkva, cur_pos, v(self.q_a), v(self.kv), self.pe_cache, v(self.ki),
+                                    eps=a.eps)
+            ops.rmsnorm_proj_q(v(self.q_a), w.q_norm, w.w_qb, v(self.q_nope), v(self.q_pe), v(self.iq), eps=a.eps)
+            ops.attn_prep(x, w.in_norm, w.wis, v(self.idx_w), v(self.kv), w.kv_norm, self.kv_cache, v(self.q_pe),
+                          self.pe_cache, v(self.iq), v(self.iq_rt), v(self.ki), self.ki_cache, w.k_norm_w, w.k_norm_b,
+                          freqs, cur_pos, eps=a.eps, rope=a.qk_rope_head_dim)
+            ops.projq_wqb(v(self.q_nope), w.w_absorb, None, v(self.q_lat))
         ops.sparse_index_topk(v(self.iq_rt), self.ki_cache, v(self.idx_w), self.idx_logits, v(self.sel), cur_pos,
                               n_keys=n_keys)
         if self.injected_sel is not None:
@@ -238,18 +242,23 @@ class DecoderLayer:
         ops.flash_sparse_mla(v(self.q_lat), v(self.q_pe), self.kv_cache, self.pe_cache, v(self.sel), cur_pos,
                              v(self.o_lat), softmax_scale=self.scale, split_size=self.mla_split, out_acc=self.o_acc,
                              lse=self.lse, lse_acc=self.lse_acc)
-        ops.projo_wkvb(v(self.o_lat), w.w_v, None, v(self.o))
-        ops.unproj_o_allreduce(v(self.o), w.w_o, None, x, 0, v(self.h), comm=self.comm)
-        if w.dense:
-            ops.rmsnorm_up_gate_silu(v(self.h), w.post_norm, w.w_gu, v(self.ffn_hidden), eps=a.eps)
-            ops.down_allreduce(v(self.ffn_hidden), w.w_down, None, v(self.h), 0, v(self.out), comm=self.comm)
-        else:
-            ops.rmsnorm_expert_proj(v(self.h), w.post_norm, w.router, v(self.scores), v(self.h_norm), eps=a.eps)
-            scores = v(self.scores) if self.forced_scores is None else self.forced_scores
-            ops.expert_select_up_gate_silu(v(self.h_norm), scores, w.router_bias, w.w_gu, v(self.ffn_hidden), v(self.probs),
-                                           v(self.eidx), dim=a.dim, n_groups=a.n_expert_groups,
-                                           n_limited_groups=a.n_limited_groups, route_scale=a.route_scale,
-                                           slot_ids=self.slot_ids, slot_w=self.slot_w)
-            ops.expert_down_allreduce(v(self.ffn_hidden), w.w_down, None, v(self.eidx), v(self.probs), v(self.h), 0,
-                                      v(self.out), slot_ids=self.slot_ids, slot_w=self.slot_w, comm=self.comm)
+        # Launch 2: value up-projection, o_proj (+ all-reduce + residual), router, experts (or the dense FFN)
+        with ops.chain(dev, chained):
+            ops.projo_wkvb(v(self.o_lat), w.w_v, None, v(self.o))
+            ops.unproj_o_allreduce(v(self.o), w.w_o, None, x, 0, v(self.h), comm=self.comm)
+            if w.dense:
+                ops.rmsnorm_up_gate_silu(v(self.h), w.post_norm, w.w_gu, v(self.ffn_hidden), eps=a.eps)
+                ops.down_allreduce(v(self.ffn_hidden), w.w_down, None, v(self.h), 0, v(self.out), comm=self.comm)
+            else:
+                ops.rmsnorm_expert_proj(v(self.h), w.post_norm, w.router, v(self.scores), None if chained else v(self.h_norm),
+                                        eps=a.eps)
+                scores = v(self.scores) if self.forced_scores is None else self.forced_scores
+                # chained: the products normalise the raw state themselves instead of waiting for the router's copy
+                ops.expert_select_up_gate_silu(v(self.h) if chained else v(self.h_norm), scores, w.router_bias, w.w_gu,
+                                               v(self.ffn_hidden), v(self.probs), v(self.eidx), dim=a.dim,
+                                               n_groups=a.n_expert_groups, n_limited_groups=a.n_limited_groups,
+                                               route_scale=a.route_scale, slot_ids=self.slot_ids, slot_w=self.slot_w,
+                                               gamma=w.post_norm if chained else None, eps=a.eps)
+                ops.expert_down_allreduce(v(self.ffn_hidden), w.w_down, None, v(self.eidx), v(self.probs), v(self.h), 0,
+                                          v(self.out), slot_ids=self.slot_ids, slot_w=self.slot_w, comm=self.comm)
         return v(self.out)

@@ -46,6 +46,32 @@ def _need(t: torch.Tensor | None, dtype, name: str, optional: bool = False) -> N
         raise ValueError(f"{name} must be contiguous.")
 
 
+class chain:
+    """Record the FP8 products issued inside the ``with`` block and launch them as ONE persistent
+    kernel at its end (``tilert_b200_chain_begin`` / ``_end``): the role of the reference's single native
+    call per decode step (modules/end2end.py:99-104).  ``rmsnorm_expert_proj``, ``projx_wis`` and
+    ``attn_prep`` may be recorded as well (they run at the start of the product that follows them);
+    any other operator raises inside the block.  ``enabled=False`` makes the block a no-op wrapper, so
+    that callers can switch between chained and separate launches."""
+
+    def __init__(self, device, enabled: bool = True):
+        self.ctx = ctypes.c_void_p(_tb.tilert_init(torch.device(device).index)) if enabled else None
+
+    def __enter__(self):
+        if self.ctx is not None:
+            _tb.check(_tb.lib().tilert_b200_chain_begin(self.ctx))
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        if self.ctx is None:
+            return False
+        if exc_type is not None:
+            _tb.lib().tilert_b200_chain_abort(self.ctx)
+            return False
+        _tb.check(_tb.lib().tilert_b200_chain_end(self.ctx, _stream()))
+        return False
+
+
 def xpack_bytes(dim: int) -> int:
     return (dim // 128) * 1056
 
@@ -208,10 +234,12 @@ def rmsnorm_expert_proj(x, gamma, w_gate, scores_out, hidden_out, profile_logs=N
 
 def expert_select_up_gate_silu(hidden_in, scores, bias, w_packed, hidden_out, probs_out, idx_out,
                                profile_logs=None, *, model_arch="deepseek_v3_2", dim, n_groups, n_limited_groups,
-                               route_scale, slot_ids=None, slot_w=None):
-    """ops/expert_sel_up_gate_silu.py:23-48.  ``hidden_in`` is the bf16 post-attention norm output;
+                               route_scale, slot_ids=None, slot_w=None, gamma=None, eps=1e-6):
+    """ops/expert_sel_up_gate_silu.py:23-48.  ``hidden_in`` is the bf16 post-attention norm output (or, with
+    ``gamma``, the raw state: the RMSNorm then runs inside the launch);
     ``w_packed`` is [n_experts + 1, tiles, kblocks, 16448] with the shared expert last."""
     _need(hidden_in, BF16, "hidden_in")
+    _need(gamma, F32, "gamma", optional=True)
     _need(scores, F32, "scores")
     _need(bias, F32, "bias", optional=True)
     _need(hidden_out, BF16, "hidden_out")
@@ -223,7 +251,7 @@ def expert_select_up_gate_silu(hidden_in, scores, bias, w_packed, hidden_out, pr
     inter = hidden_out.shape[-1]
     stride = w_packed.stride(0) * w_packed.element_size()
     _tb.check(_tb.lib().tilert_expert_select_up_gate_silu_op(
-        _ctx(scores), _p(hidden_in), _p(scores), _p(bias), _p(w_packed), stride, tokens, dim, inter, n_experts,
+        _ctx(scores), _p(hidden_in), _p(gamma), eps, _p(scores), _p(bias), _p(w_packed), stride, tokens, dim, inter, n_experts,
         n_groups, n_limited_groups, top_k, route_scale, _p(hidden_out), _p(probs_out), _p(idx_out), _p(slot_ids),
         _p(slot_w), _stream()))
 
