@@ -338,20 +338,24 @@ int tilert_argmax_exchange_op(TbContext* ctx, const float* logits, long long log
  * device memory: code running under a host runtime that owns the whole memory pool and forbids
  * cudaMalloc from plug-ins, or a serving loop with a frozen memory budget in which an allocation
  * would synchronise the device.  It takes no TbContext (creating one allocates) and calls no
- * cudaMalloc, cudaFree or allocating library routine.  Its scratch -- partial sums of row tiles
- * shared by two thread blocks, their arrival counters, and the converted activation blocks with
+ * cudaMalloc, cudaFree or allocating library routine.  Its scratch -- the partial sums of row tiles
+ * whose k blocks are spread over several thread blocks (64-bit words tagged with the launch number, so
+ * they need neither counters nor clearing), a status word, and the converted activation blocks with
  * their ready flags -- is a fixed ~2.4 MB array inside the library image, held by every GPU that
  * loads the library until the process exits.
  *
  *   x [tokens, k] bf16, w_packed for [n, k], residual [tokens, n] bf16 or NULL, out [tokens, n] bf16;
  *   tokens 1..4, k a multiple of 128 and at most 32768, n at most 131072 rows (a larger k or n
  *   returns TB_EINVAL);
- *   status_out_dev: optional device int that receives the kernel's status word (0 = completed).
+ *   status_out_dev: optional device int that receives the kernel's status word (0 = completed).  It is
+ *   the only way to learn that a bounded wait of this call ran out (the word inside the array is
+ *   cleared by the next call): callers that need error detection must pass it.
  *
  * The first call on each device looks up the array's device address and sets a function
- * attribute; make that call outside any stream capture.  All calls on a device share the one
- * array: the counters and flags are cleared at the start of every call, and two calls whose kernels overlap
- * on the GPU (different streams) race on it -- serialise them. */
+ * attribute (under a lock, so first calls from several host threads are safe); make that call outside
+ * any stream capture.  All calls on a device share the one array: the status word, the ready flags and
+ * their epoch are cleared at the start of every call, and two calls whose kernels overlap on the GPU
+ * (different streams) race on it -- serialise them. */
 int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_packed, const void* residual, int tokens, int k,
                                   int n, void* out, int* status_out_dev, void* stream);
 

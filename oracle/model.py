@@ -233,7 +233,7 @@ def layer_step(args: Args, w: LayerWeights, c: Caches, x: torch.Tensor, pos: int
               idx_logits=idx_logits, sel=sel, q_lat=q_lat, o_lat=o_lat, o=o, attn_out=h)
 
     if w.dense:
-        hid = ops.dense_up_gate_silu(h, w.post_norm, w.w_gate, w.w_up, a.eps)
+        hid = ops.dense_up_gate_silu(h, w.post_norm, w.w_gate, w.w_up, a.eps, max(a.inter_dim // a.moe_inter_dim, 1))
         ffn = ops.dense_down(hid, w.w_down, a.inter_dim // a.moe_inter_dim)
         tr.update(ffn_hidden=hid)
     else:

@@ -312,13 +312,18 @@ def expert_down(vec, down_list, probs):
     return torch.stack(outs, dim=0)[None]
 
 
-def dense_up_gate_silu(x, gamma, w_gate, w_up, eps):
-    """RMSNormUpGateSiLU.golden_forward, ops/rmsnorm_up_gate_silu.py:318-347 (the
-    per-pseudo-expert loop is a plain row split of one product)."""
+def dense_up_gate_silu(x, gamma, w_gate, w_up, eps, n_split=1):
+    """RMSNormUpGateSiLU.golden_forward, ops/rmsnorm_up_gate_silu.py:318-347: the intermediate
+    dimension is cut into ``n_split`` pseudo-experts and every token's normalised vector is
+    multiplied with each slice on its own (f32), as the golden's loops do."""
     xn = rms_norm_f32(x, gamma, eps)
-    w1 = xn @ w_gate.float().T
-    w3 = xn @ w_up.float().T
-    return (F.silu(w1) * w3).to(BF16)
+    chunk = w_gate.size(0) // n_split
+    outs = []
+    for s in range(x.size(1)):
+        w1 = torch.stack([xn[0, s].float() @ w_gate[i * chunk:(i + 1) * chunk].float().T for i in range(n_split)], dim=0)
+        w3 = torch.stack([xn[0, s].float() @ w_up[i * chunk:(i + 1) * chunk].float().T for i in range(n_split)], dim=0)
+        outs.append((F.silu(w1.float()) * w3.float()).to(BF16).reshape(-1))
+    return torch.stack(outs, dim=0)[None]
 
 
 def dense_down(vec, w_down, n_split):

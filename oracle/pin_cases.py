@@ -85,6 +85,7 @@ def oracle_results(inp: dict[str, torch.Tensor] | None = None) -> dict[str, list
     probs2 = torch.tensor([[[0.9, 0.7, 0.5, 0.4]]], dtype=torch.float32)
     names2 = ["shared_experts"] + [f"experts.{int(e)}" for e in eidx2[0, 0]]
     r["expert_down"] = [oo.expert_down(inp["ffn_hidden"], [[w1.expert(n)[2] for n in names2]], probs2)]
+    r["dense_upgate"] = [oo.dense_up_gate_silu(inp["x2"], w0.post_norm, w0.w_gate, w0.w_up, a.eps, a.inter_dim // a.moe_inter_dim)]
     r["dense_down"] = [oo.dense_down(inp["dense_hidden"], w0.w_down, a.inter_dim // a.moe_inter_dim)]
     r["head"] = [oo.rmsnorm_head_proj(inp["hidden"], sd["model.norm.weight"], sd["lm_head.weight"], a.eps)]
     r["eh_proj"] = [oo.eh_proj(inp["e_norm"], inp["h_norm"], inp["w_eh"])]

@@ -232,6 +232,21 @@ def main(ref_root: str, out_path: str) -> None:
         mine = oo.expert_down(inp["ffn_hidden"], [[w1.expert(n)[2] for n in names]], probs)
         check("expert_down", ref, mine)
 
+    def t_dense_upgate():
+        # The constructor allocates one CUDA scratch tensor that the golden never reads: build it on the host.
+        from tilert.models.deepseek_v3_2.ops.rmsnorm_up_gate_silu import RMSNormUpGateSiLU
+
+        real_zeros = torch.zeros
+        torch.zeros = lambda *a_, **k_: real_zeros(*a_, **{**k_, "device": "cpu"}) if "device" in k_ else real_zeros(*a_, **k_)
+        try:
+            op = RMSNormUpGateSiLU(margs, num_devices=1, device_id=0)
+        finally:
+            torch.zeros = real_zeros
+        op.init_reference_weights(sd0, "mlp", 0)
+        ref = op.golden_forward(inp["x2"])  # [1, seq, pseudo-experts, moe_inter]
+        mine = oo.dense_up_gate_silu(inp["x2"], w0.post_norm, w0.w_gate, w0.w_up, a.eps, a.inter_dim // a.moe_inter_dim)
+        check("dense_upgate", ref.reshape(1, ref.shape[1], -1), mine)
+
     def t_dense_down():
         op = rops.DownAllReduce(margs, num_devices=1, device_id=0)
         op.init_reference_weights(sd0, "mlp", 0)

@@ -191,14 +191,33 @@ def test_toy_model_greedy_decode_matches_oracle(tb):
     assert worst_l2 <= 2e-2, worst_l2
     assert worst_cos >= 0.999, worst_cos
 
-    # device, free running under CUDA-graph replay: own selections, own tokens
+    # device, free running under CUDA-graph replay: its own key selections, its own routing, its own tokens.
+    # Wherever its token differs from the oracle's, the difference must be a numerical tie (the oracle's
+    # top-2 margin below twice the measured logit error of that step); the sequence is then re-synchronised
+    # to the oracle's token, so that one tie cannot hide a later real regression.
     free = DsaModel(margs, sd, "cuda", cache_len=cache_len, use_graph=True)
-    toks = free.generate(prompt, n_new)
-    torch.cuda.synchronize()
-    n_same = sum(int(x == y) for x, y in zip(rtoks, toks))
-    first_div = next((k for k, (x, y) in enumerate(zip(rtoks, toks)) if x != y), n_new)
-    _log({"name": "toy.generate.free", "tokens_equal": n_same, "first_divergence": first_div})
-    assert all(0 <= t < a.vocab_size for t in toks)
+    free.reset_sequence()
+    n_same, first_div, tie_count, not_ties = 0, n_new, 0, []
+    for pos, tok in enumerate(fed):
+        free.forward(tok, pos)
+        if pos >= n_prompt - 1:
+            torch.cuda.synchronize()
+            j = pos - (n_prompt - 1)
+            dl = free.logits.view(-1).float().cpu()
+            if int(free.token_out) == rtoks[j]:
+                n_same += 1
+                continue
+            first_div = min(first_div, j)
+            top2 = torch.topk(rlogits[j], 2)[0]
+            margin, err = float(top2[0] - top2[1]), float((dl - rlogits[j]).abs().max())
+            if margin <= 2.0 * err:
+                tie_count += 1
+            else:
+                not_ties.append((j, margin, err))
+    _log({"name": "toy.generate.free", "tokens_equal": n_same, "first_divergence": first_div, "ties": tie_count,
+          "not_ties": len(not_ties)})
+    assert not not_ties, not_ties
+    assert n_same + tie_count == n_new
 
 
 def test_toy_selection_overlap_during_prefill(tb):

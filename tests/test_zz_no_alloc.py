@@ -54,6 +54,43 @@ def test_static_scratch_product_matches_context_operator_twice():
     assert tilert_b200.device_status(0) == 0
 
 
+def test_static_scratch_shared_activation_blocks_three_calls_back_to_back():
+    """A product with more units per thread block than ring slots (n = 4096, k = 8192: 2048 units), so the
+    thread blocks share the activation conversion through the X-block part of the static array and its
+    ready flags; three calls are queued on one stream without a host synchronisation in between, each with
+    new activations, so every call must find the flags and their epoch cleared by its own start."""
+    import tilert_b200
+    from tilert_b200.models.deepseek_v3_2 import ops
+
+    lib = tilert_b200.load_backend("deepseek_v3_2")
+    tilert_b200.tilert_init(0)
+    n, k, tokens = 4096, 8192, 1
+    g = torch.Generator(device="cuda").manual_seed(5)
+    wp = torch.randint(0, 120, (n // 128, k // 128, 16448), generator=g, dtype=torch.uint8, device="cuda")
+    wp[:, :, 16384:] = 0
+    wp[:, :, 16384:].view(torch.float32).copy_(torch.rand(n // 128, k // 128, 16, generator=g, device="cuda") * 1e-3 + 1e-3)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    xs = [torch.randn(1, tokens, k, generator=g, device="cuda").to(BF16) for _ in range(3)]
+    res = torch.randn(1, tokens, n, generator=g, device="cuda").to(BF16)
+    wants = []
+    for x in xs:
+        w_ = torch.zeros(1, tokens, n, dtype=BF16, device="cuda")
+        ops.unproj_o_allreduce(x, wp, None, res, 0, w_)
+        wants.append(w_)
+    torch.cuda.synchronize()
+    gots = [torch.full((1, tokens, n), 7.0, dtype=BF16, device="cuda") for _ in range(3)]
+    stats = [torch.full((1,), -1, dtype=torch.int32, device="cuda") for _ in range(3)]
+    for x, got, st in zip(xs, gots, stats):
+        rc = lib.tilert_b200_matvec_fp8_static(_p(x), _p(wp), _p(res), tokens, k, n, _p(got), _p(st), stream)
+        assert rc == 0, lib.tilert_b200_last_error()
+    torch.cuda.synchronize()
+    for i, (got, want, st) in enumerate(zip(gots, wants, stats)):
+        assert int(st) == 0, i
+        assert torch.isfinite(want.float()).all() and want.float().abs().max() > 0
+        assert torch.equal(got, want), (i, (got.float() - want.float()).abs().max().item())
+    assert not torch.equal(wants[0], wants[1])
+
+
 def test_static_scratch_product_rejects_oversized_problems():
     import tilert_b200
 

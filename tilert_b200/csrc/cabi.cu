@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <utility>
 #include <vector>
@@ -1435,6 +1436,7 @@ struct StaticScratchView {
   int num_sms = 0;
 };
 StaticScratchView g_static_view[64];
+std::mutex g_static_mutex;  // guards the one-time set-up per device
 }  // namespace
 
 extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_packed, const void* residual,
@@ -1452,6 +1454,7 @@ extern "C" int tilert_b200_matvec_fp8_static(const void* x, const uint8_t* w_pac
   TB_CUDA(cudaGetDevice(&device));
   TB_REQUIRE(device >= 0 && device < 64);
   StaticScratchView& view = g_static_view[device];
+  std::lock_guard<std::mutex> lock(g_static_mutex);
   if (view.base == nullptr) {
     // One-time set-up for this device (it must be the current device, which it is).  In host code
     // the array's name is only a handle: the address a kernel can use comes from the runtime.

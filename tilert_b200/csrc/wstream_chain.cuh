@@ -544,8 +544,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
           const float v = warp_sum(ss[t]);
           if (lane == 0) norm_part[hw * 4 + t] = v;
         }
-        asm volatile("bar.sync 2, %0;" ::"n"(kGemvHelperWarps * 32) : "memory");
       }
+      // Every phase, with or without statistics: the helper warps stay within one phase of each other, which
+      // is what lets the statistics be double-buffered by phase parity.
+      asm volatile("bar.sync 2, %0;" ::"n"(kGemvHelperWarps * 32) : "memory");
       float rinv[4];
       gemv_rinv(p, norm_part, rinv);
       if (prof != nullptr) prof[kChainProfStats] = globaltimer_ns();
