@@ -107,49 +107,74 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_reference_steps(n_steps: int, warmup: int) -> tuple[float, dict]:
-    """Time the CPU restatement of the reference's PyTorch path on one layer step of the workload.
-    Returns (seconds per step, description)."""
-    from oracle import model as om
-    from oracle import ops as oo
+def workload_inputs(S: int, cache_len: int):
+    """The seeded synthetic workload, generated on the host so that every rank -- and the CPU checker --
+    sees the same bytes: an HF-keyed FP8 state dict of the layer (only the hot experts are materialised;
+    the forced router logits never select another), the three caches, the token's hidden state."""
+    from tilert_b200 import synthetic
+    from tilert_b200.models.deepseek_v3_2.model_args import full_layer_args
 
-    torch.manual_seed(0)
-    a = om.full_layer_args(max_seq_len=CACHE_LEN)
-    ids = hot_experts(a.n_routed_experts, a.n_activated_experts)
-    sd = om.random_state_dict(a, seed=0, expert_ids=ids)
-    w = om.LayerWeights(a, sd, 0)
-    c = om.Caches(a, CACHE_LEN)
+    a = full_layer_args(max_seq_len=cache_len)
+    hot = hot_experts(a.n_routed_experts, a.n_activated_experts)
+    sd = synthetic.random_layer_state_dict(a, 0, "cpu", seed=0, expert_ids=hot)
     g = torch.Generator().manual_seed(2)
-    for t in (c.kv, c.pe, c.ki):
-        t.copy_(torch.randn(t.shape, generator=g, dtype=torch.float32).to(torch.bfloat16))
-    x = torch.randn(1, 1, a.dim, generator=g, dtype=torch.float32).to(torch.bfloat16)
-    fc = oo.precompute_freqs_cis(a)
-    fs = forced_scores(a.n_routed_experts, a.n_activated_experts)
-    for _ in range(max(warmup, 1)):  # first step also dequantises the nine active experts
-        om.layer_step(a, w, c, x, CACHE_LEN - 1, fc, forced_router_scores=fs)
-    t0 = time.perf_counter()
-    for _ in range(n_steps):
-        om.layer_step(a, w, c, x, CACHE_LEN - 1, fc, forced_router_scores=fs)
-    dt = (time.perf_counter() - t0) / n_steps
-    desc = {"kind": "port", "cores": torch.get_num_threads(),
-            "sample": f"{n_steps} decode step(s) of the same layer (weights dequantised to bf16 once, outside the "
-                      "timed region, as the reference goldens hold them)"}
-    return dt, desc
+    caches = [torch.randn(1, cache_len, d, generator=g, dtype=torch.float32).to(torch.bfloat16)
+              for d in (a.kv_lora_rank, a.qk_rope_head_dim, a.index_head_dim)]
+    x = torch.randn(1, S, a.dim, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    return a, hot, sd, caches, x
+
+
+class CpuChecker:
+    """The CPU restatement of the reference's PyTorch path (``oracle/``) on the bench's own workload: the
+    checker of the GPU result (outside every timed region) and the reported CPU baseline."""
+
+    def __init__(self, sd, caches, x, S: int, cache_len: int):
+        from oracle import model as om
+        from oracle import ops as oo
+
+        torch.set_num_threads(os.cpu_count() or 1)  # torch.distributed.run exports OMP_NUM_THREADS=1
+        self.om = om
+        self.a = om.full_layer_args(max_seq_len=cache_len)
+        self.w = om.LayerWeights(self.a, sd, 0)
+        self.c = om.Caches(self.a, cache_len)
+        for dst, src in zip((self.c.kv, self.c.pe, self.c.ki), caches):
+            dst.copy_(src)
+        self.x, self.pos = x, cache_len - S
+        self.fc = oo.precompute_freqs_cis(self.a)
+        self.fs = forced_scores(self.a.n_routed_experts, self.a.n_activated_experts).expand(1, S, -1).contiguous()
+
+    def step(self) -> torch.Tensor:
+        return self.om.layer_step(self.a, self.w, self.c, self.x, self.pos, self.fc, forced_router_scores=self.fs)
+
+    def timed(self, n_steps: int, warmup: int) -> tuple[float, dict]:
+        for _ in range(max(warmup, 1)):  # the first step also dequantises the nine active experts
+            self.step()
+        t0 = time.perf_counter()
+        for _ in range(n_steps):
+            self.step()
+        dt = (time.perf_counter() - t0) / n_steps
+        desc = {"kind": "port", "cores": torch.get_num_threads(),
+                "sample": f"{n_steps} decode step(s) of the same layer (weights dequantised to bf16 once, outside the "
+                          "timed region, as the reference goldens hold them)"}
+        return dt, desc
 
 
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = min(args.steps, 5)
-    dt, desc = cpu_reference_steps(steps, min(args.warmup, 1))
+    _, _, sd, caches, x = workload_inputs(1, CACHE_LEN)
+    chk = CpuChecker(sd, caches, x, 1, CACHE_LEN)
+    steps, warmup = max(args.steps, 1), max(args.warmup, 1)
+    dt, desc = chk.timed(steps, warmup)
     val = 1.0 / dt
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
+        "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "fp8_e4m3 weights (dequantised to bf16), f32 accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference's golden_forward path; the "
-                   "reference's GPU path is a closed binary absent from its source tree"},
+        "config": {"workload": WORKLOAD, "parallelism": f"tp{args.gpus}", "cache_rows": CACHE_LEN, "tokens_per_step": 1},
+        "note": "CPU restatement of the reference's golden_forward path on the host cores; the reference's GPU path "
+                "is a closed binary absent from its source tree",
         "cpu_baseline": {"value": val, "unit": UNIT, **desc},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -160,11 +185,8 @@ def run_ours(args) -> None:
     import torch.distributed as dist
 
     import tilert_b200
-    from tilert_b200 import synthetic
     from tilert_b200.models.deepseek_v3_2 import layer as L
     from tilert_b200.models.deepseek_v3_2 import ops
-    from tilert_b200.models.deepseek_v3_2.model_args import full_layer_args
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -184,24 +206,21 @@ def run_ours(args) -> None:
     workload = WORKLOAD if (S, cache_len) == (1, CACHE_LEN) else (
         f"C4-style verify step: one full-shape DeepSeek-V3.2 MoE decoder layer, batch 1, {S} tokens/step, "
         f"{cache_len}-row latent KV cache, FP8 e4m3 weights with 128x128 block scales")
-    a = full_layer_args(max_seq_len=cache_len)
+    a, hot, sd, caches, x_cpu = workload_inputs(S, cache_len)
     comm = None
     if world > 1:
         from tilert_b200.comm import Comm
 
         comm = Comm(a.dim, local)
-    sd = synthetic.random_layer_state_dict(a, 0, dev, seed=0)
-    weights = L.LayerWeights(a, sd, 0, dev, world, rank)
-    del sd
+    weights = L.LayerWeights(a, sd, 0, dev, world, rank, expert_ids=hot)
     torch.cuda.empty_cache()
     layer = L.DecoderLayer(a, weights, dev, cache_len, S, world, None if comm is None else comm.handle)
     if args.mla_split:
         layer.mla_split = args.mla_split
-    g = torch.Generator(device=dev).manual_seed(2)
-    for t in (layer.kv_cache, layer.pe_cache, layer.ki_cache):
-        t.copy_(torch.randn(t.shape, generator=g, dtype=torch.float32, device=dev).to(torch.bfloat16))
+    for dst, src in zip((layer.kv_cache, layer.pe_cache, layer.ki_cache), caches):
+        dst.copy_(src)
     layer.forced_scores = forced_scores(a.n_routed_experts, a.n_activated_experts).expand(1, S, -1).contiguous().to(dev)
-    x_host = torch.randn(1, S, a.dim, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).pin_memory()
+    x_host = x_cpu.pin_memory()
     out_host = torch.empty(1, S, a.dim, dtype=torch.bfloat16).pin_memory()
     x = x_host.to(dev)
     cur = torch.tensor([cache_len - S], dtype=torch.int32, device=dev)
@@ -374,6 +393,28 @@ def run_ours(args) -> None:
     upgate_ms = ev0.elapsed_time(ev1) / k_iters
     upgate_bytes = n_slots * weights.w_gu[0].numel()
 
+    # ---- output check, outside every timed region: all ranks' results bit-identical, and rank 0's result
+    # against the CPU restatement of the reference on the same seeded inputs ----
+    graph.replay()
+    torch.cuda.synchronize()
+    result = out.clone()
+    ranks_identical = True
+    if world > 1:
+        gathered = [torch.empty_like(result) for _ in range(world)]
+        dist.all_gather(gathered, result)
+        ranks_identical = all(torch.equal(gathered[0], g_) for g_ in gathered[1:])
+    parity, checker = None, None
+    if rank == 0 and not args.profile:
+        checker = CpuChecker(sd, caches, x_cpu, S, cache_len)
+        ref = checker.step().float().flatten()
+        got = result.float().cpu().flatten()
+        cos = torch.nn.functional.cosine_similarity(ref, got, dim=0).item()
+        rel = (torch.norm(ref - got) / torch.norm(ref)).item()
+        parity = {"cos": cos, "rel_l2": rel, "ranks_identical": bool(ranks_identical),
+                  "checker": "CPU restatement of the reference's golden_forward path, same seeded weights, caches and input",
+                  "bounds": {"cos_min": 0.999, "rel_l2_max": 2e-2}}
+        parity["ok"] = bool(cos >= 0.999 and rel <= 2e-2 and ranks_identical)
+
     status = tilert_b200.device_status(local)
     t = torch.tensor([dev_ms, e2e_s, float(status), chain_ms or 0.0], dtype=torch.float64, device=dev)
     if world > 1:
@@ -415,6 +456,7 @@ def run_ours(args) -> None:
             "step_roofline": {"bytes_per_step_this_gpu": step_bytes, "achieved": step_bytes / (ms_per_step * 1e-3) / 1e9,
                               "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak_gbs, "unit": "GB/s"},
             "device_status": int(status),
+            "parity": parity,
         }
         if chain_ms:
             line["chained_layers"] = {"passes_per_replay": n_chain, "ms_per_layer": chain_ms,
@@ -423,17 +465,23 @@ def run_ours(args) -> None:
             # every row is verified; on average `accept` of them are emitted per step
             line["speculative"] = {"rows_per_step": S, "assumed_mean_accepted": 3.2,
                                    "emitted_tokens_per_s": 1000.0 * min(3.2, S) / ms_per_step}
-        if world == 1 and S == 1 and not args.no_cpu_baseline:
+        if world == 1 and S == 1 and not args.no_cpu_baseline and checker is not None:
             try:
-                dt, desc = cpu_reference_steps(2, 1)
+                dt, desc = checker.timed(20, 2)
                 line["cpu_baseline"] = {"value": 1.0 / dt, "unit": UNIT, **desc}
             except Exception as e:  # noqa: BLE001  (report the GPU numbers even if the CPU leg fails)
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "error": f"{type(e).__name__}: {e}"}
         print(json.dumps(line), flush=True)
+    failed = torch.tensor([1 if (rank == 0 and parity is not None and not parity["ok"]) or status != 0 else 0], device=dev)
+    if world > 1:
+        dist.all_reduce(failed, op=dist.ReduceOp.MAX)
     if comm is not None:
         comm.close()
     if world > 1:
         dist.destroy_process_group()
+    if int(failed.item()):
+        print("bench: the output check or the device status failed (see \"parity\" / \"device_status\")", file=sys.stderr)
+        sys.exit(1)
 
 
 def run_profile_gemv(args) -> None:

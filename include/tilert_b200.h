@@ -137,14 +137,14 @@ size_t tilert_b200_xpack_bytes(int dim);
  * any of the four parts may have size 0.  k_pe is written to pe_cache[*cur_pos + t]. */
 int tilert_projx_wqkva_op(TbContext* ctx, const uint8_t* xpack, int cols_per_token, const uint8_t* w_packed,
                           int tokens, int dim, int q_lora, int kv_lora, int rope, int ki_dim, const int* cur_pos,
-                          void* q_out, void* kv_out, void* pe_cache, void* ki_out, void* stream);
+                          void* q_out, void* kv_out, void* pe_cache, int cache_rows, void* ki_out, void* stream);
 
 /* RMSNormProjxWqkva.tilert_forward (ops/rmsnorm_projx_wqkva.py:473-509) as ONE launch: the RMSNorm
  * (rmsnorm_quant_op) runs inside the product kernel, which reads the bf16 hidden state directly. */
 int tilert_rmsnorm_projx_wqkva_op(TbContext* ctx, const void* x, const float* gamma, float eps,
                                   const uint8_t* w_packed, int tokens, int dim, int q_lora, int kv_lora, int rope,
                                   int ki_dim, const int* cur_pos, void* q_out, void* kv_out, void* pe_cache,
-                                  void* ki_out, void* stream);
+                                  int cache_rows, void* ki_out, void* stream);
 
 /* rmsnorm_proj_qb_op (ops/rmsnorm_projq_wqb.py:21-43) and rmsnorm_proj_qi_op
  * (ops/rmsnorm_projq_wqi.py:21-40) in one launch: RMSNorm(q) then rows
@@ -195,6 +195,15 @@ int tilert_rmsnorm_up_gate_silu_op(TbContext* ctx, const void* x, const float* g
 int tilert_down_allreduce_op(TbContext* ctx, const void* vec, const uint8_t* w_packed, const void* x_residual,
                              int tokens, int inter, int dim, void* out, TbComm* comm, void* stream);
 
+/* rmsnorm_expert_proj_op / proj_w_op (ops/rmsnorm_expert_proj.py:151-169, ops/projx_wis.py:21-40) on the FP8
+ * weight stream: a bf16 weight [n, dim] packed by tilert_b200.pack.pack_bf16_two_term as two e4m3 rows per
+ * source row (leading and residual term, exact for bf16) goes through the same streaming kernel as the FP8
+ * products, whose epilogue adds the two rows.  out[t, :] = W . RMSNorm(x[t]) (gamma NULL: x as is),
+ * f32 (out_is_f32) or bf16.  In a chained launch this makes the router a product like the others -- the
+ * routed experts' weight addresses wait for its signal -- instead of bf16 loads on spare warps. */
+int tilert_rmsnorm_proj_rows2_op(TbContext* ctx, const void* x, const float* gamma, float eps, const uint8_t* w_packed,
+                                 int tokens, int dim, int n, void* out, int out_is_f32, void* stream);
+
 /* ---- bf16 products --------------------------------------------------------------------- */
 
 /* proj_w_op (ops/projx_wis.py:21-40): out[t, :] = W[n, k] . x[t, :]   (bf16 in, bf16 out).
@@ -227,11 +236,11 @@ int tilert_mtp_preprocess_op(TbContext* ctx, const void* e, const void* h, const
 
 /* rmsnorm_kv_op (ops/rmsnorm_kv.py:20-43): kv_cache[*cur_pos + t] = bf16(RMSNorm(kv[t]) * gamma). */
 int tilert_rmsnorm_kv_op(TbContext* ctx, const void* kv, const float* gamma, float eps, int tokens, int dim,
-                         const int* cur_pos, void* kv_cache, void* stream);
+                         const int* cur_pos, void* kv_cache, int cache_rows, void* stream);
 /* qkv_rope_op (ops/qkv_rope.py:21-50): interleaved RoPE in place on q_pe [tokens, heads, rope] and on
  * pe_cache[*cur_pos + t].  freqs [tokens, rope/2, 2] f32 = (cos, sin). */
 int tilert_qkv_rope_op(TbContext* ctx, void* q_pe, int heads, int rope, void* pe_cache, const int* cur_pos,
-                       const float* freqs, int tokens, void* stream);
+                       const float* freqs, int tokens, int cache_rows, void* stream);
 /* rotate_op (ops/rotate.py:61-105): non-interleaved RoPE on the first `rope` dims + Hadamard-128. */
 int tilert_rotate_op(TbContext* ctx, const void* in, void* out, int heads, int rope, const float* freqs,
                      int tokens, void* stream);
@@ -239,7 +248,7 @@ int tilert_rotate_op(TbContext* ctx, const void* in, void* out, int heads, int r
  * k_cache[*cur_pos + t]. */
 int tilert_layernorm_rope_rotate_op(TbContext* ctx, const void* in, const int* cur_pos, void* k_cache,
                                     const float* weight, const float* bias, const float* freqs, int rope,
-                                    int tokens, void* stream);
+                                    int tokens, int cache_rows, void* stream);
 /* proj_w_op + rmsnorm_kv_op + qkv_rope_op + rotate_op + layernorm_rope_rotate_op in one launch (the five
  * operators above, ops/projx_wis.py:21-40, ops/rmsnorm_kv.py:20-43, ops/qkv_rope.py:21-50,
  * ops/rotate.py:61-105, ops/layernorm_rope_rotate.py:23-83): they are independent of one another, and
@@ -247,12 +256,17 @@ int tilert_layernorm_rope_rotate_op(TbContext* ctx, const void* in, const int* c
  * results are those of the five operators: x [tokens, dim] raw hidden state with its input-norm gain,
  * w_is [idx_heads, dim] bf16 -> idx_w_out [tokens, idx_heads] bf16; kv [tokens, kv_dim] -> kv_cache row;
  * q_pe [tokens, heads, rope] and the pe_cache row rotated in place; iq [tokens, idx_heads, 128] ->
- * iq_out; ki [tokens, 128] -> ki_cache row.  Results are bit-identical to the separate operators. */
+ * iq_out; ki [tokens, 128] -> ki_cache row.  Results are bit-identical to the separate operators.
+ * w_is may be NULL (the head weights then come from elsewhere, e.g. tilert_rmsnorm_proj_rows2_op). */
 int tilert_attn_prep_op(TbContext* ctx, const void* x, const float* in_gamma, float eps, const void* w_is,
                         int idx_heads, int dim, void* idx_w_out, const void* kv, const float* kv_gamma, int kv_dim,
                         void* kv_cache, void* q_pe, int heads, int rope, void* pe_cache, const void* iq, void* iq_out,
                         const void* ki, void* ki_cache, const float* ln_w, const float* ln_b, const float* freqs,
-                        const int* cur_pos, int tokens, void* stream);
+                        const int* cur_pos, int tokens, int cache_rows, void* stream);
+
+/* `cache_rows` (operators above that write the cache row of position *cur_pos + t): the number of rows the
+ * cache tensors hold, 0 = unchecked.  The position lives in device memory, so only the kernel can check it:
+ * a row at or past cache_rows is not written and the status word becomes 4 (bad argument). */
 
 /* ---- DSA indexer and sparse attention ---------------------------------------------------- */
 

@@ -71,8 +71,8 @@ def test_three_chained_products_equal_separate_launches(tb, shape, tokens):
 def test_toy_layer_chained_equals_separate_launches(tb, li, tokens):
     """Both toy layers through DecoderLayer.forward with chained and with separate launches.  Router
     scores are forced and the key selection injected, so the two runs take identical discrete decisions;
-    every streaming product is then bit-identical, and the two row products that run as hooks (indexer
-    head weights, router logits) agree to rounding."""
+    every streaming product is then bit-identical, and the two bf16 row products (indexer head weights,
+    router logits), which the chained step runs as two-term FP8 products, agree to rounding."""
     from tilert_b200.models.deepseek_v3_2 import layer as L
     from tilert_b200.models.deepseek_v3_2.model_args import toy_model_args
 
@@ -120,10 +120,12 @@ def test_toy_layer_chained_equals_separate_launches(tb, li, tokens):
         assert near(ga.ffn_hidden, gb.ffn_hidden)
     for name in ("kv_cache", "pe_cache", "ki_cache"):
         assert torch.equal(getattr(ga, name), getattr(gb, name)), name
-    assert torch.allclose(ga.idx_w.float(), gb.idx_w.float(), rtol=2e-2, atol=1e-3)
+    # (the chained product rounds the normalised activations to bf16 before the product, the row kernel does not)
+    assert (ga.idx_w.float() - gb.idx_w.float()).abs().max() <= 1e-2 * ga.idx_w.float().abs().max()
     if not weights.dense:
         assert torch.equal(ga.eidx, gb.eidx) and torch.equal(ga.probs, gb.probs)
-        assert torch.allclose(ga.scores, gb.scores, rtol=1e-4, atol=1e-5)
+        # router logits: bf16 row product (separate launches) vs the two-e4m3-term product on the weight stream
+        assert torch.allclose(ga.scores, gb.scores, rtol=1e-3, atol=1e-4), (ga.scores - gb.scores).abs().max().item()
     if weights.dense:
         assert torch.equal(oa, ob), (oa.float() - ob.float()).abs().max().item()
     else:
@@ -132,7 +134,7 @@ def test_toy_layer_chained_equals_separate_launches(tb, li, tokens):
     n0 = tb.lib().tilert_b200_launch_count()
     gb.forward(x, cur, fr, n_keys=t_ctx + tokens)
     torch.cuda.synchronize()
-    assert tb.lib().tilert_b200_launch_count() - n0 <= 6
+    assert tb.lib().tilert_b200_launch_count() - n0 <= 5
 
 
 def test_chain_rejects_what_it_cannot_hold(tb):
@@ -142,7 +144,7 @@ def test_chain_rejects_what_it_cannot_hold(tb):
     gamma = torch.ones(256, dtype=F32, device="cuda")
     w = torch.zeros(8, 256, dtype=BF16, device="cuda")
     out = torch.zeros(1, 1, 8, dtype=BF16, device="cuda")
-    # a recorded row product needs a following streaming product to attach to
+    # a bf16 row product is not chainable (its two-term packed form is)
     with pytest.raises(tb.TilertError):
         with ops.chain("cuda:0"):
             ops.projx_wis(x, w, out, gamma=gamma)

@@ -320,6 +320,32 @@ def test_model_driver_sampling(tb):
     assert torch.equal(dev.topn_indices[0].long().cpu(), torch.argsort(-dev.logits.view(-1).double(), stable=True)[:256].cpu())
 
 
+def test_positions_past_the_caches_are_refused_on_the_host(tb):
+    """The driver keeps a host copy of the device-resident position: a step at or past the end of the
+    caches, a ``pos`` that differs from the device position, or a ``set_cur_pos`` outside the caches
+    raises before anything is launched."""
+    from tilert_b200.models.deepseek_v3_2.model import DsaModel
+    from tilert_b200.models.deepseek_v3_2.model_args import toy_model_args
+
+    a = om.toy_args()
+    sd = om.random_state_dict(a, seed=0)
+    dev = DsaModel(toy_model_args(), sd, "cuda", cache_len=8, use_graph=False)
+    with pytest.raises(ValueError):
+        dev.set_cur_pos(8)
+    with pytest.raises(ValueError):
+        dev.forward(1, 3)  # the device position is 0
+    n0 = tb.lib().tilert_b200_launch_count()
+    for pos in range(8):
+        dev.forward(pos + 1, pos)
+    with pytest.raises(ValueError):
+        dev.forward(1, 8)
+    with pytest.raises(ValueError):
+        dev.generate([1, 2, 3, 4, 5], 8)  # 5 + 8 steps do not fit 8 rows: raises at position 8
+    torch.cuda.synchronize()
+    assert tb.lib().tilert_b200_launch_count() > n0
+    assert tb.device_status(0) == 0
+
+
 def test_injected_caches_continue_a_sequence(tb):
     """Prefill/decode disaggregation: a model that receives the caches of a prompt (bf16, as
     DSAv32Generator.inject_cache takes them) continues exactly like the model that computed them itself;

@@ -654,6 +654,29 @@ def test_inject_cache_fp8_wire_format(env):
                              torch.zeros(1, 512, 512, dtype=BF16, device="cuda"), None, None)
 
 
+def test_cache_row_past_the_cache_is_not_written(env):
+    """The position is device-resident, so the kernels themselves check it against the cache's rows: a row
+    at or past the end is not stored and the status word reports a bad argument (4)."""
+    ops, a, w = env["ops"], env["a"], env["gw"][0]
+    g = torch.Generator().manual_seed(77)
+    rows = 16
+    kv = rn(g, 1, 1, a.kv_lora_rank).cuda()
+    cache = torch.zeros(1, rows, a.kv_lora_rank, dtype=BF16, device="cuda")
+    guard = torch.zeros(1, 4, a.kv_lora_rank, dtype=BF16, device="cuda")  # what an unchecked store at row 16.. would hit
+    # a view of a larger buffer, so that the row just past the cache is memory this test owns
+    buf = torch.zeros(1, rows + 4, a.kv_lora_rank, dtype=BF16, device="cuda")
+    cache = buf[:, :rows]
+    for pos, want_status in ((rows - 1, 0), (rows, 4), (rows + 2, 4)):
+        buf.zero_()
+        cur = torch.tensor([pos], dtype=I32, device="cuda")
+        ops.rmsnorm_kv(kv, w.kv_norm, cur, cache, eps=a.eps)
+        torch.cuda.synchronize()
+        assert env["tb"].device_status(0) == want_status
+        written = buf[0].float().abs().sum(dim=-1).nonzero().flatten().tolist()
+        assert written == ([pos] if want_status == 0 else []), (pos, written)
+    del guard
+
+
 def test_bad_arguments_raise(env):
     ops = env["ops"]
     with pytest.raises(ValueError):

@@ -83,4 +83,10 @@ def device_status(device: int | None = None) -> int:
     return st.value
 
 
-__all__ = ["load_backend", "tilert_init", "device_status", "lib", "check", "TilertError", "__version__"]
+def set_wait_budget(cycles: int, device: int | None = None) -> None:
+    """Upper bound (SM clock cycles) of every bounded wait in the library's kernels; ``cycles <= 0`` restores
+    the default of about half a second."""
+    check(lib().tilert_b200_set_wait_budget(ctypes.c_void_p(tilert_init(device)), int(cycles)))
+
+
+__all__ = ["set_wait_budget", "load_backend", "tilert_init", "device_status", "lib", "check", "TilertError", "__version__"]

@@ -41,6 +41,8 @@ struct AttnPrepParams {
   const int* pos;
   const float* freqs;
   int n_tokens;
+  int cache_rows;  // rows of the three caches (0 = unchecked); a position past them stores nothing and sets the status
+  int* status;
 };
 
 constexpr int kAttnPrepThreads = kGemvBf16SmallThreads;  // 256: eight warps per block
@@ -59,12 +61,12 @@ __global__ void __launch_bounds__(kAttnPrepThreads) attn_prep_kernel(const AttnP
   const int warp = threadIdx.x >> 5;
   constexpr int kWarps = kAttnPrepThreads / 32;
   if (b < p.kv_blocks) {
-    rmsnorm_kv_warp(b * kWarps + warp, p.kv, p.kv_stride, p.kv_gamma, p.kv_eps, p.kv_dim, p.pos, p.kv_cache, p.n_tokens);
+    rmsnorm_kv_warp(b * kWarps + warp, p.kv, p.kv_stride, p.kv_gamma, p.kv_eps, p.kv_dim, p.pos, p.kv_cache, p.n_tokens, p.cache_rows, p.status);
     return;
   }
   b -= p.kv_blocks;
   if (b < p.rope_blocks) {
-    qkv_rope_thread(b * kAttnPrepThreads + threadIdx.x, p.q_pe, p.heads, p.rope, p.pe_cache, p.pos, p.freqs, p.n_tokens);
+    qkv_rope_thread(b * kAttnPrepThreads + threadIdx.x, p.q_pe, p.heads, p.rope, p.pe_cache, p.pos, p.freqs, p.n_tokens, p.cache_rows, p.status);
     return;
   }
   b -= p.rope_blocks;
@@ -74,7 +76,8 @@ __global__ void __launch_bounds__(kAttnPrepThreads) attn_prep_kernel(const AttnP
   }
   b -= p.iq_blocks;
   if (b < p.ki_blocks)
-    rotate128_warp(b * kWarps + warp, p.ki, p.ki_cache, 1, p.rope, p.freqs, p.ln_w, p.ln_b, p.pos, p.n_tokens);
+    rotate128_warp(b * kWarps + warp, p.ki, p.ki_cache, 1, p.rope, p.freqs, p.ln_w, p.ln_b, p.pos, p.n_tokens, p.cache_rows,
+                   p.status);
 }
 
 }  // namespace tb

@@ -76,6 +76,7 @@ constexpr size_t kXpackScratchBytes = 2ull << 20;   // activation blocks of the 
 constexpr int kMaxXBlocks = 1984;                   // X blocks one launch may convert (fits kXpackScratchBytes)
 constexpr size_t kXFlagBytes = (kMaxXBlocks + 64) * sizeof(unsigned);  // flags, then {epoch, done}
 constexpr size_t kSmallScratchBytes = 64ull << 10;  // slot ids / weights for routing
+constexpr size_t kChainSignalBytes = (kChainSignals + 1) * kChainSigStride * sizeof(unsigned);
 
 }  // namespace
 
@@ -178,6 +179,17 @@ int record_phase(TbContext* ctx, GemvParams& p) {
   const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
   const int grid = chain_grid(ctx);
   p.grid_eff = units < grid ? static_cast<int>(units) : grid;
+  // A short product is not spread thinner than eight CTAs per row tile: every further CTA inside a tile is
+  // one more partial sum its owner must collect through L2 (a round trip per four), and a product this
+  // small gains nothing from more CTAs.  It then sits at the far end of the grid, away from the CTAs that
+  // earlier short phases loaded.
+  if (static_cast<long long>(p.n_tiles) * 8 < p.grid_eff) p.grid_eff = p.n_tiles * 8;
+  p.cta_base = p.grid_eff < grid ? grid - p.grid_eff : 0;
+  if (ph > 0) {
+    const GemvParams& prev = r.params.ph[ph - 1].g;
+    // short phases alternate between the two ends of the grid, so that they do not pile up on the same CTAs
+    if (p.grid_eff < grid && prev.grid_eff < grid && prev.cta_base > 0) p.cta_base = 0;
+  }
   set_partition(p, p.grid_eff);
   p.shared_x = max_cta_units(p, p.grid_eff) > kGemvStages ? 1 : 0;
   p.partial = ctx->chain_partial + static_cast<size_t>(ph) * (kPartialBytes / sizeof(float));
@@ -220,16 +232,21 @@ int record_phase(TbContext* ctx, GemvParams& p) {
   dep = imax(dep, chain_dep(r, p.residual, (static_cast<long long>(p.n_tokens - 1) * p.residual_stride + p.n_rows) * 2));
   if (p.seg_scale != nullptr)
     dep = imax(dep, chain_dep(r, p.seg_scale, static_cast<long long>(p.n_tokens) * (p.n_kb / p.kb_per_kseg) * 4));
-  if (c.hook >= 0) {
-    const ChainHook& h = r.params.hooks[c.hook];
-    if (h.kind == HOOK_ATTN_PREP) {
-      dep = imax(dep, 2 * ph - 2);  // reads cache rows and vectors of every earlier product
-    } else {
-      const GemvBf16Params& q = h.prep.wis;
-      dep = imax(dep, chain_dep(r, q.x, (static_cast<long long>(q.n_tokens - 1) * q.x_stride + q.k) * 2));
+  if (c.hook >= 0) dep = imax(dep, 2 * ph - 2);  // the vector work reads cache rows and vectors of every earlier product
+  c.wait_sig = dep;
+  if (ph > 0) {
+    // A full-width phase that does not wait for the short phase recorded just before it (router gate ->
+    // shared expert: both read the same vector) takes only the CTAs that phase left idle: the two then run
+    // side by side instead of one after the other on the short phase's CTAs.
+    const GemvParams& prev = r.params.ph[ph - 1].g;
+    const bool independent = dep < 2 * (ph - 1) && p.nseg_ids == nullptr && p.kseg_ids == nullptr && p.route.scores == nullptr;
+    if (independent && p.grid_eff == grid && prev.grid_eff * 3 <= grid && units >= 4ll * grid) {
+      p.grid_eff = grid - prev.grid_eff;
+      p.cta_base = prev.cta_base > 0 ? 0 : prev.grid_eff;
+      set_partition(p, p.grid_eff);
+      p.shared_x = max_cta_units(p, p.grid_eff) > kGemvStages ? 1 : 0;
     }
   }
-  c.wait_sig = dep;
   // weight-address dependencies
   int wdep = -1;
   if (p.nseg_ids != nullptr) wdep = imax(wdep, chain_dep(r, p.nseg_ids, 4ll * (p.n_tiles / p.tiles_per_nseg)));
@@ -254,17 +271,9 @@ int record_phase(TbContext* ctx, GemvParams& p) {
     chain_out(r, p.route.slot_w, 4ll * (p.route.top_k + 1), 2 * ph);
   }
   if (c.hook >= 0) {
-    const ChainHook& h = r.params.hooks[c.hook];
-    const GemvBf16Params& q = h.prep.wis;
-    if (q.w != nullptr) {
-      chain_out(r, q.out, (static_cast<long long>(q.n_tokens - 1) * q.out_stride + q.n) * (q.out_bf16 ? 2 : 4), 2 * ph + 1);
-      chain_out(r, q.xnorm_out, (static_cast<long long>(q.n_tokens - 1) * q.xnorm_stride + q.k) * 2, 2 * ph + 1);
-    }
-    if (h.kind == HOOK_ATTN_PREP) {
-      const AttnPrepParams& a = h.prep;
-      chain_out(r, a.q_pe, 2ll * a.n_tokens * a.heads * a.rope, 2 * ph + 1);
-      chain_out(r, a.iq_out, 2ll * a.n_tokens * a.idx_heads * 128, 2 * ph + 1);
-    }
+    const AttnPrepParams& a = r.params.hooks[c.hook].prep;
+    chain_out(r, a.q_pe, 2ll * a.n_tokens * a.heads * a.rope, 2 * ph + 1);
+    chain_out(r, a.iq_out, 2ll * a.n_tokens * a.idx_heads * 128, 2 * ph + 1);
   }
   c.g = p;
   ++r.params.n_phases;
@@ -275,7 +284,8 @@ int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
   static bool attr_set[64] = {};
   if (!attr_set[ctx->device & 63]) {
     TB_CUDA(cudaFuncSetAttribute(wstream_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBytes));
-    TB_CUDA(cudaFuncSetAttribute(wstream_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChainSmemBytes));
+    TB_CUDA(cudaFuncSetAttribute(wstream_chain_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kChainSmemBytes));
+    TB_CUDA(cudaFuncSetAttribute(wstream_chain_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kChainSmemBytes));
     attr_set[ctx->device & 63] = true;
   }
   TB_REQUIRE(p.n_tiles > 0 && p.n_kb > 0);
@@ -285,6 +295,7 @@ int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
   if (ctx->rec.active) return record_phase(ctx, p);
   int grid = ctx->num_sms < kMaxGrid ? ctx->num_sms : kMaxGrid;
   if (units < grid) grid = static_cast<int>(units);
+  if (static_cast<long long>(p.n_tiles) * 8 < grid) grid = p.n_tiles * 8;  // at most eight CTAs inside a row tile
   set_partition(p, grid);
   p.grid_eff = grid;
   p.shared_x = max_cta_units(p, grid) > kGemvStages ? 1 : 0;
@@ -323,7 +334,7 @@ void gemv_defaults(GemvParams& p) {
 }
 
 void set_region(GemvParams& p, int row_begin, int rows, void* ptr, long long token_stride, int dtype = 0,
-                const int* pos = nullptr) {
+                const int* pos = nullptr, int pos_rows = 0) {
   if (rows <= 0 || ptr == nullptr) return;
   OutRegion& r = p.regions[p.n_regions++];
   r.row_begin = row_begin;
@@ -332,6 +343,7 @@ void set_region(GemvParams& p, int row_begin, int rows, void* ptr, long long tok
   r.ptr = ptr;
   r.token_stride = token_stride;
   r.pos_ptr = pos;
+  r.pos_rows = pos_rows;
 }
 
 int set_comm(GemvParams& p, TbComm* comm, int n_rows) {
@@ -411,8 +423,8 @@ extern "C" int tilert_b200_init(int device, TbContext** ctx_out) {
   TB_CUDA(cudaMalloc(&c->partial, kPartialBytes));
   TB_CUDA(cudaMalloc(&c->chain_partial, kPartialBytes * kChainMaxPhases));
   TB_CUDA(cudaMemset(c->chain_partial, 0, kPartialBytes * kChainMaxPhases));
-  TB_CUDA(cudaMalloc(&c->chain_signals, 256));
-  TB_CUDA(cudaMemset(c->chain_signals, 0, 256));
+  TB_CUDA(cudaMalloc(&c->chain_signals, kChainSignalBytes));
+  TB_CUDA(cudaMemset(c->chain_signals, 0, kChainSignalBytes));
   TB_CUDA(cudaMalloc(&c->status, 256));
   TB_CUDA(cudaMalloc(&c->launch_calls, 256));
   TB_CUDA(cudaMemset(c->launch_calls, 0, 256));
@@ -455,7 +467,7 @@ extern "C" int tilert_b200_status(TbContext* ctx, int* status_out) {
   if (*status_out != 0) {
     // a launch that gave up may have left signal counters of a chained launch half-way: start clean
     TB_CUDA(cudaMemset(ctx->status, 0, sizeof(int)));
-    TB_CUDA(cudaMemset(ctx->chain_signals, 0, 256));
+    TB_CUDA(cudaMemset(ctx->chain_signals, 0, kChainSignalBytes));
   }
   return TB_OK;
 }
@@ -498,10 +510,20 @@ extern "C" int tilert_b200_chain_end(TbContext* ctx, void* stream) {
   if (r.params.n_phases == 0) return TB_OK;
   r.params.signals = ctx->chain_signals;
   r.params.prof = ctx->chain_prof;
+  static const int inflight = [] {
+    // TILERT_B200_INFLIGHT: 4, 8 or 12 weight blocks in flight per CTA (tuning knob)
+    const char* e = getenv("TILERT_B200_INFLIGHT");
+    const int v = e != nullptr ? atoi(e) : 8;
+    return v >= 12 ? 12 : (v >= 8 ? 8 : 4);
+  }();
+  r.params.max_inflight = inflight;
   static_assert(sizeof(ChainParams) <= 24 * 1024, "kernel parameter space");
-  static_assert(kChainSignals + 1 <= 64, "signal area");
-  TB_CUDA(launch(wstream_chain_kernel, dim3(chain_grid(ctx)), dim3(kGemvThreads), kChainSmemBytes,
-                 static_cast<cudaStream_t>(stream), r.params));
+  if (r.params.prof != nullptr)
+    TB_CUDA(launch(wstream_chain_kernel<true>, dim3(chain_grid(ctx)), dim3(kGemvThreads), kChainSmemBytes,
+                   static_cast<cudaStream_t>(stream), r.params));
+  else
+    TB_CUDA(launch(wstream_chain_kernel<false>, dim3(chain_grid(ctx)), dim3(kGemvThreads), kChainSmemBytes,
+                   static_cast<cudaStream_t>(stream), r.params));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;
@@ -630,7 +652,7 @@ extern "C" int tilert_xq_repack_op(TbContext* ctx, const uint8_t* x_q, const flo
 extern "C" int tilert_projx_wqkva_op(TbContext* ctx, const uint8_t* xpack, int cols_per_token,
                                      const uint8_t* w_packed, int tokens, int dim, int q_lora, int kv_lora, int rope,
                                      int ki_dim, const int* cur_pos, void* q_out, void* kv_out, void* pe_cache,
-                                     void* ki_out, void* stream) {
+                                     int cache_rows, void* ki_out, void* stream) {
   TB_REQUIRE(ctx != nullptr && xpack != nullptr && w_packed != nullptr);
   TB_REQUIRE(dim % TB_KBLOCK == 0 && (cols_per_token == 1 || cols_per_token == 2));
   TB_REQUIRE(tokens >= 1 && tokens * cols_per_token <= 8);
@@ -648,7 +670,7 @@ extern "C" int tilert_projx_wqkva_op(TbContext* ctx, const uint8_t* xpack, int c
   p.n_rows = rows;
   set_region(p, 0, q_lora, q_out, q_lora);
   set_region(p, q_lora, kv_lora, kv_out, kv_lora);
-  set_region(p, q_lora + kv_lora, rope, pe_cache, rope, 0, cur_pos);
+  set_region(p, q_lora + kv_lora, rope, pe_cache, rope, 0, cur_pos, cache_rows);
   set_region(p, q_lora + kv_lora + rope, ki_dim, ki_out, ki_dim);
   return launch_gemv(ctx, p, static_cast<cudaStream_t>(stream));
 }
@@ -656,7 +678,7 @@ extern "C" int tilert_projx_wqkva_op(TbContext* ctx, const uint8_t* xpack, int c
 extern "C" int tilert_rmsnorm_projx_wqkva_op(TbContext* ctx, const void* x, const float* gamma, float eps,
                                              const uint8_t* w_packed, int tokens, int dim, int q_lora, int kv_lora,
                                              int rope, int ki_dim, const int* cur_pos, void* q_out, void* kv_out,
-                                             void* pe_cache, void* ki_out, void* stream) {
+                                             void* pe_cache, int cache_rows, void* ki_out, void* stream) {
   TB_REQUIRE(ctx != nullptr && x != nullptr && gamma != nullptr && w_packed != nullptr);
   TB_REQUIRE(dim % TB_KBLOCK == 0 && tokens >= 1 && tokens <= 4);
   TB_REQUIRE(rope == 0 || cur_pos != nullptr);
@@ -672,7 +694,7 @@ extern "C" int tilert_rmsnorm_projx_wqkva_op(TbContext* ctx, const void* x, cons
   p.n_rows = rows;
   set_region(p, 0, q_lora, q_out, q_lora);
   set_region(p, q_lora, kv_lora, kv_out, kv_lora);
-  set_region(p, q_lora + kv_lora, rope, pe_cache, rope, 0, cur_pos);
+  set_region(p, q_lora + kv_lora, rope, pe_cache, rope, 0, cur_pos, cache_rows);
   set_region(p, q_lora + kv_lora + rope, ki_dim, ki_out, ki_dim);
   return launch_gemv(ctx, p, static_cast<cudaStream_t>(stream));
 }
@@ -914,6 +936,26 @@ extern "C" int tilert_rmsnorm_up_gate_silu_op(TbContext* ctx, const void* x, con
   return launch_gemv(ctx, p, st);
 }
 
+extern "C" int tilert_rmsnorm_proj_rows2_op(TbContext* ctx, const void* x, const float* gamma, float eps,
+                                            const uint8_t* w_packed, int tokens, int dim, int n, void* out,
+                                            int out_is_f32, void* stream) {
+  TB_REQUIRE(ctx != nullptr && x != nullptr && w_packed != nullptr && out != nullptr);
+  TB_REQUIRE(tokens >= 1 && tokens <= 4 && dim % TB_KBLOCK == 0 && n >= 1);
+  GemvParams p;
+  gemv_defaults(p);
+  p.w = w_packed;
+  set_x_bf16(p, x, dim, gamma, eps);
+  const int packed_rows = (n + 7) / 8 * 16;  // 8 leading-term rows + 8 residual-term rows per 8 source rows
+  p.n_tiles = (packed_rows + TB_TILE_ROWS - 1) / TB_TILE_ROWS;
+  p.n_kb = dim / TB_KBLOCK;
+  p.w_kb_per_tile = p.n_kb;
+  p.n_tokens = tokens;
+  p.epi = EPI_ADD_PAIR;
+  p.n_rows = n;
+  set_region(p, 0, n, out, n, out_is_f32 ? 1 : 0);
+  return launch_gemv(ctx, p, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int tilert_down_allreduce_op(TbContext* ctx, const void* vec, const uint8_t* w_packed,
                                         const void* x_residual, int tokens, int inter, int dim, void* out,
                                         TbComm* comm, void* stream) {
@@ -922,18 +964,17 @@ extern "C" int tilert_down_allreduce_op(TbContext* ctx, const void* vec, const u
 
 // ------------------------------------------------------------------------------ bf16 products
 namespace {
-// Small per-token work recorded into a chain: it runs on the epilogue warps at the start of the next
-// recorded product, once that product's (and the hook's own) inputs are complete.
-int record_hook(TbContext* ctx, int kind, const AttnPrepParams& prep) {
+// The per-token vector work recorded into a chain: it runs on the converter warps beside the next recorded
+// product, once that product's (and its own) inputs are complete.
+int record_hook(TbContext* ctx, const AttnPrepParams& prep) {
   ChainRecorder& r = ctx->rec;
-  if (r.pending_hook >= 0) return fail(TB_ESTATE, "chain: two hook operators in a row (a product must follow each)%s");
-  if (r.n_hooks >= kChainMaxHooks) return fail(TB_ESTATE, "chain: too many hook operators in one chain%s");
-  const GemvBf16Params& q = prep.wis;
-  if (q.w != nullptr) {
-    TB_REQUIRE(q.n_tokens >= 1 && q.n_tokens <= 4 && q.k % 256 == 0 && q.k <= 8192 && q.n <= 4096 && q.x2 == nullptr);
-  }
+  if (r.pending_hook >= 0) return fail(TB_ESTATE, "chain: two attn_prep operators in a row (a product must follow each)%s");
+  if (r.n_hooks >= kChainMaxHooks) return fail(TB_ESTATE, "chain: too many attn_prep operators in one chain%s");
+  if (prep.wis.w != nullptr)
+    return fail(TB_EINVAL, "chain: pass w_is = NULL to a recorded attn_prep (the head weights are a product of "
+                           "their own, tilert_rmsnorm_proj_rows2_op)%s");
   ChainHook& h = r.params.hooks[r.n_hooks];
-  h.kind = kind;
+  h.kind = HOOK_ATTN_PREP;
   h.prep = prep;
   r.pending_hook = r.n_hooks++;
   return TB_OK;
@@ -942,11 +983,9 @@ int record_hook(TbContext* ctx, int kind, const AttnPrepParams& prep) {
 int launch_gemv_bf16(TbContext* ctx, GemvBf16Params& p, cudaStream_t st) {
   TB_REQUIRE(p.n_tokens >= 1 && p.n_tokens <= 4);
   TB_REQUIRE(p.k % 256 == 0);
-  if (ctx->rec.active) {
-    AttnPrepParams prep{};
-    prep.wis = p;
-    return record_hook(ctx, HOOK_ROWS, prep);
-  }
+  if (ctx->rec.active)
+    return fail(TB_ESTATE, "a bf16 row product cannot be recorded into a chain (pack the weight with "
+                           "pack_bf16_two_term and use tilert_rmsnorm_proj_rows2_op)%s");
   const int tok_t = p.n_tokens == 1 ? 1 : (p.n_tokens == 2 ? 2 : 4);
   const size_t smem = static_cast<size_t>(tok_t) * p.k * sizeof(float);
   const int warps = kGemvBf16Threads / 32;
@@ -1104,25 +1143,25 @@ extern "C" int tilert_mtp_preprocess_op(TbContext* ctx, const void* e, const voi
 
 // -------------------------------------------------------------------- per-token vector operators
 extern "C" int tilert_rmsnorm_kv_op(TbContext* ctx, const void* kv, const float* gamma, float eps, int tokens,
-                                    int dim, const int* cur_pos, void* kv_cache, void* stream) {
+                                    int dim, const int* cur_pos, void* kv_cache, int cache_rows, void* stream) {
   TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && kv != nullptr && gamma != nullptr && cur_pos != nullptr && kv_cache != nullptr);
   rmsnorm_kv_kernel<<<(tokens + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(kv), dim, gamma, eps, dim, cur_pos,
-      reinterpret_cast<__nv_bfloat16*>(kv_cache), tokens);
+      reinterpret_cast<__nv_bfloat16*>(kv_cache), tokens, cache_rows, ctx->status);
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;
 }
 
 extern "C" int tilert_qkv_rope_op(TbContext* ctx, void* q_pe, int heads, int rope, void* pe_cache,
-                                  const int* cur_pos, const float* freqs, int tokens, void* stream) {
+                                  const int* cur_pos, const float* freqs, int tokens, int cache_rows, void* stream) {
   TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && q_pe != nullptr && pe_cache != nullptr && cur_pos != nullptr && freqs != nullptr);
   const int total = tokens * (heads + 1) * (rope / 2);
   qkv_rope_kernel<<<(total + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<__nv_bfloat16*>(q_pe), heads, rope, reinterpret_cast<__nv_bfloat16*>(pe_cache), cur_pos,
-      freqs, tokens);
+      freqs, tokens, cache_rows, ctx->status);
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;
@@ -1136,7 +1175,7 @@ extern "C" int tilert_rotate_op(TbContext* ctx, const void* in, void* out, int h
   const int vecs = tokens * heads;
   rotate128_kernel<<<(vecs + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), heads, rope, freqs, nullptr,
-      nullptr, nullptr, tokens);
+      nullptr, nullptr, tokens, 0, nullptr);
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;
@@ -1144,13 +1183,13 @@ extern "C" int tilert_rotate_op(TbContext* ctx, const void* in, void* out, int h
 
 extern "C" int tilert_layernorm_rope_rotate_op(TbContext* ctx, const void* in, const int* cur_pos, void* k_cache,
                                                const float* weight, const float* bias, const float* freqs, int rope,
-                                               int tokens, void* stream) {
+                                               int tokens, int cache_rows, void* stream) {
   TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && in != nullptr && cur_pos != nullptr && k_cache != nullptr);
   TB_REQUIRE(weight != nullptr && bias != nullptr && freqs != nullptr && rope == 64);
   rotate128_kernel<<<(tokens + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(k_cache), 1, rope, freqs, weight,
-      bias, cur_pos, tokens);
+      bias, cur_pos, tokens, cache_rows, ctx->status);
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;
@@ -1161,8 +1200,8 @@ extern "C" int tilert_attn_prep_op(TbContext* ctx, const void* x, const float* i
                                    int kv_dim, void* kv_cache, void* q_pe, int heads, int rope, void* pe_cache,
                                    const void* iq, void* iq_out, const void* ki, void* ki_cache, const float* ln_w,
                                    const float* ln_b, const float* freqs, const int* cur_pos, int tokens,
-                                   void* stream) {
-  TB_REQUIRE(ctx != nullptr && x != nullptr && w_is != nullptr && idx_w_out != nullptr && kv != nullptr);
+                                   int cache_rows, void* stream) {
+  TB_REQUIRE(ctx != nullptr && kv != nullptr && (w_is == nullptr || (x != nullptr && idx_w_out != nullptr)));
   TB_REQUIRE(kv_gamma != nullptr && kv_cache != nullptr && q_pe != nullptr && pe_cache != nullptr && iq != nullptr);
   TB_REQUIRE(iq_out != nullptr && ki != nullptr && ki_cache != nullptr && ln_w != nullptr && ln_b != nullptr);
   TB_REQUIRE(freqs != nullptr && cur_pos != nullptr && tokens >= 1 && tokens <= 4 && rope == 64);
@@ -1180,7 +1219,7 @@ extern "C" int tilert_attn_prep_op(TbContext* ctx, const void* x, const float* i
   p.wis.out_bf16 = 1;
   p.wis.out_stride = idx_heads;
   constexpr int kWarps = kAttnPrepThreads / 32;
-  p.wis_blocks = (idx_heads + kGemvBf16SmallRows - 1) / kGemvBf16SmallRows;
+  p.wis_blocks = w_is != nullptr ? (idx_heads + kGemvBf16SmallRows - 1) / kGemvBf16SmallRows : 0;
   p.kv = reinterpret_cast<const __nv_bfloat16*>(kv);
   p.kv_stride = kv_dim;
   p.kv_gamma = kv_gamma;
@@ -1205,6 +1244,8 @@ extern "C" int tilert_attn_prep_op(TbContext* ctx, const void* x, const float* i
   p.pos = cur_pos;
   p.freqs = freqs;
   p.n_tokens = tokens;
+  p.cache_rows = cache_rows;
+  p.status = ctx->status;
   static bool attr_set[64] = {};
   if (!attr_set[ctx->device & 63]) {
     TB_CUDA(cudaFuncSetAttribute(attn_prep_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
@@ -1212,13 +1253,7 @@ extern "C" int tilert_attn_prep_op(TbContext* ctx, const void* x, const float* i
     TB_CUDA(cudaFuncSetAttribute(attn_prep_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr_set[ctx->device & 63] = true;
   }
-  if (ctx->rec.active) {
-    // in a chain the rotary table and the epilogue warps' 256 threads stand in for the kernel's blocks
-    constexpr int kEpi = kGemvEpilogueThreads;
-    p.rope_blocks = (tokens * (heads + 1) * (rope / 2) + kEpi - 1) / kEpi;
-    static_assert(kGemvEpilogueThreads == kAttnPrepThreads, "hook blocks are sized like the kernel's");
-    return record_hook(ctx, HOOK_ATTN_PREP, p);
-  }
+  if (ctx->rec.active) return record_hook(ctx, p);
   const int grid = p.wis_blocks + p.kv_blocks + p.rope_blocks + p.iq_blocks + p.ki_blocks;
   const int tok = tokens == 1 ? 1 : (tokens == 2 ? 2 : 4);
   const size_t smem = static_cast<size_t>(tok) * dim * sizeof(float);
@@ -1281,10 +1316,35 @@ extern "C" int tilert_topk_accurate_op(TbContext* ctx, const float* logits, long
 extern "C" int tilert_sparse_index_topk_op(TbContext* ctx, const void* q, const void* k_cache, const void* weights,
                                            float* logits, long long logits_stride, int heads, int tokens, int n_keys,
                                            const int* cur_pos, int k, int* indices, void* stream) {
-  int rc = tilert_sparse_index_op(ctx, q, k_cache, weights, logits, logits_stride, heads, tokens, n_keys, cur_pos,
-                                  stream);
-  if (rc != TB_OK) return rc;
-  return tilert_topk_accurate_op(ctx, logits, logits_stride, tokens, n_keys, k, indices, stream);
+  TB_NOT_CHAINABLE(ctx);
+  TB_REQUIRE(ctx != nullptr && q != nullptr && k_cache != nullptr && weights != nullptr && logits != nullptr);
+  TB_REQUIRE(cur_pos != nullptr && indices != nullptr && n_keys > 0 && k >= 1 && tokens >= 1 && tokens <= 8);
+  TB_REQUIRE(heads == 16 || heads == 32 || heads == 64);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // scoring and selection in one launch: the last thread block of a token selects
+  const dim3 grid((n_keys + kIdxFusedKeys - 1) / kIdxFusedKeys, tokens);
+  const size_t smem = static_cast<size_t>(heads + kIdxFusedKeys) * kIdxPitch * 2;
+  static bool attr_set[64] = {};
+  if (!attr_set[ctx->device & 63]) {
+    TB_CUDA(cudaFuncSetAttribute(indexer_topk_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    TB_CUDA(cudaFuncSetAttribute(indexer_topk_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    TB_CUDA(cudaFuncSetAttribute(indexer_topk_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    attr_set[ctx->device & 63] = true;
+  }
+  const __nv_bfloat16* qq = reinterpret_cast<const __nv_bfloat16*>(q);
+  const __nv_bfloat16* kk = reinterpret_cast<const __nv_bfloat16*>(k_cache);
+  const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(weights);
+  unsigned* done = reinterpret_cast<unsigned*>(ctx->small + 8192);  // [8], zero between launches
+  const long long out_stride = k;
+  if (heads == 64)
+    TB_CUDA(launch(indexer_topk_kernel<64>, grid, dim3(kIdxFusedThreads), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, k, indices, out_stride, done));
+  else if (heads == 32)
+    TB_CUDA(launch(indexer_topk_kernel<32>, grid, dim3(kIdxFusedThreads), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, k, indices, out_stride, done));
+  else
+    TB_CUDA(launch(indexer_topk_kernel<16>, grid, dim3(kIdxFusedThreads), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, k, indices, out_stride, done));
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
 }
 
 extern "C" int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const void* q_pe, const void* kv,

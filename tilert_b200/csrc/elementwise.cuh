@@ -14,59 +14,64 @@ __device__ __forceinline__ float ld_act(const __nv_bfloat16* p) {
   return bf16_bits_to_f32(__ldcg(reinterpret_cast<const unsigned short*>(p)));
 }
 
+// A cache row index past the cache's rows (`cache_rows` > 0) is refused: nothing is stored and the status
+// word says so.  The position is device-resident, so only the device can make this check.
+__device__ __forceinline__ bool cache_row_ok(int row, int cache_rows, int* status) {
+  if (cache_rows <= 0 || (row >= 0 && row < cache_rows)) return true;
+  set_status(status, ST_BAD_ARGUMENT);
+  return false;
+}
+
+// One vector of NV * 256 elements by one warp: every load of the lane up front (8 bf16 per 16-byte load,
+// lane-contiguous), one pass.  NV is a template parameter so that only the registers in use exist.
+template <int NV>
+__device__ __forceinline__ void rmsnorm_vec_warp(const __nv_bfloat16* x, const float* __restrict__ gamma, float eps,
+                                                 __nv_bfloat16* dst) {
+  const int lane = threadIdx.x & 31;
+  constexpr int dim = NV * 256;
+  uint4 raw[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) raw[v] = __ldcg(reinterpret_cast<const uint4*>(x + (v * 32 + lane) * 8));
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const uint32_t w4[4] = {raw[v].x, raw[v].y, raw[v].z, raw[v].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = __uint_as_float(w4[j] << 16), b = __uint_as_float(w4[j] & 0xffff0000u);
+      ss += a * a + b * b;
+    }
+  }
+  ss = warp_sum(ss);
+  const float rinv = rsqrtf(ss / static_cast<float>(dim) + eps);
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int e = (v * 32 + lane) * 8;
+    const float4 g0 = *reinterpret_cast<const float4*>(gamma + e), g1 = *reinterpret_cast<const float4*>(gamma + e + 4);
+    const uint32_t w4[4] = {raw[v].x, raw[v].y, raw[v].z, raw[v].w};
+    const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      o[j] = pack_bf16x2(__uint_as_float(w4[j] << 16) * rinv * gg[2 * j], __uint_as_float(w4[j] & 0xffff0000u) * rinv * gg[2 * j + 1]);
+    *reinterpret_cast<uint4*>(dst + e) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 // kv [tokens, dim] -> cache[pos + t, dim] = bf16(rmsnorm(kv) * gamma).   One warp per token.
 __device__ __forceinline__ void rmsnorm_kv_warp(int tok, const __nv_bfloat16* __restrict__ kv, long long kv_stride,
                                                 const float* __restrict__ gamma, float eps, int dim,
                                                 const int* __restrict__ pos, __nv_bfloat16* __restrict__ cache,
-                                                int n_tokens) {
+                                                int n_tokens, int cache_rows = 0, int* status = nullptr) {
   const int lane = threadIdx.x & 31;
   if (tok >= n_tokens) return;
+  if (!cache_row_ok(*pos + tok, cache_rows, status)) return;
   const __nv_bfloat16* x = kv + tok * kv_stride;
   __nv_bfloat16* dst = cache + static_cast<long long>(*pos + tok) * dim;
-  if (dim % 256 == 0 && dim <= 1024 && (kv_stride % 8) == 0) {
-    // every load of the lane up front (8 bf16 per 16-byte load, lane-contiguous), one pass
-    constexpr int kMaxV = 4;
-    const int nv = dim / 256;
-    uint4 raw[kMaxV];
-    float4 g0[kMaxV], g1[kMaxV];
-#pragma unroll
-    for (int v = 0; v < kMaxV; ++v) {
-      if (v < nv) {
-        const int e = (v * 32 + lane) * 8;
-        raw[v] = __ldcg(reinterpret_cast<const uint4*>(x + e));
-        g0[v] = *reinterpret_cast<const float4*>(gamma + e);
-        g1[v] = *reinterpret_cast<const float4*>(gamma + e + 4);
-      }
-    }
-    float ss = 0.f;
-    float f[kMaxV][8];
-#pragma unroll
-    for (int v = 0; v < kMaxV; ++v) {
-      if (v < nv) {
-        const uint32_t w4[4] = {raw[v].x, raw[v].y, raw[v].z, raw[v].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          f[v][2 * j] = __uint_as_float(w4[j] << 16);
-          f[v][2 * j + 1] = __uint_as_float(w4[j] & 0xffff0000u);
-          ss += f[v][2 * j] * f[v][2 * j] + f[v][2 * j + 1] * f[v][2 * j + 1];
-        }
-      }
-    }
-    ss = warp_sum(ss);
-    const float rinv = rsqrtf(ss / static_cast<float>(dim) + eps);
-#pragma unroll
-    for (int v = 0; v < kMaxV; ++v) {
-      if (v < nv) {
-        const float gg[8] = {g0[v].x, g0[v].y, g0[v].z, g0[v].w, g1[v].x, g1[v].y, g1[v].z, g1[v].w};
-        uint4 o;
-        o.x = pack_bf16x2(f[v][0] * rinv * gg[0], f[v][1] * rinv * gg[1]);
-        o.y = pack_bf16x2(f[v][2] * rinv * gg[2], f[v][3] * rinv * gg[3]);
-        o.z = pack_bf16x2(f[v][4] * rinv * gg[4], f[v][5] * rinv * gg[5]);
-        o.w = pack_bf16x2(f[v][6] * rinv * gg[6], f[v][7] * rinv * gg[7]);
-        *reinterpret_cast<uint4*>(dst + (v * 32 + lane) * 8) = o;
-      }
-    }
-    return;
+  if ((kv_stride % 8) == 0) {
+    if (dim == 512) return rmsnorm_vec_warp<2>(x, gamma, eps, dst);
+    if (dim == 256) return rmsnorm_vec_warp<1>(x, gamma, eps, dst);
+    if (dim == 1024) return rmsnorm_vec_warp<4>(x, gamma, eps, dst);
   }
   float ss = 0.f;
   for (int i = lane; i < dim; i += 32) {
@@ -79,18 +84,19 @@ __device__ __forceinline__ void rmsnorm_kv_warp(int tok, const __nv_bfloat16* __
 }
 __global__ void rmsnorm_kv_kernel(const __nv_bfloat16* __restrict__ kv, long long kv_stride,
                                   const float* __restrict__ gamma, float eps, int dim, const int* __restrict__ pos,
-                                  __nv_bfloat16* __restrict__ cache, int n_tokens) {
+                                  __nv_bfloat16* __restrict__ cache, int n_tokens, int cache_rows, int* status) {
   pdl_launch_dependents();
   pdl_wait();
   rmsnorm_kv_warp(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), kv, kv_stride, gamma, eps, dim, pos, cache,
-                  n_tokens);
+                  n_tokens, cache_rows, status);
 }
 
 // Interleaved RoPE (pairs (x[2i], x[2i+1])) applied in place to q_pe [tokens, heads, rope] and to the
 // cached key rows pe_cache[pos + t, rope].  freqs: [tokens, rope/2, 2] = (cos, sin).
 __device__ __forceinline__ void qkv_rope_thread(int idx, __nv_bfloat16* __restrict__ q_pe, int heads, int rope,
                                                 __nv_bfloat16* __restrict__ pe_cache, const int* __restrict__ pos,
-                                                const float* __restrict__ freqs, int n_tokens) {
+                                                const float* __restrict__ freqs, int n_tokens, int cache_rows = 0,
+                                                int* status = nullptr) {
   const int half = rope / 2;
   const int per_tok = (heads + 1) * half;
   if (idx >= n_tokens * per_tok) return;
@@ -100,18 +106,21 @@ __device__ __forceinline__ void qkv_rope_thread(int idx, __nv_bfloat16* __restri
   __nv_bfloat16* v;
   if (h < heads)
     v = q_pe + (static_cast<long long>(tok) * heads + h) * rope + 2 * i;
-  else
+  else {
+    if (!cache_row_ok(*pos + tok, cache_rows, status)) return;
     v = pe_cache + static_cast<long long>(*pos + tok) * rope + 2 * i;
+  }
   const float a = bf2f(v[0]), b = bf2f(v[1]);
   v[0] = f2bf(a * c - b * s);
   v[1] = f2bf(a * s + b * c);
 }
 __global__ void qkv_rope_kernel(__nv_bfloat16* __restrict__ q_pe, int heads, int rope,
                                 __nv_bfloat16* __restrict__ pe_cache, const int* __restrict__ pos,
-                                const float* __restrict__ freqs, int n_tokens) {
+                                const float* __restrict__ freqs, int n_tokens, int cache_rows, int* status) {
   pdl_launch_dependents();
   pdl_wait();
-  qkv_rope_thread(blockIdx.x * blockDim.x + threadIdx.x, q_pe, heads, rope, pe_cache, pos, freqs, n_tokens);
+  qkv_rope_thread(blockIdx.x * blockDim.x + threadIdx.x, q_pe, heads, rope, pe_cache, pos, freqs, n_tokens, cache_rows,
+                  status);
 }
 
 // 128-point Walsh-Hadamard transform of a warp-distributed vector: lane l holds elements
@@ -140,10 +149,11 @@ __device__ __forceinline__ void rotate128_warp(int vec, const __nv_bfloat16* __r
                                                __nv_bfloat16* __restrict__ out, int heads, int rope,
                                                const float* __restrict__ freqs, const float* __restrict__ ln_w,
                                                const float* __restrict__ ln_b, const int* __restrict__ pos,
-                                               int n_tokens) {
+                                               int n_tokens, int cache_rows = 0, int* status = nullptr) {
   const int lane = threadIdx.x & 31;
   if (vec >= n_tokens * heads) return;
   const int tok = vec / heads;
+  if (pos != nullptr && !cache_row_ok(*pos + tok, cache_rows, status)) return;
   const __nv_bfloat16* x = in + static_cast<long long>(vec) * 128;
   float v[4];
 #pragma unroll
@@ -183,11 +193,12 @@ __device__ __forceinline__ void rotate128_warp(int vec, const __nv_bfloat16* __r
 }
 __global__ void rotate128_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int heads,
                                  int rope, const float* __restrict__ freqs, const float* __restrict__ ln_w,
-                                 const float* __restrict__ ln_b, const int* __restrict__ pos, int n_tokens) {
+                                 const float* __restrict__ ln_b, const int* __restrict__ pos, int n_tokens,
+                                 int cache_rows, int* status) {
   pdl_launch_dependents();
   pdl_wait();
   rotate128_warp(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), in, out, heads, rope, freqs, ln_w, ln_b, pos,
-                 n_tokens);
+                 n_tokens, cache_rows, status);
 }
 
 // MoE routing (sigmoid scores + bias, optional group limiting, top-k, renormalise, scale).

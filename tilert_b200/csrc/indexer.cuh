@@ -126,7 +126,9 @@ constexpr int kTopkItems = 8;  // consecutive elements per thread in the ordered
 // One CTA per row.  Selects the k largest logits among [0, n) (entries equal to -inf are skipped),
 // ties by lower index, and writes their indices in ascending order; unused slots get -1.
 // The selection for one row by one CTA of kTopkThreads threads; `dst` may be shared or global memory.
-__device__ __forceinline__ void topk_radix_row(const float* __restrict__ row, int n, int k, int* dst) {
+template <int THREADS>
+__device__ __forceinline__ void topk_radix_row(const float* row, int n, int k, int* dst) {
+  constexpr int kTopkThreads = THREADS;  // shadows the launch constant: the strides below follow the caller's block
   __shared__ int hist[256];
   __shared__ uint32_t s_prefix;
   __shared__ int s_remaining;
@@ -136,7 +138,7 @@ __device__ __forceinline__ void topk_radix_row(const float* __restrict__ row, in
 
   // count eligible entries
   int cnt = 0;
-  for (int i = tid; i < n; i += kTopkThreads) cnt += f32_order_key(row[i]) > kNegInfKey;
+  for (int i = tid; i < n; i += kTopkThreads) cnt += f32_order_key(__ldcg(row + i)) > kNegInfKey;
   if (tid < 256) hist[tid] = 0;
   if (tid == 0) { s_prefix = 0; s_remaining = 0; }
   __syncthreads();
@@ -161,7 +163,7 @@ __device__ __forceinline__ void topk_radix_row(const float* __restrict__ row, in
       if (tid < 256) hist[tid] = 0;
       __syncthreads();
       for (int i = tid; i < n; i += kTopkThreads) {
-        const uint32_t key = f32_order_key(row[i]);
+        const uint32_t key = f32_order_key(__ldcg(row + i));
         if (key > kNegInfKey && (key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1);
       }
       __syncthreads();
@@ -220,7 +222,7 @@ __device__ __forceinline__ void topk_radix_row(const float* __restrict__ row, in
     for (int j = 0; j < kTopkItems; ++j) {
       const int i = i0 + j;
       if (i < n) {
-        const uint32_t key = f32_order_key(row[i]);
+        const uint32_t key = f32_order_key(__ldcg(row + i));
         if (key > kNegInfKey) {
           if (take_all || key > thr) gt_mask |= 1u << j;
           else if (key == thr) eq_mask |= 1u << j;
@@ -238,7 +240,7 @@ __device__ __forceinline__ void topk_radix_row(const float* __restrict__ row, in
     if (lane == 31) { s_warp_gt[warp] = sc_gt; s_warp_eq[warp] = sc_eq; }
     __syncthreads();
     int pre_gt = 0, pre_eq = 0, tot_gt = 0, tot_eq = 0;
-    for (int w2 = 0; w2 < 32; ++w2) {
+    for (int w2 = 0; w2 < kTopkThreads / 32; ++w2) {
       const int a = s_warp_gt[w2], b = s_warp_eq[w2];
       if (w2 < warp) { pre_gt += a; pre_eq += b; }
       tot_gt += a; tot_eq += b;
@@ -280,23 +282,18 @@ __global__ void __launch_bounds__(kTopkThreads) topk_radix_kernel(const float* _
                                                                   int* __restrict__ out, long long out_stride) {
   pdl_launch_dependents();
   pdl_wait();
-  topk_radix_row(logits + blockIdx.x * logits_stride, n, k, out + blockIdx.x * out_stride);
+  topk_radix_row<kTopkThreads>(logits + blockIdx.x * logits_stride, n, k, out + blockIdx.x * out_stride);
 }
 
-// Same selection for rows of at most kTopkThreads * ITEMS entries: every thread keeps its ITEMS
+// Same selection for rows of at most THREADS * ITEMS entries: every thread keeps its ITEMS
 // consecutive keys in registers, so the row is read from memory once instead of once per pass.
-template <int ITEMS>
-__global__ void __launch_bounds__(kTopkThreads) topk_radix_reg_kernel(const float* __restrict__ logits,
-                                                                      long long logits_stride, int n, int k,
-                                                                      int* __restrict__ out, long long out_stride) {
-  pdl_launch_dependents();
-  pdl_wait();
+template <int THREADS, int ITEMS>
+__device__ __forceinline__ void topk_radix_reg_body(const float* row, int n, int k, int* dst) {
+  constexpr int kTopkThreads = THREADS;
   __shared__ int hist[256];
   __shared__ uint32_t s_prefix;
   __shared__ int s_remaining;
   __shared__ int s_warp_gt[32], s_warp_eq[32];
-  const float* row = logits + blockIdx.x * logits_stride;
-  int* dst = out + blockIdx.x * out_stride;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int i0 = tid * ITEMS;
 
@@ -304,7 +301,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_radix_reg_kernel(const floa
   int cnt = 0;
 #pragma unroll
   for (int j = 0; j < ITEMS; ++j) {
-    key[j] = i0 + j < n ? f32_order_key(row[i0 + j]) : 0u;  // 0 is below the key of -inf: never eligible
+    key[j] = i0 + j < n ? f32_order_key(__ldcg(row + i0 + j)) : 0u;  // 0 is below the key of -inf: never eligible
     cnt += key[j] > kNegInfKey;
   }
   if (tid < 256) hist[tid] = 0;
@@ -396,7 +393,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_radix_reg_kernel(const floa
   if (lane == 31) { s_warp_gt[warp] = sc_gt; s_warp_eq[warp] = sc_eq; }
   __syncthreads();
   int pre_gt = 0, pre_eq = 0, tot_gt = 0, tot_eq = 0;
-  for (int w2 = 0; w2 < 32; ++w2) {
+  for (int w2 = 0; w2 < kTopkThreads / 32; ++w2) {
     const int a = s_warp_gt[w2], b = s_warp_eq[w2];
     if (w2 < warp) { pre_gt += a; pre_eq += b; }
     tot_gt += a; tot_eq += b;
@@ -418,6 +415,125 @@ __global__ void __launch_bounds__(kTopkThreads) topk_radix_reg_kernel(const floa
   }
   const int n_sel = tot_gt + min(tot_eq, need_eq);
   for (int i = n_sel + tid; i < k; i += kTopkThreads) dst[i] = -1;
+}
+
+template <int ITEMS>
+__global__ void __launch_bounds__(kTopkThreads) topk_radix_reg_kernel(const float* logits, long long logits_stride, int n,
+                                                                      int k, int* out, long long out_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  topk_radix_reg_body<kTopkThreads, ITEMS>(logits + blockIdx.x * logits_stride, n, k, out + blockIdx.x * out_stride);
+}
+
+// ------------------------------------------------------------------ scoring + selection in one launch
+// Every CTA scores kIdxFusedKeys keys of one query token (16 per warp, as indexer_logits_kernel) and
+// counts itself done; the CTA that finds itself last for its token then selects that token's top-k from
+// the logits the others left in L2.  One launch instead of two: the selection of 4096 logits is a
+// single-CTA job of a few microseconds either way, and the boundary between the launches cost as much.
+constexpr int kIdxFusedWarps = 16;
+constexpr int kIdxFusedThreads = kIdxFusedWarps * 32;
+constexpr int kIdxFusedKeys = kIdxFusedWarps * kIdxKeysPerWarp;  // 256 keys per CTA
+
+template <int H>
+__global__ void __launch_bounds__(kIdxFusedThreads) indexer_topk_kernel(
+    const __nv_bfloat16* __restrict__ q,       // [tokens, H, 128]
+    const __nv_bfloat16* __restrict__ kcache,  // [T, 128]
+    const __nv_bfloat16* __restrict__ w,       // [tokens, H]
+    float* logits,                             // [tokens, logits_stride]
+    long long logits_stride, int n_keys, const int* __restrict__ pos, int k,
+    int* out, long long out_stride,            // [tokens, out_stride] selected indices, ascending, -1 padded
+    unsigned* done                             // [tokens] CTAs finished per token; zero between launches
+) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [H][pitch]
+  __nv_bfloat16* sk = sq + H * kIdxPitch;                          // [kIdxFusedKeys][pitch]
+  __shared__ float sw[H];
+  __shared__ int s_last;
+  const int tok = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int key0 = blockIdx.x * kIdxFusedKeys;
+
+  constexpr int kKIters = kIdxFusedKeys * 16 / kIdxFusedThreads;  // 8
+  uint4 kv[kKIters];
+#pragma unroll
+  for (int it = 0; it < kKIters; ++it) {
+    const int i = it * kIdxFusedThreads + threadIdx.x;
+    const int r = i >> 4, c = i & 15;
+    kv[it] = make_uint4(0, 0, 0, 0);
+    if (key0 + r < n_keys) {
+      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(kv[it].x), "=r"(kv[it].y), "=r"(kv[it].z), "=r"(kv[it].w)
+                   : "l"(kcache + static_cast<long long>(key0 + r) * 128 + c * 8));
+    }
+  }
+  for (int i = threadIdx.x; i < H * 16; i += kIdxFusedThreads)
+    *reinterpret_cast<uint4*>(sq + (i >> 4) * kIdxPitch + (i & 15) * 8) =
+        *reinterpret_cast<const uint4*>(q + (static_cast<long long>(tok) * H + (i >> 4)) * 128 + (i & 15) * 8);
+#pragma unroll
+  for (int it = 0; it < kKIters; ++it) {
+    const int i = it * kIdxFusedThreads + threadIdx.x;
+    *reinterpret_cast<uint4*>(sk + (i >> 4) * kIdxPitch + (i & 15) * 8) = kv[it];
+  }
+  for (int i = threadIdx.x; i < H; i += kIdxFusedThreads) sw[i] = bf2f(w[tok * H + i]);
+  __syncthreads();
+
+  float acc[H / 8][4];
+#pragma unroll
+  for (int n = 0; n < H / 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+  const __nv_bfloat16* wk = sk + warp * kIdxKeysPerWarp * kIdxPitch;
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    uint32_t a[4];
+    ldmatrix_x4(a, wk + (lane & 15) * kIdxPitch + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+    for (int n2 = 0; n2 < H / 16; ++n2) {
+      uint32_t b[4];
+      ldmatrix_x4(b, sq + (n2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * kIdxPitch + ks * 16 + ((lane >> 3) & 1) * 8);
+      const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+      mma_bf16_16816(acc[2 * n2], a, b0);
+      mma_bf16_16816(acc[2 * n2 + 1], a, b1);
+    }
+  }
+  const int g = lane >> 2, qd = lane & 3;
+  float lo = 0.f, hi = 0.f;
+#pragma unroll
+  for (int n = 0; n < H / 8; ++n) {
+    const float w0 = sw[n * 8 + 2 * qd], w1 = sw[n * 8 + 2 * qd + 1];
+    lo += fmaxf(acc[n][0], 0.f) * w0 + fmaxf(acc[n][1], 0.f) * w1;
+    hi += fmaxf(acc[n][2], 0.f) * w0 + fmaxf(acc[n][3], 0.f) * w1;
+  }
+  lo += __shfl_xor_sync(0xffffffffu, lo, 1);
+  lo += __shfl_xor_sync(0xffffffffu, lo, 2);
+  hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+  hi += __shfl_xor_sync(0xffffffffu, hi, 2);
+  if (qd == 0) {
+    const int last = *pos + tok;
+    const int k_lo = key0 + warp * kIdxKeysPerWarp + g, k_hi = k_lo + 8;
+    if (k_lo < n_keys) logits[tok * logits_stride + k_lo] = k_lo <= last ? lo : -INFINITY;
+    if (k_hi < n_keys) logits[tok * logits_stride + k_hi] = k_hi <= last ? hi : -INFINITY;
+  }
+
+  // ---- the last CTA of this token selects ----
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(done + tok, 1u);
+    s_last = prev == gridDim.x - 1u ? 1 : 0;
+    if (s_last) done[tok] = 0u;  // every CTA of the token has arrived: ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* row = logits + tok * logits_stride;
+  int* dst = out + tok * out_stride;
+  if (n_keys <= kIdxFusedThreads * 8)
+    topk_radix_reg_body<kIdxFusedThreads, 8>(row, n_keys, k, dst);
+  else if (n_keys <= kIdxFusedThreads * 16)
+    topk_radix_reg_body<kIdxFusedThreads, 16>(row, n_keys, k, dst);
+  else
+    topk_radix_row<kIdxFusedThreads>(row, n_keys, k, dst);
 }
 
 }  // namespace tb

@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(kTopkThreads) sample_kernel(const SampleParams
   const float log_s1 = __logf(s1);
 
   // ---- the 1024 largest logits, then sorted by (value descending, index ascending) ----
-  topk_radix_row(row, p.vocab, kSampleCandidates, s_idx);
+  topk_radix_row<kTopkThreads>(row, p.vocab, kSampleCandidates, s_idx);
   __syncthreads();
   s_val[tid] = s_idx[tid] >= 0 ? row[s_idx[tid]] : -INFINITY;
   if (s_idx[tid] < 0) s_idx[tid] = 0x7fffffff;

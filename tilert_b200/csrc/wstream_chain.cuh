@@ -13,11 +13,13 @@
 //     bounded, and set the status word when they give up.  Signals complete in index order, because every
 //     CTA goes through the phases in order: waiting for the highest needed index is enough.  The last CTA
 //     to leave the kernel clears them, so a captured CUDA graph replays without host help.
-//   * Hooks.  Small per-token work that sits between two products -- the bf16 router / indexer head-weight
-//     rows, the latent RMSNorm into the cache, the rotary embeddings, the indexer rotations -- runs on the
-//     epilogue warps at the start of the phase it is attached to, after the phase's dependencies.
+//   * Hooks.  The small per-token vector work between the products -- latent RMSNorm into the cache, rotary
+//     embeddings, indexer rotations -- runs on the two converter warps of every CTA, beside the epilogue
+//     warps' main loop of the phase it is attached to and after that phase's dependencies.  (The two bf16
+//     row products of a layer, router gate and indexer head weights, are not hooks: packed as two e4m3 terms
+//     per row they are phases of the weight stream like every other product.)
 //   * Routing.  A phase whose weight addresses depend on the router (routed experts) lets its producer
-//     warps wait for the hook that wrote the scores, route the token themselves and only then compute
+//     warps wait for the phase that wrote the scores, route the token themselves and only then compute
 //     addresses; the shared expert is a phase of its own with static addresses, so the stream covers the
 //     routing latency.
 //
@@ -34,15 +36,15 @@ namespace tb {
 constexpr int kChainMaxPhases = 12;
 constexpr int kChainMaxHooks = 3;
 constexpr int kChainSignals = 2 * kChainMaxPhases;  // main(ph) = 2 ph, hook(ph) = 2 ph + 1; [kChainSignals] = CTAs that left
+constexpr int kChainSigStride = 32;                 // one 128-byte line per counter: they are polled, and lines map to L2 slices
 
 enum ChainHookKind : int {
-  HOOK_ROWS = 1,       // out[t, r] = W[r, :] . f(x[t, :]) for a few bf16 / f32 rows (router gate)
-  HOOK_ATTN_PREP = 2,  // indexer head weights (rows) + latent norm into the cache + rotary embeddings + indexer rotations
+  HOOK_ATTN_PREP = 2,  // latent norm into the cache + rotary embeddings + indexer rotations
 };
 
 struct ChainHook {
   int kind;
-  AttnPrepParams prep;  // HOOK_ROWS uses prep.wis only
+  AttnPrepParams prep;  // (its head-weight projection is not used here: that product rides the weight stream)
 };
 
 struct ChainPhase {
@@ -56,8 +58,9 @@ struct ChainPhase {
 
 struct ChainParams {
   int n_phases;
-  unsigned* signals;         // [kChainSignals + 1], zero between launches
+  unsigned* signals;         // [kChainSignals + 1] counters, kChainSigStride words apart, zero between launches
   unsigned long long* prof;  // optional trace: [phase][grid <= 256][8] %globaltimer stamps (ChainProfSlot)
+  int max_inflight;          // weight blocks a CTA keeps in flight at most (a multiple of 4, <= kGemvStages)
   ChainHook hooks[kChainMaxHooks];
   ChainPhase ph[kChainMaxPhases];
 };
@@ -66,53 +69,72 @@ enum ChainProfSlot : int {
   kChainProfStart = 0,      // dependencies of the phase met (epilogue warp 0)
   kChainProfStats = 1,      // norm statistics ready
   kChainProfHook = 2,       // hook done (0 when the phase has none)
-  kChainProfFirstData = 3,  // first accumulator of the phase complete
-  kChainProfLastUnit = 4,   // last unit read back
+  kChainProfFixupNs = 3,    // nanoseconds this CTA spent collecting split-tile partial sums as a tile's owner
+  kChainProfFixupRounds = 4,  // polling rounds that took
   kChainProfTilesDone = 5,  // tile reductions / split-tile fix-ups done
   kChainProfSignal = 6,     // main signal raised (after the all-reduce, if any)
   kChainProfUnits = 7,      // units of this CTA in the phase
 };
 
 constexpr int kChainNormBytes = 2 * kGemvHelperWarps * 4 * 4;  // statistics double-buffered by phase parity
-constexpr int kChainSmemBytes = kGemvSmemBytes + kChainNormBytes + 64;
+constexpr int kChainHookBytes = (sizeof(ChainHook) * kChainMaxHooks + 15) / 16 * 16;  // the hooks' parameters, copied at entry
+constexpr int kChainWlandBytes = kGemvStages * 8;  // one more barrier per slot: the slot's weight block has landed
+constexpr int kChainSmemBytes = kGemvSmemBytes + kChainNormBytes + 64 + kChainHookBytes + kChainWlandBytes + 16;
 
-// Units [u0, u1) of phase `p` that CTA `cta` takes.  A phase with fewer units than CTAs is spread over its
-// first grid_eff CTAs (one unit each at least), so that a split row tile never has an idle CTA inside it.
-__device__ __forceinline__ void chain_range(const GemvParams& p, int cta, int& u0, int& u1) {
+// Units [u0, u1) of phase `p` that CTA `cta` takes.  A phase is spread over grid_eff CTAs starting at cta_base:
+// all of them for a long product; for a short one only as many as keep a split row tile to a few CTAs (the
+// hand-over of a tile's partial sums costs its owner a round trip through L2 per four guests).  `c` receives
+// the CTA's index within the phase (-1: not taking part).
+__device__ __forceinline__ void chain_range(const GemvParams& p, int cta, int& u0, int& u1, int& c) {
   const int grid = p.grid_eff;
-  if (cta >= grid) {
+  c = cta - p.cta_base;
+  if (c < 0 || c >= grid) {
+    c = -1;
     u0 = u1 = 0;
     return;
   }
   if (p.whole_tiles) {
-    u0 = static_cast<int>(gemv_range_begin(p.n_tiles, grid, cta)) * p.n_kb;
-    u1 = static_cast<int>(gemv_range_begin(p.n_tiles, grid, cta + 1)) * p.n_kb;
+    u0 = static_cast<int>(gemv_range_begin(p.n_tiles, grid, c)) * p.n_kb;
+    u1 = static_cast<int>(gemv_range_begin(p.n_tiles, grid, c + 1)) * p.n_kb;
   } else {
     const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
-    u0 = static_cast<int>(gemv_range_begin(units, grid, cta));
-    u1 = static_cast<int>(gemv_range_begin(units, grid, cta + 1));
+    u0 = static_cast<int>(gemv_range_begin(units, grid, c));
+    u1 = static_cast<int>(gemv_range_begin(units, grid, c + 1));
   }
 }
+__device__ __forceinline__ void chain_range(const GemvParams& p, int cta, int& u0, int& u1) {
+  int c;
+  chain_range(p, cta, u0, u1, c);
+}
 
-// Bounded wait for a signal counter to reach `target` (one polling thread).
+// Bounded wait for a signal counter to reach `target`.  ONE thread per role and CTA polls (the others meet it
+// at a thread-block barrier), and it backs off between polls: every poll of every CTA lands on the L2 slice
+// that holds the counter, and a slice saturated with polls delays whatever else maps to it by microseconds.
 __device__ __forceinline__ bool sig_wait(const unsigned* sig, unsigned target, const volatile int* abort) {
+  // Polls are relaxed loads (served by L2); the acquire that orders what follows is one more load of the
+  // counter once it has been seen complete.
   unsigned v;
+  bool got = false;
 #pragma unroll 1
-  for (int i = 0; i < 32; ++i) {
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(sig) : "memory");
-    if (v >= target) return true;
+  for (int i = 0; i < 4 && !got; ++i) {
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(sig) : "memory");
+    got = v >= target;
   }
-  const long long t0 = clock64();
-  const long long budget = kWaitBudgetCycles;
-  while (true) {
+  if (!got) {
+    const long long t0 = clock64();
+    const long long budget = kWaitBudgetCycles;
+    while (!got) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i) {
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(sig) : "memory");
-      if (v >= target) return true;
-      __nanosleep(32);
+      for (int i = 0; i < 64 && !got; ++i) {
+        __nanosleep(100);
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(sig) : "memory");
+        got = v >= target;
+      }
+      if (!got && (*abort != 0 || clock64() - t0 > budget)) return false;
     }
-    if (*abort != 0 || clock64() - t0 > budget) return false;
   }
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(sig) : "memory");
+  return v >= target;
 }
 // Arrivals that complete signal `sig`: the grid for a hook signal, the phase's main_target for a main signal.
 __device__ __forceinline__ unsigned sig_target(const ChainParams& cp, int sig) {
@@ -131,142 +153,39 @@ __device__ __forceinline__ void epi_bar(int id) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kGemvEpilogueThreads) : "memory");
 }
 
-// A few weight rows against the activation vector(s), by the 256 epilogue threads of every CTA: row
-// r = cta, cta + grid, ...; the eight warps split K.  Optional RMSNorm of the activations (statistics
-// computed here), optional bf16 rounding of the normalised values, bf16 or f32 weights and outputs.
-// `scratch`: 64 floats of shared memory.
-__device__ __noinline__ void chain_hook_rows(const GemvBf16Params& q, int cta, int grid, float* scratch) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  float rinv[4] = {1.f, 1.f, 1.f, 1.f};
-  if (q.gamma != nullptr) {
-    float ss[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int it = 0; it < 8; ++it) {  // k <= 8192: at most eight 8-byte chunks per thread, all requested at once
-      const int i = (it * kGemvEpilogueThreads + tid) * 4;
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        if (i < q.k && t < q.n_tokens) {
-          const uint2 r = __ldcg(reinterpret_cast<const uint2*>(q.x + t * q.x_stride + i));
-          const float a0 = __uint_as_float(r.x << 16), a1 = __uint_as_float(r.x & 0xffff0000u);
-          const float a2 = __uint_as_float(r.y << 16), a3 = __uint_as_float(r.y & 0xffff0000u);
-          ss[t] += a0 * a0 + a1 * a1 + a2 * a2 + a3 * a3;
-        }
-      }
+// The per-token vector work of attn_prep_kernel -- latent RMSNorm into the cache, rotary embeddings, indexer
+// rotations -- spread over the two auxiliary (converter) warps of every CTA: `aw` = this warp's index among
+// them, `n_aw` = their number in the launch.  Everything here is a warp- or thread-level routine with a
+// handful of registers; it runs beside the epilogue warps' main loop, off the critical path of the products.
+__device__ __noinline__ void chain_aux_attn_prep(const AttnPrepParams& a, int aw, int n_aw) {
+  const int lane = threadIdx.x & 31;
+  const int n_kv = a.n_tokens, n_iq = a.n_tokens * a.idx_heads, n_ki = a.n_tokens;
+  const int n_rope = a.n_tokens * (a.heads + 1) * (a.rope / 2);  // thread-level items
+  const int rope_warps = (n_rope + 31) / 32;
+  const int n_items = n_kv + n_ki + n_iq + rope_warps;
+  // from the far end of the grid: the first CTAs carry the most product units when a phase is short
+  for (int it = n_aw - 1 - aw; it < n_items; it += n_aw) {
+    int b = it;
+    if (b < n_kv) {
+      rmsnorm_kv_warp(b, a.kv, a.kv_stride, a.kv_gamma, a.kv_eps, a.kv_dim, a.pos, a.kv_cache, a.n_tokens, a.cache_rows, a.status);
+      continue;
     }
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const float v = warp_sum(ss[t]);
-      if (lane == 0) scratch[warp * 4 + t] = v;
+    b -= n_kv;
+    if (b < n_ki) {
+      rotate128_warp(b, a.ki, a.ki_cache, 1, a.rope, a.freqs, a.ln_w, a.ln_b, a.pos, a.n_tokens, a.cache_rows, a.status);
+      continue;
     }
-    epi_bar(kChainHookBarrier);
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      float tot = 0.f;
-#pragma unroll
-      for (int w2 = 0; w2 < kGemvEpilogueWarps; ++w2) tot += scratch[w2 * 4 + t];
-      rinv[t] = rsqrtf(tot / static_cast<float>(q.k) + q.eps);
+    b -= n_ki;
+    if (b < n_iq) {
+      rotate128_warp(b, a.iq, a.iq_out, a.idx_heads, a.rope, a.freqs, nullptr, nullptr, nullptr, a.n_tokens);
+      continue;
     }
-    epi_bar(kChainHookBarrier);  // the scratch is reused below
-    if (q.xnorm_out != nullptr && cta == 0) {
-      for (int i = tid * 4; i < q.k; i += kGemvEpilogueThreads * 4) {
-        const float4 g = __ldg(reinterpret_cast<const float4*>(q.gamma + i));
-        for (int t = 0; t < q.n_tokens; ++t) {
-          const uint2 r = __ldcg(reinterpret_cast<const uint2*>(q.x + t * q.x_stride + i));
-          uint2 o;
-          o.x = pack_bf16x2(__uint_as_float(r.x << 16) * rinv[t] * g.x, __uint_as_float(r.x & 0xffff0000u) * rinv[t] * g.y);
-          o.y = pack_bf16x2(__uint_as_float(r.y << 16) * rinv[t] * g.z, __uint_as_float(r.y & 0xffff0000u) * rinv[t] * g.w);
-          *reinterpret_cast<uint2*>(q.xnorm_out + t * q.xnorm_stride + i) = o;
-        }
-      }
-    }
-  }
-  const int kslice = q.k / kGemvEpilogueWarps;  // per warp: a multiple of 32 elements (k % 256 == 0), at most 1024
-  for (int row = cta; row < q.n; row += grid) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const int c0 = it * 128 + lane * 4;
-      if (c0 < kslice) {
-        const int k0 = warp * kslice + c0;
-        float wv[4];
-        if (q.w_is_f32) {
-          const float4 w4 = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(q.w) +
-                                                                  static_cast<long long>(row) * q.k + k0));
-          wv[0] = w4.x; wv[1] = w4.y; wv[2] = w4.z; wv[3] = w4.w;
-        } else {
-          const uint2 w2 = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(q.w) +
-                                                                static_cast<long long>(row) * q.k + k0));
-          wv[0] = __uint_as_float(w2.x << 16); wv[1] = __uint_as_float(w2.x & 0xffff0000u);
-          wv[2] = __uint_as_float(w2.y << 16); wv[3] = __uint_as_float(w2.y & 0xffff0000u);
-        }
-        float4 g = make_float4(1.f, 1.f, 1.f, 1.f);
-        if (q.gamma != nullptr) g = __ldg(reinterpret_cast<const float4*>(q.gamma + k0));
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          if (t < q.n_tokens) {
-            const uint2 r = __ldcg(reinterpret_cast<const uint2*>(q.x + t * q.x_stride + k0));
-            float x4[4] = {__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u), __uint_as_float(r.y << 16),
-                           __uint_as_float(r.y & 0xffff0000u)};
-            if (q.gamma != nullptr) {
-              const float g4[4] = {g.x, g.y, g.z, g.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                x4[j] = x4[j] * rinv[t] * g4[j];
-                if (q.round_norm_bf16) x4[j] = bf2f(f2bf(x4[j]));
-              }
-            }
-            acc[t] += wv[0] * x4[0] + wv[1] * x4[1] + wv[2] * x4[2] + wv[3] * x4[3];
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const float v = warp_sum(acc[t]);
-      if (lane == 0) scratch[warp * 4 + t] = v;
-    }
-    epi_bar(kChainHookBarrier);
-    if (tid < q.n_tokens) {
-      float s = 0.f;
-#pragma unroll
-      for (int w2 = 0; w2 < kGemvEpilogueWarps; ++w2) s += scratch[w2 * 4 + tid];
-      if (q.out_bf16)
-        reinterpret_cast<__nv_bfloat16*>(q.out)[tid * q.out_stride + row] = f2bf(s);
-      else
-        reinterpret_cast<float*>(q.out)[tid * q.out_stride + row] = s;
-    }
-    epi_bar(kChainHookBarrier);
+    b -= n_iq;
+    qkv_rope_thread(b * 32 + lane, a.q_pe, a.heads, a.rope, a.pe_cache, a.pos, a.freqs, a.n_tokens, a.cache_rows, a.status);
   }
 }
 
-// The per-token vector work of attn_prep_kernel (its blocks become loop iterations spread over the CTAs).
-__device__ __noinline__ void chain_hook_attn_prep(const AttnPrepParams& a, int cta, int grid, float* scratch) {
-  if (a.wis.w != nullptr) chain_hook_rows(a.wis, cta, grid, scratch);
-  const int warp = threadIdx.x >> 5;
-  constexpr int kWarps = kGemvEpilogueWarps;
-  const int n_vb = a.kv_blocks + a.rope_blocks + a.iq_blocks + a.ki_blocks;
-  // start from the far end of the grid: the first CTAs already carry the rows above
-  for (int vb = grid - 1 - cta; vb < n_vb; vb += grid) {
-    int b = vb;
-    if (b < a.kv_blocks) {
-      rmsnorm_kv_warp(b * kWarps + warp, a.kv, a.kv_stride, a.kv_gamma, a.kv_eps, a.kv_dim, a.pos, a.kv_cache, a.n_tokens);
-      continue;
-    }
-    b -= a.kv_blocks;
-    if (b < a.rope_blocks) {
-      qkv_rope_thread(b * kGemvEpilogueThreads + threadIdx.x, a.q_pe, a.heads, a.rope, a.pe_cache, a.pos, a.freqs, a.n_tokens);
-      continue;
-    }
-    b -= a.rope_blocks;
-    if (b < a.iq_blocks) {
-      rotate128_warp(b * kWarps + warp, a.iq, a.iq_out, a.idx_heads, a.rope, a.freqs, nullptr, nullptr, nullptr, a.n_tokens);
-      continue;
-    }
-    b -= a.iq_blocks;
-    rotate128_warp(b * kWarps + warp, a.ki, a.ki_cache, 1, a.rope, a.freqs, a.ln_w, a.ln_b, a.pos, a.n_tokens);
-  }
-}
-
+template <bool PROF>
 __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __grid_constant__ ChainParams cp) {
   extern __shared__ __align__(128) uint8_t smem[];
   float* merge = reinterpret_cast<float*>(smem + kGemvStages * kGemvSlotStride);  // [2][group threads][8]
@@ -277,14 +196,28 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(const_cast<int*>(cta_error) + 1);
   float* norm_all = reinterpret_cast<float*>(const_cast<int*>(cta_error) + 4);  // [2][helper warps][4 tokens]
   int* route_ids = reinterpret_cast<int*>(norm_all + 2 * kGemvHelperWarps * 4);  // [producer warps][kGemvRouteSlots]
+  // The hooks are separate functions that take their parameters by reference: a reference into the kernel's
+  // parameter space would make every field a dependent load from memory, so they get a shared-memory copy.
+  ChainHook* s_hooks = reinterpret_cast<ChainHook*>(
+      (reinterpret_cast<uintptr_t>(route_ids + kGemvProducerWarps * kGemvRouteSlots) + 15) & ~static_cast<uintptr_t>(15));
+  // wland[s]: the weight block of slot s has landed.  Kept apart from full[s] (which also waits for the X
+  // block) so that the producers can bound the weight bytes they have in flight without waiting for
+  // activations: see max_inflight.
+  uint64_t* wland = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_hooks) + kChainHookBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grid = gridDim.x, cta = blockIdx.x;
 
   pdl_launch_dependents();
+  {
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(&cp.hooks[0]);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(s_hooks);
+    for (int i = threadIdx.x; i < static_cast<int>(sizeof(ChainHook) * kChainMaxHooks / 4); i += kGemvThreads) dst[i] = src[i];
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kGemvStages; ++s) {
-      mbar_init(&full[s], 2);                 // the weight copy's expect-tx arrival + the X block's arrival
+      mbar_init(&full[s], 1);                 // the X block: the converting warp's arrival, or the copy's expect-tx arrival
+      mbar_init(&wland[s], 1);                // the weight copy's expect-tx arrival
       mbar_init(&empty[s], kGemvGroupWarps);  // the warps of the epilogue group that read the unit back
       mbar_init(&acc_full[s], 1);             // completion of the unit's MMAs
     }
@@ -316,7 +249,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
     const int pw = warp - kGemvFirstProducerWarp;
     int* mine = route_ids + pw * kGemvRouteSlots;
     const uint64_t pol = policy_evict_first();
-    int ibase = 0, last_gi = -1;
+    int ibase = 0, last_gi = -1, j_mine = 0;  // j_mine: copies this producer has issued so far
+    const int depth = cp.max_inflight / kGemvProducerWarps;  // of them in flight at most (a ring's worth: no bound)
     bool failed = false, after_pdl = false;
     unsigned want = 0;
     for (int ph = 0; ph < cp.n_phases; ++ph) {
@@ -331,13 +265,16 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
         // addresses depend on earlier results: wait for the predecessor kernel, then for the signal
         if (lane == 0) {
           if (!after_pdl) pdl_wait();
-          if (c.w_sig >= 0 && !failed && !sig_wait(cp.signals + c.w_sig, sig_target(cp, c.w_sig), cta_error)) {
+          if (pw == 0 && c.w_sig >= 0 && !failed &&
+              !sig_wait(cp.signals + c.w_sig * kChainSigStride, sig_target(cp, c.w_sig), cta_error)) {
             set_status(p0.status, ST_CHAIN_TIMEOUT);
             *cta_error = 1;
-            failed = true;
           }
         }
         after_pdl = true;
+        // producer warp 0 polled for all four (its acquire, then this barrier, order the others' reads)
+        if (c.w_sig >= 0) asm volatile("bar.sync 6, %0;" ::"n"(kGemvProducerWarps * 32) : "memory");
+        failed = failed || *cta_error != 0;
         failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
         if (p.route.scores != nullptr) {
           int my_id = 0;
@@ -352,7 +289,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
               expert_select_store(my_id, my_w, p.route.top_k, p.route.shared_id, p.route.probs, p.route.ids,
                                   p.route.slot_ids, p.route.slot_w);
             __syncwarp();
-            if (lane == 0) sig_raise(cp.signals + 2 * ph);  // the extra arrival of main_target
+            if (lane == 0) sig_raise(cp.signals + 2 * ph * kChainSigStride);  // the extra arrival of main_target
           }
           __syncwarp();
           if (p.route.for_kseg)
@@ -385,14 +322,22 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
             failed = true;
             break;
           }
+          // Bound the weight bytes in flight: this producer's copy of `depth` turns ago must have landed.  A
+          // ring's worth of outstanding copies per SM is several times what saturates the memory, and all of
+          // it queues ahead of every small latency-critical access of the phase transitions.
+          if (j_mine >= depth) {
+            const int gp = gi - depth * kGemvProducerWarps;
+            if (gp >= 0 && !mbar_wait(&wland[gp % kGemvStages], static_cast<uint32_t>(gp / kGemvStages) & 1, cta_error)) {
+              failed = true;
+              break;
+            }
+          }
           uint8_t* dst = smem + s * kGemvSlotStride;
-          if (j < kGemvStages) {
-            mbar_expect_tx(&full[s], TB_WBLK_BYTES);
-            bulk_g2s_stream(dst, w_src(t, kb), TB_WBLK_BYTES, &full[s], pol);
-          } else {
-            mbar_expect_tx(&full[s], TB_WBLK_BYTES + TB_XBLK_BYTES);
-            bulk_g2s_stream(dst, w_src(t, kb), TB_WBLK_BYTES, &full[s], pol);
-            mbar_arrive(&full[s]);  // stands in for the converter's arrival of the first pass
+          mbar_expect_tx(&wland[s], TB_WBLK_BYTES);
+          bulk_g2s_stream(dst, w_src(t, kb), TB_WBLK_BYTES, &wland[s], pol);
+          if (j >= kGemvStages) {
+            // beyond the phase's first pass the X block is copied from the launch's shared blocks
+            mbar_expect_tx(&full[s], TB_XBLK_BYTES);
             if (!after_pdl) {
               pdl_wait();
               after_pdl = true;
@@ -407,6 +352,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
             asm volatile("fence.proxy.async.global;" ::: "memory");
             bulk_g2s(dst + kGemvSlotXOff, p.xs + static_cast<long long>(xb) * TB_XBLK_BYTES, TB_XBLK_BYTES, &full[s]);
           }
+          ++j_mine;
           last_gi = gi;
           kb += kGemvProducerWarps;
           while (kb >= p.n_kb) {
@@ -431,6 +377,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
       // do not leave while this thread's copies may still be landing in shared memory
       for (int back = 0; back < kGemvStages && last_gi - back >= 0; back += kGemvProducerWarps) {
         const int gi = last_gi - back;
+        mbar_wait(&wland[gi % kGemvStages], static_cast<uint32_t>(gi / kGemvStages) & 1, cta_error);
         mbar_wait(&full[gi % kGemvStages], static_cast<uint32_t>(gi / kGemvStages) & 1, cta_error);
       }
     }
@@ -451,7 +398,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
       int s = mw;
       uint32_t ph_full = 0;
       for (int gi = mw; gi < total; gi += kGemvMmaWarps) {
-        if (!mbar_wait(&full[s], ph_full, cta_error)) {
+        if (!mbar_wait(&wland[s], ph_full, cta_error) || !mbar_wait(&full[s], ph_full, cta_error)) {
           set_status(p0.status, ST_WAIT_FULL_TIMEOUT);
           *cta_error = 1;
           break;
@@ -473,6 +420,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
     }
   } else {
     // ------------------------------------------------ epilogue warps (0-7) and converter warps (14-15)
+    // Static operands that the phases' prologues read with ordinary loads -- the norm gains -- are pulled
+    // into L2 now, before the wait for the predecessor.
+    if (is_epilogue) {
+      for (int ph = 0; ph < cp.n_phases; ++ph) {
+        const GemvParams& p = cp.ph[ph].g;
+        if (p.gamma == nullptr) continue;
+        const int n_lines = p.n_kb * (TB_KBLOCK * 4 / 128);
+        for (int l = cta + static_cast<int>(threadIdx.x) * grid; l < n_lines; l += kGemvEpilogueThreads * grid)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.gamma) + l * 128));
+      }
+    }
     pdl_wait();  // everything below reads or writes activations
     const bool conv = !is_epilogue;
     const int cw = warp - kGemvFirstConverterWarp;
@@ -493,22 +451,23 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
     for (int ph = 0; ph < cp.n_phases; ++ph) {
       const ChainPhase& c = cp.ph[ph];
       const GemvParams& p = c.g;
-      int u0, u1;
-      chain_range(p, cta, u0, u1);
+      int u0, u1, pc;  // pc: this CTA's index within the phase
+      chain_range(p, cta, u0, u1, pc);
       const int n = u1 - u0;
       const long long units = static_cast<long long>(p.n_tiles) * p.n_kb;
-      unsigned long long* prof = cp.prof != nullptr && warp == 0 && lane == 0 ? cp.prof + (ph * 256 + cta) * 8 : nullptr;
+      // trace slots of this (phase, CTA); the untraced instantiation carries no trace of it in registers
+      unsigned long long* const prof = PROF && warp == 0 && lane == 0 ? cp.prof + (ph * 256 + cta) * 8 : nullptr;
 
       // ---- dependencies of the activation side ----
       if (c.wait_sig >= 0) {
-        int got = 1;
-        if (lane == 0 && ok) got = sig_wait(cp.signals + c.wait_sig, sig_target(cp, c.wait_sig), cta_error) ? 1 : 0;
-        got = __shfl_sync(0xffffffffu, got, 0);
-        if (!got) {
+        // epilogue warp 0 polls for the ten helper warps (its acquire, then the barrier, order their reads)
+        if (warp == 0 && lane == 0 && ok &&
+            !sig_wait(cp.signals + c.wait_sig * kChainSigStride, sig_target(cp, c.wait_sig), cta_error)) {
           set_status(p0.status, ST_CHAIN_TIMEOUT);
           *cta_error = 1;
-          ok = false;
         }
+        asm volatile("bar.sync 2, %0;" ::"n"(kGemvHelperWarps * 32) : "memory");
+        ok = ok && *cta_error == 0;
       }
       if (prof != nullptr) prof[kChainProfStart] = globaltimer_ns();
 
@@ -552,25 +511,33 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
       gemv_rinv(p, norm_part, rinv);
       if (prof != nullptr) prof[kChainProfStats] = globaltimer_ns();
 
+      // ---- the X blocks of the phase's first pass over the ring, straight into the slots: the ten helper
+      // warps take them round-robin (the epilogue warps have nothing to read back before these exist; the
+      // slots' previous units were released by these same warps before they got here) ----
+      for (int j = hw; j < n && j < kGemvStages && ok; j += kGemvHelperWarps) {
+        const int gi = ibase + j;
+        const int s = gi % kGemvStages;
+        // the slot's previous unit must have been read back before its X block is overwritten
+        if (gi >= kGemvStages && !mbar_wait(&empty[s], ((gi / kGemvStages) & 1) ^ 1, cta_error)) {
+          set_status(p0.status, ST_WAIT_EMPTY_TIMEOUT);
+          *cta_error = 1;
+          ok = false;
+          break;
+        }
+        const int u = u0 + j;
+        const int t = u / p.n_kb, kb = u % p.n_kb;
+        const int xseg = p.tiles_per_xseg > 0 ? t / p.tiles_per_xseg : 0;
+        gemv_convert_xblock(p, xseg * p.n_kb + kb, rinv, smem + s * kGemvSlotStride + kGemvSlotXOff, lane);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[s]);
+      }
       if (conv) {
-        // ---- converter warps: the X blocks of the phase's first pass over the ring, straight into the slots ----
-        for (int j = (cw - (ibase & 1) + 2) & 1; j < n && j < kGemvStages && ok; j += kGemvConverterWarps) {
-          const int gi = ibase + j;
-          const int s = gi % kGemvStages;
-          // the slot's previous unit must have been read back before its X block is overwritten
-          if (gi >= kGemvStages && !mbar_wait(&empty[s], ((gi / kGemvStages) & 1) ^ 1, cta_error)) {
-            set_status(p0.status, ST_WAIT_EMPTY_TIMEOUT);
-            *cta_error = 1;
-            ok = false;
-            break;
-          }
-          const int u = u0 + j;
-          const int t = u / p.n_kb, kb = u % p.n_kb;
-          const int xseg = p.tiles_per_xseg > 0 ? t / p.tiles_per_xseg : 0;
-          gemv_convert_xblock(p, xseg * p.n_kb + kb, rinv, smem + s * kGemvSlotStride + kGemvSlotXOff, lane);
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&full[s]);
+        // ---- auxiliary work attached to this phase, beside the epilogue warps' main loop ----
+        if (c.hook >= 0) {
+          if (ok) chain_aux_attn_prep(s_hooks[c.hook].prep, cta * kGemvConverterWarps + cw, grid * kGemvConverterWarps);
+          asm volatile("bar.sync 7, %0;" ::"n"(kGemvConverterWarps * 32) : "memory");
+          if (cw == 0 && lane == 0) sig_raise(cp.signals + (2 * ph + 1) * kChainSigStride);
         }
         ibase += n;
         continue;
@@ -587,88 +554,68 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
         }
       }
 
-      // ---- hook ----
-      if (c.hook >= 0) {
-        const ChainHook& h = cp.hooks[c.hook];
-        if (h.kind == HOOK_ROWS)
-          chain_hook_rows(h.prep.wis, cta, grid, merge);
-        else
-          chain_hook_attn_prep(h.prep, cta, grid, merge);
-        epi_bar(kChainEpiBarrier);
-        if (threadIdx.x == 0) sig_raise(cp.signals + 2 * ph + 1);
-        if (prof != nullptr) prof[kChainProfHook] = globaltimer_ns();
-      }
-
       // ---- main loop: read the accumulators back, scale, reduce per row tile ----
       const unsigned long long ar_epoch = ar_epoch0 + static_cast<unsigned long long>(c.ar_index);
       float out[8];
 #pragma unroll
       for (int q = 0; q < 8; ++q) out[q] = 0.f;
 
-      auto split_tile = [&](int t, const float (&v)[8]) {
-        const int tile_u0 = t * p.n_kb, tile_u1 = tile_u0 + p.n_kb;
-        unsigned long long* part = reinterpret_cast<unsigned long long*>(p.partial);
-        if (u0 > tile_u0) {
-          unsigned long long* dst = part + (static_cast<long long>(cta * 4 + gw) * 32 + lane) * 8;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const unsigned long long word = (static_cast<unsigned long long>(split_tag) << 32) | __float_as_uint(v[j]);
-            asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(dst + j), "l"(word) : "memory");
-          }
-          return;
-        }
-        const int c_last = gemv_owner(tile_u1 - 1, units, p.grid_eff);
-        float sum[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) sum[j] = v[j];
+      // Partial sums of up to four guest CTAs of a split tile, polled until every word carries this launch's
+      // tag (bounded), added to `acc` in CTA order.  Guests first .. first + cnt - 1 (phase-local indices).
+      auto gather_guests = [&](int first, int cnt, float (&acc)[8], unsigned& rounds) {
+        if (cnt <= 0) return;
+        const unsigned long long* part = reinterpret_cast<const unsigned long long*>(p.partial);
         const long long t0 = clock64();
         const long long budget = kWaitBudgetCycles;
         constexpr int kBatch = 4;
-        for (int cb = cta + 1; cb <= c_last && ok; cb += kBatch) {
-          unsigned long long w[kBatch][8];
-          unsigned pending = 0;
-#pragma unroll
-          for (int g = 0; g < kBatch; ++g)
-            if (cb + g <= c_last) pending |= 1u << g;
-          while (pending != 0u) {
-#pragma unroll
-            for (int g = 0; g < kBatch; ++g) {
-              if ((pending >> g) & 1u) {
-                const unsigned long long* src = part + (static_cast<long long>((cb + g) * 4 + gw) * 32 + lane) * 8;
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w[g][j]) : "l"(src + j) : "memory");
-              }
-            }
-#pragma unroll
-            for (int g = 0; g < kBatch; ++g) {
-              if ((pending >> g) & 1u) {
-                bool all = true;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) all = all && static_cast<uint32_t>(w[g][j] >> 32) == split_tag;
-                if (all) pending &= ~(1u << g);
-              }
-            }
-            pending = __reduce_or_sync(0xffffffffu, pending);
-            if (pending != 0u && (*cta_error != 0 || clock64() - t0 > budget)) {
-              set_status(p0.status, ST_SPLIT_TIMEOUT);
-              *cta_error = 1;
-              ok = false;
-              break;
-            }
-          }
-          if (!ok) break;
+        unsigned long long w[kBatch][8];
+        unsigned pending = (1u << cnt) - 1u;
+        while (pending != 0u && ok) {
 #pragma unroll
           for (int g = 0; g < kBatch; ++g) {
-            if (cb + g <= c_last) {
+            if ((pending >> g) & 1u) {
+              // word j of lane l sits at [j][l]: the 32 lanes of one load read 256 contiguous bytes
+              const unsigned long long* src = part + static_cast<long long>((first + g) * 4 + gw) * 256 + lane;
 #pragma unroll
-              for (int j = 0; j < 8; ++j) sum[j] += __uint_as_float(static_cast<uint32_t>(w[g][j]));
+              for (int j = 0; j < 8; ++j)
+                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w[g][j]) : "l"(src + j * 32) : "memory");
             }
           }
+#pragma unroll
+          for (int g = 0; g < kBatch; ++g) {
+            if ((pending >> g) & 1u) {
+              bool all = true;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) all = all && static_cast<uint32_t>(w[g][j] >> 32) == split_tag;
+              if (all) pending &= ~(1u << g);
+            }
+          }
+          pending = __reduce_or_sync(0xffffffffu, pending);  // the warp moves on together
+          if (PROF) ++rounds;
+          if (pending != 0u && (*cta_error != 0 || clock64() - t0 > budget)) {
+            set_status(p0.status, ST_SPLIT_TIMEOUT);
+            *cta_error = 1;
+            ok = false;
+          }
         }
-        if (ok) gemv_epilogue_row(p, t, gw, lane, sum, ar_epoch);
+        if (!ok) return;
+#pragma unroll
+        for (int g = 0; g < kBatch; ++g) {
+          if (g < cnt) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += __uint_as_float(static_cast<uint32_t>(w[g][j]));
+          }
+        }
       };
 
+      // End of a row tile (every epilogue warp gets here for every tile, on every path; all conditions below
+      // are uniform over the CTA, so every barrier is met by all 256 threads).  Group 1 hands its sums to
+      // group 0.  A whole tile is finished by group 0.  A tile whose k blocks are spread over several CTAs
+      // belongs to the CTA that holds its first unit; every other CTA of the tile (a "guest") leaves its
+      // partial sums in its own slot as 64-bit words tagged with the launch number (a tagged word IS the
+      // arrival of its value), and the owner -- which reaches the tile at the very end of its range -- picks
+      // them up eight guests per round, four by each epilogue group at the same time, in a fixed order:
+      // own + (guests 1-4 one after the other) + (guests 5-8 summed among themselves), and so on.
       auto finish_tile = [&](int t) {
         float* mb = merge + (merge_buf * kGemvGroupThreads + gw * 32 + lane) * 8;
         if (eg == 1) {
@@ -682,12 +629,55 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
           const float4 m1 = *reinterpret_cast<const float4*>(mb + 4);
           out[0] += m0.x; out[1] += m0.y; out[2] += m0.z; out[3] += m0.w;
           out[4] += m1.x; out[5] += m1.y; out[6] += m1.z; out[7] += m1.w;
-          const int tile_u0 = t * p.n_kb, tile_u1 = tile_u0 + p.n_kb;
-          if (u0 <= tile_u0 && u1 >= tile_u1) {
-            if (ok) gemv_epilogue_row(p, t, gw, lane, out, ar_epoch);
-          } else {
-            split_tile(t, out);
+        }
+        const int tile_u0 = t * p.n_kb, tile_u1 = tile_u0 + p.n_kb;
+        if (u0 <= tile_u0 && u1 >= tile_u1) {
+          if (eg == 0 && ok) gemv_epilogue_row(p, t, gw, lane, out, ar_epoch);
+        } else if (u0 > tile_u0) {
+          if (eg == 0) {
+            unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.partial) +
+                                      static_cast<long long>(pc * 4 + gw) * 256 + lane;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const unsigned long long word = (static_cast<unsigned long long>(split_tag) << 32) | __float_as_uint(out[j]);
+              asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(dst + j * 32), "l"(word) : "memory");
+            }
           }
+        } else {
+          const int c_last = gemv_owner(tile_u1 - 1, units, p.grid_eff);
+          const unsigned long long fix0 = PROF ? globaltimer_ns() : 0ull;
+          unsigned fix_rounds = 0;
+          for (int first = pc + 1; first <= c_last; first += 2 * 4) {
+            const int mine = first + eg * 4;
+            const int cnt = c_last - mine + 1 < 4 ? c_last - mine + 1 : 4;
+            float* mb2 = merge + (merge_buf * kGemvGroupThreads + gw * 32 + lane) * 8;
+            // group 0 adds its guests onto its own sums one after the other; group 1 sums its guests from zero
+            float gs[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) gs[j] = eg == 0 ? out[j] : 0.f;
+            gather_guests(mine, cnt, gs, fix_rounds);
+            if (eg == 0) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) out[j] = gs[j];
+            } else {
+              *reinterpret_cast<float4*>(mb2) = make_float4(gs[0], gs[1], gs[2], gs[3]);
+              *reinterpret_cast<float4*>(mb2 + 4) = make_float4(gs[4], gs[5], gs[6], gs[7]);
+            }
+            asm volatile("bar.sync 3, %0;" ::"n"(kGemvEpilogueThreads) : "memory");
+            merge_buf ^= 1;
+            if (eg == 0 && c_last >= first + 4) {
+              const float4 m0 = *reinterpret_cast<const float4*>(mb2);
+              const float4 m1 = *reinterpret_cast<const float4*>(mb2 + 4);
+              out[0] += m0.x; out[1] += m0.y; out[2] += m0.z; out[3] += m0.w;
+              out[4] += m1.x; out[5] += m1.y; out[6] += m1.z; out[7] += m1.w;
+            }
+          }
+          ok = ok && *cta_error == 0;
+          if (PROF && prof != nullptr) {
+            prof[kChainProfFixupNs] += globaltimer_ns() - fix0;  // time this CTA spent collecting split-tile partial sums
+            prof[kChainProfFixupRounds] += fix_rounds;           // polling rounds of epilogue warp 0
+          }
+          if (eg == 0 && ok) gemv_epilogue_row(p, t, gw, lane, out, ar_epoch);
         }
 #pragma unroll
         for (int q = 0; q < 8; ++q) out[q] = 0.f;
@@ -707,7 +697,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
             *cta_error = 1;
             ok = false;
           } else {
-            if (prof != nullptr && j < 2 && prof[kChainProfFirstData] == 0ull) prof[kChainProfFirstData] = globaltimer_ns();
             tc_fence_after();
             uint32_t dr[8];
             tmem_ld8_issue(tmem_base + lane_base + static_cast<uint32_t>(s * kGemvAccCols), dr);
@@ -734,7 +723,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
           phs ^= 1u;
         }
         if (kb == p.n_kb - 1 || j == n - 1) {
-          if (j == n - 1 && prof != nullptr) prof[kChainProfLastUnit] = globaltimer_ns();
           finish_tile(t);
         }
       }
@@ -793,7 +781,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
       // ---- the phase's results of this CTA are stored: raise its main signal ----
       ok = ok && *cta_error == 0;
       epi_bar(kChainEpiBarrier);
-      if (threadIdx.x == 0) sig_raise(cp.signals + 2 * ph);
+      if (threadIdx.x == 0) sig_raise(cp.signals + 2 * ph * kChainSigStride);
       if (prof != nullptr) prof[kChainProfSignal] = globaltimer_ns();
       ibase += n;
     }
@@ -813,9 +801,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
     // The last CTA to leave clears the signals and opens the next epoch of the shared X blocks: by then
     // every CTA has passed every wait of this launch.
     __threadfence();
-    const unsigned prev = atomicAdd(cp.signals + kChainSignals, 1u);
+    const unsigned prev = atomicAdd(cp.signals + kChainSignals * kChainSigStride, 1u);
     if (prev == static_cast<unsigned>(grid) - 1u) {
-      for (int i = 0; i <= kChainSignals; ++i) cp.signals[i] = 0u;
+      for (int i = 0; i <= kChainSignals; ++i) cp.signals[i * kChainSigStride] = 0u;
       *reinterpret_cast<volatile unsigned*>(p0.xstate) = *reinterpret_cast<const volatile unsigned*>(p0.xstate) + 1u;
       __threadfence();
     }

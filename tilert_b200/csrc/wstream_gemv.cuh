@@ -29,6 +29,7 @@ namespace tb {
 enum Epilogue : int {
   EPI_STORE = 0,     // out = acc (+ residual)
   EPI_SILU_MUL = 1,  // rows g / g+8 of each 16-row group are (gate, up): out = silu(gate) * up
+  EPI_ADD_PAIR = 2,  // rows g / g+8 of each 16-row group are the two e4m3 terms of one bf16 weight row: out = sum
 };
 
 struct OutRegion {
@@ -38,6 +39,7 @@ struct OutRegion {
   void* ptr;                 // destination of token 0, row row_begin
   long long token_stride;    // elements between tokens
   const int* pos_ptr;        // optional device int: destination starts at token index *pos_ptr
+  int pos_rows;              // with pos_ptr: rows of the destination (0 = unchecked); a row past them is not stored
 };
 
 // All-reduce endpoint of one rank.  A partial sum travels as one 64-bit word {call number, f32 bits}
@@ -134,7 +136,8 @@ struct GemvParams {
   int n_tokens;
   int whole_tiles;       // 1: CTAs take whole row tiles (set by the host when that balances well enough)
   int shared_x;          // X_BF16: 1 when some CTA has more units than ring slots, so the CTAs share the conversion
-  int grid_eff;          // chained launches: CTAs that take units of this phase (min(grid, units)); the rest idle through it
+  int grid_eff;          // chained launches: CTAs that take units of this phase; the rest idle through it
+  int cta_base;          // chained launches: first of those CTAs (a short phase sits at the far end of the grid)
   int only_token;        // >= 0: store only this token's results (per-token expert lists)
   int cols_per_token;
   int epi;
@@ -274,14 +277,15 @@ __device__ __forceinline__ bool flag_wait(const unsigned* flag, unsigned want, c
     if (v == want) return true;
   }
   const long long t0 = clock64();
+  const long long budget = kWaitBudgetCycles;
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
+      __nanosleep(64);
       asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
       if (v == want) return true;
-      __nanosleep(64);
     }
-    if (*abort != 0 || clock64() - t0 > kWaitBudgetCycles) return false;
+    if (*abort != 0 || clock64() - t0 > budget) return false;
   }
 }
 
@@ -312,7 +316,13 @@ __device__ __forceinline__ void gemv_store(const GemvParams& p, int row, int tok
     if (i < p.n_regions && row >= p.regions[i].row_begin && row < p.regions[i].row_end) {
       const OutRegion& r = p.regions[i];
       long long tok = token;
-      if (r.pos_ptr != nullptr) tok += *r.pos_ptr;
+      if (r.pos_ptr != nullptr) {
+        tok += *r.pos_ptr;
+        if (r.pos_rows > 0 && (tok < 0 || tok >= r.pos_rows)) {
+          set_status(p.status, ST_BAD_ARGUMENT);
+          continue;
+        }
+      }
       const long long off = tok * r.token_stride + (row - r.row_begin);
       if (r.dtype == 0)
         reinterpret_cast<__nv_bfloat16*>(r.ptr)[off] = f2bf(v);
@@ -338,8 +348,9 @@ __device__ __forceinline__ void gemv_epilogue_row(const GemvParams& p, int tile,
 #pragma unroll
     for (int t = 0; t < 8; ++t) val[t] = v[t];
   }
-  if (p.epi == EPI_SILU_MUL) {
-    // every 16 packed rows are 8 gate rows followed by their 8 up rows: lane l (bit 3 clear) pairs with l + 8
+  if (p.epi == EPI_SILU_MUL || p.epi == EPI_ADD_PAIR) {
+    // every 16 packed rows are 8 gate rows followed by their 8 up rows (or 8 leading-term rows followed by
+    // their 8 residual-term rows): lane l (bit 3 clear) pairs with l + 8
     const int n16 = (tile * TB_TILE_ROWS + row_in_tile) >> 4;
 #pragma unroll
     for (int t = 0; t < 8; ++t) {
@@ -347,7 +358,8 @@ __device__ __forceinline__ void gemv_epilogue_row(const GemvParams& p, int tile,
         const float up = __shfl_xor_sync(0xffffffffu, val[t], 8);
         if ((lane & 8) == 0) {
           const float gate = val[t];
-          gemv_store(p, n16 * 8 + (lane & 7), t, __fdividef(gate, 1.0f + __expf(-gate)) * up);
+          gemv_store(p, n16 * 8 + (lane & 7), t,
+                     p.epi == EPI_SILU_MUL ? __fdividef(gate, 1.0f + __expf(-gate)) * up : gate + up);
         }
       }
     }
@@ -818,11 +830,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       const int tile_u0 = t * p.n_kb, tile_u1 = tile_u0 + p.n_kb;
       unsigned long long* part = reinterpret_cast<unsigned long long*>(p.partial);
       if (u0 > tile_u0) {
-        unsigned long long* dst = part + (static_cast<long long>(cta * 4 + gw) * 32 + lane) * 8;
+        // word j of lane l sits at [j][l]: the 32 lanes of one store (and of the owner's load) cover 256
+        // contiguous bytes instead of 32 separate sectors
+        unsigned long long* dst = part + static_cast<long long>(cta * 4 + gw) * 256 + lane;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const unsigned long long word = (static_cast<unsigned long long>(split_tag) << 32) | __float_as_uint(v[j]);
-          asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(dst + j), "l"(word) : "memory");
+          asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(dst + j * 32), "l"(word) : "memory");
         }
         return;
       }
@@ -843,10 +857,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
 #pragma unroll
           for (int g = 0; g < kBatch; ++g) {
             if ((pending >> g) & 1u) {
-              const unsigned long long* src = part + (static_cast<long long>((cb + g) * 4 + gw) * 32 + lane) * 8;
+              const unsigned long long* src = part + static_cast<long long>((cb + g) * 4 + gw) * 256 + lane;
 #pragma unroll
               for (int j = 0; j < 8; ++j)
-                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w[g][j]) : "l"(src + j) : "memory");
+                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w[g][j]) : "l"(src + j * 32) : "memory");
             }
           }
 #pragma unroll
@@ -868,12 +882,27 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
           }
         }
         if (!ok) break;
+        // Guests are added in rounds of eight: the first four onto the running sum one after the other,
+        // the next four summed among themselves first (the chained kernel gathers those two halves with
+        // its two epilogue groups at the same time; the grouping is kept the same here so that both
+        // kernels give the same bits).
+        const bool second_half = ((cb - (cta + 1)) & 4) != 0;
+        float half[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) half[j] = 0.f;
 #pragma unroll
         for (int g = 0; g < kBatch; ++g) {
           if (cb + g <= c_last) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sum[j] += __uint_as_float(static_cast<uint32_t>(w[g][j]));
+            for (int j = 0; j < 8; ++j) {
+              const float v2 = __uint_as_float(static_cast<uint32_t>(w[g][j]));
+              if (second_half) half[j] += v2; else sum[j] += v2;
+            }
           }
+        }
+        if (second_half) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sum[j] += half[j];
         }
       }
       if (ok) gemv_epilogue_row(p, t, gw, lane, sum, ar_epoch);

@@ -77,6 +77,8 @@ class LayerWeights:
         self.k_norm_w = f32(f"{at}.indexer.k_norm.weight")
         self.k_norm_b = f32(f"{at}.indexer.k_norm.bias")
         self.wis = g(f"{at}.indexer.weights_proj.weight").to(BF16).contiguous()
+        # the same weight as two e4m3 terms per row (exact for bf16): rides the FP8 weight stream in chained launches
+        self.wis2 = pack.pack_bf16_two_term(self.wis)
         # q_a | kv_a | k_pe | indexer wk: replicated on every rank
         self.w_qkva = pack.pack_concat([
             (g(f"{at}.q_a_proj.weight"), g(f"{at}.q_a_proj.weight_scale_inv")),
@@ -117,6 +119,8 @@ class LayerWeights:
             r = slice(rank * il, (rank + 1) * il)
             rs_ = slice(rank * il // 128, (rank + 1) * il // 128)
             self.router = g(f"{m}.gate.weight").contiguous()
+            # bf16 in HF checkpoints: packed like wis2 for the weight stream; an f32 gate keeps its row product
+            self.router2 = pack.pack_bf16_two_term(self.router) if self.router.dtype == BF16 else None
             self.router_bias = f32(f"{m}.gate.e_score_correction_bias")
             n_e = a.n_routed_experts
             gu_tiles, n_kb = 2 * il // 128, a.dim // 128
@@ -230,10 +234,12 @@ class DecoderLayer:
         with ops.chain(dev, chained):
             ops.rmsnorm_projx_wqkva(x, w.in_norm, w.w_qkva, cur_pos, v(self.q_a), v(self.kv), self.pe_cache, v(self.ki),
                                     eps=a.eps)
+            if chained:  # the indexer head weights as one more product of the stream (it waits for nothing)
+                ops.rmsnorm_proj_rows2(x, w.in_norm, w.wis2, v(self.idx_w), eps=a.eps)
             ops.rmsnorm_proj_q(v(self.q_a), w.q_norm, w.w_qb, v(self.q_nope), v(self.q_pe), v(self.iq), eps=a.eps)
-            ops.attn_prep(x, w.in_norm, w.wis, v(self.idx_w), v(self.kv), w.kv_norm, self.kv_cache, v(self.q_pe),
-                          self.pe_cache, v(self.iq), v(self.iq_rt), v(self.ki), self.ki_cache, w.k_norm_w, w.k_norm_b,
-                          freqs, cur_pos, eps=a.eps, rope=a.qk_rope_head_dim)
+            ops.attn_prep(x, w.in_norm, None if chained else w.wis, v(self.idx_w), v(self.kv), w.kv_norm, self.kv_cache,
+                          v(self.q_pe), self.pe_cache, v(self.iq), v(self.iq_rt), v(self.ki), self.ki_cache, w.k_norm_w,
+                          w.k_norm_b, freqs, cur_pos, eps=a.eps, rope=a.qk_rope_head_dim)
             ops.projq_wqb(v(self.q_nope), w.w_absorb, None, v(self.q_lat))
         ops.sparse_index_topk(v(self.iq_rt), self.ki_cache, v(self.idx_w), self.idx_logits, v(self.sel), cur_pos,
                               n_keys=n_keys)
@@ -250,8 +256,12 @@ class DecoderLayer:
                 ops.rmsnorm_up_gate_silu(v(self.h), w.post_norm, w.w_gu, v(self.ffn_hidden), eps=a.eps)
                 ops.down_allreduce(v(self.ffn_hidden), w.w_down, None, v(self.h), 0, v(self.out), comm=self.comm)
             else:
-                ops.rmsnorm_expert_proj(v(self.h), w.post_norm, w.router, v(self.scores), None if chained else v(self.h_norm),
-                                        eps=a.eps)
+                if chained and w.router2 is not None:
+                    # router logits on the weight stream, ahead of the shared expert that covers the routing
+                    ops.rmsnorm_proj_rows2(v(self.h), w.post_norm, w.router2, v(self.scores), eps=a.eps)
+                else:
+                    ops.rmsnorm_expert_proj(v(self.h), w.post_norm, w.router, v(self.scores),
+                                            None if chained else v(self.h_norm), eps=a.eps)
                 scores = v(self.scores) if self.forced_scores is None else self.forced_scores
                 # chained: the products normalise the raw state themselves instead of waiting for the router's copy
                 ops.expert_select_up_gate_silu(v(self.h) if chained else v(self.h_norm), scores, w.router_bias, w.w_gu,

@@ -38,6 +38,10 @@ class DsaModel:
         self.token_out = torch.zeros(1, dtype=torch.int64, device=dev)
         self.use_graph = use_graph
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        # Host copy of the device-resident position: the kernels write cache row ``cur_pos`` and mask on it,
+        # while the host picks the indexer's scan length from ``pos``; the two must not drift, and a position
+        # past the caches or the rotary table must be refused before anything is launched.
+        self._pos = 0
         # sampling state (the reference's SAMPLING_CONFIG / TOP_P_SCORES / TOP_N_LOG_PROBS / TOP_N_INDICES
         # temp vars, temp_var_indices.py:64-73): greedy until set_sampling is called
         self.sampling_config = torch.tensor([0.0, 1.0, 0.0, 0.0], dtype=F32, device=dev)  # temperature, top_p, top_k, use_top_p
@@ -52,9 +56,14 @@ class DsaModel:
     # -- reference driver controls (end2end.py:551-577) --
     def reset_sequence(self) -> None:
         self.cur_pos.zero_()
+        self._pos = 0
 
     def set_cur_pos(self, pos: int) -> None:
+        if not 0 <= pos < min(self.cache_len, self.freqs.shape[0]):
+            raise ValueError(f"set_cur_pos({pos}): the caches hold {self.cache_len} rows, the rotary table "
+                             f"{self.freqs.shape[0]} positions")
         self.cur_pos.fill_(pos)
+        self._pos = pos
 
     def set_sampling(self, temperature: float = 0.0, top_p: float = 1.0, top_k: int = 0, use_top_p: bool = False,
                      seed: int | None = None) -> None:
@@ -117,10 +126,16 @@ class DsaModel:
     def forward(self, token: int | torch.Tensor, pos: int) -> None:
         """Run one decode step for ``token`` at position ``pos`` (asynchronous; results in
         ``self.logits`` / ``self.token_out``)."""
+        if pos != self._pos:
+            raise ValueError(f"forward(pos={pos}): the device position is {self._pos} (use set_cur_pos to move it)")
+        if pos >= self.cache_len or pos >= self.freqs.shape[0]:
+            raise ValueError(f"forward(pos={pos}): past the end of the caches ({self.cache_len} rows) or of the rotary "
+                             f"table ({self.freqs.shape[0]} positions)")
         if isinstance(token, int):
             self.token.fill_(token)
         else:
             self.token.copy_(token.view(-1)[:1])
+        self._pos = pos + 1
         n_keys = self._bucket(pos)
         if not self.use_graph:
             self._step_ops(n_keys)

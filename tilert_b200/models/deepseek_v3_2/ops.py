@@ -33,6 +33,11 @@ def _ctx(t: torch.Tensor):
     return ctypes.c_void_p(_tb.tilert_init(t.device.index))
 
 
+def _rows(cache: torch.Tensor | None) -> int:
+    """Rows of a cache tensor [..., T, d]: the kernels refuse to write a position at or past it."""
+    return 0 if cache is None else int(cache.shape[-2])
+
+
 def _need(t: torch.Tensor | None, dtype, name: str, optional: bool = False) -> None:
     if t is None:
         if optional:
@@ -125,7 +130,7 @@ def projx_wqkva_packed(xpack, cols_per_token, w_packed, tokens, dim, q_lora, kv_
     _need(cur_pos, I32, "cur_pos", optional=rope == 0)
     _tb.check(_tb.lib().tilert_projx_wqkva_op(_ctx(w_packed), _p(xpack), cols_per_token, _p(w_packed), tokens, dim,
                                               q_lora, kv_lora, rope, ki_dim, _p(cur_pos), _p(q_out), _p(kv_out),
-                                              _p(pe_cache), _p(ki_out), _stream()))
+                                              _p(pe_cache), _rows(pe_cache), _p(ki_out), _stream()))
 
 
 def rmsnorm_projx_wqkva(x, gamma, w_packed, cur_pos, q_out, kv_out, pe_cache, ki_out=None, *, eps=1e-6):
@@ -143,8 +148,8 @@ def rmsnorm_projx_wqkva(x, gamma, w_packed, cur_pos, q_out, kv_out, pe_cache, ki
     ki_dim = 0 if ki_out is None else ki_out.shape[-1]
     _tb.check(_tb.lib().tilert_rmsnorm_projx_wqkva_op(_ctx(x), _p(x), _p(gamma), eps, _p(w_packed), tokens, dim,
                                                       q_out.shape[-1], kv_out.shape[-1], pe_cache.shape[-1], ki_dim,
-                                                      _p(cur_pos), _p(q_out), _p(kv_out), _p(pe_cache), _p(ki_out),
-                                                      _stream()))
+                                                      _p(cur_pos), _p(q_out), _p(kv_out), _p(pe_cache), _rows(pe_cache),
+                                                      _p(ki_out), _stream()))
 
 
 def projx_wqkva(x_in, x_scale, w_packed, cur_pos, q_out, kv_out, pe_cache, profile_logs=None, *,
@@ -230,6 +235,20 @@ def rmsnorm_expert_proj(x, gamma, w_gate, scores_out, hidden_out, profile_logs=N
     _tb.check(_tb.lib().tilert_rmsnorm_expert_proj_op(_ctx(x), _p(x), _p(gamma), eps, _p(w_gate),
                                                       int(w_gate.dtype == F32), tokens, dim, w_gate.shape[0],
                                                       _p(scores_out), _p(hidden_out), _stream()))
+
+
+def rmsnorm_proj_rows2(x, gamma, w_packed2, out, *, eps=1e-6):
+    """``out = W . RMSNorm(x)`` for a bf16 weight packed as two e4m3 terms per row (``pack.pack_bf16_two_term``)
+    on the FP8 weight stream: the router gate (ops/rmsnorm_expert_proj.py:151-169, f32 ``out``) and the indexer
+    head weights (ops/projx_wis.py:21-40, bf16 ``out``).  ``gamma`` None: ``x`` is used as it is."""
+    _need(x, BF16, "x")
+    _need(gamma, F32, "gamma", optional=True)
+    _need(w_packed2, U8, "w_packed2")
+    if out.dtype not in (BF16, F32):
+        raise ValueError("out must be bfloat16 or float32")
+    tokens, dim = x.shape[-2], x.shape[-1]
+    _tb.check(_tb.lib().tilert_rmsnorm_proj_rows2_op(_ctx(x), _p(x), _p(gamma), eps, _p(w_packed2), tokens, dim,
+                                                     out.shape[-1], _p(out), int(out.dtype == F32), _stream()))
 
 
 def expert_select_up_gate_silu(hidden_in, scores, bias, w_packed, hidden_out, probs_out, idx_out,
@@ -386,7 +405,7 @@ def rmsnorm_kv(kv, gamma, cur_pos, kv_cache, profile_logs=None, *, model_arch="d
     _need(cur_pos, I32, "cur_pos")
     _need(kv_cache, BF16, "kv_cache")
     _tb.check(_tb.lib().tilert_rmsnorm_kv_op(_ctx(kv), _p(kv), _p(gamma), eps, kv.shape[-2], kv.shape[-1],
-                                             _p(cur_pos), _p(kv_cache), _stream()))
+                                             _p(cur_pos), _p(kv_cache), _rows(kv_cache), _stream()))
 
 
 def qkv_rope(q_pe, pe_cache, rope_freqs, cur_pos, profile_logs=None, *, model_arch="deepseek_v3_2"):
@@ -397,7 +416,7 @@ def qkv_rope(q_pe, pe_cache, rope_freqs, cur_pos, profile_logs=None, *, model_ar
     _need(cur_pos, I32, "cur_pos")
     tokens, heads, rope = q_pe.shape[-3], q_pe.shape[-2], q_pe.shape[-1]
     _tb.check(_tb.lib().tilert_qkv_rope_op(_ctx(q_pe), _p(q_pe), heads, rope, _p(pe_cache), _p(cur_pos),
-                                           _p(rope_freqs), tokens, _stream()))
+                                           _p(rope_freqs), tokens, _rows(pe_cache), _stream()))
 
 
 def rotate(x_in, out, freqs, profile_logs=None, *, model_arch="deepseek_v3_2", rope=64):
@@ -423,7 +442,7 @@ def layernorm_rope_rotate(x_in, cur_pos, k_cache, weight, bias, freqs, profile_l
     if x_in.shape[-1] != 128:
         raise ValueError("dim must be 128")
     _tb.check(_tb.lib().tilert_layernorm_rope_rotate_op(_ctx(x_in), _p(x_in), _p(cur_pos), _p(k_cache), _p(weight),
-                                                        _p(bias), _p(freqs), rope, x_in.shape[-2], _stream()))
+                                                        _p(bias), _p(freqs), rope, x_in.shape[-2], _rows(k_cache), _stream()))
 
 
 def attn_prep(x, in_gamma, w_is, idx_w_out, kv, kv_gamma, kv_cache, q_pe, pe_cache, iq, iq_out, ki, ki_cache,
@@ -431,10 +450,11 @@ def attn_prep(x, in_gamma, w_is, idx_w_out, kv, kv_gamma, kv_cache, q_pe, pe_cac
     """projx_wis + rmsnorm_kv + qkv_rope + rotate + layernorm_rope_rotate in one launch
     (ops/projx_wis.py:21-40, ops/rmsnorm_kv.py:20-43, ops/qkv_rope.py:21-50, ops/rotate.py:61-105,
     ops/layernorm_rope_rotate.py:23-83); same arguments and bit-identical results."""
-    for t, nm in ((x, "x"), (w_is, "w_is"), (idx_w_out, "idx_w_out"), (kv, "kv"), (kv_cache, "kv_cache"),
-                  (q_pe, "q_pe"), (pe_cache, "pe_cache"), (iq, "iq"), (iq_out, "iq_out"), (ki, "ki"),
-                  (ki_cache, "ki_cache")):
+    for t, nm in ((kv, "kv"), (kv_cache, "kv_cache"), (q_pe, "q_pe"), (pe_cache, "pe_cache"), (iq, "iq"),
+                  (iq_out, "iq_out"), (ki, "ki"), (ki_cache, "ki_cache")):
         _need(t, BF16, nm)
+    for t, nm in ((x, "x"), (w_is, "w_is"), (idx_w_out, "idx_w_out")):  # w_is None: no head-weight projection here
+        _need(t, BF16, nm, optional=w_is is None)
     for t, nm in ((in_gamma, "in_gamma"), (kv_gamma, "kv_gamma"), (ln_weight, "ln_weight"), (ln_bias, "ln_bias"),
                   (freqs, "freqs")):
         _need(t, F32, nm)
@@ -443,9 +463,11 @@ def attn_prep(x, in_gamma, w_is, idx_w_out, kv, kv_gamma, kv_cache, q_pe, pe_cac
         raise ValueError("dim must be 128")
     tokens, heads = q_pe.shape[-3], q_pe.shape[-2]
     _tb.check(_tb.lib().tilert_attn_prep_op(
-        _ctx(x), _p(x), _p(in_gamma), eps, _p(w_is), w_is.shape[0], w_is.shape[1], _p(idx_w_out), _p(kv), _p(kv_gamma),
+        _ctx(kv), _p(x), _p(in_gamma), eps, _p(w_is), iq.shape[-2], 0 if w_is is None else w_is.shape[1], _p(idx_w_out),
+        _p(kv), _p(kv_gamma),
         kv.shape[-1], _p(kv_cache), _p(q_pe), heads, rope, _p(pe_cache), _p(iq), _p(iq_out), _p(ki), _p(ki_cache),
-        _p(ln_weight), _p(ln_bias), _p(freqs), _p(cur_pos), tokens, _stream()))
+        _p(ln_weight), _p(ln_bias), _p(freqs), _p(cur_pos), tokens,
+        min(_rows(kv_cache), _rows(pe_cache), _rows(ki_cache)), _stream()))
 
 
 # ------------------------------------------------------------ indexer and sparse attention

@@ -119,6 +119,31 @@ def pack_gate_up(w_gate, s_gate, w_up, s_up) -> torch.Tensor:
     return pack_rows(w, rs)
 
 
+def pack_bf16_two_term(w: torch.Tensor) -> torch.Tensor:
+    """A bf16 weight [N, K] (router gate, indexer head weights: bf16 in the checkpoint) as TWO e4m3 rows per
+    source row, so that it can ride the FP8 weight stream: ``w = hi * s + lo * s / 16`` with a power-of-two
+    scale ``s`` per (8 rows x 128 columns).  bf16 has 8 significant bits and e4m3 has 4, so the split is exact
+    unless an element is more than ~2^13 times smaller than its group's largest (then it keeps fewer bits; the
+    error is below 2^-22 of the group maximum).  Packed rows: for every group of 8 source rows, the 8 ``hi``
+    rows followed by the 8 ``lo`` rows; the kernel's pair-add epilogue sums row l and row l + 8.
+    Returns uint8 [ceil(2 N / 128), K / 128, 16448]."""
+    n, k = w.shape
+    assert k % KB == 0
+    npad = (n + 7) // 8 * 8
+    wf = torch.zeros(npad, k, dtype=torch.float32, device=w.device)
+    wf[:n] = w.float()
+    g = wf.view(npad // 8, 8, k // KB, KB)
+    amax = g.abs().amax(dim=(1, 3), keepdim=True)
+    s = torch.where(amax > 0, torch.exp2(torch.ceil(torch.log2(amax / 448.0))), torch.ones_like(amax))
+    hi = (g / s).clamp(-448, 448).to(torch.float8_e4m3fn)
+    r = g - hi.float() * s
+    lo = (r / (s / 16)).clamp(-448, 448).to(torch.float8_e4m3fn)
+    rows = torch.stack([hi.view(torch.uint8).reshape(npad // 8, 8, k), lo.view(torch.uint8).reshape(npad // 8, 8, k)], dim=1)
+    sc = s.reshape(npad // 8, 1, k // KB)
+    rs = torch.stack([sc.expand(-1, 8, -1), (sc / 16).expand(-1, 8, -1)], dim=1)
+    return pack_rows(rows.reshape(2 * npad, k), rs.reshape(2 * npad, k // KB).contiguous())
+
+
 def unpack_rows(packed: torch.Tensor, n: int) -> tuple[torch.Tensor, torch.Tensor]:
     """Inverse of ``pack_rows`` (for round-trip tests): returns (uint8 [n, K], row scales [n/8.., ...])."""
     n_t, n_kb, _ = packed.shape
