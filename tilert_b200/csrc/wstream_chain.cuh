@@ -544,10 +544,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_chain_kernel(const __
       }
 
       // ---- epilogue warps: this CTA's share of the launch's shared X blocks ----
-      if (p.shared_x && ok) {
+      if (p.shared_x && ok && pc >= 0) {
+        // (only the CTAs that take units of this phase: the others may still be busy with a phase that runs
+        // beside it, and every participant's producers wait for these blocks)
         const int n_xsegs = p.tiles_per_xseg > 0 ? p.n_tiles / p.tiles_per_xseg : 1;
         const int n_xblocks = n_xsegs * p.n_kb;
-        for (int xb = cta + warp * grid; xb < n_xblocks; xb += kGemvEpilogueWarps * grid) {
+        for (int xb = pc + warp * p.grid_eff; xb < n_xblocks; xb += kGemvEpilogueWarps * p.grid_eff) {
           gemv_convert_xblock(p, xb, rinv, p.xs + static_cast<long long>(xb) * TB_XBLK_BYTES, lane);
           __syncwarp();
           if (lane == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.xflag + xb), "r"(want) : "memory");
