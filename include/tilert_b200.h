@@ -47,6 +47,9 @@ typedef struct TbComm TbComm;
  * context (scratch for split tiles, status word). */
 int tilert_b200_init(int device, TbContext** ctx_out);
 int tilert_b200_destroy(TbContext* ctx);
+/* The process-wide context of `device`, created on first use and never destroyed: what the ctypes binding and
+ * the dispatcher registration library (libtilert_dsv32.so) both use, so that they share one set of scratch. */
+int tilert_b200_default_context(int device, TbContext** ctx_out);
 /* Reads and clears the device status word (synchronises the device).  0 = no kernel gave up. */
 int tilert_b200_status(TbContext* ctx, int* status_out);
 const char* tilert_b200_last_error(void);

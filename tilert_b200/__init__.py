@@ -71,7 +71,7 @@ def tilert_init(device: int | None = None) -> int:
     dev = torch.cuda.current_device() if device is None else device
     if dev not in _contexts:
         ctx = ctypes.c_void_p()
-        check(lib().tilert_b200_init(dev, ctypes.byref(ctx)))
+        check(lib().tilert_b200_default_context(dev, ctypes.byref(ctx)))
         _contexts[dev] = ctx.value
     return _contexts[dev]
 

@@ -20,6 +20,29 @@ NVCC_FLAGS = [
 ]
 
 
+BIND_SRC = PKG / "csrc" / "torch_binding.cpp"
+BIND_OUT = PKG / "libtilert_dsv32.so"
+
+
+def build_binding(force: bool = False) -> Path:
+    """The dispatcher registration library (TORCH_LIBRARY translation unit over the C ABI): g++ against the
+    installed torch headers, linked to libtilert_b200.so next to it."""
+    import torch
+
+    if not force and BIND_OUT.exists() and BIND_OUT.stat().st_mtime >= max(BIND_SRC.stat().st_mtime, OUT.stat().st_mtime):
+        return BIND_OUT
+    t = Path(torch.__file__).resolve().parent
+    cuda_inc = "/usr/local/cuda/include"
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           f"-I{t / 'include'}", f"-I{t / 'include' / 'torch' / 'csrc' / 'api' / 'include'}", f"-I{cuda_inc}", str(BIND_SRC),
+           "-o", str(BIND_OUT), f"-L{t / 'lib'}", "-ltorch", "-ltorch_cpu", "-lc10", "-lc10_cuda", f"-L{PKG}",
+           "-l:libtilert_b200.so", "-Wl,-rpath,$ORIGIN"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"g++ failed:\n{res.stdout}\n{res.stderr}")
+    return BIND_OUT
+
+
 def needs_build() -> bool:
     if not OUT.exists():
         return True
@@ -41,3 +64,4 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 if __name__ == "__main__":
     print(build(force=True, verbose="-v" in sys.argv))
+    print(build_binding(force=True))

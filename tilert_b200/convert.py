@@ -26,9 +26,9 @@ from .models.deepseek_v3_2.layer import LayerWeights
 from .models.deepseek_v3_2.model_args import ModelArgs, full_layer_args, toy_model_args
 
 FORMAT = "tilert_b200.packed.v1"
-_COMMON = ("in_norm", "post_norm", "q_norm", "kv_norm", "k_norm_w", "k_norm_b", "wis", "w_qkva", "w_qb", "w_absorb",
-           "w_v", "w_o", "w_gu", "w_down")
-_MOE_ONLY = ("router", "router_bias")
+_COMMON = ("in_norm", "post_norm", "q_norm", "kv_norm", "k_norm_w", "k_norm_b", "wis", "wis2", "w_qkva", "w_qb",
+           "w_absorb", "w_v", "w_o", "w_gu", "w_down")
+_MOE_ONLY = ("router", "router_bias", "router2")
 
 
 class HFCheckpoint:
@@ -71,7 +71,7 @@ def save_layer(lw: LayerWeights, path: str | os.PathLike) -> None:
     from safetensors.torch import save_file
 
     names = _COMMON + (() if lw.dense else _MOE_ONLY)
-    tensors = {n: getattr(lw, n).detach().cpu().contiguous() for n in names}
+    tensors = {n: getattr(lw, n).detach().cpu().contiguous() for n in names if getattr(lw, n, None) is not None}
     meta = {"format": FORMAT, "dense": str(int(lw.dense)), "inter_local": str(int(lw.inter_local))}
     Path(path).parent.mkdir(parents=True, exist_ok=True)
     save_file(tensors, str(path), metadata=meta)
@@ -87,9 +87,28 @@ def load_layer(path: str | os.PathLike, device) -> LayerWeights:
             raise ValueError(f"{path}: not a {FORMAT} file")
         lw.dense = bool(int(meta["dense"]))
         lw.inter_local = int(meta["inter_local"])
+        lw.router2 = None  # an f32 router gate has no two-term form
         for n in h.keys():
             setattr(lw, n, h.get_tensor(n).to(device))
     return lw
+
+
+def load_model(out_dir: str | os.PathLike, device, rank: int = 0) -> dict:
+    """Everything ``DsaModel`` needs from a converted directory, for one rank: ``{"layers": [LayerWeights...],
+    "embed", "final_norm", "head", "world", "mtp": {...} or None}``."""
+    root = Path(out_dir)
+    manifest = json.loads((root / "manifest.json").read_text())
+    if manifest.get("format") != FORMAT:
+        raise ValueError(f"{root}: not a {FORMAT} directory")
+    rdir = root / f"rank{rank}"
+    main_layers = [li for li in manifest["layers"] if li != manifest.get("mtp_layer")]
+    out = {"layers": [load_layer(rdir / f"layer_{li:03d}.safetensors", device) for li in main_layers],
+           "world": int(manifest["world"]), "mtp": None}
+    out.update(load_head(rdir / "head.safetensors", device))
+    if manifest.get("mtp_layer") is not None:
+        out["mtp"] = load_mtp(rdir / "mtp.safetensors", device)
+        out["mtp"]["layer"] = load_layer(rdir / f"layer_{manifest['mtp_layer']:03d}.safetensors", device)
+    return out
 
 
 def save_head(sd, args: ModelArgs, world: int, rank: int, path: str | os.PathLike) -> None:

@@ -443,6 +443,21 @@ extern "C" int tilert_b200_init(int device, TbContext** ctx_out) {
   return TB_OK;
 }
 
+extern "C" int tilert_b200_default_context(int device, TbContext** ctx_out) {
+  // one context per device and process, shared by every binding that asks for it (ctypes, the dispatcher
+  // registration library): their launches then use one set of scratch, in stream order
+  static std::mutex mu;
+  static TbContext* ctxs[64] = {};
+  TB_REQUIRE(ctx_out != nullptr && device >= 0 && device < 64);
+  std::lock_guard<std::mutex> lock(mu);
+  if (ctxs[device] == nullptr) {
+    const int rc = tilert_b200_init(device, &ctxs[device]);
+    if (rc != TB_OK) return rc;
+  }
+  *ctx_out = ctxs[device];
+  return TB_OK;
+}
+
 extern "C" int tilert_b200_destroy(TbContext* ctx) {
   if (ctx == nullptr) return TB_OK;
   cudaSetDevice(ctx->device);

@@ -148,11 +148,104 @@ class LayerWeights:
         return n
 
 
+class LayerScratch:
+    """The per-step scratch tensors of a decoder layer (one rank).  Layers run one after the other, so a model
+    can give all its layers ONE of these -- the reference does the same with its ``temp_vars`` list
+    (modules/dsa.py:105-229), and ``from_temp_vars`` builds a scratch set on top of such a list, indexed by
+    ``DsaTempVarIdx``.  The layer output alternates between two buffers, because a layer still reads its input
+    (the previous layer's output) while it writes its own."""
+
+    def __init__(self, args: ModelArgs, device, cache_len: int, max_tokens: int = 1, world: int = 1):
+        a, dev, s = args, torch.device(device), max_tokens
+        hl = a.n_heads // world
+        z = lambda *shape, dtype=BF16: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
+        self.q_a = z(1, s, a.q_lora_rank)
+        self.kv = z(1, s, a.kv_lora_rank)
+        self.ki = z(1, s, a.index_head_dim)
+        self.idx_w = z(1, s, a.index_n_heads)
+        self.q_nope = z(1, s, hl, a.qk_nope_head_dim)
+        self.q_pe = z(1, s, hl, a.qk_rope_head_dim)
+        self.iq = z(1, s, a.index_n_heads, a.index_head_dim)
+        self.iq_rt = z(1, s, a.index_n_heads, a.index_head_dim)
+        self.idx_logits = z(1, s, cache_len, dtype=F32)
+        self.sel = torch.full((1, s, a.index_topk), -1, dtype=I32, device=dev)
+        self.q_lat = z(1, s, hl, a.kv_lora_rank)
+        self.o_lat = z(1, s, hl, a.kv_lora_rank)
+        n_splits = (a.index_topk + 63) // 64
+        self.o_acc = z(1, s, hl, n_splits, a.kv_lora_rank, dtype=F32)
+        self.lse = z(1, s, hl, dtype=F32)
+        self.lse_acc = z(1, s, hl, n_splits, dtype=F32)
+        self.o = z(1, s, hl, a.v_head_dim)
+        self.h = z(1, s, a.dim)
+        self.h_norm = z(1, s, a.dim)
+        self.outs = [z(1, s, a.dim), z(1, s, a.dim)]
+        n_slots = a.n_activated_experts + 1
+        self.scores = z(1, s, a.n_routed_experts, dtype=F32)
+        self.probs = z(1, s, a.n_activated_experts, dtype=F32)
+        self.eidx = z(1, s, a.n_activated_experts, dtype=I32)
+        self.slot_ids = z(s, n_slots, dtype=I32)
+        self.slot_w = z(s, n_slots, dtype=F32)
+        dense_local = a.inter_dim // world if a.n_dense_layers > 0 else 0
+        self.ffn_flat = z(s * max(n_slots * (a.moe_inter_dim // world), dense_local))
+
+    @classmethod
+    def from_temp_vars(cls, args: ModelArgs, tv: list[torch.Tensor], cache_len: int, max_tokens: int = 1,
+                       world: int = 1) -> "LayerScratch":
+        """A scratch set whose tensors ARE the driver's ``temp_vars`` (tilert/models/deepseek_v3_2/
+        temp_var_indices.py:15-76), so that code reading ``temp_vars[Idx.X]`` after a step sees the step's values."""
+        from .temp_var_indices import Idx
+
+        a, s = args, max_tokens
+        hl = a.n_heads // world
+        n_splits = (a.index_topk + 63) // 64
+        n_slots = a.n_activated_experts + 1
+        self = cls.__new__(cls)
+
+        def take(idx, *shape):
+            t = tv[idx]
+            n = 1
+            for d in shape:
+                n *= d
+            if t.numel() < n:
+                raise ValueError(f"temp_vars[{Idx(idx).name}] holds {t.numel()} elements, the step needs {n}")
+            return t.reshape(-1)[:n].view(*shape)
+
+        self.q_a = take(Idx.Q, 1, s, a.q_lora_rank)
+        self.kv = take(Idx.KV, 1, s, a.kv_lora_rank)
+        self.ki = take(Idx.KI, 1, s, a.index_head_dim)
+        self.idx_w = take(Idx.IDX_SCORES, 1, s, a.index_n_heads)
+        self.q_nope = take(Idx.Q_NOPE_DOWN, 1, s, hl, a.qk_nope_head_dim)
+        self.q_pe = take(Idx.Q_PE, 1, s, hl, a.qk_rope_head_dim)
+        self.iq = take(Idx.IQ, 1, s, a.index_n_heads, a.index_head_dim)
+        self.iq_rt = take(Idx.IQ_RT, 1, s, a.index_n_heads, a.index_head_dim)
+        self.idx_logits = take(Idx.IDX_LOGITS, 1, s, cache_len)
+        self.sel = take(Idx.IDX_SELECTS, 1, s, a.index_topk)
+        self.q_lat = take(Idx.Q_NOPE, 1, s, hl, a.kv_lora_rank)
+        self.o_lat = take(Idx.O, 1, s, hl, a.kv_lora_rank)
+        self.o_acc = take(Idx.O_ACC, 1, s, hl, n_splits, a.kv_lora_rank)
+        self.lse = take(Idx.O_LSE, 1, s, hl)
+        self.lse_acc = take(Idx.O_LSE_ACC, 1, s, hl, n_splits)
+        self.o = take(Idx.PROJ_O, 1, s, hl, a.v_head_dim)
+        self.h = take(Idx.UNPROJ_O, 1, s, a.dim)
+        self.h_norm = take(Idx.X_MLP_IN, 1, s, a.dim)
+        self.outs = [take(Idx.EXP_OUT, 1, s, a.dim), take(Idx.X_TENSOR, 1, s, a.dim)]
+        self.scores = take(Idx.SCORES, 1, s, a.n_routed_experts)
+        self.probs = take(Idx.SEL_PROBS, 1, s, a.n_activated_experts)
+        self.eidx = take(Idx.SEL_INDICES, 1, s, a.n_activated_experts)
+        dev = tv[Idx.Q].device
+        self.slot_ids = torch.zeros(s, n_slots, dtype=I32, device=dev)   # (no counterpart among the temp vars)
+        self.slot_w = torch.zeros(s, n_slots, dtype=F32, device=dev)
+        dense_local = a.inter_dim // world if a.n_dense_layers > 0 else 0
+        self.ffn_flat = take(Idx.UP_GATE, s * max(n_slots * (a.moe_inter_dim // world), dense_local))
+        return self
+
+
 class DecoderLayer:
-    """Scratch tensors, caches and the operator sequence of one layer (one rank)."""
+    """Caches, scratch tensors (its own, or a set shared with the model's other layers) and the operator
+    sequence of one layer (one rank)."""
 
     def __init__(self, args: ModelArgs, weights: LayerWeights, device, cache_len: int, max_tokens: int = 1,
-                 world: int = 1, comm: int | None = None):
+                 world: int = 1, comm: int | None = None, scratch: LayerScratch | None = None, out_slot: int = 0):
         a, dev, s = args, torch.device(device), max_tokens
         self.args, self.w, self.world, self.comm = a, weights, world, comm
         self.hl = a.n_heads // world
@@ -161,37 +254,19 @@ class DecoderLayer:
         self.kv_cache = z(1, cache_len, a.kv_lora_rank)
         self.pe_cache = z(1, cache_len, a.qk_rope_head_dim)
         self.ki_cache = z(1, cache_len, a.index_head_dim)
-        self.q_a = z(1, s, a.q_lora_rank)
-        self.kv = z(1, s, a.kv_lora_rank)
-        self.ki = z(1, s, a.index_head_dim)
-        self.idx_w = z(1, s, a.index_n_heads)
-        self.q_nope = z(1, s, self.hl, a.qk_nope_head_dim)
-        self.q_pe = z(1, s, self.hl, a.qk_rope_head_dim)
-        self.iq = z(1, s, a.index_n_heads, a.index_head_dim)
-        self.iq_rt = z(1, s, a.index_n_heads, a.index_head_dim)
-        self.idx_logits = z(1, s, cache_len, dtype=F32)
-        self.sel = torch.full((1, s, a.index_topk), -1, dtype=I32, device=dev)
-        self.q_lat = z(1, s, self.hl, a.kv_lora_rank)
-        self.o_lat = z(1, s, self.hl, a.kv_lora_rank)
+        sc = scratch if scratch is not None else LayerScratch(a, dev, cache_len, s, world)
+        self.scratch = sc
+        for name in ("q_a", "kv", "ki", "idx_w", "q_nope", "q_pe", "iq", "iq_rt", "idx_logits", "sel", "q_lat", "o_lat",
+                     "o_acc", "lse", "lse_acc", "o", "h", "h_norm", "scores", "probs", "eidx", "slot_ids", "slot_w"):
+            setattr(self, name, getattr(sc, name))
+        self.out = sc.outs[out_slot & 1]
         self.mla_split = 64  # keys per attention split (a multiple of 64): splits x groups of 16 heads x tokens CTAs
         self.n_splits = (a.index_topk + 63) // 64
-        self.o_acc = z(1, s, self.hl, self.n_splits, a.kv_lora_rank, dtype=F32)
-        self.lse = z(1, s, self.hl, dtype=F32)
-        self.lse_acc = z(1, s, self.hl, self.n_splits, dtype=F32)
-        self.o = z(1, s, self.hl, a.v_head_dim)
-        self.h = z(1, s, a.dim)
-        self.h_norm = z(1, s, a.dim)
-        self.out = z(1, s, a.dim)
         if weights.dense:
-            self.ffn_hidden = z(1, s, weights.inter_local)
+            self.ffn_hidden = sc.ffn_flat[: s * weights.inter_local].view(1, s, weights.inter_local)
         else:
             n_slots = a.n_activated_experts + 1
-            self.scores = z(1, s, a.n_routed_experts, dtype=F32)
-            self.probs = z(1, s, a.n_activated_experts, dtype=F32)
-            self.eidx = z(1, s, a.n_activated_experts, dtype=I32)
-            self.slot_ids = z(s, n_slots, dtype=I32)
-            self.slot_w = z(s, n_slots, dtype=F32)
-            self.ffn_hidden = z(1, s, n_slots, weights.inter_local)
+            self.ffn_hidden = sc.ffn_flat[: s * n_slots * weights.inter_local].view(1, s, n_slots, weights.inter_local)
         self.forced_scores: torch.Tensor | None = None
         # When set ([1, S, topk] int32), replaces the indexer's selection before attention -- the role of
         # the reference's receive_selected_token_ids (ops/receive_selected_token_ids.py:10-35), used by

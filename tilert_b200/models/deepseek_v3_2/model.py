@@ -8,7 +8,7 @@ from __future__ import annotations
 import torch
 
 from . import ops
-from .layer import DecoderLayer, LayerWeights, precompute_freqs
+from .layer import DecoderLayer, LayerScratch, LayerWeights, precompute_freqs
 from .model_args import ModelArgs
 
 BF16 = torch.bfloat16
@@ -18,17 +18,39 @@ I32 = torch.int32
 
 class DsaModel:
     def __init__(self, args: ModelArgs, sd: dict[str, torch.Tensor], device="cuda", cache_len: int | None = None,
-                 world: int = 1, rank: int = 0, comm: int | None = None, use_graph: bool = True):
+                 world: int = 1, rank: int = 0, comm: int | None = None, use_graph: bool = True,
+                 share_scratch: bool | None = None, temp_vars: list[torch.Tensor] | None = None):
+        """``share_scratch``: one scratch set for all layers instead of one per layer (default: when the model
+        has more than four layers).  ``temp_vars``: the reference driver's list of 56 scratch tensors
+        (``DsaTempVarIdx``); the layers' scratch, the logits and the output token then live in it."""
         self.args, self.device = args, torch.device(device)
         self.world, self.rank, self.comm = world, rank, comm
         dev = self.device
         self.cache_len = cache_len or args.max_seq_len
-        self.embed = sd["model.embed_tokens.weight"].to(dev, BF16)
-        self.final_norm = sd["model.norm.weight"].to(dev, F32)
         v_l = args.vocab_size // world
-        self.head = sd["lm_head.weight"][rank * v_l:(rank + 1) * v_l].to(dev, BF16).contiguous()
+        if args.vocab_size % world != 0:
+            raise ValueError(f"vocab_size {args.vocab_size} does not divide over {world} ranks")
+        packed = sd if isinstance(sd, dict) and "layers" in sd else None  # a converted model (convert.load_model)
+        if packed is not None:
+            if packed["world"] != world:
+                raise ValueError(f"the converted weights were sharded for {packed['world']} ranks, not {world}")
+            self.embed, self.final_norm, self.head = packed["embed"], packed["final_norm"], packed["head"]
+            layer_weights = packed["layers"]
+        else:
+            self.embed = sd["model.embed_tokens.weight"].to(dev, BF16)
+            self.final_norm = sd["model.norm.weight"].to(dev, F32)
+            self.head = sd["lm_head.weight"][rank * v_l:(rank + 1) * v_l].to(dev, BF16).contiguous()
+            layer_weights = None
+        if share_scratch is None:
+            share_scratch = args.n_layers > 4 or temp_vars is not None
+        scratch = None
+        if temp_vars is not None:
+            scratch = LayerScratch.from_temp_vars(args, temp_vars, self.cache_len, 1, world)
+        elif share_scratch:
+            scratch = LayerScratch(args, dev, self.cache_len, 1, world)
         self.layers = [
-            DecoderLayer(args, LayerWeights(args, sd, li, dev, world, rank), dev, self.cache_len, 1, world, comm)
+            DecoderLayer(args, layer_weights[li] if layer_weights is not None else LayerWeights(args, sd, li, dev, world, rank),
+                         dev, self.cache_len, 1, world, comm, scratch=scratch, out_slot=li)
             for li in range(args.n_layers)
         ]
         self.freqs = precompute_freqs(args).to(dev)
@@ -36,6 +58,12 @@ class DsaModel:
         self.token = torch.zeros(1, dtype=torch.int64, device=dev)
         self.logits = torch.zeros(1, 1, v_l, dtype=F32, device=dev)
         self.token_out = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.temp_vars = temp_vars
+        if temp_vars is not None:
+            from .temp_var_indices import Idx
+
+            self.logits = temp_vars[Idx.LOGITS_OUT].reshape(-1)[:v_l].view(1, 1, v_l)
+            self.cur_pos = temp_vars[Idx.CUR_POS].reshape(-1)[:1]
         self.use_graph = use_graph
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
         # Host copy of the device-resident position: the kernels write cache row ``cur_pos`` and mask on it,
@@ -52,6 +80,14 @@ class DsaModel:
         self.token_logprob = torch.zeros(1, dtype=F32, device=dev)
         self.topn_logprobs = torch.zeros(1, 256, dtype=F32, device=dev)
         self.topn_indices = torch.zeros(1, 256, dtype=I32, device=dev)
+
+    @classmethod
+    def from_converted(cls, args: ModelArgs, out_dir, device="cuda", rank: int = 0, **kw) -> "DsaModel":
+        """A model on the per-rank packed files that ``python -m tilert_b200.convert`` wrote."""
+        from tilert_b200 import convert
+
+        packed = convert.load_model(out_dir, device, rank)
+        return cls(args, packed, device, world=packed["world"], rank=rank, **kw)
 
     # -- reference driver controls (end2end.py:551-577) --
     def reset_sequence(self) -> None:
@@ -117,6 +153,11 @@ class DsaModel:
             self.token_out.copy_(self.sampled)
         else:
             self.token_out.copy_(torch.argmax(self.logits.view(-1)))
+        if self.temp_vars is not None:
+            from .temp_var_indices import Idx
+
+            self.temp_vars[Idx.TOKEN_OUT].view(-1)[:1].copy_(self.token_out)
+            self.temp_vars[Idx.TOKEN_ID].view(-1)[:1].copy_(self.token)
         self.cur_pos += 1
 
     def _bucket(self, pos: int) -> int:

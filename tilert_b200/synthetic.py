@@ -68,3 +68,31 @@ def random_layer_state_dict(args: ModelArgs, li: int, device, seed: int = 0, std
             fp8(f"{m}.{nm}.up_proj", a.moe_inter_dim, a.dim)
             fp8(f"{m}.{nm}.down_proj", a.dim, a.moe_inter_dim)
     return sd
+
+
+def random_model_state_dict(args: ModelArgs, device, seed: int = 0, std: float = 0.02, with_mtp: bool = False,
+                            expert_ids=None) -> dict[str, torch.Tensor]:
+    """A whole random-init model under HF keys: embedding, every decoder layer, final norm and head; with
+    ``with_mtp`` also the multi-token-prediction layer under ``model.layers.{n_layers}`` (an MoE decoder layer
+    plus ``enorm`` / ``hnorm`` / ``eh_proj`` / ``shared_head.norm``, the checkpoint layout the reference's
+    converter reads, tilert/models/preprocess/weight_converter.py:243-537)."""
+    a = args
+    gen = torch.Generator(device=device).manual_seed(seed * 1000 + 999)
+    sd: dict[str, torch.Tensor] = {}
+    sd["model.embed_tokens.weight"] = (torch.randn(a.vocab_size, a.dim, generator=gen, dtype=torch.float32,
+                                                   device=device) * std).to(BF16)
+    for li in range(a.n_layers):
+        sd.update(random_layer_state_dict(a, li, device, seed=seed, std=std, expert_ids=expert_ids))
+    sd["model.norm.weight"] = torch.ones(a.dim, dtype=torch.float32, device=device)
+    sd["lm_head.weight"] = (torch.randn(a.vocab_size, a.dim, generator=gen, dtype=torch.float32, device=device) * std).to(BF16)
+    if with_mtp:
+        li = a.n_layers
+        from dataclasses import replace
+
+        sd.update(random_layer_state_dict(replace(a, n_dense_layers=0), li, device, seed=seed, std=std, expert_ids=expert_ids))
+        p = f"model.layers.{li}"
+        sd[f"{p}.enorm.weight"] = torch.ones(a.dim, dtype=torch.float32, device=device)
+        sd[f"{p}.hnorm.weight"] = torch.ones(a.dim, dtype=torch.float32, device=device)
+        sd[f"{p}.eh_proj.weight"] = (torch.randn(a.dim, 2 * a.dim, generator=gen, dtype=torch.float32, device=device) * std).to(BF16)
+        sd[f"{p}.shared_head.norm.weight"] = torch.ones(a.dim, dtype=torch.float32, device=device)
+    return sd
