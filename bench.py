@@ -484,6 +484,203 @@ def run_ours(args) -> None:
         sys.exit(1)
 
 
+def _peak_gbs() -> tuple[float, str]:
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        return float(json.loads(pk.read_text()).get("hbm_gbs", 6650.0)), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback 6650 GB/s"
+
+
+def run_c2(args) -> None:
+    """Workload C2: the whole model -- ``--layers`` decoder layers of the full shape (61 in the real model, the
+    first three dense), vocabulary 129280 -- tensor-parallel over the ranks, greedy decoding from a context of
+    ``--ctx`` tokens whose caches are filled with N(0, 1).  Weights are drawn at random per rank directly in
+    the packed block format on the device.  Reports the time per output token (CUDA events around every
+    graph replay of a step: layers, head, greedy token exchange), its median, tokens/s and the fraction of
+    the HBM roofline."""
+    import torch.distributed as dist
+
+    import tilert_b200
+    from dataclasses import replace
+    from tilert_b200 import synthetic
+    from tilert_b200.models.deepseek_v3_2.model import DsaModel
+    from tilert_b200.models.deepseek_v3_2.model_args import ModelArgs
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tilert_b200.load_backend("deepseek_v3_2")
+    tilert_b200.tilert_init(local)
+    n_new = args.steps
+    cache_len = (args.ctx + n_new + 16 + 255) // 256 * 256
+    a = replace(ModelArgs(), n_layers=args.layers, n_dense_layers=min(3, max(args.layers - 1, 0)), max_seq_len=cache_len)
+    comm = None
+    if world > 1:
+        from tilert_b200.comm import Comm
+
+        comm = Comm(a.dim, local)
+    t0 = time.perf_counter()
+    packed = synthetic.random_packed_model(a, dev, world, rank, seed=0)
+    model = DsaModel(a, packed, dev, cache_len=cache_len, world=world, rank=rank,
+                     comm=None if comm is None else comm.handle, share_scratch=True)
+    g = torch.Generator(device=dev).manual_seed(5)  # the same cache contents on every rank
+    for layer in model.layers:
+        for t in (layer.kv_cache, layer.pe_cache, layer.ki_cache):
+            t[:, : args.ctx].copy_(torch.randn(1, args.ctx, t.shape[-1], generator=g, device=dev).to(torch.bfloat16))
+    torch.cuda.synchronize()
+    build_s = time.perf_counter() - t0
+    weight_bytes = sum(l.w.weight_bytes(a) for l in model.layers) + model.head.numel() * 2
+    kv_bytes = a.n_layers * (a.index_topk * (a.kv_lora_rank + a.qk_rope_head_dim) * 2 + args.ctx * a.index_head_dim * 2)
+
+    model.set_cur_pos(args.ctx)
+    tok = torch.tensor([1], dtype=torch.int64, device=dev)
+    for i in range(max(args.warmup, 3)):  # also captures the graph of this scan-length bucket
+        model.forward(tok, args.ctx + i)
+        tok = model.token_out.clone()
+    pos = args.ctx + max(args.warmup, 3)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_new)]
+    for i in range(n_new):
+        ev[i][0].record()
+        model.forward(tok, pos + i)
+        ev[i][1].record()
+        tok = model.token_out  # the device feeds the next step: no host read in the loop
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    times = torch.tensor([s.elapsed_time(e) for s, e in ev], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    status = torch.tensor([tilert_b200.device_status(local)], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    peak, peak_src = _peak_gbs()
+    if rank == 0:
+        ts = sorted(times.tolist())
+        med = ts[len(ts) // 2]
+        bytes_gpu = weight_bytes + kv_bytes
+        line = {
+            "metric": "batch1_decode_tpot_ms", "value": med, "unit": "ms", "n_gpus": world, "steps": n_new,
+            "warmup": max(args.warmup, 3), "ms_per_step": sum(ts) / len(ts), "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "tokens_per_s": 1000.0 / med, "dtype": "fp8_e4m3 weights, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"C2: {a.n_layers}-layer DeepSeek-V3.2-shape model ({a.n_dense_layers} dense), vocab "
+                                   f"{a.vocab_size}, batch 1 greedy decode after a {args.ctx}-token context",
+                       "parallelism": f"tp{world}", "context": args.ctx,
+                       "weights": "random e4m3 blocks drawn per rank in the packed format on the device",
+                       "timing": "CUDA events around every graph replay of a step (layers + head + token exchange), max over ranks"},
+            "tpot_ms": {"median": med, "min": ts[0], "p90": ts[int(len(ts) * 0.9)]},
+            "step_roofline": {"bytes_per_step_this_gpu": bytes_gpu, "achieved": bytes_gpu / (med * 1e-3) / 1e9,
+                              "frac": bytes_gpu / (med * 1e-3) / 1e9 / peak, "unit": "GB/s", "peak": peak, "peak_source": peak_src},
+            "reference_published": {"tokens_per_s": 600, "source": "reference README: DeepSeek-V3.2 on 8x B200, best case"},
+            "build_seconds": build_s, "clocks": clocks, "device_status": int(status.item()),
+        }
+        print(json.dumps(line), flush=True)
+    if comm is not None:
+        comm.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_c3(args) -> None:
+    """Workload C3: the long-context indexer stress at the full layer shape -- ``--ctx`` (131072) cached keys
+    drawn from N(0, 1), one query token, exact top-2048, then sparse MLA over the selected latent rows.  Reports
+    the microseconds of scoring + selection (one launch) and of attention (+ combine), the key-scan rate against
+    the HBM peak, and the checks: indices identical to a CPU selection on the device's own scores, attention
+    within cosine 0.999 of the CPU restatement on the same selection."""
+    import tilert_b200
+    from tilert_b200.models.deepseek_v3_2 import ops
+    from tilert_b200.models.deepseek_v3_2.layer import softmax_scale
+    from tilert_b200.models.deepseek_v3_2.model_args import full_layer_args
+
+    tilert_b200.load_backend("deepseek_v3_2")
+    tilert_b200.tilert_init(0)
+    dev = torch.device("cuda", 0)
+    T = args.ctx
+    a = full_layer_args(max_seq_len=T)
+    H, k = a.index_n_heads, a.index_topk
+    g = torch.Generator(device=dev).manual_seed(7)
+    rn = lambda *s, sc=1.0: (torch.randn(*s, generator=g, device=dev) * sc).to(torch.bfloat16)  # noqa: E731
+    ki, kv, pe = rn(1, T, 128), rn(1, T, a.kv_lora_rank), rn(1, T, a.qk_rope_head_dim)
+    iq, w = rn(1, 1, H, 128), rn(1, 1, H, sc=0.3)
+    q_lat, q_pe = rn(1, 1, a.n_heads, a.kv_lora_rank, sc=0.3), rn(1, 1, a.n_heads, a.qk_rope_head_dim, sc=0.3)
+    logits = torch.zeros(1, 1, T, dtype=torch.float32, device=dev)
+    sel = torch.zeros(1, 1, k, dtype=torch.int32, device=dev)
+    cur = torch.tensor([T - 1], dtype=torch.int32, device=dev)
+    out = torch.zeros(1, 1, a.n_heads, a.kv_lora_rank, dtype=torch.bfloat16, device=dev)
+    n_splits = k // 64
+    o_acc = torch.zeros(1, 1, a.n_heads, n_splits, a.kv_lora_rank, dtype=torch.float32, device=dev)
+    lse_acc = torch.zeros(1, 1, a.n_heads, n_splits, dtype=torch.float32, device=dev)
+    lse = torch.zeros(1, 1, a.n_heads, dtype=torch.float32, device=dev)
+    scale = softmax_scale(a)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def select():
+        ops.sparse_index_topk(iq, ki, w, logits, sel, cur, n_keys=T)
+
+    def attend():
+        ops.flash_sparse_mla(q_lat, q_pe, kv, pe, sel, cur, out, softmax_scale=scale, split_size=64, out_acc=o_acc, lse=lse,
+                             lse_acc=lse_acc)
+
+    def timed(fn, n):
+        ts = []
+        for i in range(n):
+            flush.fill_(i & 255)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return sorted(ts)[len(ts) // 2]
+
+    for _ in range(max(args.warmup, 3)):
+        select(); attend()
+    torch.cuda.synchronize()
+    us_sel, us_att = timed(select, args.steps), timed(attend, args.steps)
+    # checks (outside the timed regions)
+    lg = logits[0, 0, :T].float().cpu()
+    kk = min(k, T)
+    want = torch.sort(torch.topk(lg, kk, sorted=False).indices).values
+    thr = torch.topk(lg, kk).values.min()
+    got = sel[0, 0].cpu().long()
+    got = torch.sort(got[got >= 0]).values
+    if int((lg == thr).sum()) == 1:  # no tie at the threshold: the index set is unique
+        idx_exact = bool(torch.equal(want, got))
+    else:
+        idx_exact = bool(got.numel() == kk and set(got.tolist()) >= set(torch.nonzero(lg > thr).flatten().tolist()))
+    s_idx = sel[0, 0].long()
+    s_idx = s_idx[s_idx >= 0]
+    kq = torch.cat([kv[0, s_idx].float(), pe[0, s_idx].float()], dim=-1)                      # [k, 576]
+    qq = torch.cat([q_lat[0, 0].float(), q_pe[0, 0].float()], dim=-1)                         # [h, 576]
+    p_ = torch.softmax(qq @ kq.T * scale, dim=-1).to(torch.bfloat16).float()
+    ref = (p_ @ kv[0, s_idx].float())
+    cos = torch.nn.functional.cosine_similarity(ref.flatten(), out[0, 0].float().flatten(), dim=0).item()
+    peak, peak_src = _peak_gbs()
+    scan_bytes = T * 256
+    line = {
+        "metric": "dsa_stress_select_plus_attention_us", "value": us_sel + us_att, "unit": "us", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": (us_sel + us_att) * 1e-3, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16 keys and latent rows, f32 scores", "data": "synthetic",
+        "config": {"workload": f"C3: DSA long-context stress, {T} keys, 1 query token, indexer {H}x128, top-{k}, sparse MLA over "
+                               f"{a.n_heads} heads", "l2": "256 MB buffer written before every timed launch"},
+        "select_us": us_sel, "attention_us": us_att,
+        "roofline": {"bound": "hbm", "kernel": "indexer_topk_kernel (key scan + selection)", "achieved": scan_bytes / us_sel / 1e3,
+                     "peak": peak, "unit": "GB/s", "frac": scan_bytes / us_sel / 1e3 / peak, "peak_source": peak_src,
+                     "bytes_per_launch": scan_bytes, "traffic": None},
+        "parity": {"indices_exact_on_device_scores": idx_exact, "attention_cos": cos, "ok": bool(idx_exact and cos >= 0.999)},
+        "device_status": tilert_b200.device_status(0),
+    }
+    print(json.dumps(line), flush=True)
+    if not line["parity"]["ok"]:
+        sys.exit(1)
+
+
 def run_profile_gemv(args) -> None:
     """One weight-streaming product alone: N = 7168 rows, K = 32768 (235 MB of FP8 weights, larger
     than L2), a few launches.  Small device footprint, meant to be captured by a profiler."""
@@ -579,6 +776,11 @@ def main() -> None:
                     help="short run for a profiler: no clock-sampling loop, no CPU baseline")
     ap.add_argument("--trace-step", action="store_true",
                     help="print the per-launch phase stamps of the streaming products of one step")
+    ap.add_argument("--config", default="c1", choices=["c1", "c2", "c3"],
+                    help="c1: the headline layer step; c2: whole-model decode (time per output token); c3: long-context "
+                         "indexer + sparse attention stress")
+    ap.add_argument("--ctx", type=int, default=None, help="c2: context length (default 1024); c3: cached keys (default 131072)")
+    ap.add_argument("--layers", type=int, default=61, help="c2: decoder layers (61 = the real model; needs 8 GPUs)")
     ap.add_argument("--gemv-k", type=int, default=32768)
     ap.add_argument("--gemv-packed", action="store_true", help="profile-gemv: activations packed beforehand")
     ap.add_argument("--profile-gemv", action="store_true",
@@ -586,7 +788,13 @@ def main() -> None:
     args = ap.parse_args()
     if args.profile:
         args.no_cpu_baseline = True
-    if args.profile_gemv:
+    if args.config == "c2" and args.impl == "ours":
+        args.ctx = args.ctx or 1024
+        run_c2(args)
+    elif args.config == "c3" and args.impl == "ours":
+        args.ctx = args.ctx or 131072
+        run_c3(args)
+    elif args.profile_gemv:
         run_profile_gemv(args)
     elif args.impl == "reference":
         run_reference(args)

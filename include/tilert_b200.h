@@ -282,7 +282,11 @@ int tilert_sparse_index_op(TbContext* ctx, const void* q, const void* k_cache, c
  * equal to -inf never selected); indices ascending, unused slots -1. */
 int tilert_topk_accurate_op(TbContext* ctx, const float* logits, long long logits_stride, int rows, int n, int k,
                             int* indices, void* stream);
-/* sparse_index_topk_dsv32_op (ops/sparse_index.py:72-128): the two above back to back. */
+/* sparse_index_topk_dsv32_op (ops/sparse_index.py:72-128): the two above with the same results, as ONE
+ * cooperative launch: at most one thread block per SM (tokens <= 8 share them), each scoring a contiguous range
+ * of keys; the k-th largest score is found over histograms that all blocks add to, meeting at four grid-wide
+ * barriers (bounded waits: status word 7 when a block gives up), and every block writes its part of the
+ * ascending index list.  Uses a work area of the context that the launch clears itself. */
 int tilert_sparse_index_topk_op(TbContext* ctx, const void* q, const void* k_cache, const void* weights,
                                 float* logits, long long logits_stride, int heads, int tokens, int n_keys,
                                 const int* cur_pos, int k, int* indices, void* stream);

@@ -136,6 +136,40 @@ def main() -> int:
         if n_dev != r["n_accepted"] or (step == 1 and n_dev < 2):
             failures.append(("speculative accepted", step, n_dev, r["n_accepted"]))
         draft = r["next_draft"]
+    # The full-shape MoE layer of the benchmark (hidden 7168, 128 heads, 256 experts of which eight are forced
+    # hot, indexer 64 x 128, top-2048, 4096-row caches), sharded over the ranks exactly as bench.py times it:
+    # rank 0 compares with the CPU restatement of the reference's unsharded layer, all ranks must agree bit for bit.
+    if os.environ.get("TB_MG_FULL", "1") != "0":
+        import bench
+
+        fa, hot, fsd, fcaches, fx = bench.workload_inputs(1, bench.CACHE_LEN)
+        fcomm = Comm(fa.dim, local)
+        flayer = L.DecoderLayer(fa, L.LayerWeights(fa, fsd, 0, dev, world, rank, expert_ids=hot), dev, bench.CACHE_LEN, 1,
+                                world, fcomm.handle)
+        for dst, src in zip((flayer.kv_cache, flayer.pe_cache, flayer.ki_cache), fcaches):
+            dst.copy_(src)
+        flayer.forced_scores = bench.forced_scores(fa.n_routed_experts, fa.n_activated_experts).to(dev)
+        cur = torch.tensor([bench.CACHE_LEN - 1], dtype=torch.int32, device=dev)
+        fr = L.precompute_freqs(fa)[bench.CACHE_LEN - 1: bench.CACHE_LEN].contiguous().to(dev)
+        for step in range(2):  # twice: both halves of the receive buffers
+            fout = flayer.forward(fx.to(dev), cur, fr, bench.CACHE_LEN).clone()
+            torch.cuda.synchronize()
+        gathered = [torch.empty_like(fout) for _ in range(world)]
+        dist.all_gather(gathered, fout)
+        same = all(torch.equal(gathered[0], t) for t in gathered)
+        ok_flag = torch.ones(1, device=dev)
+        if rank == 0:
+            ref = bench.CpuChecker(fsd, fcaches, fx, 1, bench.CACHE_LEN).step().float().flatten()
+            got = fout.float().cpu().flatten()
+            cos = torch.nn.functional.cosine_similarity(ref, got, dim=0).item()
+            l2 = (torch.norm(ref - got) / torch.norm(ref)).item()
+            print(f"full-shape layer, {world} ranks: cos {cos:.6f} rel_l2 {l2:.3e} ranks_identical {same}", flush=True)
+            if not (cos >= 0.999 and l2 <= 2e-2 and same):
+                failures.append(("full", cos, l2, same))
+        elif not same:
+            failures.append(("full", same))
+        dist.barrier()
+        fcomm.close()
     status = tilert_b200.device_status(local)
     if status != 0:
         failures.append(("device_status", status))

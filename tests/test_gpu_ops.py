@@ -327,6 +327,38 @@ def test_indexer_plus_topk_matches_oracle_selection(env):
     assert torch.equal(sel.cpu(), ref)
 
 
+@pytest.mark.parametrize("heads,t_len,tokens,k,distinct", [
+    (16, 300, 1, 256, 0), (32, 4096, 2, 2048, 0), (64, 5000, 4, 2048, 37), (64, 40000, 1, 2048, 0),
+    (64, 40000, 3, 2048, 500), (16, 2048, 1, 2048, 0), (64, 37888, 8, 512, 3)])
+def test_indexer_plus_topk_cooperative_selection(env, heads, t_len, tokens, k, distinct):
+    """The one-launch scoring + selection on rows long enough for several thread blocks per token, with
+    repeated key vectors (``distinct`` > 0: exact ties that straddle the blocks' key ranges, so the lowest
+    positions must win across blocks), masked tails and several tokens; run twice back to back, because the
+    launch clears its own histograms and counters for the next one."""
+    ops = env["ops"]
+    g = torch.Generator().manual_seed(heads * 7 + t_len + tokens)
+    q, w = rn(g, 1, tokens, heads, 128), rn(g, 1, tokens, heads, scale=0.5)
+    if distinct:
+        base = rn(g, distinct, 128)
+        kc = base[torch.randint(0, distinct, (t_len,), generator=g)][None]
+    else:
+        kc = rn(g, 1, t_len, 128)
+    n_valid = t_len - 3                       # the newest token sees keys 0 .. n_valid - 1
+    cur = torch.tensor([n_valid - tokens], dtype=I32, device="cuda")
+    stride = (t_len + 8 + 3) // 4 * 4
+    qd, kd, wd = q.cuda(), kc.cuda(), w.cuda()
+    for _ in range(2):
+        logits = torch.zeros(1, tokens, stride, dtype=F32, device="cuda")
+        sel = torch.zeros(1, tokens, k, dtype=I32, device="cuda")
+        ops.sparse_index_topk(qd, kd, wd, logits, sel, cur, n_keys=t_len)
+        got_logits = logits[..., :t_len].cpu()
+        ref_logits = oo.indexer_logits(q, kc, w, n_valid)
+        fin = torch.isfinite(ref_logits)
+        assert torch.equal(torch.isinf(got_logits) & (got_logits < 0), ~fin)
+        close("indexer.coop.logits", ref_logits[fin], got_logits[fin], cos_min=0.99999, l2_max=1e-3)
+        assert torch.equal(sel.cpu(), oo.topk_indices(got_logits, k))
+
+
 def test_dsa_stress_128k_context(env):
     """Long-context stress case: one query against 131072 cached keys (64 indexer heads), exact
     top-2048, then sparse MLA over the selected rows.  Synthetic N(0,1) keys stand in for a real cache."""

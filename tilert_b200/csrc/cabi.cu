@@ -76,6 +76,7 @@ constexpr size_t kXpackScratchBytes = 2ull << 20;   // activation blocks of the 
 constexpr int kMaxXBlocks = 1984;                   // X blocks one launch may convert (fits kXpackScratchBytes)
 constexpr size_t kXFlagBytes = (kMaxXBlocks + 64) * sizeof(unsigned);  // flags, then {epoch, done}
 constexpr size_t kSmallScratchBytes = 64ull << 10;  // slot ids / weights for routing
+constexpr size_t kIdxWorkBytes = 8ull * kIdxWorkWords * 4;  // the indexer's selection work area, eight query tokens
 constexpr size_t kChainSignalBytes = (kChainSignals + 1) * kChainSigStride * sizeof(unsigned);
 
 }  // namespace
@@ -104,6 +105,7 @@ struct TbContext {
   float* partial = nullptr;
   float* chain_partial = nullptr;      // split-tile slots of chained launches: one region per phase
   unsigned* chain_signals = nullptr;   // signal counters of chained launches (self-clearing)
+  unsigned* idx_work = nullptr;        // histograms and barrier counters of the indexer's selection (self-clearing)
   unsigned long long* chain_prof = nullptr;  // caller-owned trace of chained launches, see tilert_b200_set_chain_profile
   ChainRecorder rec;
   unsigned long long* launch_calls = nullptr;  // device-resident launch number of the streaming kernel
@@ -404,7 +406,7 @@ int pack_flat(const void* x, int tokens, int k, const float* seg_scale, int n_se
 extern "C" const char* tilert_b200_last_error(void) { return g_last_error.c_str(); }
 extern "C" int tilert_b200_dsa_temp_vars_size(void) { return 56; }
 extern "C" size_t tilert_b200_context_bytes(void) {
-  return kPartialBytes * (1 + kChainMaxPhases) + 1024 + 2 * kXpackScratchBytes + kXFlagBytes + kSmallScratchBytes;
+  return kPartialBytes * (1 + kChainMaxPhases) + 1024 + 2 * kXpackScratchBytes + kXFlagBytes + kSmallScratchBytes + kIdxWorkBytes;
 }
 extern "C" size_t tilert_b200_xpack_bytes(int dim) { return static_cast<size_t>(dim / TB_KBLOCK) * TB_XBLK_BYTES; }
 
@@ -425,6 +427,8 @@ extern "C" int tilert_b200_init(int device, TbContext** ctx_out) {
   TB_CUDA(cudaMemset(c->chain_partial, 0, kPartialBytes * kChainMaxPhases));
   TB_CUDA(cudaMalloc(&c->chain_signals, kChainSignalBytes));
   TB_CUDA(cudaMemset(c->chain_signals, 0, kChainSignalBytes));
+  TB_CUDA(cudaMalloc(&c->idx_work, kIdxWorkBytes));
+  TB_CUDA(cudaMemset(c->idx_work, 0, kIdxWorkBytes));
   TB_CUDA(cudaMalloc(&c->status, 256));
   TB_CUDA(cudaMalloc(&c->launch_calls, 256));
   TB_CUDA(cudaMemset(c->launch_calls, 0, 256));
@@ -464,6 +468,7 @@ extern "C" int tilert_b200_destroy(TbContext* ctx) {
   cudaFree(ctx->partial);
   cudaFree(ctx->chain_partial);
   cudaFree(ctx->chain_signals);
+  cudaFree(ctx->idx_work);
   cudaFree(ctx->launch_calls);
   cudaFree(ctx->status);
   cudaFree(ctx->xpack);
@@ -483,6 +488,7 @@ extern "C" int tilert_b200_status(TbContext* ctx, int* status_out) {
     // a launch that gave up may have left signal counters of a chained launch half-way: start clean
     TB_CUDA(cudaMemset(ctx->status, 0, sizeof(int)));
     TB_CUDA(cudaMemset(ctx->chain_signals, 0, kChainSignalBytes));
+    TB_CUDA(cudaMemset(ctx->idx_work, 0, kIdxWorkBytes));
   }
   return TB_OK;
 }
@@ -1336,27 +1342,50 @@ extern "C" int tilert_sparse_index_topk_op(TbContext* ctx, const void* q, const 
   TB_REQUIRE(cur_pos != nullptr && indices != nullptr && n_keys > 0 && k >= 1 && tokens >= 1 && tokens <= 8);
   TB_REQUIRE(heads == 16 || heads == 32 || heads == 64);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // scoring and selection in one launch: the last thread block of a token selects
-  const dim3 grid((n_keys + kIdxFusedKeys - 1) / kIdxFusedKeys, tokens);
-  const size_t smem = static_cast<size_t>(heads + kIdxFusedKeys) * kIdxPitch * 2;
+  const __nv_bfloat16* qq = reinterpret_cast<const __nv_bfloat16*>(q);
+  const __nv_bfloat16* kk = reinterpret_cast<const __nv_bfloat16*>(k_cache);
+  const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(weights);
+  const long long out_stride = k;
   static bool attr_set[64] = {};
+  constexpr size_t kIdxSelSmemMax = 200 * 1024;
   if (!attr_set[ctx->device & 63]) {
     TB_CUDA(cudaFuncSetAttribute(indexer_topk_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
     TB_CUDA(cudaFuncSetAttribute(indexer_topk_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
     TB_CUDA(cudaFuncSetAttribute(indexer_topk_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    TB_CUDA(cudaFuncSetAttribute(indexer_select_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kIdxSelSmemMax));
+    TB_CUDA(cudaFuncSetAttribute(indexer_select_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kIdxSelSmemMax));
+    TB_CUDA(cudaFuncSetAttribute(indexer_select_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kIdxSelSmemMax));
     attr_set[ctx->device & 63] = true;
   }
-  const __nv_bfloat16* qq = reinterpret_cast<const __nv_bfloat16*>(q);
-  const __nv_bfloat16* kk = reinterpret_cast<const __nv_bfloat16*>(k_cache);
-  const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(weights);
-  unsigned* done = reinterpret_cast<unsigned*>(ctx->small + 8192);  // [8], zero between launches
-  const long long out_stride = k;
+  if (n_keys <= kIdxFusedThreads * 16) {
+    // short rows: the last thread block of a token selects, the row in its registers
+    const dim3 grid((n_keys + kIdxFusedKeys - 1) / kIdxFusedKeys, tokens);
+    const size_t smem = static_cast<size_t>(heads + kIdxFusedKeys) * kIdxPitch * 2;
+    unsigned* done = reinterpret_cast<unsigned*>(ctx->small + 8192);  // [8], zero between launches
+    if (heads == 64)
+      TB_CUDA(launch(indexer_topk_kernel<64>, grid, dim3(kIdxFusedThreads), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, k, indices, out_stride, done));
+    else if (heads == 32)
+      TB_CUDA(launch(indexer_topk_kernel<32>, grid, dim3(kIdxFusedThreads), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, k, indices, out_stride, done));
+    else
+      TB_CUDA(launch(indexer_topk_kernel<16>, grid, dim3(kIdxFusedThreads), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, k, indices, out_stride, done));
+    ++g_launches;
+    TB_CUDA(cudaGetLastError());
+    return TB_OK;
+  }
+  // scoring and selection in one cooperative launch: at most one thread block per SM over all tokens, every block
+  // a contiguous range of keys (a multiple of 16)
+  const int max_g = std::max(1, std::min(kIdxSelMaxCtas, ctx->num_sms) / tokens);
+  const int n_ctas = std::min((n_keys + kIdxFusedKeys - 1) / kIdxFusedKeys, max_g);
+  const int keys_per_cta = (((n_keys + n_ctas - 1) / n_ctas) + 15) & ~15;
+  const dim3 grid(n_ctas, tokens);
+  const size_t smem = static_cast<size_t>(heads + kIdxFusedKeys) * kIdxPitch * 2 + static_cast<size_t>(keys_per_cta) * 4;
+  if (smem > kIdxSelSmemMax) return fail(TB_EINVAL, "sparse_index_topk: too many keys per thread block for its shared memory%s");
   if (heads == 64)
-    TB_CUDA(launch(indexer_topk_kernel<64>, grid, dim3(kIdxFusedThreads), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, k, indices, out_stride, done));
+    TB_CUDA(launch(indexer_select_kernel<64>, grid, dim3(kIdxFusedThreads), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, k, indices, out_stride, ctx->idx_work, keys_per_cta, ctx->status));
   else if (heads == 32)
-    TB_CUDA(launch(indexer_topk_kernel<32>, grid, dim3(kIdxFusedThreads), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, k, indices, out_stride, done));
+    TB_CUDA(launch(indexer_select_kernel<32>, grid, dim3(kIdxFusedThreads), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, k, indices, out_stride, ctx->idx_work, keys_per_cta, ctx->status));
   else
-    TB_CUDA(launch(indexer_topk_kernel<16>, grid, dim3(kIdxFusedThreads), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, k, indices, out_stride, done));
+    TB_CUDA(launch(indexer_select_kernel<16>, grid, dim3(kIdxFusedThreads), smem, st, qq, kk, ww, logits, logits_stride, n_keys, cur_pos, k, indices, out_stride, ctx->idx_work, keys_per_cta, ctx->status));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;

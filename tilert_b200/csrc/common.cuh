@@ -19,6 +19,7 @@ enum Status : int {
   ST_BAD_ARGUMENT = 4,
   ST_SPLIT_TIMEOUT = 5,       // a row tile's owner gave up waiting for another CTA's partial sums
   ST_CHAIN_TIMEOUT = 6,       // a phase of a chained launch gave up waiting for an earlier phase's signal
+  ST_GRID_TIMEOUT = 7,        // a CTA of a cooperative launch gave up waiting for the others at a grid-wide barrier
 };
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {

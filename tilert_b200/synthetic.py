@@ -96,3 +96,70 @@ def random_model_state_dict(args: ModelArgs, device, seed: int = 0, std: float =
         sd[f"{p}.eh_proj.weight"] = (torch.randn(a.dim, 2 * a.dim, generator=gen, dtype=torch.float32, device=device) * std).to(BF16)
         sd[f"{p}.shared_head.norm.weight"] = torch.ones(a.dim, dtype=torch.float32, device=device)
     return sd
+
+
+def random_packed_layer(args: ModelArgs, li: int, device, world: int = 1, rank: int = 0, seed: int = 0):
+    """One rank's ``LayerWeights`` of layer ``li`` drawn directly in the packed block format (random e4m3 bytes,
+    one constant scale): what a 61-layer random-init model is built from when its HF-format tensors (84 GB per
+    rank at eight ranks, 670 GB in all) are not worth materialising first.  Timing-equivalent to converted
+    weights -- same tensors, same shapes, same bytes streamed -- but not derived from an HF-keyed state dict,
+    so there is no CPU restatement to compare values with."""
+    from . import pack
+    from .models.deepseek_v3_2.layer import LayerWeights
+
+    a, dev = args, torch.device(device)
+    gen = torch.Generator(device=dev).manual_seed(seed * 100003 + li * 131 + rank + 1)  # this rank's shards
+    gen_all = torch.Generator(device=dev).manual_seed(seed * 100003 + li * 131)         # tensors every rank replicates
+    hl = a.n_heads // world
+
+    def blocks(*lead, shared=False):
+        g_ = gen_all if shared else gen
+        t = torch.randint(0, 127, (*lead, pack.WBLK_BYTES), generator=g_, dtype=torch.uint8, device=dev)
+        t[..., :16384] |= torch.randint(0, 2, (*lead, 16384), generator=g_, dtype=torch.uint8, device=dev) << 7
+        t[..., 16384:] = 0
+        t[..., 16384:].view(torch.float32).fill_(2.2e-4)  # random e4m3 codes have an rms near 90: weights of rms ~0.02
+        return t
+
+    ones = lambda n: torch.ones(n, dtype=torch.float32, device=dev)  # noqa: E731
+    lw = LayerWeights.__new__(LayerWeights)
+    lw.in_norm, lw.post_norm, lw.q_norm, lw.kv_norm = ones(a.dim), ones(a.dim), ones(a.q_lora_rank), ones(a.kv_lora_rank)
+    lw.k_norm_w, lw.k_norm_b = ones(a.index_head_dim), torch.zeros(a.index_head_dim, dtype=torch.float32, device=dev)
+    lw.wis = (torch.randn(a.index_n_heads, a.dim, generator=gen_all, device=dev) * 0.02).to(BF16)
+    lw.wis2 = pack.pack_bf16_two_term(lw.wis)
+    n_kb = a.dim // 128
+    qkva_rows = a.q_lora_rank + a.kv_lora_rank + a.qk_rope_head_dim + a.index_head_dim
+    lw.w_qkva = blocks((qkva_rows + 127) // 128, n_kb, shared=True)
+    own_rows, idx_rows = hl * (a.qk_nope_head_dim + a.qk_rope_head_dim), a.index_n_heads * a.index_head_dim
+    assert own_rows % 128 == 0 and idx_rows % 128 == 0
+    lw.w_qb = torch.cat([blocks(own_rows // 128, a.q_lora_rank // 128),
+                         blocks(idx_rows // 128, a.q_lora_rank // 128, shared=True)], dim=0)
+    lw.w_absorb = blocks(hl * a.kv_lora_rank // 128, a.qk_nope_head_dim // 128)
+    lw.w_v = blocks(hl * a.v_head_dim // 128, a.kv_lora_rank // 128)
+    lw.w_o = blocks(a.dim // 128, hl * a.v_head_dim // 128)
+    lw.dense = li < a.n_dense_layers
+    if lw.dense:
+        il = a.inter_dim // world
+        lw.w_gu, lw.w_down = blocks(2 * il // 128, n_kb), blocks(a.dim // 128, il // 128)
+    else:
+        il = a.moe_inter_dim // world
+        lw.router = (torch.randn(a.n_routed_experts, a.dim, generator=gen_all, device=dev) * 0.02).to(BF16)
+        lw.router2 = pack.pack_bf16_two_term(lw.router)
+        lw.router_bias = torch.zeros(a.n_routed_experts, dtype=torch.float32, device=dev)
+        lw.w_gu = blocks(a.n_routed_experts + 1, 2 * il // 128, n_kb)
+        lw.w_down = blocks(a.n_routed_experts + 1, a.dim // 128, il // 128)
+    lw.inter_local = il
+    return lw
+
+
+def random_packed_model(args: ModelArgs, device, world: int = 1, rank: int = 0, seed: int = 0) -> dict:
+    """The ``packed`` dictionary ``DsaModel`` takes (as ``convert.load_model`` returns it), drawn at random on the
+    device for one rank: every layer by ``random_packed_layer``, the embedding, the final norm and the rank's slice
+    of the vocabulary head."""
+    a, dev = args, torch.device(device)
+    gen = torch.Generator(device=dev).manual_seed(seed * 7919 + 17)  # same embedding on every rank
+    v_l = a.vocab_size // world
+    embed = (torch.randn(a.vocab_size, a.dim, generator=gen, device=dev) * 0.02).to(BF16)
+    gen_r = torch.Generator(device=dev).manual_seed(seed * 7919 + 101 + rank)
+    head = (torch.randn(v_l, a.dim, generator=gen_r, device=dev) * 0.02).to(BF16)
+    return {"layers": [random_packed_layer(a, li, dev, world, rank, seed) for li in range(a.n_layers)], "world": world,
+            "embed": embed, "final_norm": torch.ones(a.dim, dtype=torch.float32, device=dev), "head": head, "mtp": None}
