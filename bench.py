@@ -493,11 +493,12 @@ def _peak_gbs() -> tuple[float, str]:
 
 def run_c2(args) -> None:
     """Workload C2: the whole model -- ``--layers`` decoder layers of the full shape (61 in the real model, the
-    first three dense), vocabulary 129280 -- tensor-parallel over the ranks, greedy decoding from a context of
-    ``--ctx`` tokens whose caches are filled with N(0, 1).  Weights are drawn at random per rank directly in
-    the packed block format on the device.  Reports the time per output token (CUDA events around every
-    graph replay of a step: layers, head, greedy token exchange), its median, tokens/s and the fraction of
-    the HBM roofline."""
+    first three dense), vocabulary 129280 -- tensor-parallel over the ranks, greedy decoding from contexts of
+    ``--ctx`` tokens (a comma-separated list: the model is built once) whose caches are filled with N(0, 1).
+    Weights are drawn at random per rank directly in the packed block format on the device.  Prints one JSON
+    line per context (and per launch mode with ``--chain both``): the time per output token (CUDA events around
+    every step: graph replay of layers, head and greedy token exchange), its median, tokens/s and the fraction
+    of the HBM roofline.  ``--with-mtp`` times speculative steps (four rows verified, three drafted)."""
     import torch.distributed as dist
 
     import tilert_b200
@@ -515,8 +516,10 @@ def run_c2(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
     tilert_b200.load_backend("deepseek_v3_2")
     tilert_b200.tilert_init(local)
-    n_new = args.steps
-    cache_len = (args.ctx + n_new + 16 + 255) // 256 * 256
+    n_new, n_warm = args.steps, max(args.warmup, 3)
+    contexts = [int(c) for c in str(args.ctx).split(",")]
+    rows = 4 if args.with_mtp else 1
+    cache_len = (max(contexts) + rows * (n_new + n_warm) * 2 + 16 + 255) // 256 * 256
     a = replace(ModelArgs(), n_layers=args.layers, n_dense_layers=min(3, max(args.layers - 1, 0)), max_seq_len=cache_len)
     comm = None
     if world > 1:
@@ -524,65 +527,105 @@ def run_c2(args) -> None:
 
         comm = Comm(a.dim, local)
     t0 = time.perf_counter()
-    packed = synthetic.random_packed_model(a, dev, world, rank, seed=0)
-    model = DsaModel(a, packed, dev, cache_len=cache_len, world=world, rank=rank,
-                     comm=None if comm is None else comm.handle, share_scratch=True)
+    packed = synthetic.random_packed_model(a, dev, world, rank, seed=0, with_mtp=args.with_mtp)
+    handle = None if comm is None else comm.handle
+    if args.with_mtp:
+        from tilert_b200.models.deepseek_v3_2.mtp import MtpDsaModel
+
+        model = MtpDsaModel(a, packed, dev, cache_len=cache_len, world=world, rank=rank, comm=handle)
+        layers = model.layers + [model.mtp_layer]
+    else:
+        model = DsaModel(a, packed, dev, cache_len=cache_len, world=world, rank=rank, comm=handle, share_scratch=True)
+        layers = model.layers
     g = torch.Generator(device=dev).manual_seed(5)  # the same cache contents on every rank
-    for layer in model.layers:
+    for layer in layers:
         for t in (layer.kv_cache, layer.pe_cache, layer.ki_cache):
-            t[:, : args.ctx].copy_(torch.randn(1, args.ctx, t.shape[-1], generator=g, device=dev).to(torch.bfloat16))
+            t[:, : max(contexts)].copy_(torch.randn(1, max(contexts), t.shape[-1], generator=g, device=dev).to(torch.bfloat16))
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
     weight_bytes = sum(l.w.weight_bytes(a) for l in model.layers) + model.head.numel() * 2
-    kv_bytes = a.n_layers * (a.index_topk * (a.kv_lora_rank + a.qk_rope_head_dim) * 2 + args.ctx * a.index_head_dim * 2)
-
-    model.set_cur_pos(args.ctx)
-    tok = torch.tensor([1], dtype=torch.int64, device=dev)
-    for i in range(max(args.warmup, 3)):  # also captures the graph of this scan-length bucket
-        model.forward(tok, args.ctx + i)
-        tok = model.token_out.clone()
-    pos = args.ctx + max(args.warmup, 3)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_new)]
-    for i in range(n_new):
-        ev[i][0].record()
-        model.forward(tok, pos + i)
-        ev[i][1].record()
-        tok = model.token_out  # the device feeds the next step: no host read in the loop
-    torch.cuda.synchronize()
-    clocks = sampler.stop() if rank == 0 else None
-    times = torch.tensor([s.elapsed_time(e) for s, e in ev], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    status = torch.tensor([tilert_b200.device_status(local)], dtype=torch.int64, device=dev)
-    if world > 1:
-        dist.all_reduce(status, op=dist.ReduceOp.MAX)
     peak, peak_src = _peak_gbs()
-    if rank == 0:
-        ts = sorted(times.tolist())
-        med = ts[len(ts) // 2]
-        bytes_gpu = weight_bytes + kv_bytes
-        line = {
-            "metric": "batch1_decode_tpot_ms", "value": med, "unit": "ms", "n_gpus": world, "steps": n_new,
-            "warmup": max(args.warmup, 3), "ms_per_step": sum(ts) / len(ts), "higher_is_better": False, "scaling": "strong",
-            "vs_baseline": None, "tokens_per_s": 1000.0 / med, "dtype": "fp8_e4m3 weights, f32 accumulate", "data": "synthetic",
-            "config": {"workload": f"C2: {a.n_layers}-layer DeepSeek-V3.2-shape model ({a.n_dense_layers} dense), vocab "
-                                   f"{a.vocab_size}, batch 1 greedy decode after a {args.ctx}-token context",
-                       "parallelism": f"tp{world}", "context": args.ctx,
-                       "weights": "random e4m3 blocks drawn per rank in the packed format on the device",
-                       "timing": "CUDA events around every graph replay of a step (layers + head + token exchange), max over ranks"},
-            "tpot_ms": {"median": med, "min": ts[0], "p90": ts[int(len(ts) * 0.9)]},
-            "step_roofline": {"bytes_per_step_this_gpu": bytes_gpu, "achieved": bytes_gpu / (med * 1e-3) / 1e9,
-                              "frac": bytes_gpu / (med * 1e-3) / 1e9 / peak, "unit": "GB/s", "peak": peak, "peak_source": peak_src},
-            "reference_published": {"tokens_per_s": 600, "source": "reference README: DeepSeek-V3.2 on 8x B200, best case"},
-            "build_seconds": build_s, "clocks": clocks, "device_status": int(status.item()),
-        }
-        print(json.dumps(line), flush=True)
+    modes = {"both": [True, False], "on": [True], "off": [False], "default": [None]}[args.chain]
+
+    for ctx_len in contexts:
+        for chained in modes:
+            if chained is not None:
+                for layer in layers:
+                    layer.chained = chained
+            model._graphs.clear()
+            model.set_cur_pos(ctx_len)
+            accepted = []
+            if args.with_mtp:
+                draft = torch.ones(4, dtype=torch.int64, device=dev)
+
+                def step(_i):
+                    nonlocal draft
+                    model.forward(draft)
+                    accepted.append(model.get_num_accepted())  # one host read per step, as in the reference's loop
+                    draft = model.next_draft.clone()
+            else:
+                tok = torch.tensor([1], dtype=torch.int64, device=dev)
+
+                def step(i):
+                    nonlocal tok
+                    model.forward(tok, ctx_len + i)
+                    tok = model.token_out  # the device feeds the next step: no host read in the loop
+            for i in range(n_warm):  # also captures the graph of this scan-length bucket
+                step(i)
+            accepted.clear()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            sampler = ClockSampler(local)
+            if rank == 0:
+                sampler.start()
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_new)]
+            for i in range(n_new):
+                ev[i][0].record()
+                step(n_warm + i)
+                ev[i][1].record()
+            torch.cuda.synchronize()
+            clocks = sampler.stop() if rank == 0 else None
+            times = torch.tensor([s_.elapsed_time(e_) for s_, e_ in ev], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(times, op=dist.ReduceOp.MAX)
+            status = torch.tensor([tilert_b200.device_status(local)], dtype=torch.int64, device=dev)
+            if world > 1:
+                dist.all_reduce(status, op=dist.ReduceOp.MAX)
+            if rank != 0:
+                continue
+            ts = sorted(times.tolist())
+            med = ts[len(ts) // 2]
+            kv_bytes = a.n_layers * (a.index_topk * (a.kv_lora_rank + a.qk_rope_head_dim) * 2 + ctx_len * a.index_head_dim * 2)
+            bytes_gpu = weight_bytes + kv_bytes
+            line = {
+                "metric": "batch1_decode_tpot_ms", "value": med, "unit": "ms", "n_gpus": world, "steps": n_new,
+                "warmup": n_warm, "ms_per_step": sum(ts) / len(ts), "higher_is_better": False, "scaling": "strong",
+                "vs_baseline": None, "tokens_per_s": 1000.0 / med, "dtype": "fp8_e4m3 weights, f32 accumulate",
+                "data": "synthetic",
+                "config": {"workload": f"C2: {a.n_layers}-layer DeepSeek-V3.2-shape model ({a.n_dense_layers} dense), vocab "
+                                       f"{a.vocab_size}, batch 1 greedy decode after a {ctx_len}-token context",
+                           "parallelism": f"tp{world}", "context": ctx_len, "with_mtp": bool(args.with_mtp),
+                           "chained_launches": layers[0].chained,
+                           "weights": "random e4m3 blocks drawn per rank in the packed format on the device",
+                           "timing": "CUDA events around every step (graph replay of layers + head + token exchange), "
+                                     "max over ranks"},
+                "tpot_ms": {"median": med, "min": ts[0], "p90": ts[int(len(ts) * 0.9)]},
+                "speculative": None if not args.with_mtp else {
+                    "rows_per_step": 4, "mean_accepted": sum(accepted) / max(len(accepted), 1),
+                    "note": "value is the time of one speculative step (four rows verified, three drafted); with random "
+                            "weights the drafts are almost never accepted, so tokens/s here is the floor: multiply by the "
+                            "mean accepted length of a trained model",
+                    "tokens_per_s_at_accept": {str(n): n * 1000.0 / med for n in (1, 2, 3, 4)}},
+                "step_roofline": {"bytes_per_step_this_gpu": bytes_gpu, "achieved": bytes_gpu / (med * 1e-3) / 1e9,
+                                  "frac": bytes_gpu / (med * 1e-3) / 1e9 / peak, "unit": "GB/s", "peak": peak,
+                                  "peak_source": peak_src,
+                                  "note": "bytes of one single-row pass; a speculative step streams more (four rows route "
+                                          "to more experts, three more passes of the prediction layer and the head)"},
+                "reference_published": {"tokens_per_s": 600, "source": "reference README: DeepSeek-V3.2 on 8x B200, best case"},
+                "build_seconds": build_s, "clocks": clocks, "device_status": int(status.item()),
+            }
+            print(json.dumps(line), flush=True)
     if comm is not None:
         comm.close()
     if world > 1:
@@ -779,7 +822,11 @@ def main() -> None:
     ap.add_argument("--config", default="c1", choices=["c1", "c2", "c3"],
                     help="c1: the headline layer step; c2: whole-model decode (time per output token); c3: long-context "
                          "indexer + sparse attention stress")
-    ap.add_argument("--ctx", type=int, default=None, help="c2: context length (default 1024); c3: cached keys (default 131072)")
+    ap.add_argument("--ctx", default=None, help="c2: context length(s), comma separated (default 1024); c3: cached keys "
+                                                "(default 131072)")
+    ap.add_argument("--chain", default="default", choices=["default", "on", "off", "both"],
+                    help="c2: run the layers' products as chained launches, as single launches, or time both")
+    ap.add_argument("--with-mtp", action="store_true", help="c2: speculative decoding steps with the prediction layer")
     ap.add_argument("--layers", type=int, default=61, help="c2: decoder layers (61 = the real model; needs 8 GPUs)")
     ap.add_argument("--gemv-k", type=int, default=32768)
     ap.add_argument("--gemv-packed", action="store_true", help="profile-gemv: activations packed beforehand")
@@ -792,7 +839,7 @@ def main() -> None:
         args.ctx = args.ctx or 1024
         run_c2(args)
     elif args.config == "c3" and args.impl == "ours":
-        args.ctx = args.ctx or 131072
+        args.ctx = int(args.ctx or 131072)
         run_c3(args)
     elif args.profile_gemv:
         run_profile_gemv(args)

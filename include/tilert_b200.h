@@ -15,7 +15,11 @@
  *   - the return value is 0 on success, a negative TB_E* code otherwise; `tilert_b200_last_error`
  *     gives the message.  A kernel that gives up on a bounded wait records a positive code in the
  *     context's device status word, read with `tilert_b200_status`;
- *   - a context owns scratch memory used by the calls made with it: use one context per stream.
+ *   - a context owns scratch memory used by the calls made with it: calls made with one context must be
+ *     ordered on one stream.  Whatever the context, streaming launches (every FP8 product, chained launches, the
+ *     indexer's selection, `tilert_b200_matvec_fp8_static`) must not overlap on a device: each needs all of its
+ *     thread blocks resident at once (they wait on one another, bounded), so two of them running side by side from
+ *     different streams can each be left half resident, wait out their budget and return a status code.
  *
  * Weight operands named `*_packed` are in the library's block format (128x128 e4m3 tiles in
  * the tensor core's shared-memory operand order followed by their scales, see tilert_b200/csrc/formats.h); they are

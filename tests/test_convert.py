@@ -106,3 +106,21 @@ def test_convert_writes_the_prediction_layer(tmp_path):
     # asking for specific layers leaves the prediction layer out unless it is named
     files = convert.convert(str(hf), str(tmp_path / "some"), a, world=1, layers=[0], with_head=False)
     assert len(files) == 1
+
+
+def test_pack_rows_ragged_row_count_round_trips():
+    """A weight whose row count is neither a multiple of 128 nor of 8 (1001 rows) packs: the padding rows are
+    zero bytes that repeat the last real row's scales, and unpacking returns the bytes and row scales."""
+    from tilert_b200 import pack
+
+    g = torch.Generator().manual_seed(1001)
+    n, k = 1001, 384
+    w = torch.randint(0, 255, (n, k), generator=g, dtype=torch.uint8)
+    scale = torch.rand((n + 127) // 128, k // 128, generator=g) + 0.5
+    packed = pack.pack_matrix(w, scale)
+    assert packed.shape == (8, 3, pack.WBLK_BYTES)
+    w2, rs2 = pack.unpack_rows(packed, n)
+    assert torch.equal(w2, w)
+    assert torch.equal(rs2, pack.row_scales(scale, n))
+    two = pack.pack_bf16_two_term((torch.randn(70, 256, generator=g) * 0.02).to(torch.bfloat16))  # 70 rows: padded to 72
+    assert two.shape == (2, 2, pack.WBLK_BYTES)

@@ -28,6 +28,12 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   return t;
 }
 
+__device__ __forceinline__ unsigned sm_id() {
+  unsigned v;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(v));
+  return v;
+}
+
 __device__ __forceinline__ void set_status(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }

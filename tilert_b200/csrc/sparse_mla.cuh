@@ -123,11 +123,18 @@ __global__ void __launch_bounds__(kMlaThreads) sparse_mla_kernel(const MlaParams
   for (int blk = 0; blk < p.blocks_per_split; ++blk) {
     // ---- 64 selected rows (block 0 was requested before the loop) ----
     if (blk > 0) n_valid = issue_gather(blk);
+    bool gave_up = false;
     if (n_valid > 0) {
-      if (!mbar_wait(bar, phase & 1)) set_status(p.status, ST_WAIT_FULL_TIMEOUT);
+      gave_up = !mbar_wait(bar, phase & 1);
+      if (gave_up) set_status(p.status, ST_WAIT_FULL_TIMEOUT);
       ++phase;
     }
-    __syncthreads();
+    // a wait that ran out ends the loop for the whole CTA: no further copies are requested, and the one wait
+    // below gives the copies already in flight the same budget again before the kernel returns
+    if (__syncthreads_or(gave_up ? 1 : 0)) {
+      mbar_wait(bar, (phase - 1) & 1);
+      break;
+    }
 
     // ---- S = Q K^T for this warp's 16 keys ----
     float s[2][4];

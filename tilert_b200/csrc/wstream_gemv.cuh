@@ -166,7 +166,7 @@ enum GemvProfSlot : int {
   kGemvProfExit = 7,          // epilogue warp 0: end of kernel (after the all-reduce, if any)
   kGemvProfWaitCycles = 8,    // epilogue warp 0: SM cycles spent waiting for accumulators, summed over its units
   kGemvProfMathCycles = 9,    // epilogue warp 0: SM cycles spent reading back and scaling, summed over its units
-  kGemvProfUnits = 10,        // epilogue warp 0: number of units it read back
+  kGemvProfUnits = 10,        // epilogue warp 0: number of units it read back (low 32 bits) and the SM it ran on (high 32)
   kGemvProfMmaWaitFull = 11,  // MMA warp 0: cycles waiting for its slots to fill
   kGemvProfMmaIssue = 12,     // MMA warp 0: cycles issuing MMAs and their commit
   kGemvProfNormDone = 13,     // converter 0: RMSNorm statistics of the activations are ready (%globaltimer)
@@ -996,7 +996,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
       if (p.prof != nullptr) {
         p.prof[blockIdx.x * 16 + kGemvProfWaitCycles] = prof_wait;
         p.prof[blockIdx.x * 16 + kGemvProfMathCycles] = prof_math;
-        p.prof[blockIdx.x * 16 + kGemvProfUnits] = prof_units;
+        p.prof[blockIdx.x * 16 + kGemvProfUnits] = static_cast<unsigned long long>(prof_units) | (static_cast<unsigned long long>(sm_id()) << 32);
       }
     }
 

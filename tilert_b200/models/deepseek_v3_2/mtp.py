@@ -38,7 +38,8 @@ N_TOKENS = 4  # rows per step: the reference's ``forward_max_seq_len`` (end2end.
 class MtpDsaModel:
     """Main model + prediction layer on one rank of ``world`` (tensor parallel like ``DsaModel``: heads,
     expert slices and vocabulary rows per rank, fused all-reduces, ``comm`` from ``tilert_b200.comm``).
-    ``sd`` is an HF-keyed FP8 state dict whose prediction layer sits under ``model.layers.{n_layers}``."""
+    ``sd`` is an HF-keyed FP8 state dict whose prediction layer sits under ``model.layers.{n_layers}``, or a
+    dictionary of packed per-rank weights with an ``"mtp"`` entry (``synthetic.random_packed_model``)."""
 
     def __init__(self, args: ModelArgs, sd: dict[str, torch.Tensor], device="cuda", cache_len: int | None = None,
                  use_graph: bool = True, world: int = 1, rank: int = 0, comm: int | None = None):
@@ -46,21 +47,30 @@ class MtpDsaModel:
         self.world, self.rank, self.comm = world, rank, comm
         dev, s = self.device, N_TOKENS
         self.cache_len = cache_len or args.max_seq_len
-        p = f"model.layers.{args.n_layers}"
-        self.embed = sd["model.embed_tokens.weight"].to(dev, BF16)
-        self.final_norm = sd["model.norm.weight"].to(dev, F32)
-        # with several ranks every rank holds vocab / world rows of the head (shared by both models) and
-        # the greedy tokens come from the (value, index) exchange over peer memory
         v_l = args.vocab_size // world
-        self.head = sd["lm_head.weight"][rank * v_l:(rank + 1) * v_l].to(dev, BF16).contiguous()
-        self.enorm = sd[f"{p}.enorm.weight"].to(dev, F32)
-        self.hnorm = sd[f"{p}.hnorm.weight"].to(dev, F32)
-        self.w_eh = sd[f"{p}.eh_proj.weight"].to(dev, BF16).contiguous()
-        self.mtp_norm = sd[f"{p}.shared_head.norm.weight"].to(dev, F32)
-        self.layers = [DecoderLayer(args, LayerWeights(args, sd, li, dev, world, rank), dev, self.cache_len, s, world, comm)
-                       for li in range(args.n_layers)]
-        self.mtp_layer = DecoderLayer(args, LayerWeights(args, sd, args.n_layers, dev, world, rank), dev,
-                                      self.cache_len, s, world, comm)
+        packed = sd if isinstance(sd, dict) and "layers" in sd else None  # converted or randomly drawn packed weights
+        if packed is not None:
+            if packed["world"] != world or packed.get("mtp") is None:
+                raise ValueError("the packed weights are for another number of ranks or lack the prediction layer")
+            m = packed["mtp"]
+            self.embed, self.final_norm, self.head = packed["embed"], packed["final_norm"], packed["head"]
+            self.enorm, self.hnorm, self.w_eh, self.mtp_norm = m["enorm"], m["hnorm"], m["w_eh"], m["norm"]
+            main_w, mtp_w = packed["layers"], m["layer"]
+        else:
+            p = f"model.layers.{args.n_layers}"
+            self.embed = sd["model.embed_tokens.weight"].to(dev, BF16)
+            self.final_norm = sd["model.norm.weight"].to(dev, F32)
+            # with several ranks every rank holds vocab / world rows of the head (shared by both models) and
+            # the greedy tokens come from the (value, index) exchange over peer memory
+            self.head = sd["lm_head.weight"][rank * v_l:(rank + 1) * v_l].to(dev, BF16).contiguous()
+            self.enorm = sd[f"{p}.enorm.weight"].to(dev, F32)
+            self.hnorm = sd[f"{p}.hnorm.weight"].to(dev, F32)
+            self.w_eh = sd[f"{p}.eh_proj.weight"].to(dev, BF16).contiguous()
+            self.mtp_norm = sd[f"{p}.shared_head.norm.weight"].to(dev, F32)
+            main_w = [LayerWeights(args, sd, li, dev, world, rank) for li in range(args.n_layers)]
+            mtp_w = LayerWeights(args, sd, args.n_layers, dev, world, rank)
+        self.layers = [DecoderLayer(args, main_w[li], dev, self.cache_len, s, world, comm) for li in range(args.n_layers)]
+        self.mtp_layer = DecoderLayer(args, mtp_w, dev, self.cache_len, s, world, comm)
         self.freqs = precompute_freqs(args).to(dev)
         z = lambda *shape, dtype: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
         self.cur_pos = z(1, dtype=I32)

@@ -36,8 +36,10 @@ def pack_rows(w: torch.Tensor, rscale: torch.Tensor) -> torch.Tensor:
     n_t, n_kb = (n + TILE - 1) // TILE, k // KB
     npad = n_t * TILE
     if npad != n:
+        # padding rows are zero bytes; they repeat the last real row's scales, so that a ragged row count
+        # (n not a multiple of 8) still has one scale per aligned group of 8 packed rows
         w = torch.cat([w, torch.zeros(npad - n, k, dtype=torch.uint8, device=w.device)], 0)
-        rscale = torch.cat([rscale, torch.zeros(npad - n, n_kb, dtype=rscale.dtype, device=w.device)], 0)
+        rscale = torch.cat([rscale, rscale[-1:].expand(npad - n, n_kb)], 0)
     g8 = rscale.view(npad // 8, 8, n_kb)
     if not bool((g8 == g8[:, :1]).all()):
         raise ValueError("each aligned group of 8 packed rows must share one scale per k block")

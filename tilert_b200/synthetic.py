@@ -151,15 +151,21 @@ def random_packed_layer(args: ModelArgs, li: int, device, world: int = 1, rank: 
     return lw
 
 
-def random_packed_model(args: ModelArgs, device, world: int = 1, rank: int = 0, seed: int = 0) -> dict:
-    """The ``packed`` dictionary ``DsaModel`` takes (as ``convert.load_model`` returns it), drawn at random on the
-    device for one rank: every layer by ``random_packed_layer``, the embedding, the final norm and the rank's slice
-    of the vocabulary head."""
+def random_packed_model(args: ModelArgs, device, world: int = 1, rank: int = 0, seed: int = 0, with_mtp: bool = False) -> dict:
+    """The ``packed`` dictionary ``DsaModel`` / ``MtpDsaModel`` take (as ``convert.load_model`` returns it), drawn
+    at random on the device for one rank: every layer by ``random_packed_layer``, the embedding, the final norm
+    and the rank's slice of the vocabulary head; with ``with_mtp`` also the prediction layer (one more MoE layer,
+    its two input norms, ``eh_proj`` and the shared head's norm)."""
     a, dev = args, torch.device(device)
     gen = torch.Generator(device=dev).manual_seed(seed * 7919 + 17)  # same embedding on every rank
     v_l = a.vocab_size // world
     embed = (torch.randn(a.vocab_size, a.dim, generator=gen, device=dev) * 0.02).to(BF16)
     gen_r = torch.Generator(device=dev).manual_seed(seed * 7919 + 101 + rank)
     head = (torch.randn(v_l, a.dim, generator=gen_r, device=dev) * 0.02).to(BF16)
+    ones = torch.ones(a.dim, dtype=torch.float32, device=dev)
+    mtp = None
+    if with_mtp:
+        mtp = {"layer": random_packed_layer(a, a.n_layers, dev, world, rank, seed), "enorm": ones.clone(), "hnorm": ones.clone(),
+               "w_eh": (torch.randn(a.dim, 2 * a.dim, generator=gen, device=dev) * 0.01).to(BF16), "norm": ones.clone()}
     return {"layers": [random_packed_layer(a, li, dev, world, rank, seed) for li in range(a.n_layers)], "world": world,
-            "embed": embed, "final_norm": torch.ones(a.dim, dtype=torch.float32, device=dev), "head": head, "mtp": None}
+            "embed": embed, "final_norm": ones, "head": head, "mtp": mtp}
