@@ -448,6 +448,30 @@ def test_mla_full_topk_and_masking(env):
     close("mla.2048", oo.flash_sparse_mla(ql, qp, kvc, pec, sel_ref, pos, oo.softmax_scale(a)), o)
 
 
+@pytest.mark.parametrize("heads,topk,tokens", [(16, 384, 1), (32, 320, 2), (16, 64, 1), (128, 2048, 1), (48, 1024, 4)])
+def test_mla_chunk_counts_head_groups_and_tokens(env, heads, topk, tokens):
+    """Odd and even chunk counts (6, 5, 1, 32, 16 chunks of 64 rows), several head groups and tokens, padding inside
+    the last chunk, the log-sum-exp output; run twice."""
+    ops, a = env["ops"], env["a"]
+    g = torch.Generator().manual_seed(heads + topk + tokens)
+    t_len = 3000
+    pos = t_len - tokens
+    ql, qp = rn(g, 1, tokens, heads, 512, scale=0.3), rn(g, 1, tokens, heads, 64)
+    kvc, pec = rn(g, 1, t_len, 512), rn(g, 1, t_len, 64)
+    sel = torch.stack([torch.sort(torch.randperm(pos + 1, generator=g)[:topk])[0] for _ in range(tokens)]).to(I32)
+    sel = sel.view(1, tokens, topk)
+    sel[0, 0, -7:] = -1                                   # padding inside the last chunk
+    cur = torch.tensor([pos], dtype=I32, device="cuda")
+    ref = oo.flash_sparse_mla(ql, qp, kvc, pec, sel, pos, oo.softmax_scale(a))
+    for _ in range(2):
+        o = torch.zeros(1, tokens, heads, 512, dtype=BF16, device="cuda")
+        lse = torch.zeros(1, tokens, heads, dtype=F32, device="cuda")
+        ops.flash_sparse_mla(ql.cuda(), qp.cuda(), kvc.cuda(), pec.cuda(), sel.cuda(), cur, o,
+                             softmax_scale=oo.softmax_scale(a), lse=lse)
+        close(f"mla.{heads}.{topk}", ref, o)
+        assert torch.isfinite(lse).all()
+
+
 # ------------------------------------------------------------------------------- MoE / FFN
 def test_router_and_expert_path(env):
     ops, a, w, gw = env["ops"], env["a"], env["w"][1], env["gw"][1]
