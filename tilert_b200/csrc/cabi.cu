@@ -106,6 +106,7 @@ struct TbContext {
   float* chain_partial = nullptr;      // split-tile slots of chained launches: one region per phase
   unsigned* chain_signals = nullptr;   // signal counters of chained launches (self-clearing)
   unsigned* idx_work = nullptr;        // histograms and barrier counters of the indexer's selection (self-clearing)
+  int grid_limit = 0;                  // > 0: streaming launches use at most this many CTAs (tilert_b200_set_grid_limit)
   unsigned long long* chain_prof = nullptr;  // caller-owned trace of chained launches, see tilert_b200_set_chain_profile
   ChainRecorder rec;
   unsigned long long* launch_calls = nullptr;  // device-resident launch number of the streaming kernel
@@ -296,6 +297,7 @@ int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
   TB_REQUIRE(units < (1ll << 30));
   if (ctx->rec.active) return record_phase(ctx, p);
   int grid = ctx->num_sms < kMaxGrid ? ctx->num_sms : kMaxGrid;
+  if (ctx->grid_limit > 0 && ctx->grid_limit < grid) grid = ctx->grid_limit;  // SMs left to a concurrent stream
   if (units < grid) grid = static_cast<int>(units);
   if (static_cast<long long>(p.n_tiles) * 8 < grid) grid = p.n_tiles * 8;  // at most eight CTAs inside a row tile
   set_partition(p, grid);
@@ -490,6 +492,12 @@ extern "C" int tilert_b200_status(TbContext* ctx, int* status_out) {
     TB_CUDA(cudaMemset(ctx->chain_signals, 0, kChainSignalBytes));
     TB_CUDA(cudaMemset(ctx->idx_work, 0, kIdxWorkBytes));
   }
+  return TB_OK;
+}
+
+extern "C" int tilert_b200_set_grid_limit(TbContext* ctx, int max_ctas) {
+  TB_REQUIRE(ctx != nullptr && max_ctas >= 0);
+  ctx->grid_limit = max_ctas;
   return TB_OK;
 }
 

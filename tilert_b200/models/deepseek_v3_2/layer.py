@@ -44,6 +44,23 @@ def precompute_freqs(args: ModelArgs) -> torch.Tensor:
     return torch.view_as_real(torch.polar(torch.ones_like(ang), ang)).contiguous()
 
 
+# The two-stream step: the indexer's scoring + selection may run beside a streaming product only while it is the
+# short-row kernel (its thread blocks never wait on one another); beyond this many keys it is a cooperative launch
+# that needs every SM and runs alone.  The product beside it leaves 20 of the 148 SMs free.
+FORK_MAX_KEYS = 8192
+FORK_PRODUCT_CTAS = 128
+
+
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream(dev: torch.device) -> "torch.cuda.Stream":
+    """One second stream per device, shared by all layers."""
+    if dev not in _SIDE_STREAMS:
+        _SIDE_STREAMS[dev] = torch.cuda.Stream(device=dev)
+    return _SIDE_STREAMS[dev]
+
+
 def softmax_scale(args: ModelArgs) -> float:
     """tilert/models/deepseek_v3_2/ops/flash_sparse_mla.py:125-130."""
     scale = (args.qk_nope_head_dim + args.qk_rope_head_dim) ** -0.5
@@ -277,6 +294,12 @@ class DecoderLayer:
         # boundaries), or, with TILERT_B200_CHAIN=1, as two chained persistent launches: measured, the single
         # launches are 4-6 % faster on one and two GPUs
         self.chained = os.environ.get("TILERT_B200_CHAIN", "0") == "1"
+        # With single launches: the absorbed-q product beside the vector work and the indexer (two streams;
+        # measured 6 us per layer step faster on one GPU; TILERT_B200_FORK=0 keeps everything on one stream)
+        self.fork = os.environ.get("TILERT_B200_FORK", "1") != "0"
+        self._side = _side_stream(dev) if self.fork else None
+        self._ev_fork = torch.cuda.Event() if self.fork else None
+        self._ev_join = torch.cuda.Event() if self.fork else None
 
     def inject_cache(self, ki: torch.Tensor, kv: torch.Tensor, pe: torch.Tensor, start_pos: int = 0) -> None:
         """Rows ``start_pos ..`` of the three caches from bf16 tensors [seq, 128 / 512 / 64] computed by an
@@ -298,6 +321,17 @@ class DecoderLayer:
         ops.inject_cache_fp8(kv_raw.to(dev).contiguous(), pe_raw.to(dev).contiguous(), ki_pages.to(dev).contiguous(),
                              seq_len, start_pos, self.kv_cache, self.pe_cache, self.ki_cache)
 
+    def _attn_prep_and_select(self, x, freqs, cur_pos, n_keys: int, s: int, chained: bool) -> None:
+        a, w = self.args, self.w
+        v = lambda t: t[:, :s]  # noqa: E731
+        ops.attn_prep(x, w.in_norm, None if chained else w.wis, v(self.idx_w), v(self.kv), w.kv_norm, self.kv_cache,
+                      v(self.q_pe), self.pe_cache, v(self.iq), v(self.iq_rt), v(self.ki), self.ki_cache, w.k_norm_w,
+                      w.k_norm_b, freqs, cur_pos, eps=a.eps, rope=a.qk_rope_head_dim)
+        ops.sparse_index_topk(v(self.iq_rt), self.ki_cache, v(self.idx_w), self.idx_logits, v(self.sel), cur_pos,
+                              n_keys=n_keys)
+        if self.injected_sel is not None:
+            v(self.sel).copy_(self.injected_sel)
+
     def forward(self, x: torch.Tensor, cur_pos: torch.Tensor, freqs: torch.Tensor, n_keys: int) -> torch.Tensor:
         """``x`` [1, S, dim] bf16, ``cur_pos`` int32[1] (position of token 0), ``freqs`` f32 [S, rope/2, 2],
         ``n_keys`` = number of cache rows the indexer scans (>= cur_pos + S).  Returns [1, S, dim] bf16."""
@@ -308,20 +342,40 @@ class DecoderLayer:
         # Launch 1: the three FP8 products of the query path and the small per-token work between them
         # (indexer head weights, latent norm into the cache, RoPE, indexer rotations) as one persistent
         # kernel; with ``chained = False`` the same operators run as separate launches.
+        fork = self.fork and not chained and n_keys <= FORK_MAX_KEYS
         with ops.chain(dev, chained):
             ops.rmsnorm_projx_wqkva(x, w.in_norm, w.w_qkva, cur_pos, v(self.q_a), v(self.kv), self.pe_cache, v(self.ki),
                                     eps=a.eps)
             if chained:  # the indexer head weights as one more product of the stream (it waits for nothing)
                 ops.rmsnorm_proj_rows2(x, w.in_norm, w.wis2, v(self.idx_w), eps=a.eps)
             ops.rmsnorm_proj_q(v(self.q_a), w.q_norm, w.w_qb, v(self.q_nope), v(self.q_pe), v(self.iq), eps=a.eps)
-            ops.attn_prep(x, w.in_norm, None if chained else w.wis, v(self.idx_w), v(self.kv), w.kv_norm, self.kv_cache,
-                          v(self.q_pe), self.pe_cache, v(self.iq), v(self.iq_rt), v(self.ki), self.ki_cache, w.k_norm_w,
-                          w.k_norm_b, freqs, cur_pos, eps=a.eps, rope=a.qk_rope_head_dim)
-            ops.projq_wqb(v(self.q_nope), w.w_absorb, None, v(self.q_lat))
-        ops.sparse_index_topk(v(self.iq_rt), self.ki_cache, v(self.idx_w), self.idx_logits, v(self.sel), cur_pos,
-                              n_keys=n_keys)
-        if self.injected_sel is not None:
-            v(self.sel).copy_(self.injected_sel)
+            if fork:
+                # The absorbed-q product needs only q_nope; the per-token vector work and the indexer's scoring +
+                # selection need only the rest of the q_b launch's outputs.  Run them side by side: the product on
+                # this stream with a capped grid, the two small launches (whose thread blocks never wait on one
+                # another, so they cannot starve the product's) on a second stream over the SMs left free.
+                main = torch.cuda.current_stream(dev)
+                self._ev_fork.record(main)
+                self._side.wait_event(self._ev_fork)
+                with torch.cuda.stream(self._side):
+                    self._attn_prep_and_select(x, freqs, cur_pos, n_keys, s, chained)
+                    self._ev_join.record(self._side)
+                ops.set_grid_limit(dev, FORK_PRODUCT_CTAS)
+                try:
+                    ops.projq_wqb(v(self.q_nope), w.w_absorb, None, v(self.q_lat))
+                finally:
+                    ops.set_grid_limit(dev, 0)
+                main.wait_event(self._ev_join)
+            else:
+                ops.attn_prep(x, w.in_norm, None if chained else w.wis, v(self.idx_w), v(self.kv), w.kv_norm,
+                              self.kv_cache, v(self.q_pe), self.pe_cache, v(self.iq), v(self.iq_rt), v(self.ki),
+                              self.ki_cache, w.k_norm_w, w.k_norm_b, freqs, cur_pos, eps=a.eps, rope=a.qk_rope_head_dim)
+                ops.projq_wqb(v(self.q_nope), w.w_absorb, None, v(self.q_lat))
+        if not fork:
+            ops.sparse_index_topk(v(self.iq_rt), self.ki_cache, v(self.idx_w), self.idx_logits, v(self.sel), cur_pos,
+                                  n_keys=n_keys)
+            if self.injected_sel is not None:
+                v(self.sel).copy_(self.injected_sel)
         ops.flash_sparse_mla(v(self.q_lat), v(self.q_pe), self.kv_cache, self.pe_cache, v(self.sel), cur_pos,
                              v(self.o_lat), softmax_scale=self.scale, split_size=self.mla_split, out_acc=self.o_acc,
                              lse=self.lse, lse_acc=self.lse_acc)

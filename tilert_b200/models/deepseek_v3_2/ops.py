@@ -51,6 +51,15 @@ def _need(t: torch.Tensor | None, dtype, name: str, optional: bool = False) -> N
         raise ValueError(f"{name} must be contiguous.")
 
 
+def set_grid_limit(device, max_ctas: int) -> None:
+    """Cap the thread blocks of the streaming launches issued from now on (0 = one per SM); see
+    ``tilert_b200_set_grid_limit``."""
+    import ctypes
+
+    dev = torch.device(device)
+    _tb.check(_tb.lib().tilert_b200_set_grid_limit(ctypes.c_void_p(_tb.tilert_init(dev.index or 0)), max_ctas))
+
+
 class chain:
     """Record the FP8 products issued inside the ``with`` block and launch them as ONE persistent
     kernel at its end (``tilert_b200_chain_begin`` / ``_end``): the role of the reference's single native
