@@ -187,7 +187,11 @@ int tilert_unproj_o_allreduce_op(TbContext* ctx, const void* vec, const uint8_t*
  * shared expert last; rows of each expert interleave gate and up in groups of 8.
  * hidden_out [tokens, top_k + 1, inter] bf16 (slot 0 = shared expert).
  * slot_ids / slot_w [tokens, top_k + 1]: expert id and weight per slot (inputs of the down op).
- * Under tensor parallelism every rank holds an `inter`-row slice of every expert. */
+ * Under tensor parallelism every rank holds an `inter`-row slice of every expert.
+ * One token: one launch that also routes.  Several tokens (<= 4): a routing launch, then ONE product launch over the
+ * flat slot list [shared, token 0's experts, token 1's experts, ...] -- the shared expert is streamed once and every
+ * (token, expert) pair once; besides hidden_out the launch leaves every token's column of every slot in a buffer
+ * of the context, which the down operator uses when it is given this hidden_out next. */
 int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* hidden, const float* gamma, float eps,
                                          const float* scores, const float* bias, const uint8_t* w_packed, long long expert_stride,
                                          int tokens, int dim, int inter, int n_experts, int n_groups,
@@ -196,7 +200,9 @@ int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* hidden, con
                                          void* stream);
 
 /* expert_down_allreduce_op (ops/expert_down_allreduce.py:23-63):
- * out = all_reduce(sum_slots w_slot * W2[slot_ids] . vec[slot]) + x_residual. */
+ * out = all_reduce(sum_slots w_slot * W2[slot_ids] . vec[slot]) + x_residual.  Several tokens: ONE launch when
+ * `vec` is the hidden_out of the preceding expert_select_up_gate_silu_op call on this context (K = the flat slot
+ * list, a token's weight 0 at the other tokens' slots), else one launch per token. */
 int tilert_expert_down_allreduce_op(TbContext* ctx, const void* vec, const uint8_t* w_packed,
                                     long long expert_stride, const int* slot_ids, const float* slot_w,
                                     const void* x_residual, int tokens, int inter, int dim, int n_slots, void* out,

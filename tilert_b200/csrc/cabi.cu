@@ -76,6 +76,7 @@ constexpr size_t kXpackScratchBytes = 2ull << 20;   // activation blocks of the 
 constexpr int kMaxXBlocks = 1984;                   // X blocks one launch may convert (fits kXpackScratchBytes)
 constexpr size_t kXFlagBytes = (kMaxXBlocks + 64) * sizeof(unsigned);  // flags, then {epoch, done}
 constexpr size_t kSmallScratchBytes = 64ull << 10;  // slot ids / weights for routing
+constexpr size_t kMoeFlatBytes = 2ull << 20;  // expert hidden states of up to 4 tokens x 33 slots x 4096 values, bf16
 constexpr size_t kIdxWorkBytes = 8ull * kIdxWorkWords * 4;  // the indexer's selection work area, eight query tokens
 constexpr size_t kChainSignalBytes = (kChainSignals + 1) * kChainSigStride * sizeof(unsigned);
 
@@ -107,6 +108,12 @@ struct TbContext {
   unsigned* chain_signals = nullptr;   // signal counters of chained launches (self-clearing)
   unsigned* idx_work = nullptr;        // histograms and barrier counters of the indexer's selection (self-clearing)
   int grid_limit = 0;                  // > 0: streaming launches use at most this many CTAs (tilert_b200_set_grid_limit)
+  // Several tokens through the experts in ONE launch each (gate/up, down): the gate/up launch leaves every token's
+  // column for every (token, expert) slot here, [tokens][1 + tokens * top_k][inter] bf16, and remembers whose
+  // hidden_out it belongs to; the down launch that gets that hidden_out reads this instead.
+  void* moe_flat = nullptr;
+  const void* moe_flat_owner = nullptr;
+  int moe_flat_tokens = 0, moe_flat_inter = 0, moe_flat_topk = 0;
   unsigned long long* chain_prof = nullptr;  // caller-owned trace of chained launches, see tilert_b200_set_chain_profile
   ChainRecorder rec;
   unsigned long long* launch_calls = nullptr;  // device-resident launch number of the streaming kernel
@@ -408,7 +415,7 @@ int pack_flat(const void* x, int tokens, int k, const float* seg_scale, int n_se
 extern "C" const char* tilert_b200_last_error(void) { return g_last_error.c_str(); }
 extern "C" int tilert_b200_dsa_temp_vars_size(void) { return 56; }
 extern "C" size_t tilert_b200_context_bytes(void) {
-  return kPartialBytes * (1 + kChainMaxPhases) + 1024 + 2 * kXpackScratchBytes + kXFlagBytes + kSmallScratchBytes + kIdxWorkBytes;
+  return kPartialBytes * (1 + kChainMaxPhases) + 1024 + 2 * kXpackScratchBytes + kXFlagBytes + kSmallScratchBytes + kIdxWorkBytes + kMoeFlatBytes;
 }
 extern "C" size_t tilert_b200_xpack_bytes(int dim) { return static_cast<size_t>(dim / TB_KBLOCK) * TB_XBLK_BYTES; }
 
@@ -429,6 +436,8 @@ extern "C" int tilert_b200_init(int device, TbContext** ctx_out) {
   TB_CUDA(cudaMemset(c->chain_partial, 0, kPartialBytes * kChainMaxPhases));
   TB_CUDA(cudaMalloc(&c->chain_signals, kChainSignalBytes));
   TB_CUDA(cudaMemset(c->chain_signals, 0, kChainSignalBytes));
+  TB_CUDA(cudaMalloc(&c->moe_flat, kMoeFlatBytes));
+  TB_CUDA(cudaMemset(c->moe_flat, 0, kMoeFlatBytes));
   TB_CUDA(cudaMalloc(&c->idx_work, kIdxWorkBytes));
   TB_CUDA(cudaMemset(c->idx_work, 0, kIdxWorkBytes));
   TB_CUDA(cudaMalloc(&c->status, 256));
@@ -471,6 +480,7 @@ extern "C" int tilert_b200_destroy(TbContext* ctx) {
   cudaFree(ctx->chain_partial);
   cudaFree(ctx->chain_signals);
   cudaFree(ctx->idx_work);
+  cudaFree(ctx->moe_flat);
   cudaFree(ctx->launch_calls);
   cudaFree(ctx->status);
   cudaFree(ctx->xpack);
@@ -830,6 +840,7 @@ extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* 
   if (slot_ids == nullptr) slot_ids = reinterpret_cast<int*>(ctx->small);
   if (slot_w == nullptr) slot_w = reinterpret_cast<float*>(ctx->small + 4096);
   const int n_slots = top_k + 1;
+  ctx->moe_flat_owner = nullptr;
   auto base = [&](GemvParams& p) {
     gemv_defaults(p);
     p.w = w_packed;
@@ -882,29 +893,48 @@ extern "C" int tilert_expert_select_up_gate_silu_op(TbContext* ctx, const void* 
     }
     return TB_OK;
   }
-  // One token: the product launch routes the token itself.  Several tokens: a routing launch first,
-  // then one product launch per token (each token has its own expert list).
-  const bool route_in_kernel = tokens == 1;
-  if (!route_in_kernel) {
-    TB_CUDA(launch(expert_select_kernel, dim3((tokens + 3) / 4), dim3(128), 0, st, scores, bias, n_experts, n_groups,
-                   n_limited_groups, top_k, route_scale, n_experts, probs_out, idx_out, slot_ids, slot_w, tokens));
-    ++g_launches;
-    TB_CUDA(cudaGetLastError());
-  }
-  for (int t = 0; t < tokens; ++t) {
+  // One token: the product launch routes the token itself.
+  if (tokens == 1) {
     GemvParams p;
     base(p);
     p.n_tiles = n_slots * p.tiles_per_nseg;
-    if (route_in_kernel)
-      route(p, 0);
-    else
-      p.nseg_ids = slot_ids + t * n_slots;
-    p.only_token = tokens > 1 ? t : -1;
+    route(p, 0);
     p.n_rows = n_slots * inter;
     set_region(p, 0, p.n_rows, hidden_out, p.n_rows);
-    int rc = launch_gemv(ctx, p, st);
-    if (rc != TB_OK) return rc;
+    return launch_gemv(ctx, p, st);
   }
+  // Several tokens: a routing launch, then ONE product launch over the flat slot list [shared, token 0's experts,
+  // token 1's experts, ...].  Every slot's rows are computed for every token anyway (the tokens are columns of the
+  // same activation block), so all of them are stored in the context's flat buffer, where the down product finds
+  // its input; hidden_out [tokens][top_k + 1][inter] gets the shared rows of every token and, of the routed slots,
+  // the owning token's rows only.
+  const int n_flat = 1 + tokens * top_k;
+  TB_REQUIRE(static_cast<size_t>(tokens) * n_flat * inter * 2 <= kMoeFlatBytes);
+  int* flat_ids = reinterpret_cast<int*>(ctx->small + 16384);      // [n_flat]
+  float* flat_w = reinterpret_cast<float*>(ctx->small + 16896);    // [tokens][n_flat]
+  TB_CUDA(launch(expert_select_kernel, dim3((tokens + 3) / 4), dim3(128), 0, st, scores, bias, n_experts, n_groups,
+                 n_limited_groups, top_k, route_scale, n_experts, probs_out, idx_out, slot_ids, slot_w, tokens, flat_ids,
+                 flat_w));
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  GemvParams p;
+  base(p);
+  p.n_tiles = n_flat * p.tiles_per_nseg;
+  p.nseg_ids = flat_ids;
+  p.n_rows = n_flat * inter;
+  __nv_bfloat16* ho = reinterpret_cast<__nv_bfloat16*>(hidden_out);
+  set_region(p, 0, p.n_rows, ctx->moe_flat, static_cast<long long>(n_flat) * inter);
+  set_region(p, 0, inter, ho, static_cast<long long>(n_slots) * inter);
+  // routed slot 1 + t * top_k + j of the flat list is slot 1 + j of token t: row r goes to r + t * inter
+  set_region(p, inter, tokens * top_k * inter, ho + inter, inter);
+  p.regions[2].tok_div = top_k;
+  p.regions[2].slot_rows = inter;
+  int rc = launch_gemv(ctx, p, st);
+  if (rc != TB_OK) return rc;
+  ctx->moe_flat_owner = hidden_out;
+  ctx->moe_flat_tokens = tokens;
+  ctx->moe_flat_inter = inter;
+  ctx->moe_flat_topk = top_k;
   return TB_OK;
 }
 
@@ -919,6 +949,32 @@ extern "C" int tilert_expert_down_allreduce_op(TbContext* ctx, const void* vec, 
   if (slot_w == nullptr) slot_w = reinterpret_cast<const float*>(ctx->small + 4096);
   TB_REQUIRE(tokens >= 1 && tokens <= 4);
   int rc = TB_OK;
+  if (tokens > 1 && !ctx->rec.active && ctx->moe_flat_owner == vec && ctx->moe_flat_tokens == tokens &&
+      ctx->moe_flat_inter == inter && ctx->moe_flat_topk == n_slots - 1) {
+    // Several tokens in one launch: the K dimension is the flat slot list of the gate/up launch that produced
+    // `vec` (its flat buffer holds every token's column for every slot); a token's weight is its routing weight
+    // at its own slots, 1 at the shared slot and 0 at the other tokens' slots.
+    const int n_flat = 1 + tokens * (n_slots - 1);
+    GemvParams p;
+    gemv_defaults(p);
+    p.w = w_packed;
+    set_x_bf16(p, ctx->moe_flat, static_cast<long long>(n_flat) * inter, nullptr, 0.f,
+               reinterpret_cast<const float*>(ctx->small + 16896));
+    p.n_rows = dim;
+    p.n_tiles = (dim + TB_TILE_ROWS - 1) / TB_TILE_ROWS;
+    p.kb_per_kseg = inter / TB_KBLOCK;
+    p.n_kb = n_flat * p.kb_per_kseg;
+    p.w_kb_per_tile = p.kb_per_kseg;
+    p.kseg_ids = reinterpret_cast<const int*>(ctx->small + 16384);
+    p.expert_stride = expert_stride;
+    p.n_tokens = tokens;
+    p.residual = reinterpret_cast<const __nv_bfloat16*>(x_residual);
+    p.residual_stride = dim;
+    set_region(p, 0, dim, out, dim);
+    rc = set_comm(p, comm, dim);
+    if (rc != TB_OK) return rc;
+    return launch_gemv(ctx, p, st);
+  }
   for (int t = 0; t < tokens; ++t) {
     GemvParams p;
     gemv_defaults(p);

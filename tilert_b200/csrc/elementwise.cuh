@@ -301,10 +301,14 @@ __device__ __forceinline__ void expert_select_store(int my_id, float my_w, int t
   }
 }
 
+// One warp per token.  Besides the per-token lists, optionally the flat form that lets ONE product launch serve
+// every token: flat_ids = [shared, token 0's experts, token 1's experts, ...] and flat_w [n_tokens][1 + n_tokens *
+// top_k] = the token's routing weight at its own slots, 1 at the shared slot, 0 elsewhere.
 __global__ void expert_select_kernel(const float* __restrict__ scores, const float* __restrict__ bias,
                                      int n_experts, int n_groups, int n_limited, int top_k, float route_scale,
                                      int shared_id, float* __restrict__ probs, int* __restrict__ ids,
-                                     int* __restrict__ slot_ids, float* __restrict__ slot_w, int n_tokens) {
+                                     int* __restrict__ slot_ids, float* __restrict__ slot_w, int n_tokens,
+                                     int* __restrict__ flat_ids, float* __restrict__ flat_w) {
   pdl_launch_dependents();
   pdl_wait();
   const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -314,6 +318,19 @@ __global__ void expert_select_kernel(const float* __restrict__ scores, const flo
   expert_select_warp(scores + tok * n_experts, bias, n_experts, n_groups, n_limited, top_k, route_scale, my_id, my_w);
   expert_select_store(my_id, my_w, top_k, shared_id, probs + tok * top_k, ids + tok * top_k,
                       slot_ids + tok * (top_k + 1), slot_w + tok * (top_k + 1));
+  if (flat_ids != nullptr) {
+    const int lane = threadIdx.x & 31, n_flat = 1 + n_tokens * top_k;
+    float* row = flat_w + tok * n_flat;
+    for (int j = lane; j < n_flat; j += 32) {
+      const bool mine = j >= 1 + tok * top_k && j < 1 + (tok + 1) * top_k;
+      if (!mine) row[j] = j == 0 ? 1.0f : 0.0f;
+    }
+    if (lane < top_k) {
+      row[1 + tok * top_k + lane] = my_w;
+      flat_ids[1 + tok * top_k + lane] = my_id;
+    }
+    if (tok == 0 && lane == 0) flat_ids[0] = shared_id;
+  }
 }
 
 }  // namespace tb

@@ -685,7 +685,7 @@ __global__ void __launch_bounds__(kIdxFusedThreads) indexer_select_kernel(
   __shared__ int hist[2048];
   __shared__ float sw[H];
   __shared__ int s_warp[kIdxFusedWarps], s_res[2], s_warp_gt[kIdxFusedWarps], s_warp_eq[kIdxFusedWarps];
-  __shared__ int s_cnt[2], s_base[4], s_run[2], s_last;
+  __shared__ int s_base[4], s_run[2], s_last;
   const int tok = blockIdx.y, cta = blockIdx.x, n_ctas = gridDim.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   unsigned* work = work_all + static_cast<long long>(tok) * kIdxWorkWords;

@@ -40,6 +40,8 @@ struct OutRegion {
   long long token_stride;    // elements between tokens
   const int* pos_ptr;        // optional device int: destination starts at token index *pos_ptr
   int pos_rows;              // with pos_ptr: rows of the destination (0 = unchecked); a row past them is not stored
+  int tok_div;               // > 0: the region is cut into slots of slot_rows rows and slot j keeps only token j / tok_div
+  int slot_rows;
 };
 
 // All-reduce endpoint of one rank.  A partial sum travels as one 64-bit word {call number, f32 bits}
@@ -315,6 +317,7 @@ __device__ __forceinline__ void gemv_store(const GemvParams& p, int row, int tok
   for (int i = 0; i < TB_MAX_REGIONS; ++i) {
     if (i < p.n_regions && row >= p.regions[i].row_begin && row < p.regions[i].row_end) {
       const OutRegion& r = p.regions[i];
+      if (r.tok_div > 0 && token != ((row - r.row_begin) / r.slot_rows) / r.tok_div) continue;
       long long tok = token;
       if (r.pos_ptr != nullptr) {
         tok += *r.pos_ptr;
