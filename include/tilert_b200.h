@@ -76,11 +76,13 @@ int tilert_b200_set_profile(TbContext* ctx, unsigned long long* trace);
 /* Same with room for several launches: `trace` is u64 [n_records][256][16] and the k-th streaming
  * launch after this call writes record k % n_records (one decode step = one record per product). */
 int tilert_b200_set_profile_ring(TbContext* ctx, unsigned long long* trace, int n_records);
-/* Caps the thread blocks of the streaming launches made with this context from now on (0 = one per SM).  A launch
- * with fewer blocks than SMs leaves the others to kernels of another stream that do NOT wait on one another (the
- * layer runs the per-token vector work and the indexer's short-row scoring + selection beside the absorbed-q product
- * this way); two streaming launches must still not overlap.  Host-side state: not captured in a graph, it applies to
- * the launches recorded while it is set. */
+/* Caps the thread blocks of the streaming launches and of the cooperative indexer selection made with this context
+ * from now on (0 = one per SM).  A launch with fewer blocks than SMs leaves the others to kernels of another stream:
+ * either kernels whose blocks do NOT wait on one another (the layer runs the per-token vector work and the indexer's
+ * short-row scoring + selection beside the absorbed-q product this way), or ONE other capped launch, when the two
+ * caps add up to at most the SM count, so that both are always fully resident (the layer runs the cooperative
+ * long-row selection on 84 SMs beside the absorbed-q product on 64).  Host-side state: it applies to the launches
+ * issued while it is set, also when they are captured in a graph. */
 int tilert_b200_set_grid_limit(TbContext* ctx, int max_ctas);
 
 /* Upper bound, in SM clock cycles, of every bounded wait in the library's kernels on the context's device

@@ -1438,7 +1438,9 @@ extern "C" int tilert_sparse_index_topk_op(TbContext* ctx, const void* q, const 
   }
   // scoring and selection in one cooperative launch: at most one thread block per SM over all tokens, every block
   // a contiguous range of keys (a multiple of 16)
-  const int max_g = std::max(1, std::min(kIdxSelMaxCtas, ctx->num_sms) / tokens);
+  int sel_sms = std::min(kIdxSelMaxCtas, ctx->num_sms);
+  if (ctx->grid_limit > 0) sel_sms = std::min(sel_sms, ctx->grid_limit);  // SMs left to a concurrent streaming launch
+  const int max_g = std::max(1, sel_sms / tokens);
   const int n_ctas = std::min((n_keys + kIdxFusedKeys - 1) / kIdxFusedKeys, max_g);
   const int keys_per_cta = (((n_keys + n_ctas - 1) / n_ctas) + 15) & ~15;
   const dim3 grid(n_ctas, tokens);

@@ -44,11 +44,15 @@ def precompute_freqs(args: ModelArgs) -> torch.Tensor:
     return torch.view_as_real(torch.polar(torch.ones_like(ang), ang)).contiguous()
 
 
-# The two-stream step: the indexer's scoring + selection may run beside a streaming product only while it is the
-# short-row kernel (its thread blocks never wait on one another); beyond this many keys it is a cooperative launch
-# that needs every SM and runs alone.  The product beside it leaves 20 of the 148 SMs free.
+# The two-stream step.  Up to FORK_MAX_KEYS keys the indexer's scoring + selection is the short-row kernel, whose
+# thread blocks never wait on one another: it and the vector launch take whatever SMs the product beside them
+# (capped at FORK_PRODUCT_CTAS of the 148) leaves free.  Beyond that the selection is a cooperative launch whose
+# blocks meet at grid-wide barriers: it and the product then get fixed shares of the SMs that add up to the SM count
+# (FORK_LONG_PRODUCT_SHARE of them for the product, the rest for the selection), so both are always fully resident
+# whatever the order they start in.
 FORK_MAX_KEYS = 8192
 FORK_PRODUCT_CTAS = 128
+FORK_LONG_PRODUCT_SHARE = 64 / 148  # of the SM count; the selection gets the rest
 
 
 _SIDE_STREAMS: dict = {}
@@ -300,6 +304,9 @@ class DecoderLayer:
         self._side = _side_stream(dev) if self.fork else None
         self._ev_fork = torch.cuda.Event() if self.fork else None
         self._ev_join = torch.cuda.Event() if self.fork else None
+        n_sm = ops.num_sms(dev) if self.fork else 0
+        self._long_product_ctas = max(1, int(n_sm * FORK_LONG_PRODUCT_SHARE))
+        self._long_select_ctas = max(1, n_sm - self._long_product_ctas)
 
     def inject_cache(self, ki: torch.Tensor, kv: torch.Tensor, pe: torch.Tensor, start_pos: int = 0) -> None:
         """Rows ``start_pos ..`` of the three caches from bf16 tensors [seq, 128 / 512 / 64] computed by an
@@ -342,7 +349,8 @@ class DecoderLayer:
         # Launch 1: the three FP8 products of the query path and the small per-token work between them
         # (indexer head weights, latent norm into the cache, RoPE, indexer rotations) as one persistent
         # kernel; with ``chained = False`` the same operators run as separate launches.
-        fork = self.fork and not chained and n_keys <= FORK_MAX_KEYS
+        fork = self.fork and not chained
+        long_rows = n_keys > FORK_MAX_KEYS
         with ops.chain(dev, chained):
             ops.rmsnorm_projx_wqkva(x, w.in_norm, w.w_qkva, cur_pos, v(self.q_a), v(self.kv), self.pe_cache, v(self.ki),
                                     eps=a.eps)
@@ -358,9 +366,13 @@ class DecoderLayer:
                 self._ev_fork.record(main)
                 self._side.wait_event(self._ev_fork)
                 with torch.cuda.stream(self._side):
-                    self._attn_prep_and_select(x, freqs, cur_pos, n_keys, s, chained)
+                    ops.set_grid_limit(dev, self._long_select_ctas if long_rows else 0)
+                    try:
+                        self._attn_prep_and_select(x, freqs, cur_pos, n_keys, s, chained)
+                    finally:
+                        ops.set_grid_limit(dev, 0)
                     self._ev_join.record(self._side)
-                ops.set_grid_limit(dev, FORK_PRODUCT_CTAS)
+                ops.set_grid_limit(dev, self._long_product_ctas if long_rows else FORK_PRODUCT_CTAS)
                 try:
                     ops.projq_wqb(v(self.q_nope), w.w_absorb, None, v(self.q_lat))
                 finally:

@@ -60,6 +60,12 @@ def set_grid_limit(device, max_ctas: int) -> None:
     _tb.check(_tb.lib().tilert_b200_set_grid_limit(ctypes.c_void_p(_tb.tilert_init(dev.index or 0)), max_ctas))
 
 
+def num_sms(device) -> int:
+    """SMs of the device (the grid of a streaming launch)."""
+    dev = torch.device(device)
+    return int(_tb.lib().tilert_b200_num_sms(ctypes.c_void_p(_tb.tilert_init(dev.index or 0))))
+
+
 class chain:
     """Record the FP8 products issued inside the ``with`` block and launch them as ONE persistent
     kernel at its end (``tilert_b200_chain_begin`` / ``_end``): the role of the reference's single native
