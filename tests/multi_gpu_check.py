@@ -95,6 +95,24 @@ def main() -> int:
             print(f"model pos {pos}: logits rel_l2 {l2:.3e} token {picked} expected {expected}", flush=True)
         if not (l2 <= 2e-2 and all(p == expected for p in picked)):
             failures.append(("model", pos, l2, picked, expected))
+    # Sampling with the head split across ranks: the slices are gathered, every rank draws with the same seed and
+    # step counter, so all ranks must hold the same token, and it must be one of the top_k of the gathered logits.
+    dm.set_sampling(temperature=0.8, top_p=0.95, top_k=20, use_top_p=True, seed=7)
+    pos = len(toks)
+    tok = toks[-1]
+    for _ in range(4):
+        dm.forward(tok, pos)
+        torch.cuda.synchronize()
+        picked = [torch.empty_like(dm.token_out) for _ in range(world)]
+        dist.all_gather(picked, dm.token_out)
+        picked = [int(p) for p in picked]
+        top = torch.topk(dm.full_logits, 20).indices.tolist()
+        if rank == 0:
+            print(f"sampled pos {pos}: tokens {picked} in top-20 {picked[0] in top}", flush=True)
+        if not (all(p == picked[0] for p in picked) and picked[0] in top):
+            failures.append(("sampling", pos, picked))
+        tok, pos = picked[0], pos + 1
+    dm.set_sampling(temperature=0.0)
     # Speculative decoding across ranks: chunked prefill, then verify steps fed with the oracle's drafts
     # (the second one with the true continuation, so several drafts are accepted).  The four rows' logits,
     # gathered over the vocabulary slices, must match the oracle's; the predicted tokens must be the arg-max

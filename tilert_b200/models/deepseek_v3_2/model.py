@@ -77,6 +77,7 @@ class DsaModel:
         self.sampling = False
         self.sample_step = torch.zeros(2, dtype=torch.int64, device=dev)  # advanced by every launch (graph replay safe)
         self.sampled = torch.zeros(1, dtype=I32, device=dev)
+        self.full_logits: torch.Tensor | None = None  # world > 1 and sampling: every rank's slice, gathered
         self.token_logprob = torch.zeros(1, dtype=F32, device=dev)
         self.topn_logprobs = torch.zeros(1, 256, dtype=F32, device=dev)
         self.topn_indices = torch.zeros(1, 256, dtype=I32, device=dev)
@@ -108,7 +109,13 @@ class DsaModel:
         The token's log-probability and the top-256 log-probabilities / ids are left in ``token_logprob``,
         ``topn_logprobs`` and ``topn_indices`` after every step."""
         if self.world > 1:
-            raise ValueError("sampling needs the whole vocabulary on one rank; the split head decodes greedily")
+            import torch.distributed as dist
+
+            if not (dist.is_available() and dist.is_initialized()):
+                raise ValueError("sampling over a vocabulary split across ranks gathers the logits with "
+                                 "torch.distributed: initialise the default process group first")
+            if self.full_logits is None:
+                self.full_logits = torch.zeros(self.args.vocab_size, dtype=F32, device=self.device)
         self.sampling_config.copy_(torch.tensor([temperature, top_p, float(top_k), 1.0 if use_top_p else 0.0]))
         if seed is not None and seed != self.sampling_seed:
             self.sampling_seed = seed
@@ -143,7 +150,16 @@ class DsaModel:
         for layer in self.layers:
             x = layer.forward(x, self.cur_pos, fr, n_keys)
         ops.rmsnorm_head_proj(x, self.final_norm, self.head, None, self.logits, eps=self.args.eps)
-        if self.world > 1:
+        if self.world > 1 and self.sampling:
+            # every rank gathers all slices of the logits (517 KB) and draws the same token: same seed, same step
+            import torch.distributed as dist
+
+            dist.all_gather_into_tensor(self.full_logits, self.logits.view(-1))
+            ops.sample(self.full_logits.view(1, -1), self.sampling_config, self.sampled, seed=self.sampling_seed,
+                       step=self.sample_step, token_logprob=self.token_logprob, topn_logprobs=self.topn_logprobs,
+                       topn_indices=self.topn_indices)
+            self.token_out.copy_(self.sampled)
+        elif self.world > 1:
             # every rank holds vocab / world rows of the head: exchange (value, index) pairs over peer memory
             ops.argmax_exchange(self.logits, self.rank * self.logits.shape[-1], self.token_out, comm=self.comm)
         elif self.sampling:
@@ -178,7 +194,7 @@ class DsaModel:
             self.token.copy_(token.view(-1)[:1])
         self._pos = pos + 1
         n_keys = self._bucket(pos)
-        if not self.use_graph:
+        if not self.use_graph or (self.sampling and self.world > 1):  # the gather is a library collective: not captured
             self._step_ops(n_keys)
             return
         if n_keys not in self._graphs:
