@@ -39,7 +39,14 @@ def main() -> int:
     comm = Comm(a.dim, local)
     fc = oo.precompute_freqs_cis(a)
     failures = []
-    for li in (0, 1):
+    # The toy model shards only as far as its smallest dimension allows (expert intermediate 512: 128-row scale blocks
+    # give at most 4 ranks); with more ranks only the full-shape layer at the end is checked.
+    toy_ok = (a.moe_inter_dim % (128 * world) == 0 and a.inter_dim % (128 * world) == 0 and a.n_heads % world == 0
+              and a.vocab_size % world == 0)
+    if not toy_ok and rank == 0:
+        print(f"toy layers, toy model, sampling and speculative steps skipped: the toy shapes do not shard {world} ways",
+              flush=True)
+    for li in ((0, 1) if toy_ok else ()):
         for tokens in (1, 2):
             g = torch.Generator().manual_seed(300 + li + tokens)
             t_ctx, cache_len, n_steps = 400, 512, 3
@@ -72,88 +79,89 @@ def main() -> int:
                           flush=True)
                 if not (cos >= 0.999 and l2 <= 2e-2 and same):
                     failures.append((li, tokens, step, cos, l2, same))
-    # The whole toy model with the vocabulary head split across ranks: the greedy token comes from the
-    # (value, index) exchange over peer memory and must be the arg-max of the gathered logits on every
-    # rank; graph replay is on, so the exchange's device-resident epoch is exercised too.
-    from tilert_b200.models.deepseek_v3_2.model import DsaModel
-    toks = torch.randint(0, a.vocab_size, (10,), generator=torch.Generator().manual_seed(3)).tolist()
-    dm = DsaModel(margs, sd, dev, cache_len=256, world=world, rank=rank, comm=comm.handle)
-    ref = om.Model(a, sd, cache_len=256)
-    for pos, t in enumerate(toks):
-        dm.forward(t, pos)
-        torch.cuda.synchronize()
-        _, rl = ref.step(t)
-        parts = [torch.empty_like(dm.logits) for _ in range(world)]
-        dist.all_gather(parts, dm.logits)
-        full = torch.cat([p.view(-1) for p in parts]).float().cpu()
-        l2 = (torch.norm(rl.float() - full) / torch.norm(rl.float())).item()
-        picked = [torch.empty_like(dm.token_out) for _ in range(world)]
-        dist.all_gather(picked, dm.token_out)
-        picked = [int(p) for p in picked]
-        expected = int(torch.argmax(full))
-        if rank == 0:
-            print(f"model pos {pos}: logits rel_l2 {l2:.3e} token {picked} expected {expected}", flush=True)
-        if not (l2 <= 2e-2 and all(p == expected for p in picked)):
-            failures.append(("model", pos, l2, picked, expected))
-    # Sampling with the head split across ranks: the slices are gathered, every rank draws with the same seed and
-    # step counter, so all ranks must hold the same token, and it must be one of the top_k of the gathered logits.
-    dm.set_sampling(temperature=0.8, top_p=0.95, top_k=20, use_top_p=True, seed=7)
-    pos = len(toks)
-    tok = toks[-1]
-    for _ in range(4):
-        dm.forward(tok, pos)
-        torch.cuda.synchronize()
-        picked = [torch.empty_like(dm.token_out) for _ in range(world)]
-        dist.all_gather(picked, dm.token_out)
-        picked = [int(p) for p in picked]
-        top = torch.topk(dm.full_logits, 20).indices.tolist()
-        if rank == 0:
-            print(f"sampled pos {pos}: tokens {picked} in top-20 {picked[0] in top}", flush=True)
-        if not (all(p == picked[0] for p in picked) and picked[0] in top):
-            failures.append(("sampling", pos, picked))
-        tok, pos = picked[0], pos + 1
-    dm.set_sampling(temperature=0.0)
-    # Speculative decoding across ranks: chunked prefill, then verify steps fed with the oracle's drafts
-    # (the second one with the true continuation, so several drafts are accepted).  The four rows' logits,
-    # gathered over the vocabulary slices, must match the oracle's; the predicted tokens must be the arg-max
-    # of the gathered logits and, like the accepted count and the next drafts, the same on every rank.
-    from tilert_b200.models.deepseek_v3_2.mtp import MtpDsaModel
-    sd_mtp = om.random_state_dict(a, seed=0, with_mtp=True)
-    prompt = torch.randint(0, a.vocab_size, (21,), generator=torch.Generator().manual_seed(11)).tolist()
-    plain, _ = om.Model(a, sd_mtp, cache_len=256).generate(prompt, 8)
-    ref = om.MtpModel(a, sd_mtp, cache_len=256)
-    ref.generate_mtp(prompt, 0)
-    spec = MtpDsaModel(margs, sd_mtp, dev, cache_len=256, world=world, rank=rank, comm=comm.handle)
-    spec.generate(prompt, 0)
-    draft = [prompt[-1]] * 4
-    for step in range(3):
-        if step == 1:
-            k = ref.pos - (len(prompt) - 1)
-            draft = [draft[0]] + plain[k: k + 3]
-        r = ref.verify_step(list(draft))
-        spec.forward(draft)
-        torch.cuda.synchronize()
-        parts = [torch.empty_like(spec.logits) for _ in range(world)]
-        dist.all_gather(parts, spec.logits)
-        full = torch.cat(parts, dim=-1)[0].float().cpu()
-        l2 = (torch.norm(r["logits"] - full) / torch.norm(r["logits"])).item()
-        mine = torch.cat([spec.predicted, spec.n_accepted, spec.next_draft])
-        everyone = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(everyone, mine)
-        same = all(torch.equal(everyone[0], t) for t in everyone)
-        pred = spec.predicted.cpu().tolist()
-        exact = pred == torch.argmax(full, dim=-1).tolist()
-        n_dev = spec.get_num_accepted()
-        if rank == 0:
-            print(f"speculative step {step}: logits rel_l2 {l2:.3e} predicted {pred} oracle {r['predicted']} "
-                  f"accepted {n_dev} oracle {r['n_accepted']} ranks_identical {same}", flush=True)
-        if not (l2 <= 2e-2 and same and exact):
-            failures.append(("speculative", step, l2, same, exact))
-        if pred != r["predicted"]:
-            break  # an arg-max tie fell the other way: the sequences part ways here
-        if n_dev != r["n_accepted"] or (step == 1 and n_dev < 2):
-            failures.append(("speculative accepted", step, n_dev, r["n_accepted"]))
-        draft = r["next_draft"]
+    if toy_ok:
+        # The whole toy model with the vocabulary head split across ranks: the greedy token comes from the
+        # (value, index) exchange over peer memory and must be the arg-max of the gathered logits on every
+        # rank; graph replay is on, so the exchange's device-resident epoch is exercised too.
+        from tilert_b200.models.deepseek_v3_2.model import DsaModel
+        toks = torch.randint(0, a.vocab_size, (10,), generator=torch.Generator().manual_seed(3)).tolist()
+        dm = DsaModel(margs, sd, dev, cache_len=256, world=world, rank=rank, comm=comm.handle)
+        ref = om.Model(a, sd, cache_len=256)
+        for pos, t in enumerate(toks):
+            dm.forward(t, pos)
+            torch.cuda.synchronize()
+            _, rl = ref.step(t)
+            parts = [torch.empty_like(dm.logits) for _ in range(world)]
+            dist.all_gather(parts, dm.logits)
+            full = torch.cat([p.view(-1) for p in parts]).float().cpu()
+            l2 = (torch.norm(rl.float() - full) / torch.norm(rl.float())).item()
+            picked = [torch.empty_like(dm.token_out) for _ in range(world)]
+            dist.all_gather(picked, dm.token_out)
+            picked = [int(p) for p in picked]
+            expected = int(torch.argmax(full))
+            if rank == 0:
+                print(f"model pos {pos}: logits rel_l2 {l2:.3e} token {picked} expected {expected}", flush=True)
+            if not (l2 <= 2e-2 and all(p == expected for p in picked)):
+                failures.append(("model", pos, l2, picked, expected))
+        # Sampling with the head split across ranks: the slices are gathered, every rank draws with the same seed and
+        # step counter, so all ranks must hold the same token, and it must be one of the top_k of the gathered logits.
+        dm.set_sampling(temperature=0.8, top_p=0.95, top_k=20, use_top_p=True, seed=7)
+        pos = len(toks)
+        tok = toks[-1]
+        for _ in range(4):
+            dm.forward(tok, pos)
+            torch.cuda.synchronize()
+            picked = [torch.empty_like(dm.token_out) for _ in range(world)]
+            dist.all_gather(picked, dm.token_out)
+            picked = [int(p) for p in picked]
+            top = torch.topk(dm.full_logits, 20).indices.tolist()
+            if rank == 0:
+                print(f"sampled pos {pos}: tokens {picked} in top-20 {picked[0] in top}", flush=True)
+            if not (all(p == picked[0] for p in picked) and picked[0] in top):
+                failures.append(("sampling", pos, picked))
+            tok, pos = picked[0], pos + 1
+        dm.set_sampling(temperature=0.0)
+        # Speculative decoding across ranks: chunked prefill, then verify steps fed with the oracle's drafts
+        # (the second one with the true continuation, so several drafts are accepted).  The four rows' logits,
+        # gathered over the vocabulary slices, must match the oracle's; the predicted tokens must be the arg-max
+        # of the gathered logits and, like the accepted count and the next drafts, the same on every rank.
+        from tilert_b200.models.deepseek_v3_2.mtp import MtpDsaModel
+        sd_mtp = om.random_state_dict(a, seed=0, with_mtp=True)
+        prompt = torch.randint(0, a.vocab_size, (21,), generator=torch.Generator().manual_seed(11)).tolist()
+        plain, _ = om.Model(a, sd_mtp, cache_len=256).generate(prompt, 8)
+        ref = om.MtpModel(a, sd_mtp, cache_len=256)
+        ref.generate_mtp(prompt, 0)
+        spec = MtpDsaModel(margs, sd_mtp, dev, cache_len=256, world=world, rank=rank, comm=comm.handle)
+        spec.generate(prompt, 0)
+        draft = [prompt[-1]] * 4
+        for step in range(3):
+            if step == 1:
+                k = ref.pos - (len(prompt) - 1)
+                draft = [draft[0]] + plain[k: k + 3]
+            r = ref.verify_step(list(draft))
+            spec.forward(draft)
+            torch.cuda.synchronize()
+            parts = [torch.empty_like(spec.logits) for _ in range(world)]
+            dist.all_gather(parts, spec.logits)
+            full = torch.cat(parts, dim=-1)[0].float().cpu()
+            l2 = (torch.norm(r["logits"] - full) / torch.norm(r["logits"])).item()
+            mine = torch.cat([spec.predicted, spec.n_accepted, spec.next_draft])
+            everyone = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(everyone, mine)
+            same = all(torch.equal(everyone[0], t) for t in everyone)
+            pred = spec.predicted.cpu().tolist()
+            exact = pred == torch.argmax(full, dim=-1).tolist()
+            n_dev = spec.get_num_accepted()
+            if rank == 0:
+                print(f"speculative step {step}: logits rel_l2 {l2:.3e} predicted {pred} oracle {r['predicted']} "
+                      f"accepted {n_dev} oracle {r['n_accepted']} ranks_identical {same}", flush=True)
+            if not (l2 <= 2e-2 and same and exact):
+                failures.append(("speculative", step, l2, same, exact))
+            if pred != r["predicted"]:
+                break  # an arg-max tie fell the other way: the sequences part ways here
+            if n_dev != r["n_accepted"] or (step == 1 and n_dev < 2):
+                failures.append(("speculative accepted", step, n_dev, r["n_accepted"]))
+            draft = r["next_draft"]
     # The full-shape MoE layer of the benchmark (hidden 7168, 128 heads, 256 experts of which eight are forced
     # hot, indexer 64 x 128, top-2048, 4096-row caches), sharded over the ranks exactly as bench.py times it:
     # rank 0 compares with the CPU restatement of the reference's unsharded layer, all ranks must agree bit for bit.

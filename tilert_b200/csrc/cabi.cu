@@ -323,6 +323,11 @@ int launch_gemv(TbContext* ctx, GemvParams& p, cudaStream_t st) {
   }
   p.prof = ctx->prof;
   if (ctx->prof != nullptr) p.prof += (ctx->prof_next++ % ctx->prof_records) * (256 * 16);
+  static const unsigned stagger_ns = [] {
+    const char* e = getenv("TILERT_B200_STAGGER_NS");
+    return e != nullptr ? static_cast<unsigned>(atoi(e)) : 0u;
+  }();
+  p.stagger_ns = stagger_ns;
   TB_CUDA(launch(wstream_gemv_kernel, dim3(grid), dim3(kGemvThreads), kGemvSmemBytes, st, p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());

@@ -152,6 +152,7 @@ struct GemvParams {
   unsigned long long* launch_calls;  // scratch: kArUnit per completed launch that used `partial` (self-maintained)
   int* status;
   unsigned long long* prof;  // optional trace: [grid][16] (see GemvProfSlot)
+  unsigned stagger_ns;       // pause between one producer's copies of the first pass over the ring (0 = none)
   AllReduce ar;
 };
 
@@ -636,6 +637,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         // predecessor; later units take their X blocks from the launch's shared blocks.
         for (; u < u1 && u - u0 < kGemvStages; u += kGemvProducerWarps) {
           const int s = u - u0;
+          // The copies of a launch's first pass all start within a microsecond, 29 MB over the GPU, and the memory
+          // system serves them interleaved: without a pause between a producer's copies every slot, the first
+          // included, lands only when most of the burst has.
+          if (s >= kGemvProducerWarps && p.stagger_ns > 0) __nanosleep(p.stagger_ns);
           mbar_expect_tx(&full[s], TB_WBLK_BYTES);
           bulk_g2s_stream(smem + s * kGemvSlotStride, w_src(u / p.n_kb, u % p.n_kb), TB_WBLK_BYTES, &full[s], pol);
           gemv_timeline(p, 1, s);
