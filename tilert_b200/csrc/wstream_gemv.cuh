@@ -637,9 +637,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) wstream_gemv_kernel(const __g
         // predecessor; later units take their X blocks from the launch's shared blocks.
         for (; u < u1 && u - u0 < kGemvStages; u += kGemvProducerWarps) {
           const int s = u - u0;
-          // The copies of a launch's first pass all start within a microsecond, 29 MB over the GPU, and the memory
-          // system serves them interleaved: without a pause between a producer's copies every slot, the first
-          // included, lands only when most of the burst has.
+          // A pause between a producer's copies of the first pass: the launch ramps up instead of putting a full
+          // ring per CTA in flight at once while the predecessor's last CTAs are still streaming.
           if (s >= kGemvProducerWarps && p.stagger_ns > 0) __nanosleep(p.stagger_ns);
           mbar_expect_tx(&full[s], TB_WBLK_BYTES);
           bulk_g2s_stream(smem + s * kGemvSlotStride, w_src(u / p.n_kb, u % p.n_kb), TB_WBLK_BYTES, &full[s], pol);
