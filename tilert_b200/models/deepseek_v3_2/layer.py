@@ -46,12 +46,12 @@ def precompute_freqs(args: ModelArgs) -> torch.Tensor:
 
 # The two-stream step.  Up to FORK_MAX_KEYS keys the indexer's scoring + selection is the short-row kernel, whose
 # thread blocks never wait on one another: it and the vector launch take whatever SMs the product beside them
-# (capped at FORK_PRODUCT_CTAS of the 148) leaves free.  Beyond that the selection is a cooperative launch whose
+# (capped at FORK_PRODUCT_CTAS of the 148 SMs) leaves free.  Beyond that the selection is a cooperative launch whose
 # blocks meet at grid-wide barriers: it and the product then get fixed shares of the SMs that add up to the SM count
 # (FORK_LONG_PRODUCT_SHARE of them for the product, the rest for the selection), so both are always fully resident
 # whatever the order they start in.
 FORK_MAX_KEYS = 8192
-FORK_PRODUCT_CTAS = 128
+FORK_PRODUCT_CTAS = int(os.environ.get("TILERT_B200_FORK_CTAS", "112"))  # 96-128 measure the same within 0.5 %
 FORK_LONG_PRODUCT_SHARE = 64 / 148  # of the SM count; the selection gets the rest
 
 
