@@ -394,3 +394,49 @@ def test_injected_caches_continue_a_sequence(tb):
         assert c >= 0.999, c
         c, _ = _m(ki, ly.ki_cache[0, :n])
         assert c >= 0.998, c
+
+
+@pytest.mark.parametrize("t_ctx,cache_len", [(400, 512), (9000, 9216)])
+def test_two_stream_step_equals_one_stream_step(t_ctx, cache_len):
+    """The layer step on two streams (absorbed-q product beside the vector launch and the indexer's scoring +
+    selection; long rows: the cooperative selection on its share of the SMs) gives the same bytes as the step on one
+    stream, eagerly and from a captured graph, with one and with four rows."""
+    import tilert_b200
+    from tilert_b200.models.deepseek_v3_2 import layer as L
+    from tilert_b200.models.deepseek_v3_2.model_args import toy_model_args
+
+    tilert_b200.load_backend("deepseek_v3_2")
+    tilert_b200.tilert_init(0)
+    margs = toy_model_args()
+    from dataclasses import replace
+
+    margs = replace(margs, max_seq_len=max(margs.max_seq_len, cache_len))
+    a = om.toy_args()
+    sd = om.random_state_dict(a, seed=0)
+    g = torch.Generator().manual_seed(t_ctx)
+    for tokens in (1, 4):
+        gl = L.DecoderLayer(margs, L.LayerWeights(margs, sd, 1, "cuda"), "cuda", cache_len, tokens)
+        for c in (gl.kv_cache, gl.pe_cache, gl.ki_cache):
+            c[:, :t_ctx].copy_(torch.randn(1, t_ctx, c.shape[-1], generator=g).to(torch.bfloat16))
+        x = torch.randn(1, tokens, a.dim, generator=g).to(torch.bfloat16).cuda()
+        cur = torch.tensor([t_ctx], dtype=torch.int32, device="cuda")
+        fr = L.precompute_freqs(margs)[t_ctx: t_ctx + tokens].contiguous().cuda()
+        n_keys = (t_ctx + tokens + 255) // 256 * 256
+        outs = {}
+        for fork in (False, True):
+            gl.fork = fork
+            outs[fork, "eager"] = gl.forward(x, cur, fr, n_keys).clone()
+            sel_eager = gl.sel.clone()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                y = gl.forward(x, cur, fr, n_keys)
+            graph.replay()
+            torch.cuda.synchronize()
+            outs[fork, "graph"] = y.clone()
+            assert torch.equal(sel_eager, gl.sel)
+        ref = outs[False, "eager"]
+        assert torch.isfinite(ref.float()).all()
+        for key, val in outs.items():
+            assert torch.equal(ref, val), key
+    assert tilert_b200.device_status(0) == 0

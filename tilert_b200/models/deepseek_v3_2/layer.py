@@ -301,10 +301,10 @@ class DecoderLayer:
         # With single launches: the absorbed-q product beside the vector work and the indexer (two streams;
         # measured 6 us per layer step faster on one GPU; TILERT_B200_FORK=0 keeps everything on one stream)
         self.fork = os.environ.get("TILERT_B200_FORK", "1") != "0"
-        self._side = _side_stream(dev) if self.fork else None
-        self._ev_fork = torch.cuda.Event() if self.fork else None
-        self._ev_join = torch.cuda.Event() if self.fork else None
-        n_sm = ops.num_sms(dev) if self.fork else 0
+        self._side = _side_stream(dev)  # (the attribute ``fork`` may be switched at any time between steps)
+        self._ev_fork = torch.cuda.Event()
+        self._ev_join = torch.cuda.Event()
+        n_sm = ops.num_sms(dev)
         self._long_product_ctas = max(1, int(n_sm * FORK_LONG_PRODUCT_SHARE))
         self._long_select_ctas = max(1, n_sm - self._long_product_ctas)
 
