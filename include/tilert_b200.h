@@ -181,6 +181,12 @@ int tilert_projo_wkvb_op(TbContext* ctx, const void* o_lat, const uint8_t* w_pac
 int tilert_unproj_o_allreduce_op(TbContext* ctx, const void* vec, const uint8_t* w_packed, const void* x_residual,
                                  int tokens, int k, int n, void* out, TbComm* comm, void* stream);
 
+/* padded_allreduce_add_op (ops/padded_allreduce_add.py:17-41): out = all_reduce(partial) + x_residual, bf16
+ * [tokens, n], as a launch of its own over the communicator's peer buffers (n must be the communicator's row
+ * count); one call of the communicator's sequence.  comm == NULL: out = partial + x_residual. */
+int tilert_padded_allreduce_add_op(TbContext* ctx, const void* partial, const void* x_residual, int tokens, int n,
+                                   void* out, TbComm* comm, void* stream);
+
 /* expert_select_up_gate_silu_op (ops/expert_sel_up_gate_silu.py:23-48): routing (sigmoid + bias,
  * group-limited top-k, renormalise, scale) then SiLU(W1 x) * (W3 x) for the shared expert and the
  * selected routed experts.  hidden [tokens, dim] bf16 is the normalised post-attention state

@@ -39,6 +39,26 @@ def main() -> int:
     comm = Comm(a.dim, local)
     fc = oo.precompute_freqs_cis(a)
     failures = []
+    # The stand-alone all-reduce + residual add (the reference's padded_allreduce_add_op): every rank contributes a
+    # vector of its own; all ranks must hold the f32 sum in rank order plus the residual, bit for bit, on every call
+    # (three calls: both halves of the receive buffers, and the call number shared with the fused all-reduces).
+    from tilert_b200.models.deepseek_v3_2 import ops as _ops
+    for call, tokens in enumerate((1, 4, 2)):
+        gens = [torch.Generator().manual_seed(900 + 10 * call + r) for r in range(world)]
+        parts = [torch.randn(1, tokens, a.dim, generator=gr).to(torch.bfloat16) for gr in gens]
+        resid = torch.randn(1, tokens, a.dim, generator=torch.Generator().manual_seed(800 + call)).to(torch.bfloat16)
+        got = torch.zeros(1, tokens, a.dim, dtype=torch.bfloat16, device=dev)
+        _ops.padded_allreduce_add(parts[rank].to(dev), resid.to(dev), 0, got, comm=comm.handle)
+        torch.cuda.synchronize()
+        acc = torch.zeros(1, tokens, a.dim, dtype=torch.float32)
+        for pt in parts:
+            acc += pt.float()
+        want = (acc + resid.float()).to(torch.bfloat16)
+        ok_here = torch.equal(got.cpu(), want)
+        if rank == 0:
+            print(f"allreduce_add call {call} tokens {tokens}: exact {ok_here}", flush=True)
+        if not ok_here:
+            failures.append(("allreduce_add", call, tokens))
     # The toy model shards only as far as its smallest dimension allows (expert intermediate 512: 128-row scale blocks
     # give at most 4 ranks); with more ranks only the full-shape layer at the end is checked.
     toy_ok = (a.moe_inter_dim % (128 * world) == 0 and a.inter_dim % (128 * world) == 0 and a.n_heads % world == 0

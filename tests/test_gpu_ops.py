@@ -586,6 +586,25 @@ def test_mtp_preprocess_and_eh_proj(env, tokens):
     close("eh_proj", oo.eh_proj(e_ref, h_ref, w), out2, cos_min=0.9999, l2_max=8e-3)
 
 
+def test_padded_allreduce_add_single_rank(env):
+    """Without a communicator the stand-alone all-reduce + residual add is partial + x_in, through the C ABI wrapper
+    and through the reference's dispatcher name."""
+    ops = env["ops"]
+    g = torch.Generator().manual_seed(77)
+    for tokens in (1, 4):
+        part, x = rn(g, 1, tokens, 7168), rn(g, 1, tokens, 7168, scale=2.0)
+        out = torch.zeros(1, tokens, 7168, dtype=BF16, device="cuda")
+        ops.padded_allreduce_add(part.cuda(), x.cuda(), 0, out)
+        ref = (part.float() + x.float()).to(BF16)
+        assert torch.equal(out.cpu(), ref)
+        from tilert_b200 import torch_ops
+
+        torch_ops.register()
+        out2 = torch.zeros_like(out)
+        torch.ops.tilert.padded_allreduce_add_op(part.cuda(), x.cuda(), 0, out2, None, "deepseek_v3_2", "bf16")
+        assert torch.equal(out2.cpu(), ref)
+
+
 def test_torch_ops_namespace_calls_reach_the_kernels(env):
     """A reference-style call through torch.ops.tilert gives the same bytes as the direct wrapper."""
     from tilert_b200 import torch_ops

@@ -16,6 +16,7 @@
 #include "attn_prep.cuh"
 #include "indexer.cuh"
 #include "sparse_mla.cuh"
+#include "allreduce_add.cuh"
 #include "sampler.cuh"
 #include "wstream_gemv.cuh"
 #include "wstream_chain.cuh"
@@ -1233,6 +1234,33 @@ extern "C" int tilert_mtp_preprocess_op(TbContext* ctx, const void* e, const voi
   TB_REQUIRE(w != nullptr && out != nullptr);
   return launch_eh_proj(ctx, e, h, gamma_e, gamma_h, eps, w, tokens, dim, e_norm_out, h_norm_out, out,
                         static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tilert_padded_allreduce_add_op(TbContext* ctx, const void* partial, const void* x_residual, int tokens,
+                                              int n, void* out, TbComm* comm, void* stream) {
+  TB_NOT_CHAINABLE(ctx);
+  TB_REQUIRE(ctx != nullptr && partial != nullptr && out != nullptr && tokens >= 1 && tokens <= 4 && n >= 1);
+  ArAddParams p{};
+  p.partial = reinterpret_cast<const __nv_bfloat16*>(partial);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(x_residual);
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.n_tokens = tokens;
+  p.n_rows = n;
+  p.ar.world = 1;
+  p.status = ctx->status;
+  if (comm != nullptr && comm->world > 1) {
+    TB_REQUIRE(n == comm->max_rows);  // slot stride of the receive buffers
+    p.ar.world = comm->world;
+    p.ar.rank = comm->rank;
+    const size_t off = comm_state_offset(comm->world, comm->max_rows);
+    for (int r = 0; r < comm->world; ++r) p.ar.recv[r] = reinterpret_cast<unsigned long long*>(comm->buffers[r]);
+    p.ar.state = reinterpret_cast<AllReduceState*>(reinterpret_cast<uint8_t*>(comm->buffers[comm->rank]) + off);
+  }
+  const int grid = std::max(1, std::min(16, (tokens * n + 4 * kArAddThreads - 1) / (4 * kArAddThreads)));
+  TB_CUDA(launch(allreduce_add_kernel, dim3(grid), dim3(kArAddThreads), 0, static_cast<cudaStream_t>(stream), p));
+  ++g_launches;
+  TB_CUDA(cudaGetLastError());
+  return TB_OK;
 }
 
 // -------------------------------------------------------------------- per-token vector operators

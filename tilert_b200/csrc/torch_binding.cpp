@@ -189,6 +189,12 @@ void unproj_o_allreduce_op(const Tensor& vec, const Tensor& w, OptTensor, const 
                                      out.size(-1), ptr(out), nullptr, stream_of(out)));
 }
 
+void padded_allreduce_add_op(const Tensor& partial_buf, const Tensor& x_in, int64_t, Tensor vec_out, OptTensor, Str, Str) {
+  need(partial_buf, BF16, "partial_buf"); need(x_in, BF16, "x_in"); need(vec_out, BF16, "vec_out");
+  check(tilert_padded_allreduce_add_op(ctx_of(vec_out), ptr(partial_buf), ptr(x_in), vec_out.size(-2), vec_out.size(-1),
+                                       ptr(vec_out), nullptr, stream_of(vec_out)));
+}
+
 void down_allreduce_op(const Tensor& vec, const Tensor& w, OptTensor, const Tensor& x_residual, int64_t, Tensor out, Str, Str,
                        OptTensor) {
   unproj_o_allreduce_op(vec, w, std::nullopt, x_residual, 0, out, std::nullopt, "", "");
@@ -291,6 +297,8 @@ TORCH_LIBRARY(tilert, m) {
   m.def("projo_wkvb_op(Tensor o, Tensor w, Tensor? w_scales, Tensor(a!) out, " TB_S ", Tensor? placeholder=None) -> ()", &projo_wkvb_op);
   m.def("unproj_o_allreduce_op(Tensor vec, Tensor w, Tensor? w_scale, Tensor x_residual, int flag, Tensor(a!) out, "
         "Tensor? profile_logs, str model_arch, str kernel_type) -> ()", &unproj_o_allreduce_op);
+  m.def("padded_allreduce_add_op(Tensor partial_buf, Tensor x_in, int flag, Tensor(a!) vec_out, Tensor? profile_logs, "
+        "str model_arch, str compute_kernel_type=\"bf16\") -> ()", &padded_allreduce_add_op);
   m.def("down_allreduce_op(Tensor vec, Tensor w, Tensor? w_scale, Tensor x_residual, int flag, Tensor(a!) out, " TB_S ") -> ()",
         &down_allreduce_op);
   m.def("rmsnorm_expert_proj_op(Tensor x, Tensor gamma, Tensor w_gate, Tensor(a!) scores_out, Tensor(b!) hidden_out, " TB_S ") -> ()",

@@ -237,6 +237,19 @@ def unproj_o_allreduce(vec_in, w_packed, w_scale, x_in, flag, hidden_out, profil
                                                      None if comm is None else ctypes.c_void_p(comm), _stream()))
 
 
+def padded_allreduce_add(partial_buf, x_in, flag, vec_out, profile_logs=None, *, model_arch="deepseek_v3_2",
+                         compute_kernel_type="bf16", comm=None):
+    """ops/padded_allreduce_add.py:17-41: ``vec_out = all_reduce(partial_buf) + x_in`` (bf16 [1, L, dim]).  ``flag`` is
+    ignored: the call number lives in device memory."""
+    _need(partial_buf, BF16, "partial_buf")
+    _need(vec_out, BF16, "vec_out")
+    _need(x_in, BF16, "x_in", optional=True)
+    tokens = vec_out.shape[-2]
+    _tb.check(_tb.lib().tilert_padded_allreduce_add_op(_ctx(vec_out), _p(partial_buf), _p(x_in), tokens,
+                                                       vec_out.shape[-1], _p(vec_out),
+                                                       None if comm is None else ctypes.c_void_p(comm), _stream()))
+
+
 def rmsnorm_expert_proj(x, gamma, w_gate, scores_out, hidden_out, profile_logs=None, *,
                         model_arch="deepseek_v3_2", eps=1e-6):
     """ops/rmsnorm_expert_proj.py:151-169."""

@@ -24,7 +24,7 @@ NATIVE_OPS = [
     "tilert_init_op", "tilert_force_init_op", "dsa_temp_vars_size", "alloc_misc_ws", "rmsnorm_op", "rmsnorm_quant_op",
     "projx_wqkva_op", "proj_w_op", "rmsnorm_proj_qb_op", "rmsnorm_kv_op", "qkv_rope_op", "rotate_op",
     "layernorm_rope_rotate_op", "sparse_index_op", "sparse_index_topk_dsv32_op", "topk_accurate_op", "topk_approximate_op",
-    "projq_wqb_op", "flash_sparse_mla_op", "projo_wkvb_op", "unproj_o_allreduce_op", "down_allreduce_op",
+    "projq_wqb_op", "flash_sparse_mla_op", "projo_wkvb_op", "unproj_o_allreduce_op", "down_allreduce_op", "padded_allreduce_add_op",
     "rmsnorm_expert_proj_op", "expert_select_up_gate_silu_op", "expert_down_allreduce_op", "rmsnorm_up_gate_silu_op",
     "rmsnorm_head_proj_op", "eh_proj_allreduce_op",
 ]
