@@ -259,6 +259,15 @@ int tilert_eh_proj_allreduce_op(TbContext* ctx, const void* e_norm, const void* 
 int tilert_mtp_preprocess_op(TbContext* ctx, const void* e, const void* h, const float* gamma_e,
                              const float* gamma_h, float eps, const void* w, int tokens, int dim, void* e_norm_out,
                              void* h_norm_out, void* out, void* stream);
+/* The same for output rows [row_begin, row_begin + n_rows) only (`w` is still the whole [dim, 2 dim] weight, `out` the
+ * whole [tokens, dim] tensor, of which only those columns are written).  With the ranks of a tensor-parallel group
+ * each taking dim / world rows into a buffer that is zero elsewhere, padded_allreduce_add_op assembles the vector on
+ * every rank: each rank streams 1 / world of eh_proj (the reference splits K and all-reduces,
+ * ops/eh_proj_allreduce.py:159-183; rows keep every output's sum on one rank, so the result is bit-identical to the
+ * unsharded product). */
+int tilert_mtp_preprocess_rows_op(TbContext* ctx, const void* e, const void* h, const float* gamma_e,
+                                  const float* gamma_h, float eps, const void* w, int tokens, int dim, int row_begin,
+                                  int n_rows, void* e_norm_out, void* h_norm_out, void* out, void* stream);
 
 /* ---- per-token vector operators -------------------------------------------------------- */
 

@@ -1186,15 +1186,21 @@ extern "C" int tilert_rmsnorm_head_proj_op(TbContext* ctx, const void* x, const 
 // Multi-token-prediction input: (optionally enorm / hnorm, then) concat and eh_proj [dim, 2*dim] bf16.
 // At most two tokens fit the kernel's shared memory at 2*dim = 14336; more tokens take two launches.
 namespace {
+// Rows [row_begin, row_begin + n_rows) of the product (n_rows <= 0: all of them); `out` is the full [tokens, dim] tensor.
 int launch_eh_proj(TbContext* ctx, const void* e, const void* h, const float* gamma_e, const float* gamma_h, float eps,
                    const void* w, int tokens, int dim, void* e_norm_out, void* h_norm_out, void* out,
-                   cudaStream_t st) {
+                   cudaStream_t st, int row_begin = 0, int n_rows = 0) {
   TB_REQUIRE(tokens >= 1 && tokens <= 4 && dim % 128 == 0);
+  if (n_rows <= 0) {
+    row_begin = 0;
+    n_rows = dim;
+  }
+  TB_REQUIRE(row_begin >= 0 && row_begin + n_rows <= dim);
   for (int t0 = 0; t0 < tokens; t0 += 2) {
     const int nt = tokens - t0 < 2 ? tokens - t0 : 2;
     GemvBf16Params p{};
-    p.w = w;
-    p.n = dim;
+    p.w = reinterpret_cast<const __nv_bfloat16*>(w) + static_cast<long long>(row_begin) * 2 * dim;
+    p.n = n_rows;
     p.k = 2 * dim;
     p.k1 = dim;
     p.x = reinterpret_cast<const __nv_bfloat16*>(e) + static_cast<long long>(t0) * dim;
@@ -1210,7 +1216,7 @@ int launch_eh_proj(TbContext* ctx, const void* e, const void* h, const float* ga
     p.xnorm_stride = dim;
     if (h_norm_out != nullptr) p.xnorm2_out = reinterpret_cast<__nv_bfloat16*>(h_norm_out) + static_cast<long long>(t0) * dim;
     p.xnorm2_stride = dim;
-    p.out = reinterpret_cast<__nv_bfloat16*>(out) + static_cast<long long>(t0) * dim;
+    p.out = reinterpret_cast<__nv_bfloat16*>(out) + static_cast<long long>(t0) * dim + row_begin;
     p.out_bf16 = 1;
     p.out_stride = dim;
     const int rc = launch_gemv_bf16(ctx, p, st);
@@ -1261,6 +1267,16 @@ extern "C" int tilert_padded_allreduce_add_op(TbContext* ctx, const void* partia
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;
+}
+
+extern "C" int tilert_mtp_preprocess_rows_op(TbContext* ctx, const void* e, const void* h, const float* gamma_e,
+                                             const float* gamma_h, float eps, const void* w, int tokens, int dim,
+                                             int row_begin, int n_rows, void* e_norm_out, void* h_norm_out, void* out,
+                                             void* stream) {
+  TB_REQUIRE(ctx != nullptr && e != nullptr && h != nullptr && gamma_e != nullptr && gamma_h != nullptr);
+  TB_REQUIRE(w != nullptr && out != nullptr && n_rows >= 1);
+  return launch_eh_proj(ctx, e, h, gamma_e, gamma_h, eps, w, tokens, dim, e_norm_out, h_norm_out, out,
+                        static_cast<cudaStream_t>(stream), row_begin, n_rows);
 }
 
 // -------------------------------------------------------------------- per-token vector operators

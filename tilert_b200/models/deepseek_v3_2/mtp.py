@@ -87,6 +87,7 @@ class MtpDsaModel:
         self.guess_logits = z(s - 1, v_l, dtype=F32)
         # scratch
         self.mtp_in = z(1, s, args.dim, dtype=BF16)
+        self.eh_part = z(1, s, args.dim, dtype=BF16)  # this rank's rows of eh_proj's output, zero elsewhere
         self.mtp_logits = z(1, s, v_l, dtype=F32)
         self.chain_pos = z(1, dtype=I32)
         self.chain_in = z(1, 1, args.dim, dtype=BF16)
@@ -140,7 +141,15 @@ class MtpDsaModel:
                   x_in: torch.Tensor, logits_out: torch.Tensor) -> torch.Tensor:
         s = next_tokens.numel()
         e = self.embed[next_tokens].view(1, s, -1)
-        ops.mtp_preprocess(e, h, self.enorm, self.hnorm, self.w_eh, x_in, eps=self.args.eps)
+        if self.world > 1 and self.args.dim % self.world == 0:
+            # every rank streams dim / world rows of eh_proj into its zero-padded buffer; the stand-alone all-reduce
+            # assembles the vector on all ranks (adding zeros: the same bits as the unsharded product)
+            rows = self.args.dim // self.world
+            part = self.eh_part[:, :s]
+            ops.mtp_preprocess_rows(e, h, self.enorm, self.hnorm, self.w_eh, part, self.rank * rows, rows, eps=self.args.eps)
+            ops.padded_allreduce_add(part, None, 0, x_in, comm=self.comm)
+        else:
+            ops.mtp_preprocess(e, h, self.enorm, self.hnorm, self.w_eh, x_in, eps=self.args.eps)
         fr = self.freqs[pos.long() + self.rows[:s]]
         x = self.mtp_layer.forward(x_in, pos, fr, n_keys)
         ops.rmsnorm_head_proj(x, self.mtp_norm, self.head, None, logits_out, eps=self.args.eps)

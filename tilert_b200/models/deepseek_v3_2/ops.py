@@ -426,6 +426,20 @@ def mtp_preprocess(e, h, gamma_e, gamma_h, w, hidden_out, profile_logs=None, *, 
                                                  dim, _p(e_norm_out), _p(h_norm_out), _p(hidden_out), _stream()))
 
 
+def mtp_preprocess_rows(e, h, gamma_e, gamma_h, w, hidden_out, row_begin, n_rows, *, eps=1e-6):
+    """``mtp_preprocess`` for output rows [row_begin, row_begin + n_rows) only: one rank's share when eh_proj is split
+    by rows over a tensor-parallel group (``hidden_out`` is the whole [1, S, dim] tensor; only those columns change)."""
+    _need(e, BF16, "e")
+    _need(h, BF16, "h")
+    _need(gamma_e, F32, "gamma_e")
+    _need(gamma_h, F32, "gamma_h")
+    _need(w, BF16, "w")
+    _need(hidden_out, BF16, "hidden_out")
+    tokens, dim = e.shape[-2], e.shape[-1]
+    _tb.check(_tb.lib().tilert_mtp_preprocess_rows_op(_ctx(w), _p(e), _p(h), _p(gamma_e), _p(gamma_h), eps, _p(w), tokens,
+                                                      dim, row_begin, n_rows, None, None, _p(hidden_out), _stream()))
+
+
 def rmsnorm_kv(kv, gamma, cur_pos, kv_cache, profile_logs=None, *, model_arch="deepseek_v3_2", eps=1e-6):
     """ops/rmsnorm_kv.py:20-43."""
     _need(kv, BF16, "kv")
