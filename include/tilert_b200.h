@@ -331,6 +331,15 @@ int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const void* q_pe, 
                                const int* indices, int topk, const int* cur_pos, int heads, int tokens, int n_cache,
                                float softmax_scale, int split_size, void* out, float* out_acc, float* lse,
                                float* lse_acc, void* stream);
+/* flash_sparse_mla_op followed by projo_wkvb_op (ops/projo_wkvb.py) in two launches instead of three: the merge of
+ * the attention chunks also multiplies each head's latent output with that head's W_kv_b value rows (w_v_packed:
+ * [heads] row tiles of 128 x 512, as projo_wkvb_op takes them; kv_lora 512, v_dim 128) and writes o_out
+ * [tokens, heads, 128] bf16.  `out` (the latent output) may be NULL. */
+int tilert_flash_sparse_mla_vproj_op(TbContext* ctx, const void* q, const void* q_pe, const void* kv, const void* k_pe,
+                                     const int* indices, int topk, const int* cur_pos, int heads, int tokens,
+                                     int n_cache, float softmax_scale, int split_size, void* out, float* out_acc,
+                                     float* lse, float* lse_acc, const uint8_t* w_v_packed, int kv_lora, int v_dim,
+                                     void* o_out, void* stream);
 
 /* ---- sampling --------------------------------------------------------------------------- */
 

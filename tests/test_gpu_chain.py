@@ -94,6 +94,7 @@ def test_toy_layer_chained_equals_separate_launches(tb, li, tokens):
     for chained in (False, True):
         gl = L.DecoderLayer(margs, weights, "cuda", cache_len, max_tokens=tokens)
         gl.chained = chained
+        gl.fuse_vproj = False  # the value up-projection as the streaming product in both runs (same bits)
         for dst, src in zip((gl.kv_cache, gl.pe_cache, gl.ki_cache), caches):
             dst.copy_(src)
         gl.injected_sel = sel
@@ -135,6 +136,41 @@ def test_toy_layer_chained_equals_separate_launches(tb, li, tokens):
     gb.forward(x, cur, fr, n_keys=t_ctx + tokens)
     torch.cuda.synchronize()
     assert tb.lib().tilert_b200_launch_count() - n0 <= 5
+
+
+@pytest.mark.parametrize("tokens", [1, 4])
+def test_value_projection_inside_the_attention_merge(tb, tokens):
+    """The merge of the attention chunks fused with the value up-projection (f32 multiply-adds on the bf16 latent
+    vector) against the streaming product on the same vector (two e4m3 terms on the tensor core): the same
+    numbers up to the order of f32 additions."""
+    from tilert_b200.models.deepseek_v3_2 import layer as L
+    from tilert_b200.models.deepseek_v3_2.model_args import toy_model_args
+
+    a, margs = om.toy_args(), toy_model_args()
+    sd = om.random_state_dict(a, seed=0)
+    g = torch.Generator().manual_seed(17 + tokens)
+    t_ctx, cache_len = 500, 1024
+    caches = [torch.randn(1, cache_len, d, generator=g).to(BF16) for d in (a.kv_lora_rank, a.qk_rope_head_dim, a.index_head_dim)]
+    x = torch.randn(1, tokens, a.dim, generator=g).to(BF16).cuda()
+    fr = torch.view_as_real(oo.precompute_freqs_cis(a)[t_ctx: t_ctx + tokens]).contiguous().cuda()
+    cur = torch.tensor([t_ctx], dtype=I32, device="cuda")
+    weights = L.LayerWeights(margs, sd, 1, "cuda")
+    res = {}
+    for fused in (False, True):
+        gl = L.DecoderLayer(margs, weights, "cuda", cache_len, max_tokens=tokens)
+        gl.fuse_vproj = fused
+        for dst, src in zip((gl.kv_cache, gl.pe_cache, gl.ki_cache), caches):
+            dst.copy_(src)
+        out = gl.forward(x, cur, fr, n_keys=t_ctx + tokens).clone()
+        torch.cuda.synchronize()
+        res[fused] = (gl.o_lat.clone(), gl.o.clone(), gl.lse.clone(), out)
+    assert torch.equal(res[False][0], res[True][0])      # the merged latent vector: identical
+    assert torch.equal(res[False][2], res[True][2])
+    d = (res[False][1].float() - res[True][1].float()).norm() / res[False][1].float().norm()
+    assert d.item() <= 1e-3, d.item()
+    d = (res[False][3].float() - res[True][3].float()).norm() / res[False][3].float().norm()
+    assert d.item() <= 2e-3, d.item()
+    assert tb.device_status(0) == 0
 
 
 def test_chain_rejects_what_it_cannot_hold(tb):

@@ -1510,18 +1510,22 @@ extern "C" int tilert_sparse_index_topk_op(TbContext* ctx, const void* q, const 
   return TB_OK;
 }
 
-extern "C" int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const void* q_pe, const void* kv,
-                                          const void* k_pe, const int* indices, int topk, const int* cur_pos,
-                                          int heads, int tokens, int n_cache, float softmax_scale, int split_size,
-                                          void* out, float* out_acc, float* lse, float* lse_acc, void* stream) {
+namespace {
+// The attention launch, then the merge of its chunks: alone, or fused with the value up-projection (w_v != NULL).
+int launch_sparse_mla(TbContext* ctx, const void* q, const void* q_pe, const void* kv, const void* k_pe,
+                      const int* indices, int topk, const int* cur_pos, int heads, int tokens, int n_cache,
+                      float softmax_scale, int split_size, void* out, float* out_acc, float* lse, float* lse_acc,
+                      const uint8_t* w_v, void* o_out, cudaStream_t st) {
   TB_NOT_CHAINABLE(ctx);
   TB_REQUIRE(ctx != nullptr && q != nullptr && q_pe != nullptr && kv != nullptr && k_pe != nullptr);
-  TB_REQUIRE(indices != nullptr && cur_pos != nullptr && out != nullptr && out_acc != nullptr && lse_acc != nullptr);
+  TB_REQUIRE(indices != nullptr && cur_pos != nullptr && out_acc != nullptr && lse_acc != nullptr);
   TB_REQUIRE(split_size > 0 && split_size % kMlaKeys == 0 && topk > 0);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  TB_REQUIRE(w_v != nullptr ? o_out != nullptr : out != nullptr);
   static bool attr_set = false;
   if (!attr_set) {
     TB_CUDA(cudaFuncSetAttribute(sparse_mla_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmemBytes));
+    TB_CUDA(cudaFuncSetAttribute(sparse_mla_combine_vproj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kMlaCvSmemBytes));
     attr_set = true;
   }
   MlaParams p{};
@@ -1537,6 +1541,7 @@ extern "C" int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const v
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.blocks_per_split = split_size / kMlaKeys;
   p.n_splits = (topk + split_size - 1) / split_size;
+  TB_REQUIRE(p.n_splits <= 64);
   p.o_acc = out_acc;
   p.lse_acc = lse_acc;
   p.status = ctx->status;
@@ -1544,11 +1549,36 @@ extern "C" int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const v
   TB_CUDA(launch(sparse_mla_kernel, dim3(grid), dim3(kMlaThreads), kMlaSmemBytes, st, p));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
-  TB_CUDA(launch(sparse_mla_combine_kernel, dim3(dim3(heads, tokens)), dim3(128), 0, st, out_acc, lse_acc, p.n_splits,
-                                                                 reinterpret_cast<__nv_bfloat16*>(out), lse));
+  if (w_v != nullptr)
+    TB_CUDA(launch(sparse_mla_combine_vproj_kernel, dim3(dim3(heads, tokens)), dim3(128), kMlaCvSmemBytes, st, out_acc,
+                   lse_acc, p.n_splits, reinterpret_cast<__nv_bfloat16*>(out), lse, w_v,
+                   reinterpret_cast<__nv_bfloat16*>(o_out), ctx->status));
+  else
+    TB_CUDA(launch(sparse_mla_combine_kernel, dim3(dim3(heads, tokens)), dim3(128), 0, st, out_acc, lse_acc, p.n_splits,
+                   reinterpret_cast<__nv_bfloat16*>(out), lse));
   ++g_launches;
   TB_CUDA(cudaGetLastError());
   return TB_OK;
+}
+}  // namespace
+
+extern "C" int tilert_flash_sparse_mla_op(TbContext* ctx, const void* q, const void* q_pe, const void* kv,
+                                          const void* k_pe, const int* indices, int topk, const int* cur_pos,
+                                          int heads, int tokens, int n_cache, float softmax_scale, int split_size,
+                                          void* out, float* out_acc, float* lse, float* lse_acc, void* stream) {
+  return launch_sparse_mla(ctx, q, q_pe, kv, k_pe, indices, topk, cur_pos, heads, tokens, n_cache, softmax_scale,
+                           split_size, out, out_acc, lse, lse_acc, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tilert_flash_sparse_mla_vproj_op(TbContext* ctx, const void* q, const void* q_pe, const void* kv,
+                                                const void* k_pe, const int* indices, int topk, const int* cur_pos,
+                                                int heads, int tokens, int n_cache, float softmax_scale,
+                                                int split_size, void* out, float* out_acc, float* lse, float* lse_acc,
+                                                const uint8_t* w_v_packed, int kv_lora, int v_dim, void* o_out,
+                                                void* stream) {
+  TB_REQUIRE(w_v_packed != nullptr && o_out != nullptr && kv_lora == kMlaDV && v_dim == TB_TILE_ROWS);
+  return launch_sparse_mla(ctx, q, q_pe, kv, k_pe, indices, topk, cur_pos, heads, tokens, n_cache, softmax_scale,
+                           split_size, out, out_acc, lse, lse_acc, w_v_packed, o_out, static_cast<cudaStream_t>(stream));
 }
 
 // ------------------------------------------------------------------------------ sampling

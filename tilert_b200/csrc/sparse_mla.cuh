@@ -8,6 +8,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "formats.h"
 
 namespace tb {
 
@@ -319,6 +320,128 @@ __global__ void __launch_bounds__(128) sparse_mla_combine_kernel(const float* __
   o2.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
   *reinterpret_cast<uint2*>(out + th * kMlaDV + threadIdx.x * 4) = o2;
   if (threadIdx.x == 0 && lse_out != nullptr) lse_out[th] = den > 0.f ? s_mx + logf(den) : -INFINITY;
+}
+
+// Merge of the chunks fused with the value up-projection of the same head: o[h, :] = W_v[h] . o_lat[h] (128 x 512
+// e4m3 with block scales, the head's row tile of the packed weight: four 16 KB blocks).  The blocks are requested with
+// bulk copies before the wait for the attention launch -- weights depend on nothing -- so they are in shared memory
+// when the merged latent vector is; thread r then owns output row r.  Saves the separate product launch, which is
+// pure latency at this size (8 MB over the GPU, 1 MB per rank of eight).
+// grid = (heads, tokens), block = 128, dynamic smem = kMlaCvSmemBytes; n_splits <= 64; kv_lora 512, v_head_dim 128.
+constexpr int kMlaCvSmemBytes = 4 * TB_WBLK_BYTES + kMlaDV * 4 + 16;
+
+__global__ void __launch_bounds__(128) sparse_mla_combine_vproj_kernel(const float* __restrict__ o_acc,
+                                                                       const float* __restrict__ lse_acc, int n_splits,
+                                                                       __nv_bfloat16* __restrict__ o_lat_out,
+                                                                       float* __restrict__ lse_out,
+                                                                       const uint8_t* __restrict__ w_v,
+                                                                       __nv_bfloat16* __restrict__ o_out, int* status) {
+  extern __shared__ __align__(128) uint8_t cv_smem[];
+  uint8_t* sW = cv_smem;                                              // [4 k blocks][16448]
+  float* s_o = reinterpret_cast<float*>(cv_smem + 4 * TB_WBLK_BYTES);  // [512] merged latent vector (bf16 values)
+  uint64_t* bar = reinterpret_cast<uint64_t*>(s_o + kMlaDV);
+  __shared__ float s_w[64];
+  __shared__ float s_den, s_mx;
+  const int head = blockIdx.x, tok = blockIdx.y, heads = gridDim.x;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+    mbar_expect_tx(bar, 4 * TB_WBLK_BYTES);
+    for (int kb = 0; kb < 4; ++kb)
+      bulk_g2s(sW + kb * TB_WBLK_BYTES, w_v + (static_cast<long long>(head) * 4 + kb) * TB_WBLK_BYTES, TB_WBLK_BYTES, bar);
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long th = static_cast<long long>(tok) * heads + head;
+  if (tid < 32) {
+    const int lane = tid;
+    const float l0 = lane < n_splits ? lse_acc[th * n_splits + lane] : -INFINITY;
+    const float l1 = lane + 32 < n_splits ? lse_acc[th * n_splits + lane + 32] : -INFINITY;
+    const float mx = warp_max(fmaxf(l0, l1));
+    const float w0 = mx == -INFINITY ? 0.f : expf(l0 - mx), w1 = mx == -INFINITY ? 0.f : expf(l1 - mx);
+    const float den = warp_sum(w0 + w1);
+    s_w[lane] = w0;
+    s_w[lane + 32] = w1;
+    if (lane == 0) {
+      s_den = den;
+      s_mx = mx;
+    }
+  }
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const float* src = o_acc + th * n_splits * kMlaDV + tid * 4;
+  constexpr int kBatch = 16;
+  float4 v[kBatch];
+#pragma unroll
+  for (int j = 0; j < kBatch; ++j)
+    v[j] = j < n_splits ? __ldcs(reinterpret_cast<const float4*>(src + static_cast<long long>(j) * kMlaDV))
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+  __syncthreads();
+  for (int i0 = 0; i0 < n_splits; i0 += kBatch) {
+    float4 nxt[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int i = i0 + kBatch + j;
+      nxt[j] = i < n_splits ? __ldcs(reinterpret_cast<const float4*>(src + static_cast<long long>(i) * kMlaDV))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (i0 + j < n_splits) {
+        const float wgt = s_w[i0 + j];
+        acc[0] += wgt * v[j].x; acc[1] += wgt * v[j].y; acc[2] += wgt * v[j].z; acc[3] += wgt * v[j].w;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) v[j] = nxt[j];
+  }
+  const float den = s_den;
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  uint2 o2;
+  o2.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
+  o2.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
+  if (o_lat_out != nullptr) *reinterpret_cast<uint2*>(o_lat_out + th * kMlaDV + tid * 4) = o2;
+  if (tid == 0 && lse_out != nullptr) lse_out[th] = den > 0.f ? s_mx + logf(den) : -INFINITY;
+  // the product sees the same bf16 values the separate launch would read back
+  s_o[tid * 4 + 0] = __uint_as_float(o2.x << 16);
+  s_o[tid * 4 + 1] = __uint_as_float(o2.x & 0xffff0000u);
+  s_o[tid * 4 + 2] = __uint_as_float(o2.y << 16);
+  s_o[tid * 4 + 3] = __uint_as_float(o2.y & 0xffff0000u);
+  __syncthreads();
+  if (!mbar_wait(bar, 0)) {
+    set_status(status, ST_WAIT_FULL_TIMEOUT);
+    return;
+  }
+  // output row tid: bytes of W[row, 32 c + 16 kc + b] sit at c * 4096 + (row / 8) * 256 + kc * 128 + (row % 8) * 16 + b
+  float y = 0.f;
+#pragma unroll
+  for (int kb = 0; kb < 4; ++kb) {
+    const uint8_t* blk = sW + kb * TB_WBLK_BYTES;
+    const uint8_t* rowp = blk + (tid >> 3) * 256 + (tid & 7) * 16;
+    float part = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int kc = 0; kc < 2; ++kc) {
+        const uint4 q = *reinterpret_cast<const uint4*>(rowp + c * 4096 + kc * 128);
+        const uint32_t wds[4] = {q.x, q.y, q.z, q.w};
+        const float* xo = s_o + kb * 128 + c * 32 + kc * 16;
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(wds[wi] & 0xffffu), __NV_E4M3);
+          const __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(wds[wi] >> 16), __NV_E4M3);
+          const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+          const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+          part = fmaf(f01.x, xo[wi * 4 + 0], part);
+          part = fmaf(f01.y, xo[wi * 4 + 1], part);
+          part = fmaf(f23.x, xo[wi * 4 + 2], part);
+          part = fmaf(f23.y, xo[wi * 4 + 3], part);
+        }
+      }
+    }
+    y = fmaf(part, *reinterpret_cast<const float*>(blk + TB_WBLK_DATA + (tid >> 3) * 4), y);
+  }
+  o_out[th * 128 + tid] = f2bf(y);
 }
 
 }  // namespace tb

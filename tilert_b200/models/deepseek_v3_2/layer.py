@@ -301,6 +301,10 @@ class DecoderLayer:
         # With single launches: the absorbed-q product beside the vector work and the indexer (two streams;
         # measured 6 us per layer step faster on one GPU; TILERT_B200_FORK=0 keeps everything on one stream)
         self.fork = os.environ.get("TILERT_B200_FORK", "1") != "0"
+        # value up-projection inside the merge of the attention chunks (one launch less; TILERT_B200_FUSE_VPROJ=0:
+        # the streaming product as a launch of its own)
+        self.fuse_vproj = (os.environ.get("TILERT_B200_FUSE_VPROJ", "1") != "0" and a.kv_lora_rank == 512
+                           and a.v_head_dim == 128)
         self._side = _side_stream(dev)  # (the attribute ``fork`` may be switched at any time between steps)
         self._ev_fork = torch.cuda.Event()
         self._ev_join = torch.cuda.Event()
@@ -388,12 +392,16 @@ class DecoderLayer:
                                   n_keys=n_keys)
             if self.injected_sel is not None:
                 v(self.sel).copy_(self.injected_sel)
+        # With single launches the merge of the attention chunks also does the value up-projection of its head
+        fuse_v = self.fuse_vproj and not chained
         ops.flash_sparse_mla(v(self.q_lat), v(self.q_pe), self.kv_cache, self.pe_cache, v(self.sel), cur_pos,
                              v(self.o_lat), softmax_scale=self.scale, split_size=self.mla_split, out_acc=self.o_acc,
-                             lse=self.lse, lse_acc=self.lse_acc)
+                             lse=self.lse, lse_acc=self.lse_acc, w_v=w.w_v if fuse_v else None,
+                             o_out=v(self.o) if fuse_v else None)
         # Launch 2: value up-projection, o_proj (+ all-reduce + residual), router, experts (or the dense FFN)
         with ops.chain(dev, chained):
-            ops.projo_wkvb(v(self.o_lat), w.w_v, None, v(self.o))
+            if not fuse_v:
+                ops.projo_wkvb(v(self.o_lat), w.w_v, None, v(self.o))
             ops.unproj_o_allreduce(v(self.o), w.w_o, None, x, 0, v(self.h), comm=self.comm)
             if w.dense:
                 ops.rmsnorm_up_gate_silu(v(self.h), w.post_norm, w.w_gu, v(self.ffn_hidden), eps=a.eps)

@@ -559,8 +559,9 @@ def sparse_index_topk(q, kv, weights, logits, indices, cur_pos, profile_logs=Non
 
 
 def flash_sparse_mla(q, q_pe, kv, k_pe, indices, cur_pos, output, profile_logs=None, *, softmax_scale,
-                     model_arch="deepseek_v3_2", split_size=64, out_acc=None, lse=None, lse_acc=None):
-    """ops/flash_sparse_mla.py:18-93."""
+                     model_arch="deepseek_v3_2", split_size=64, out_acc=None, lse=None, lse_acc=None, w_v=None, o_out=None):
+    """ops/flash_sparse_mla.py:18-93.  With ``w_v`` (the packed value rows of kv_b) and ``o_out`` [.., heads, 128] the
+    merge of the attention chunks also does the value up-projection (ops/projo_wkvb.py): one launch less."""
     _need(q, BF16, "q")
     _need(q_pe, BF16, "q_pe")
     _need(kv, BF16, "kv")
@@ -575,6 +576,13 @@ def flash_sparse_mla(q, q_pe, kv, k_pe, indices, cur_pos, output, profile_logs=N
         out_acc = torch.empty(tokens, heads, n_splits, 512, dtype=F32, device=q.device)
     if lse_acc is None:
         lse_acc = torch.empty(tokens, heads, n_splits, dtype=F32, device=q.device)
+    if w_v is not None:
+        _need(o_out, BF16, "o_out")
+        _tb.check(_tb.lib().tilert_flash_sparse_mla_vproj_op(_ctx(q), _p(q), _p(q_pe), _p(kv), _p(k_pe), _p(indices), topk,
+                                                             _p(cur_pos), heads, tokens, kv.shape[-2], softmax_scale,
+                                                             split_size, _p(output), _p(out_acc), _p(lse), _p(lse_acc),
+                                                             _p(w_v), q.shape[-1], o_out.shape[-1], _p(o_out), _stream()))
+        return
     _tb.check(_tb.lib().tilert_flash_sparse_mla_op(_ctx(q), _p(q), _p(q_pe), _p(kv), _p(k_pe), _p(indices), topk,
                                                    _p(cur_pos), heads, tokens, kv.shape[-2], softmax_scale,
                                                    split_size, _p(output), _p(out_acc), _p(lse), _p(lse_acc),
